@@ -1,0 +1,111 @@
+"""The engine against the plain implementation, through trace replay: each request alone and
+whole; with its last 32 tokens one by one; in batches of unequal lengths whose shorter
+requests end earlier, one batch after another so that slots and pages are used again. In
+float32 and in bfloat16, for every tiny configuration."""
+import numpy as np
+import pytest
+
+import tiny
+import trace_util as tu
+
+pytestmark = pytest.mark.gpu
+
+# Largest |difference| over largest |reference logit|. float32: sums of a few hundred float32
+# products per element over at most 8 layers. bfloat16: activations and cache rounded to 8 bits
+# of mantissa between kernels.
+TOL = {"float32": 1e-5, "bfloat16": 3e-2}
+COS = {"float32": 0.999999, "bfloat16": 0.998}
+LENGTHS = [1, 4, 7, 16, 23, 40, 70, 5, 9, 13, 33, 64, 65, 129]
+
+
+def requests_for(name):
+    return {f"r{i}": tiny.prompt(name, n, salt=i) for i, n in enumerate(LENGTHS)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {(n, d): tiny.make_folder(root, n, d) for n in tiny.CONFIGS for d in ("float32", "bfloat16")}
+
+
+@pytest.fixture(scope="module")
+def replayers(folders):
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    made = {}
+
+    def get(name, dtype, max_tokens=1024):
+        key = (name, dtype, max_tokens)
+        if key not in made:
+            made[key] = Replayer(load_model(folders[(name, dtype)], dtype=dtype), max_tokens, None)
+        return made[key]
+    return get
+
+
+@pytest.fixture(scope="module")
+def references(folders):
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            made[(name, dtype)] = tu.plain_logits(folders[(name, dtype)], requests_for(name))
+        return made[(name, dtype)]
+    return get
+
+
+def check(name, dtype, steps, replayers, references):
+    rp = replayers(name, dtype)
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    got = tu.collect(steps, tu.run_in_process(rp, steps), vocab)
+    gap, where, cos = tu.worst_gap(got, references(name, dtype))
+    assert gap <= TOL[dtype], f"{name} {dtype}: gap {gap:.3e} at {where}"
+    assert cos >= COS[dtype], f"{name} {dtype}: cosine {cos}"
+    rp.cache.check()
+    assert rp.cache.slots.held_count == 0 and rp.cache.tokens_held() == 0
+    return got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_whole(name, dtype, replayers, references):
+    check(name, dtype, tu.whole_trace(requests_for(name)), replayers, references)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_last_32_one_by_one(name, dtype, replayers, references):
+    check(name, dtype, tu.tail_trace(requests_for(name), 32), replayers, references)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+@pytest.mark.parametrize("batch", [3, 5])
+def test_unequal_batches(name, dtype, batch, replayers, references):
+    check(name, dtype, tu.batch_trace(requests_for(name), batch), replayers, references)
+
+
+@pytest.mark.parametrize("name", ["A", "W"])
+def test_float32_cutting_changes_almost_nothing(name, replayers, references):
+    """Whole, one by one and batched runs agree with each other far inside the tolerance."""
+    reqs = requests_for(name)
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    rp = replayers(name, "float32")
+    runs = [tu.collect(s, tu.run_in_process(rp, s), vocab)
+            for s in (tu.whole_trace(reqs), tu.tail_trace(reqs, 32), tu.batch_trace(reqs, 4))]
+    scale = max(np.abs(v).max() for v in runs[0].values())
+    for other in runs[1:]:
+        gap = max(np.abs(other[k] - runs[0][k]).max() for k in runs[0]) / scale
+        assert gap <= 2e-6, f"{name}: runs differ by {gap:.3e}"
+
+
+def test_program_matches_in_process(folders, tmp_path):
+    """bin/trace_run, driven over its standard input, writes what the in-process replayer returns."""
+    name, dtype = "B", "float32"
+    reqs = {k: v for k, v in list(requests_for(name).items())[:5]}
+    steps = tu.batch_trace(reqs, 3)
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    out = tu.run_program(folders[(name, dtype)], dtype, steps, str(tmp_path / "out"), 512, vocab)
+    got = tu.collect(steps, out, vocab)
+    ref = tu.plain_logits(folders[(name, dtype)], reqs)
+    gap, where, _ = tu.worst_gap(got, ref)
+    assert gap <= TOL[dtype], f"gap {gap:.3e} at {where}"

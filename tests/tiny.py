@@ -1,0 +1,76 @@
+"""The tiny LFM3 configurations the tests use, and helpers to write them as model folders.
+
+A and B are the two small shapes the build's baseline names; they differ in every size and
+option (layers, widths that are no power of two, heads and groups, head size, taps, bias,
+theta, eps, tied or untied head). R is the layout the reference's own loader reads:
+sandwich norms, a gate per head, partly rotated heads, a sliding layer whose window is
+shorter than the test prompts, 7 taps (tests/parity/model/make_tiny.py:113-140 of the
+reference). W adds to B's options a sliding layer with an odd window and two rope bases.
+"""
+import os
+
+from xpu_serve_b200.config import Lfm3Config
+from xpu_serve_b200.weights import write_random_model
+
+CONFIG_A = {
+    "model_type": "lfm3", "vocab_size": 512, "hidden_size": 64, "intermediate_size": 192,
+    "num_hidden_layers": 4, "layer_types": ["conv", "conv", "attn", "conv"],
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 10000.0, "norm_eps": 1e-5,
+    "max_position_embeddings": 4096, "tie_word_embeddings": True,
+    "use_sandwich_norm": False, "attn_head_gate": False, "initializer_range": 0.02,
+}
+
+CONFIG_B = {
+    "model_type": "lfm3", "vocab_size": 1000, "hidden_size": 96, "intermediate_size": 320,
+    "num_hidden_layers": 6, "layer_types": ["attn", "conv", "conv", "attn", "conv", "attn"],
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 32,
+    "conv_L_cache": 4, "conv_bias": True, "rope_theta": 500000.0, "norm_eps": 1e-6,
+    "max_position_embeddings": 2048, "tie_word_embeddings": False,
+    "use_sandwich_norm": False, "attn_head_gate": False, "initializer_range": 0.05,
+}
+
+CONFIG_R = {
+    "model_type": "lfm3", "vocab_size": 300, "hidden_size": 64, "intermediate_size": 96,
+    "num_hidden_layers": 8,
+    "layer_types": ["conv", "conv", "full_attention", "conv", "sliding_attention", "conv", "full_attention", "conv"],
+    "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 32,
+    "conv_L_cache": 7, "conv_bias": False, "norm_eps": 1e-5, "max_position_embeddings": 1024,
+    "sliding_window": 16, "tie_word_embeddings": True, "eos_token_id": 1,
+    "rope_parameters": {"full_attention": {"rope_theta": 200.0, "partial_rotary_factor": 0.5},
+                        "sliding_attention": {"rope_theta": 50.0}},
+}
+
+CONFIG_W = {
+    "model_type": "lfm3", "vocab_size": 777, "hidden_size": 80, "intermediate_size": 200,
+    "num_hidden_layers": 5,
+    "layer_types": ["sliding_attention", "conv", "full_attention", "sliding_attention", "conv"],
+    "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 48,
+    "conv_L_cache": 2, "conv_bias": False, "norm_eps": 3e-6, "max_position_embeddings": 512,
+    "sliding_window": 37, "tie_word_embeddings": False, "use_sandwich_norm": True, "attn_head_gate": True,
+    "rope_parameters": {"full_attention": {"rope_theta": 1000.0, "partial_rotary_factor": 1.0},
+                        "sliding_attention": {"rope_theta": 77.0, "partial_rotary_factor": 0.67}},
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "R": CONFIG_R, "W": CONFIG_W}
+SEEDS = {"A": 0, "B": 1, "R": 2, "W": 3}
+# Plain N(0, sigma) weights give near-uniform attention and near-linear layers. These factors make the
+# parts matter: q and k large enough for peaked scores, taps and gates of order one.
+LIVELY = {"q_proj.weight": 6.0, "k_proj.weight": 6.0, "conv.conv.weight": 12.0, "gate_proj.weight": 8.0,
+          "embed_tokens.weight": 10.0}
+
+
+def make_folder(root, name: str, dtype: str = "float32", lively: bool = True) -> str:
+    """Writes configuration `name` with random weights under `root` and returns the folder."""
+    cfg = Lfm3Config.from_json(CONFIGS[name])
+    folder = os.path.join(str(root), f"lfm3_{name}_{dtype}")
+    if not os.path.isfile(os.path.join(folder, "model.safetensors")):
+        write_random_model(folder, cfg, SEEDS[name], dtype=dtype,
+                           norm_range=(0.5, 1.5) if lively else None,
+                           scale=LIVELY if lively else None)
+    return folder
+
+
+def prompt(name: str, length: int, salt: int = 0):
+    V = CONFIGS[name]["vocab_size"]
+    return [(i * 37 + 5 + 11 * salt + (i * i) % 7) % V for i in range(length)]

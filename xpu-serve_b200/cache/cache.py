@@ -1,0 +1,239 @@
+"""The cache: a slot per sequence, keys and values per layer call, fixed-size state beside them.
+
+Layer calls are grouped by what they need (parts/base.py: KVNeed, StateNeed). Calls
+that keep every key of the same geometry form one group with one page pool and one
+page table; calls that keep a window form another, whose pages behind the window are
+given back as a sequence grows; calls with a fixed-size state (the short convolution's
+last kernel-1 inputs here, any recurrent state elsewhere) form groups that hold one
+row per slot. Each group owns its storage. A slot's length is advanced only by
+`end_step`, and `begin_step` changes nothing unless everything the step needs is
+available (the reference leaves a failed step's state as it was,
+src/backend/cpu_ref/cpu_backend.cpp:157-177).
+
+Storage of a key/value call: [pages, 2 (keys, values), kv_heads, page_size, head_dim].
+Storage of a state call:     [max_slots, *shape].
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..parts.base import KVNeed, StateNeed
+from .pools import CacheError, CacheFull, IndexPool
+
+PAGE_SIZE = 64
+
+
+def _ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+class KVGroup:
+    def __init__(self, need: KVNeed, calls: List[int], n_pages: int, page_size: int, max_slots: int,
+                 max_seq_pages: int, dtype: torch.dtype, device):
+        self.need = need
+        self.calls = list(calls)
+        self.page_size = page_size
+        self.pages = IndexPool(n_pages, "page")
+        self.max_seq_pages = max_seq_pages
+        # logical page -> physical page, -1 where none is held
+        self.table = np.full((max_slots, max_seq_pages), -1, dtype=np.int32)
+        self.first_held = np.zeros(max_slots, dtype=np.int64)    # pages below it were given back
+        self.end_held = np.zeros(max_slots, dtype=np.int64)      # pages from it on are not held yet
+        self.storage: Dict[int, torch.Tensor] = {
+            c: torch.zeros((max(n_pages, 1), 2, need.kv_heads, page_size, need.head_dim),
+                           dtype=dtype, device=device) for c in calls}
+
+    def _first_needed_page(self, start: int) -> int:
+        """The lowest page a query at position `start` or later can still see."""
+        if self.need.window <= 0:
+            return 0
+        return max(0, start - self.need.window + 1) // self.page_size
+
+    def pages_wanted(self, slot: int, new_len: int) -> int:
+        return max(0, _ceil_div(new_len, self.page_size) - int(self.end_held[slot]))
+
+    def reserve(self, slot: int, new_len: int) -> None:
+        want = self.pages_wanted(slot, new_len)
+        if want == 0:
+            return
+        end = int(self.end_held[slot])
+        if end + want > self.max_seq_pages:
+            raise CacheError(f"a sequence of {new_len} positions exceeds the cache's {self.max_seq_pages} pages a sequence")
+        self.table[slot, end:end + want] = self.pages.take(want)
+        self.end_held[slot] = end + want
+
+    def trim(self, slot: int, length: int) -> None:
+        first = min(self._first_needed_page(length), int(self.end_held[slot]))
+        lo = int(self.first_held[slot])
+        if first > lo:
+            self.pages.give_back(int(p) for p in self.table[slot, lo:first])
+            self.table[slot, lo:first] = -1
+            self.first_held[slot] = first
+
+    def release(self, slot: int) -> None:
+        lo, hi = int(self.first_held[slot]), int(self.end_held[slot])
+        self.pages.give_back(int(p) for p in self.table[slot, lo:hi])
+        self.table[slot, :] = -1
+        self.first_held[slot] = 0
+        self.end_held[slot] = 0
+
+
+class StateGroup:
+    def __init__(self, need: StateNeed, calls: List[int], max_slots: int, compute_dtype: torch.dtype, device):
+        self.need = need
+        self.calls = list(calls)
+        dtype = torch.float32 if need.dtype == "float32" else compute_dtype
+        self.storage: Dict[int, torch.Tensor] = {
+            c: torch.zeros((max(max_slots, 1), *need.shape), dtype=dtype, device=device) for c in calls}
+
+    def zero(self, slots: torch.Tensor) -> None:
+        for t in self.storage.values():
+            t.index_fill_(0, slots, 0)
+
+
+@dataclass
+class CallView:
+    """What a mixer is handed for one layer call."""
+    call: int
+    group: int                 # index into Cache.groups; -1 for none
+    storage: Optional[torch.Tensor]
+    need: object
+    owner: bool                # False when this call reads another call's cache
+
+
+class Cache:
+    """needs[i] is the need of call i of the running order (None: nothing kept), and
+    shares[i] the call whose cache call i reads (None: its own)."""
+
+    def __init__(self, needs: Sequence[object], shares: Sequence[Optional[int]], max_tokens: int, *,
+                 page_size: int = PAGE_SIZE, max_slots: Optional[int] = None,
+                 max_seq_tokens: Optional[int] = None, dtype: torch.dtype = torch.bfloat16, device="cuda"):
+        if max_tokens <= 0:
+            raise ValueError("max_tokens must be positive")
+        self.page_size = page_size
+        self.max_tokens = _ceil_div(max_tokens, page_size) * page_size
+        n_pages = self.max_tokens // page_size
+        self.max_slots = n_pages if max_slots is None else max_slots
+        self.max_seq_tokens = self.max_tokens if max_seq_tokens is None else min(max_seq_tokens, self.max_tokens)
+        max_seq_pages = _ceil_div(self.max_seq_tokens, page_size)
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.slots = IndexPool(self.max_slots, "slot")
+        self.lens = np.zeros(self.max_slots, dtype=np.int64)
+        self.groups: List[object] = []
+        by_need: Dict[object, List[int]] = {}
+        for call, (need, share) in enumerate(zip(needs, shares)):
+            if need is not None and share is None:
+                by_need.setdefault(need, []).append(call)
+        self._group_of_call: Dict[int, int] = {}
+        for need, calls in by_need.items():
+            if isinstance(need, KVNeed):
+                g: object = KVGroup(need, calls, n_pages, page_size, self.max_slots, max_seq_pages, dtype, self.device)
+            elif isinstance(need, StateNeed):
+                g = StateGroup(need, calls, self.max_slots, dtype, self.device)
+            else:
+                raise TypeError(f"call {calls[0]} declares an unknown cache need {need!r}")
+            for c in calls:
+                self._group_of_call[c] = len(self.groups)
+            self.groups.append(g)
+        self.views: List[CallView] = []
+        for call, (need, share) in enumerate(zip(needs, shares)):
+            src = call if share is None else share
+            if src in self._group_of_call and (share is None or needs[call] is not None):
+                gi = self._group_of_call[src]
+                self.views.append(CallView(call, gi, self.groups[gi].storage[src], self.groups[gi].need, share is None))
+            else:
+                self.views.append(CallView(call, -1, None, None, True))
+        self.kv_groups = [i for i, g in enumerate(self.groups) if isinstance(g, KVGroup)]
+
+    # ------------------------------------------------------------ sequences
+    def open(self, n: int) -> List[int]:
+        """n free slots, their fixed-size state zeroed and their length 0."""
+        slots = self.slots.take(n)
+        self.lens[slots] = 0
+        state_groups = [g for g in self.groups if isinstance(g, StateGroup)]
+        if state_groups and slots:
+            idx = torch.tensor(slots, dtype=torch.int64, device=self.device)
+            for g in state_groups:
+                g.zero(idx)
+        return slots
+
+    def close(self, slots: Sequence[int]) -> None:
+        slots = list(slots)
+        for s in slots:
+            if not self.slots.is_held(s):
+                raise CacheError(f"slot {s} is freed twice or was never held")
+        if len(set(slots)) != len(slots):
+            raise CacheError("a slot is freed twice in one call")
+        for s in slots:
+            for g in self.groups:
+                if isinstance(g, KVGroup):
+                    g.release(s)
+            self.lens[s] = 0
+        self.slots.give_back(slots)
+
+    # ---------------------------------------------------------------- steps
+    def begin_step(self, slots: Sequence[int], q_lens: Sequence[int]) -> np.ndarray:
+        """Reserves what the step writes. Returns each sequence's length before the step.
+        Raises, with nothing changed, when a slot is not held, a sequence would outgrow
+        max_seq_tokens, or pages run out."""
+        if len(slots) != len(q_lens) or len(slots) == 0:
+            raise CacheError("a step needs one token count per slot, and at least one slot")
+        if len(set(slots)) != len(slots):
+            raise CacheError("a slot appears twice in one step")
+        for s, q in zip(slots, q_lens):
+            if not self.slots.is_held(s):
+                raise CacheError(f"slot {s} is not held")
+            if q <= 0:
+                raise CacheError(f"slot {s}: a step needs at least one token")
+            if self.lens[s] + q > self.max_seq_tokens:
+                raise CacheError(f"slot {s}: {int(self.lens[s]) + q} positions exceed the limit of "
+                                 f"{self.max_seq_tokens} a sequence")
+        for gi in self.kv_groups:
+            g = self.groups[gi]
+            want = sum(g.pages_wanted(s, int(self.lens[s]) + q) for s, q in zip(slots, q_lens))
+            if want > g.pages.free_count:
+                raise CacheFull(f"the step needs {want} more pages, {g.pages.free_count} of {g.pages.count} are free")
+        starts = self.lens[list(slots)].copy()
+        for gi in self.kv_groups:
+            g = self.groups[gi]
+            for s, q in zip(slots, q_lens):
+                g.reserve(s, int(self.lens[s]) + q)
+        return starts
+
+    def end_step(self, slots: Sequence[int], q_lens: Sequence[int]) -> None:
+        for s, q in zip(slots, q_lens):
+            self.lens[s] += q
+            for gi in self.kv_groups:
+                g = self.groups[gi]
+                if g.need.window > 0:
+                    g.trim(s, int(self.lens[s]))
+
+    def page_table(self, group: int, slots: Sequence[int], width: Optional[int] = None) -> np.ndarray:
+        """[len(slots), width] int32 rows of the group's table (width: the widest row held)."""
+        g = self.groups[group]
+        if width is None:
+            width = max(1, int(g.end_held[list(slots)].max()))
+        return g.table[list(slots), :width]
+
+    def tokens_held(self) -> int:
+        """Positions reserved in the largest key/value group, in whole pages."""
+        return max((self.groups[gi].pages.held_count for gi in self.kv_groups), default=0) * self.page_size
+
+    def check(self) -> None:
+        self.slots.check()
+        for gi in self.kv_groups:
+            g = self.groups[gi]
+            g.pages.check()
+            held = [int(p) for s in range(self.max_slots) for p in g.table[s] if p >= 0]
+            if len(held) != len(set(held)):
+                raise CacheError("a page is in two page tables")
+            if len(held) != g.pages.held_count:
+                raise CacheError(f"{g.pages.held_count} pages are held but the tables name {len(held)}")
+            for s in range(self.max_slots):
+                if not self.slots.is_held(s) and (g.table[s] >= 0).any():
+                    raise CacheError(f"free slot {s} still has pages")

@@ -1,0 +1,116 @@
+"""A model on a device: its parts, its cache, and the step function.
+
+`Model.step` is the one function through which every token passes, for prompts and for
+decoding, for generation and for trace replay. It takes a batch of sequences (their slots,
+each one's next tokens, and the places whose logits are wanted), runs only those tokens
+from what the cache holds, and returns float32 logits for the wanted places.
+
+The reference runs one graph for one sequence per step (src/backend/backend.h:46-87,
+src/models/lfm3/lfm3_model.cpp:34-44); the layer order and formulas are the same
+(src/models/lfm3/lfm3_decoder.cpp:49-90), batching and the wanted places are added.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import registry
+from ..cache import Cache
+from ..config.json_util import ConfigError, read_json
+from ..config.spec import ModelSpec
+from ..ops import lib as ops
+from ..parts.block import Block, ResidualStream
+from ..weights.loader import load_weights
+from .runtime import Runtime
+from .step import StepContext, StepStager
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], dtype: str = "bfloat16",
+                 device="cuda:0", config=None):
+        """`weights`: tensors by name without the model prefix (weights.loader.load_weights)."""
+        spec.validate()
+        self.spec, self.config = spec, config
+        self.rt = Runtime(dtype, device)
+        rt = self.rt
+        self.embed = rt.matrix(weights[spec.names["embed"]])
+        self.head = self.embed if spec.tied_head else rt.matrix(weights[spec.names["head"]])
+        self.final_norm = rt.vector(weights[spec.names["final_norm"]])
+        self.blocks: List[Block] = []
+        for layer in spec.layers:
+            own = {k[len(layer.prefix):]: v for k, v in weights.items() if k.startswith(layer.prefix)}
+            self.blocks.append(Block(layer, own, rt))
+        self.stager = StepStager(rt.device)
+        self.launches = 0
+
+    # ----------------------------------------------------------------- cache
+    def cache_needs(self):
+        needs, shares = [], []
+        for call in self.spec.order:
+            mixer = self.spec.layers[call.layer].mixer
+            needs.append(registry.mixer_class(mixer.kind).cache_need(mixer))
+            shares.append(call.cache_of)
+        return needs, shares
+
+    def new_cache(self, max_tokens: int, max_slots: Optional[int] = None,
+                  max_seq_tokens: Optional[int] = None) -> Cache:
+        needs, shares = self.cache_needs()
+        limit = self.spec.max_position if max_seq_tokens is None else min(max_seq_tokens, self.spec.max_position)
+        return Cache(needs, shares, max_tokens, max_slots=max_slots, max_seq_tokens=limit,
+                     dtype=self.rt.act_dtype, device=self.rt.device)
+
+    # ------------------------------------------------------------------ step
+    def check_tokens(self, token_lists: Sequence[Sequence[int]]) -> None:
+        V = self.spec.vocab
+        for toks in token_lists:
+            for t in toks:
+                if not 0 <= int(t) < V:
+                    raise ValueError(f"token id {int(t)} outside the vocabulary ({V})")
+
+    def step(self, cache: Cache, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Runs each sequence's next tokens. `want[i]` lists the places among sequence i's tokens of
+        this step whose logits are returned (default: the last). Returns [wanted, vocab] float32 on
+        the device, in the order of the sequences and of `want`. On an error nothing of the cache's
+        accounting has changed."""
+        if want is None:
+            want = [[len(t) - 1] for t in token_lists]
+        if len(slots) != len(token_lists) or len(want) != len(slots):
+            raise ValueError("a step needs one token list and one list of wanted places per slot")
+        self.check_tokens(token_lists)
+        for toks, places in zip(token_lists, want):
+            for p in places:
+                if not 0 <= int(p) < len(toks):
+                    raise ValueError(f"wanted place {p} is not among the {len(toks)} tokens of the step")
+        q_lens = [len(t) for t in token_lists]
+        starts = cache.begin_step(slots, q_lens)
+        ctx = self.stager.stage(cache, slots, token_lists, want, starts)
+        logits = self.forward(ctx, cache)
+        cache.end_step(slots, q_lens)
+        return logits
+
+    def forward(self, ctx: StepContext, cache: Cache) -> torch.Tensor:
+        rt, spec = self.rt, self.spec
+        h = rt.ws.get("stream", (ctx.n_tokens, spec.hidden), torch.float32)
+        ops.embed(self.embed, ctx.tokens, h)
+        stream = ResidualStream(h, rt)
+        for i, call in enumerate(spec.order):
+            self.blocks[call.layer].forward(stream, ctx, cache.views[i])
+        if ctx.want_rows.numel() == 0:
+            stream.flush()
+            return torch.empty((0, spec.vocab), dtype=torch.float32, device=rt.device)
+        y = stream.norm(self.final_norm, spec.final_norm.eps, ctx.want_rows)
+        return rt.linear(y, self.head, "logits", out_dtype=torch.float32)
+
+
+def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> Model:
+    """The model a folder's config.json names, with the folder's safetensors."""
+    cfg_json = read_json(os.path.join(folder, "config.json"))
+    arch = registry.architecture_for(cfg_json)
+    config = arch.config_class.from_json(cfg_json)
+    spec = config.model_spec()
+    weights = load_weights(spec, folder)
+    return Model(spec, weights, dtype=dtype, device=device, config=config)

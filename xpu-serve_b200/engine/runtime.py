@@ -1,0 +1,88 @@
+"""What the parts share on one device: the precision mode, scratch buffers, matrix products.
+
+Two modes. "bfloat16": matrices, activations between kernels and the cache are bfloat16;
+norm weights, the residual stream, softmax, rotation tables and logits are float32.
+"float32": everything is float32 and every matrix product runs on CUDA-core FMAs (no
+tensor cores, no TF32), slower but exact enough to show what bfloat16 hides.
+
+Matrix products: the float32 mode uses this library's own kernel for every shape. The
+bfloat16 mode uses this library's kernels where the reference uses its own (products with
+few rows, src/backend/sycl/sycl_kernels.cpp:630-714, `kGemvMaxRows`) and the vendor's
+GEMM library where the reference calls one (prefill-sized products, oneMKL there,
+src/backend/sycl/sycl_matmul.cpp:44-110; cuBLAS through torch.mm here).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..ops import lib as ops
+
+DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+class Workspace:
+    """Named scratch buffers that grow to the largest request and are then reused.
+    A name is used by one producer at a time; layers run one after another and share them."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"scratch buffer '{name}' would have to grow after it was frozen")
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+
+class Runtime:
+    def __init__(self, dtype: str = "bfloat16", device="cuda:0"):
+        if dtype not in DTYPES:
+            raise ValueError(f"dtype '{dtype}' is not supported (bfloat16, float32 are)")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        self.act_dtype = DTYPES[dtype]
+        self.mode = "bfloat16" if self.act_dtype == torch.bfloat16 else "float32"
+        self.ws = Workspace(self.device)
+        self.shared: Dict[Tuple, object] = {}     # parts memoise what equal specs can share (tables)
+        # cuBLAS may otherwise reduce split products in bfloat16
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        self.small_m = 8      # products with at most this many rows use this library's streaming kernel
+        ops.load()
+
+    # -------------------------------------------------------------- weights
+    def matrix(self, t: torch.Tensor) -> torch.Tensor:
+        """A matrix or table in the mode's element type, on the device."""
+        return t.to(device=self.device, dtype=self.act_dtype).contiguous()
+
+    def vector(self, t: torch.Tensor) -> torch.Tensor:
+        """Norm weights, taps and biases stay float32 in both modes."""
+        return t.to(device=self.device, dtype=torch.float32).contiguous()
+
+    # ------------------------------------------------------ matrix products
+    def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`."""
+        M, N = x.shape[0], w.shape[0]
+        out_dtype = out_dtype or self.act_dtype
+        out = self.ws.get(name, (M, N), out_dtype)
+        if self.mode == "float32" or bias is not None:
+            ops.gemm_generic(x, w, out, bias)
+        elif M <= self.small_m and hasattr(ops, "gemv_small_m"):
+            ops.gemv_small_m(x, w, out)
+        elif out_dtype == torch.float32:
+            out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+        else:
+            torch.mm(x, w.t(), out=out)
+        return out

@@ -1,0 +1,271 @@
+"""Loads the compiled CUDA library and calls its `extern "C"` functions on torch tensors.
+
+There is no fallback: if the library cannot be built or loaded, or a function reports an
+error, an exception says so. Tensors are passed as raw device pointers with their sizes;
+launches go to torch's current CUDA stream, so they order with torch's own work and can
+be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_int64, c_uint64, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or failed to launch."""
+
+
+_lib = None
+
+
+def _signatures(lib) -> None:
+    P, I, L, F = c_void_p, c_int, c_int64, c_float
+    sig = {
+        "xs_embed": [P, I, P, P, I, I, P],
+        "xs_add_rmsnorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
+        "xs_silu_mul": [P, P, I, I, I, L, P],
+        "xs_zero_rows": [P, P, I, L, P],
+        "xs_gemm_generic": [P, P, P, P, I, I, I, I, I, L, L, L, P],
+        "xs_qk_norm_rope_store": [P, L, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P],
+        "xs_attention_generic": [P, P, P, I, P, P, P, L, P, I, I, I, I, I, F, I, I, P],
+        "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "xs_argmax": [P, L, I, I, P, P],
+        "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
+        "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
+        "xs_note_tokens": [P, P, I, I, P, P, I, P],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+    lib.xs_last_error.restype = ctypes.c_char_p
+    lib.xs_last_error.argtypes = []
+    lib.xs_uniform.restype = c_double
+    lib.xs_uniform.argtypes = [c_uint64, c_uint64]
+    lib.xs_abi_version.restype = c_int
+
+
+def load(verbose: bool = True):
+    """The library handle, built first if its file is missing."""
+    global _lib
+    if _lib is None:
+        path = _build.build(verbose=verbose)
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"the CUDA library {path} cannot be loaded: {e}") from None
+        _signatures(lib)
+        _lib = lib
+    return _lib
+
+
+def loaded_path() -> Optional[str]:
+    return None if _lib is None else _lib._name
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(_lib.xs_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not supported (float32, bfloat16 are)") from None
+
+
+def _need(t: torch.Tensor, what: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, is {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+def uniform(seed: int, counter: int) -> float:
+    """The uniform in [0, 1) that the sampling kernel derives from (seed, counter)."""
+    return float(load().xs_uniform(seed & (2 ** 64 - 1), counter & (2 ** 64 - 1)))
+
+
+# ------------------------------------------------------------------ wrappers
+def embed(table: torch.Tensor, ids: torch.Tensor, h: torch.Tensor) -> None:
+    _need(table, "embedding table"); _need(ids, "ids", torch.int32); _need(h, "h", torch.float32)
+    T, H = h.shape
+    _check(load().xs_embed(table.data_ptr(), _code(table), ids.data_ptr(), h.data_ptr(), T, H, _stream()))
+
+
+def add_rmsnorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[torch.Tensor],
+                w: Optional[torch.Tensor], y: Optional[torch.Tensor], rows: Optional[torch.Tensor], eps: float,
+                eps_post: Optional[float] = None) -> None:
+    """h += post(m) (if m); y = RMSNorm(h, w) (if w), over `rows` of h when given."""
+    _need(h, "h", torch.float32)
+    H = h.shape[-1]
+    n = h.shape[0] if rows is None else rows.numel()
+    if m is not None:
+        _need(m, "m")
+        if m.shape != h.shape:
+            raise KernelError(f"m is {tuple(m.shape)}, h is {tuple(h.shape)}")
+    for v, name in ((post_w, "post_w"), (w, "w")):
+        if v is not None:
+            _need(v, name, torch.float32)
+            if v.numel() != H:
+                raise KernelError(f"{name} has {v.numel()} elements for rows of {H}")
+    if y is not None:
+        _need(y, "y")
+        if y.shape[0] < n or y.shape[-1] != H:
+            raise KernelError(f"y is {tuple(y.shape)} for {n} rows of {H}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _check(load().xs_add_rmsnorm(h.data_ptr(), _ptr(m), F32 if m is None else _code(m), _ptr(post_w), _ptr(w),
+                                 _ptr(y), F32 if y is None else _code(y), _ptr(rows), n, H,
+                                 float(eps if eps_post is None else eps_post), float(eps), _stream()))
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
+    _need(gu, "gate_up"); _need(out, "out", gu.dtype)
+    T, F = out.shape
+    if gu.shape[0] != T or gu.shape[1] < 2 * F:
+        raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
+    _check(load().xs_silu_mul(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), _stream()))
+
+
+def zero_rows(state: torch.Tensor, slots: torch.Tensor) -> None:
+    _need(state, "state"); _need(slots, "slots", torch.int32)
+    row_bytes = state[0].numel() * state.element_size()
+    _check(load().xs_zero_rows(state.data_ptr(), slots.data_ptr(), slots.numel(), row_bytes, _stream()))
+
+
+def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] = x[M, K] . w[N, K]^T (+ bias). Rows may be strided; columns are contiguous."""
+    for t, name in ((x, "x"), (w, "w"), (out, "out")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm: {name} must be a CUDA matrix with contiguous rows")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or x.dtype != w.dtype:
+        raise KernelError(f"gemm: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    _check(load().xs_gemm_generic(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), _code(x), _code(out),
+                                  M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()))
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, pool: Optional[torch.Tensor],
+                       page_table: Optional[torch.Tensor], seq_of_token: torch.Tensor, positions: torch.Tensor,
+                       q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], rope: Optional[torch.Tensor],
+                       heads: int, kv_heads: int, head_dim: int, page_size: int, eps: float, write_kv: bool) -> None:
+    _need(q_out, "q_out", qkv.dtype)
+    if qkv.stride(1) != 1:
+        raise KernelError("qkv rows must be contiguous")
+    T = qkv.shape[0]
+    width = (heads + (2 * kv_heads if write_kv else 0)) * head_dim
+    if qkv.shape[1] < width:
+        raise KernelError(f"qkv is {tuple(qkv.shape)}, needs {width} columns")
+    if write_kv:
+        _need(pool, "cache", qkv.dtype); _need(page_table, "page table", torch.int32)
+        if tuple(pool.shape[1:]) != (2, kv_heads, page_size, head_dim):
+            raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 2, {kv_heads}, {page_size}, {head_dim}]")
+    for v, name in ((q_w, "q_norm"), (k_w, "k_norm")):
+        if v is not None:
+            _need(v, name, torch.float32)
+            if v.numel() != head_dim:
+                raise KernelError(f"{name} has {v.numel()} elements for heads of {head_dim}")
+    if rope is not None:
+        _need(rope, "rope table", torch.float32)
+        if tuple(rope.shape[1:]) != (head_dim // 2, 2):
+            raise KernelError(f"rope table is {tuple(rope.shape)}, expected [*, {head_dim // 2}, 2]")
+    P = 0 if page_table is None else page_table.shape[1]
+    _check(load().xs_qk_norm_rope_store(
+        qkv.data_ptr(), qkv.stride(0), q_out.data_ptr(), _ptr(pool), _ptr(page_table), P, seq_of_token.data_ptr(),
+        positions.data_ptr(), _ptr(q_w), _ptr(k_w), _ptr(rope), T, heads, kv_heads, head_dim, page_size, float(eps),
+        1 if write_kv else 0, _code(qkv), _stream()))
+
+
+def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, seq_of_token: torch.Tensor,
+                      positions: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, kv_heads: int,
+                      page_size: int, scale: float, window: int) -> None:
+    _need(q, "q"); _need(out, "out", q.dtype); _need(pool, "cache", q.dtype); _need(page_table, "page table", torch.int32)
+    T, heads, D = q.shape
+    if tuple(pool.shape[1:]) != (2, kv_heads, page_size, D):
+        raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 2, {kv_heads}, {page_size}, {D}]")
+    ld_gate = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < heads:
+            raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {heads} heads")
+        ld_gate = gate.stride(0)
+    _check(load().xs_attention_generic(
+        q.data_ptr(), pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], seq_of_token.data_ptr(),
+        positions.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), T, heads, kv_heads, D, page_size, float(scale),
+        int(window), _code(q), _stream()))
+
+
+def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+               seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor) -> None:
+    _need(out, "out", bcx.dtype); _need(state, "state", bcx.dtype); _need(w_t, "taps", torch.float32)
+    T, H = out.shape
+    K = w_t.shape[0]
+    if bcx.stride(1) != 1 or bcx.shape[0] != T or bcx.shape[1] < 3 * H or w_t.shape[1] != H:
+        raise KernelError(f"short_conv: bcx {tuple(bcx.shape)}, taps {tuple(w_t.shape)}, out {tuple(out.shape)}")
+    if tuple(state.shape[1:]) != (K - 1, H):
+        raise KernelError(f"short_conv: state is {tuple(state.shape)}, expected [*, {K - 1}, {H}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    _check(load().xs_short_conv(bcx.data_ptr(), bcx.stride(0), w_t.data_ptr(), _ptr(bias), state.data_ptr(),
+                                seq_of_token.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(),
+                                T, slots.numel(), H, K, _code(bcx), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
+    n, V = logits.shape
+    _check(load().xs_argmax(logits.data_ptr(), logits.stride(0), n, V, out.data_ptr(), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
+    n, V = logits.shape
+    for t, name, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                        (top_p, "top_p", torch.float32), (min_p, "min_p", torch.float32),
+                        (seeds, "seeds", torch.int64), (counters, "counters", torch.int64)):
+        _need(t, name, dt)
+        if t.numel() < n:
+            raise KernelError(f"{name} has {t.numel()} entries for {n} rows")
+    _check(load().xs_sample(logits.data_ptr(), logits.stride(0), n, V, temperature.data_ptr(), top_k.data_ptr(),
+                            top_p.data_ptr(), min_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(),
+                            out.data_ptr(), _stream()))
+
+
+def apply_penalties(logits: torch.Tensor, seen: torch.Tensor, gen_count: torch.Tensor, state_rows: torch.Tensor,
+                    repetition: torch.Tensor, presence: torch.Tensor, frequency: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32); _need(seen, "seen", torch.uint8); _need(gen_count, "counts", torch.int32)
+    n, V = logits.shape
+    _check(load().xs_apply_penalties(logits.data_ptr(), logits.stride(0), n, V, seen.data_ptr(), gen_count.data_ptr(),
+                                     state_rows.data_ptr(), repetition.data_ptr(), presence.data_ptr(),
+                                     frequency.data_ptr(), _stream()))
+
+
+def note_tokens(tokens: torch.Tensor, rows_of_token: torch.Tensor, seen: torch.Tensor, gen_count: torch.Tensor,
+                generated: bool) -> None:
+    _need(tokens, "tokens", torch.int32); _need(rows_of_token, "rows", torch.int32)
+    V = seen.shape[1]
+    _check(load().xs_note_tokens(tokens.data_ptr(), rows_of_token.data_ptr(), tokens.numel(), V, seen.data_ptr(),
+                                 gen_count.data_ptr(), 1 if generated else 0, _stream()))

@@ -1,0 +1,100 @@
+"""Grouped-query attention over the paged cache, with per-head q/k norms, rotary position
+encoding and an optional sigmoid gate per head (src/models/common/blocks.cpp:143-187,
+src/models/lfm3/lfm3_decoder.cpp:114-141).
+
+One matrix product gives q, k, v and the gate logits: the four weights are stacked at
+load ([q; k; v; gate], the gate rows padded to a multiple of 8). The cache keeps normed,
+rotated keys and raw values. A call that reads another call's cache computes q (and the
+gate) only.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import registry
+from ..ops import lib as ops
+from .base import KVNeed, Mixer, TensorSpec
+
+
+class AttentionMixer(Mixer):
+    kind = "attention"
+
+    @classmethod
+    def tensors(cls, spec) -> Dict[str, TensorSpec]:
+        n = spec.names
+        qd, kd = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+        out = {
+            n["q"]: TensorSpec((qd, spec.hidden)), n["k"]: TensorSpec((kd, spec.hidden)),
+            n["v"]: TensorSpec((kd, spec.hidden)), n["o"]: TensorSpec((spec.hidden, qd)),
+        }
+        if spec.head_gate:
+            out[n["gate"]] = TensorSpec((spec.heads, spec.hidden))
+        if spec.qk_norm:
+            out[n["q_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
+            out[n["k_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        return KVNeed(spec.kv_heads, spec.head_dim, spec.window)
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        if spec.head_dim % 2 != 0 or spec.head_dim > 256:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be even and at most 256")
+        if spec.heads % spec.kv_heads != 0:
+            raise ValueError(f"attention: {spec.heads} heads over {spec.kv_heads} kv heads")
+        self.spec, self.rt = spec, rt
+        n = spec.names
+        self.q_dim = spec.heads * spec.head_dim
+        self.kv_dim = spec.kv_heads * spec.head_dim
+        rows = [weights[n["q"]], weights[n["k"]], weights[n["v"]]]
+        q_rows = [weights[n["q"]]]
+        if spec.head_gate:
+            g = weights[n["gate"]]
+            pad = (-g.shape[0]) % 8
+            if pad:
+                g = torch.cat([g, torch.zeros(pad, g.shape[1], dtype=g.dtype)], 0)
+            rows.append(g)
+            q_rows.append(g)
+        self.w_qkvg = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
+        self._q_rows = q_rows          # stacked on the device on the first use as a reader of another cache
+        self.w_qg = None
+        self.w_o = rt.matrix(weights[n["o"]])
+        self.q_norm = rt.vector(weights[n["q_norm"]]) if spec.qk_norm else None
+        self.k_norm = rt.vector(weights[n["k_norm"]]) if spec.qk_norm else None
+        self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
+                         if spec.position is not None else None)
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        T = x.shape[0]
+        if cache is None or cache.storage is None:
+            raise RuntimeError("attention needs a key/value cache")
+        if cache.owner:
+            proj = rt.linear(x, self.w_qkvg, "attn_qkv")
+            gate_at = self.q_dim + 2 * self.kv_dim
+        else:
+            if self.w_qg is None:
+                self.w_qg = rt.matrix(torch.cat([r.to(torch.float32) for r in self._q_rows], 0))
+            proj = rt.linear(x, self.w_qg, "attn_qkv")
+            gate_at = self.q_dim
+        table = step.page_tables[cache.group]
+        rope = self.position.table(step.max_positions) if self.position is not None else None
+        q = rt.ws.get("attn_q", (T, s.heads, s.head_dim), rt.act_dtype)
+        ops.qk_norm_rope_store(proj, q, cache.storage, table, step.seq_of_token, step.positions, self.q_norm,
+                               self.k_norm, rope, s.heads, s.kv_heads, s.head_dim, step.page_size, s.qk_norm_eps,
+                               write_kv=cache.owner)
+        o = rt.ws.get("attn_o", (T, s.heads, s.head_dim), rt.act_dtype)
+        gate = proj[:, gate_at:] if s.head_gate else None
+        self.attend(q, cache, table, step, gate, o)
+        return rt.linear(o.view(T, self.q_dim), self.w_o, "mixer_out")
+
+    def attend(self, q, cache, table, step, gate, o) -> None:
+        s = self.spec
+        ops.attention_generic(q, cache.storage, table, step.seq_of_token, step.positions, gate, o, s.kv_heads,
+                              step.page_size, s.scale, s.window)
+
+
+registry.register_mixer(AttentionMixer.kind, AttentionMixer)
