@@ -1,0 +1,291 @@
+#!/usr/bin/env python3
+"""Decode and prefill speed of LFM3 at the 1.2B layer shape on one B200, with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
+
+A step is one decode step of a batch whose sequences hold 2,048-token prompts (context
+4,096). Prints ONE JSON line: decoded tokens a second timed on the device (`value`), the
+same through the Python entry point with host tokens in and out (`e2e`), a 2,048-token
+prefill (`prefill`), the decode step against the HBM roofline (`roofline`), and decode at
+batch 1 and 64 (`points`). Peaks come from MEASURED_PEAKS.json when present. Inputs are
+synthetic token ids; every timed step reads all weights (2.3 GB), far more than the 126 MB
+L2, so no cache flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the 1.2B family shape
+SHAPE_1_2B = {
+    "model_type": "lfm3", "vocab_size": 65536, "hidden_size": 2048, "intermediate_size": 8192,
+    "num_hidden_layers": 16,
+    "layer_types": ["conv", "conv", "attn", "conv", "conv", "attn", "conv", "conv", "attn", "conv", "attn", "conv",
+                    "attn", "conv", "attn", "conv"],
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "conv_L_cache": 3, "conv_bias": False,
+    "rope_theta": 1000000.0, "norm_eps": 1e-5, "max_position_embeddings": 4096, "tie_word_embeddings": True,
+    "use_sandwich_norm": False, "attn_head_gate": False, "initializer_range": 0.02,
+}
+PROMPT = 2048
+CONTEXT = 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    "source": "measured"}
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self._proc = None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                           "--format=csv,noheader,nounits", "-lms", "100"],
+                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self._proc = None
+
+    def _read(self):
+        for line in self._proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+        mhz = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:6]) if v == "Active"})
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def model_numbers(cfg: dict, n_layers_run: int):
+    """Bytes a decode step must read and flops of a prefill, from the configuration."""
+    H, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    Hq, Hkv, D, K = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["conv_L_cache"]
+    kinds = cfg["layer_types"][:n_layers_run]
+    n_attn = sum(1 for k in kinds if k != "conv")
+    n_conv = len(kinds) - n_attn
+    ffn = 3 * H * F
+    conv = 4 * H * H
+    attn = 2 * H * Hq * D + 2 * H * Hkv * D
+    layer_params = len(kinds) * ffn + n_conv * conv + n_attn * attn
+    weight_bytes = 2 * (layer_params + V * H)              # bfloat16; the tied table is read once, as the head
+    kv_bytes_per_token = n_attn * 2 * Hkv * D * 2
+    state_bytes = n_conv * (K - 1) * H * 2 * 2              # read and written
+    return {"layer_params": layer_params, "weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token,
+            "state_bytes": state_bytes, "n_attn": n_attn, "n_conv": n_conv}
+
+
+def prefill_flops(cfg: dict, nums: dict, T: int) -> float:
+    Hq, D, H, V = cfg["num_attention_heads"], cfg["head_dim"], cfg["hidden_size"], cfg["vocab_size"]
+    return 2.0 * T * nums["layer_params"] + nums["n_attn"] * 2.0 * T * T * D * Hq + 2.0 * H * V
+
+
+def synthetic_prompt(V: int, n: int, salt: int):
+    return [(salt * 7919 + i * 31 + (i * i) % 11 + 1) % V for i in range(n)]
+
+
+def time_decode(model, batch: int, steps: int, warmup: int, V: int):
+    """Device time of `steps` decode steps (model step + argmax) of `batch` sequences after
+    2,048-token prompts. Returns (ms per step, kernel launches per step)."""
+    import torch
+    from xpu_serve_b200.ops import lib as ops
+    cache = model.new_cache(batch * CONTEXT, max_slots=batch, max_seq_tokens=CONTEXT)
+    slots = cache.open(batch)
+    chunk = max(1, 8192 // PROMPT)
+    for b0 in range(0, batch, chunk):           # prompts in pieces of at most 8,192 tokens a step
+        part = list(range(b0, min(batch, b0 + chunk)))
+        model.step(cache, [slots[i] for i in part], [synthetic_prompt(V, PROMPT, i) for i in part],
+                   [[] for _ in part])
+    out = torch.empty(batch, dtype=torch.int32, device=model.rt.device)
+    tokens = [[(7 * i + 3) % V] for i in range(batch)]
+
+    def one():
+        logits = model.step(cache, slots, tokens)
+        ops.argmax(logits, out)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    before = ops.launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = (ops.launches - before) / steps
+    cache.close(slots)
+    del cache
+    torch.cuda.empty_cache()
+    return ms, launches
+
+
+def time_prefill(model, V: int, warmup: int, runs: int):
+    import torch
+    cache = model.new_cache(CONTEXT, max_slots=1, max_seq_tokens=CONTEXT)
+    times = []
+    for r in range(warmup + runs):
+        (slot,) = cache.open(1)
+        prompt = synthetic_prompt(V, PROMPT, 100 + r)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        model.step(cache, [slot], [prompt])
+        end.record()
+        torch.cuda.synchronize()
+        if r >= warmup:
+            times.append(start.elapsed_time(end))
+        cache.close([slot])
+    return statistics.median(times)
+
+
+def time_e2e(folder: str, batch: int, steps: int, warmup: int, V: int):
+    """The same decode rate through Engine.generate: host token ids in, host token ids out, every
+    step with its host-to-device copy of the step's description and its device-to-host copy of the
+    chosen tokens."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    engine = Engine(folder, precision="bf16", ctx=CONTEXT, max_tokens=batch * CONTEXT, max_batch=batch)
+    reqs = [GenerateRequest(synthetic_prompt(V, PROMPT, 200 + i), SamplingParams(temperature=0.0), steps + warmup + 1, [])
+            for i in range(batch)]
+    stamps = []
+
+    def on_token(i, t):
+        if i == 0:
+            stamps.append(time.perf_counter())
+        return True
+
+    results = engine.generate(reqs, on_token)
+    bad = [r.error for r in results if r.finish == "error"]
+    if bad:
+        raise RuntimeError(bad[0])
+    # request 0's token k arrives after decode step k - 1; skip the warm-up steps
+    span = stamps[warmup + steps] - stamps[warmup]
+    h2d = engine.model.stager.last_h2d_bytes      # the step's description: tokens, positions, slots, page tables
+    return batch * steps / span, h2d, 4 * batch
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run only the first N layers (reported in config)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "v1k22/xpu-serve is a C++/SYCL program for Intel GPUs with no Python package and no CUDA "
+                          "backend; pip cannot install it and its loader refuses this configuration "
+                          "(use_sandwich_norm false)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from xpu_serve_b200 import load_model
+    from xpu_serve_b200.config import Lfm3Config
+    from xpu_serve_b200.weights import write_random_model
+
+    cfg = dict(SHAPE_1_2B)
+    full_layers = cfg["num_hidden_layers"]
+    n_layers = full_layers if args.layers is None else max(1, min(args.layers, full_layers))
+    cfg["num_hidden_layers"] = n_layers
+    cfg["layer_types"] = cfg["layer_types"][:n_layers]
+    V = cfg["vocab_size"]
+    pk = peaks()
+    nums = model_numbers(cfg, n_layers)
+
+    with tempfile.TemporaryDirectory() as root:
+        folder = write_random_model(os.path.join(root, "lfm3_1_2b"), Lfm3Config.from_json(cfg), seed=0, dtype="bfloat16")
+        model = load_model(folder, dtype="bfloat16")
+
+        prefill_ms = time_prefill(model, V, warmup=2, runs=3)
+        pf = prefill_flops(cfg, nums, PROMPT)
+
+        sampler = ClockSampler()
+        sampler.start()
+        ms, launches = time_decode(model, args.batch, args.steps, args.warmup, V)
+        clocks = sampler.stop()
+
+        points = {}
+        if not args.skip_points:
+            for b in (1, 64):
+                pms, _ = time_decode(model, b, max(8, args.steps // 4), 3, V)
+                points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+        del model
+        torch.cuda.empty_cache()
+        e2e_value, h2d, d2h = time_e2e(folder, args.batch, min(args.steps, 32), args.warmup, V)
+
+    value = args.batch * 1000.0 / ms
+    step_bytes = nums["weight_bytes"] + args.batch * (PROMPT * nums["kv_bytes_per_token"] + nums["state_bytes"])
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "LFM3-1.2B-shape decode tok/s (batch 8, 2,048-token prompts)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random weights N(0, 0.02)", "impl": "ours",
+        "config": {
+            "model": "LFM3 1.2B shape", "layers": n_layers, "layers_of_shape": full_layers,
+            "hidden": cfg["hidden_size"], "ffn": cfg["intermediate_size"], "vocab": V,
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "conv_kernel": cfg["conv_L_cache"],
+            "attn_layers": nums["n_attn"], "conv_layers": nums["n_conv"], "global_batch": args.batch,
+            "seq_len": PROMPT, "context": CONTEXT, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (2.3 GB of weights a step)"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "prefill": {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes,
+                     "peaks": pk["source"]},
+        "points": points,
+        "clocks": clocks,
+        "gpu_launches": int(round(launches * args.steps)),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -36,6 +36,8 @@ def read_safetensors(path: str) -> Dict[str, np.ndarray]:
             a = np.frombuffer(raw, dtype="<f4")
         elif e["dtype"] == "F16":
             a = np.frombuffer(raw, dtype="<f2")
+        elif e["dtype"] in ("I64", "I32"):
+            a = np.frombuffer(raw, dtype="<i8" if e["dtype"] == "I64" else "<i4")
         else:
             raise ValueError(f"{name}: dtype {e['dtype']}")
         out[name] = a.astype(np.float64).reshape(e["shape"])

@@ -1,0 +1,175 @@
+"""Slots and pages: nothing lost, held twice or freed twice; windows give pages back; a refused
+step changes nothing. Runs on the CPU (the cache's storage is allocated there)."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from xpu_serve_b200.cache import Cache, CacheError, CacheFull, IndexPool
+from xpu_serve_b200.parts.base import KVNeed, StateNeed
+
+
+def make(max_tokens=1024, window=0, max_slots=None, max_seq=None):
+    needs = [StateNeed((2, 8)), KVNeed(2, 16, 0), StateNeed((2, 8)), KVNeed(2, 16, window), None, KVNeed(1, 32, 0)]
+    shares = [None, None, None, None, None, None]
+    return Cache(needs, shares, max_tokens, max_slots=max_slots, max_seq_tokens=max_seq, dtype=torch.float32,
+                 device="cpu")
+
+
+def test_index_pool_accounting():
+    p = IndexPool(4, "slot")
+    a = p.take(3)
+    assert a == [0, 1, 2] and p.free_count == 1
+    with pytest.raises(CacheFull):
+        p.take(2)
+    p.give_back([1])
+    with pytest.raises(CacheError, match="freed twice"):
+        p.give_back([1])
+    with pytest.raises(CacheError, match="freed twice"):
+        p.give_back([0, 0])
+    assert p.is_held(0)                       # the refused call changed nothing
+    with pytest.raises(CacheError, match="does not exist"):
+        p.give_back([7])
+    assert p.take(1) == [1]                   # the lowest free index is used again first
+    p.check()
+
+
+def test_groups_by_need():
+    c = make()
+    kinds = [type(g).__name__ for g in c.groups]
+    assert kinds.count("StateGroup") == 1 and kinds.count("KVGroup") == 2      # window 0: calls 1 and 3 share a group
+    c2 = make(window=100)
+    assert [type(g).__name__ for g in c2.groups].count("KVGroup") == 3        # the window makes its own group
+    assert c2.views[4].storage is None
+    assert c.views[1].storage.shape == (16, 2, 2, 64, 16) and c.views[0].storage.shape[1:] == (2, 8)
+    assert c.views[1].storage.data_ptr() != c.views[3].storage.data_ptr()
+
+
+def test_steps_reserve_pages_and_lengths_advance():
+    c = make()
+    s = c.open(2)
+    starts = c.begin_step(s, [70, 5])
+    assert list(starts) == [0, 0]
+    c.end_step(s, [70, 5])
+    assert list(c.lens[s]) == [70, 5] and c.tokens_held() == 3 * 64
+    assert list(c.begin_step(s, [1, 1])) == [70, 5]
+    c.end_step(s, [1, 1])
+    t = c.page_table(c.kv_groups[0], s)
+    assert t.shape == (2, 2) and t[0, 0] != t[0, 1] and t[1, 1] == -1
+    c.check()
+    c.close([s[1]])
+    assert c.tokens_held() == 2 * 64
+    c.close([s[0]])
+    assert c.tokens_held() == 0 and c.slots.held_count == 0
+    c.check()
+
+
+def test_refused_step_changes_nothing():
+    c = make(max_tokens=256)
+    s = c.open(3)
+    c.begin_step(s[:2], [100, 60])
+    c.end_step(s[:2], [100, 60])
+    before = (c.lens.copy(), [g.pages.free_count for g in c.groups if hasattr(g, "pages")])
+    with pytest.raises(CacheFull):
+        c.begin_step(s, [1, 1, 129])          # needs 3 more pages, 1 is free
+    with pytest.raises(CacheError, match="not held"):
+        c.begin_step([s[0], 3], [1, 1])
+    with pytest.raises(CacheError, match="twice"):
+        c.begin_step([s[0], s[0]], [1, 1])
+    with pytest.raises(CacheError, match="at least one token"):
+        c.begin_step([s[0]], [0])
+    after = (c.lens.copy(), [g.pages.free_count for g in c.groups if hasattr(g, "pages")])
+    assert np.array_equal(before[0], after[0]) and before[1] == after[1]
+    c.check()
+
+
+def test_close_twice_is_refused():
+    c = make()
+    s = c.open(2)
+    c.close([s[0]])
+    with pytest.raises(CacheError, match="freed twice"):
+        c.close([s[0]])
+    with pytest.raises(CacheError, match="freed twice"):
+        c.close([s[1], s[1]])
+    c.close([s[1]])
+    c.check()
+
+
+def test_sequence_limit():
+    c = make(max_tokens=1024, max_seq=100)
+    s = c.open(1)
+    with pytest.raises(CacheError, match="exceed the limit of 100"):
+        c.begin_step(s, [101])
+    c.begin_step(s, [100])
+
+
+def test_window_group_gives_pages_back():
+    c = make(max_tokens=2048, window=70)
+    win = [i for i in c.kv_groups if c.groups[i].need.window == 70][0]
+    full = [i for i in c.kv_groups if c.groups[i].need.window == 0][0]
+    (s,) = c.open(1)
+    c.begin_step([s], [300])
+    c.end_step([s], [300])
+    # the next query stands at 300 and sees keys from 231 on: pages 0..2 (positions < 192) are free again
+    assert c.groups[win].pages.held_count == 2 and c.groups[full].pages.held_count == 5
+    t = c.page_table(win, [s])
+    assert list(t[0, :3]) == [-1, -1, -1] and t[0, 3] >= 0 and t[0, 4] >= 0
+    for _ in range(200):
+        c.begin_step([s], [1])
+        c.end_step([s], [1])
+    assert c.groups[win].pages.held_count <= 3 and c.groups[full].pages.held_count == 8
+    c.check()
+    c.close([s])
+    assert c.groups[win].pages.held_count == 0
+    c.check()
+
+
+def test_fixed_size_state_is_zeroed_on_open():
+    c = make()
+    s = c.open(2)
+    state = c.views[0].storage
+    state[s[0]] = 3.0
+    state[s[1]] = 4.0
+    c.close(s)
+    s2 = c.open(1)
+    assert s2 == [s[0]] and float(state[s2[0]].abs().sum()) == 0.0 and float(state[s[1]].abs().sum()) > 0
+
+
+def test_shared_cache_view():
+    needs = [KVNeed(2, 16, 0), KVNeed(2, 16, 0), StateNeed((1, 4))]
+    c = Cache(needs, [None, 0, None], 256, dtype=torch.float32, device="cpu")
+    assert c.views[1].storage.data_ptr() == c.views[0].storage.data_ptr()
+    assert c.views[0].owner and not c.views[1].owner and len(c.groups) == 2
+    assert c.groups[c.views[0].group].calls == [0]
+
+
+def test_random_traffic_keeps_the_books():
+    rng = random.Random(0)
+    c = make(max_tokens=64 * 40, window=90, max_slots=12)
+    live = {}
+    for _ in range(600):
+        r = rng.random()
+        if r < 0.25 and c.slots.free_count:
+            for s in c.open(rng.randint(1, min(3, c.slots.free_count))):
+                live[s] = 0
+        elif r < 0.4 and live:
+            gone = rng.sample(sorted(live), rng.randint(1, min(3, len(live))))
+            c.close(gone)
+            for s in gone:
+                del live[s]
+        elif live:
+            batch = rng.sample(sorted(live), rng.randint(1, len(live)))
+            q = [rng.choice([1, 1, 1, 7, 64, 65, 130]) for _ in batch]
+            try:
+                c.begin_step(batch, q)
+            except CacheError:
+                continue
+            c.end_step(batch, q)
+            for s, n in zip(batch, q):
+                live[s] += n
+        c.check()
+        assert {s: int(c.lens[s]) for s in live} == live
+    c.close(sorted(live))
+    c.check()
+    assert c.tokens_held() == 0 and c.slots.held_count == 0

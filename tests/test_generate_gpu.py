@@ -1,0 +1,174 @@
+"""Generation through the Python entry point, and the sampling kernels, against the plain
+implementation."""
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen_models")
+    return {(n, d): tiny.make_folder(root, n, d) for n in ("A", "B", "W") for d in ("float32", "bfloat16")}
+
+
+def plain_greedy(cfg, W, prompt, n, stops=()):
+    seq, out, margins = list(prompt), [], []
+    for _ in range(n):
+        logits = plain.forward(cfg, W, seq)[-1]
+        order = np.argsort(-logits)
+        t = int(order[0])
+        if t in stops:
+            break
+        margins.append(float(logits[order[0]] - logits[order[1]]) / float(np.abs(logits).max()))
+        out.append(t)
+        seq.append(t)
+    return out, margins
+
+
+@pytest.mark.parametrize("name,lengths,steps", [("A", (5, 9, 13), 8), ("B", (1, 4, 7, 16, 23), 12), ("W", (3, 50, 41), 10)])
+def test_greedy_float32_matches_plain(folders, name, lengths, steps):
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders[(name, "float32")]
+    cfg, W = plain.load_folder(folder)
+    engine = Engine(folder, precision="f32", ctx=256, max_batch=8)
+    prompts = [tiny.prompt(name, n, salt=i) for i, n in enumerate(lengths)]
+    res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), steps, []) for p in prompts])
+    for p, r in zip(prompts, res):
+        want, margins = plain_greedy(cfg, W, p, steps)
+        assert min(margins) > 1e-4, "the test's own tokens are near ties; pick another prompt"
+        assert r.finish == "length" and r.tokens == want
+    engine.stepper.cache.check()
+    assert engine.stepper.cache.slots.held_count == 0
+
+
+def test_greedy_bfloat16_follows_plain_until_a_near_tie(folders):
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders[("A", "bfloat16")]
+    cfg, W = plain.load_folder(folder)
+    engine = Engine(folder, precision="bf16", ctx=256, max_batch=8)
+    prompts = [tiny.prompt("A", n, salt=i) for i, n in enumerate((5, 9, 13))]
+    res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), 8, []) for p in prompts])
+    for p, r in zip(prompts, res):
+        seq = list(p)
+        for t in r.tokens:
+            logits = plain.forward(cfg, W, seq)[-1]
+            best = int(np.argmax(logits))
+            assert t == best or (logits[best] - logits[t]) / np.abs(logits).max() < 2e-2
+            seq.append(t)
+
+
+def test_stop_tokens_and_early_enders(folders):
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders[("B", "float32")]
+    cfg, W = plain.load_folder(folder)
+    engine = Engine(folder, precision="f32", ctx=128, max_tokens=64 * 4, max_batch=3)
+    prompts = [tiny.prompt("B", n, salt=i) for i, n in enumerate((4, 7, 16, 23, 2))]
+    free_run = [plain_greedy(cfg, W, p, 10)[0] for p in prompts]
+    stops = [[free_run[0][3]], [], [free_run[2][0]], [free_run[3][9]], []]
+    news = [10, 3, 10, 10, 6]
+    res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), n, s)
+                           for p, n, s in zip(prompts, news, stops)])
+    for p, r, n, s in zip(prompts, res, news, stops):
+        want, _ = plain_greedy(cfg, W, p, n, s)
+        assert r.tokens == want
+        assert r.finish == ("stop" if len(want) < n else "length")
+    assert [r.stats.batch_size for r in res] == [3, 3, 3, 2, 2]      # two batches, one after the other
+    engine.stepper.cache.check()
+
+
+def test_seeded_sampling_matches_plain_sampler(folders):
+    """Temperature 0.8 with a seed: the kernel's choice equals the plain sampler's given the same
+    uniform, step after step (configuration B's workload: prompts 1/4/7/16/23, 12 steps)."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders[("B", "float32")]
+    cfg, W = plain.load_folder(folder)
+    engine = Engine(folder, precision="f32", ctx=128, max_batch=8)
+    prompts = [tiny.prompt("B", n, salt=i) for i, n in enumerate((1, 4, 7, 16, 23))]
+    params = [SamplingParams(temperature=0.8, seed=11 + i) for i in range(3)] + \
+             [SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=5),
+              SamplingParams(temperature=1.3, min_p=0.05, top_p=0.95, seed=2 ** 63 + 9)]
+    res = engine.generate([GenerateRequest(p, sp, 12, []) for p, sp in zip(prompts, params)])
+    again = engine.generate([GenerateRequest(p, sp, 12, []) for p, sp in zip(prompts, params)])
+    for p, sp, r, r2 in zip(prompts, params, res, again):
+        assert r.tokens == r2.tokens, "the same seed gives the same tokens"
+        seq = list(p)
+        for step, t in enumerate(r.tokens):
+            logits = plain.forward(cfg, W, seq)[-1]
+            u = plain.uniform(sp.seed, step)
+            want = plain.sample(logits, sp.temperature, sp.top_k, sp.top_p, sp.min_p, u)
+            if t != want:    # only a uniform that lands within rounding of a boundary may differ
+                w = plain.kept_weights(logits, sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+                c = np.cumsum(w) / w.sum()
+                assert min(abs(c[t] - u), abs(c[want] - u), abs(c[t - 1] - u)) < 1e-5, (step, t, want)
+            seq.append(t)
+
+
+def test_sampling_kernel_distribution_and_cuts():
+    """The kernel's kept set and draw against the plain sampler over many uniforms, on logits with
+    ties, a wide vocabulary that is no power of two, and every combination of cuts."""
+    from xpu_serve_b200.ops import lib as ops
+    rng = np.random.default_rng(0)
+    V = 5003
+    base = rng.normal(0, 2.5, size=V).astype(np.float32)
+    base[100:110] = base[100]                     # ties inside the likely region
+    base[7] = base.max() + 0.5
+    cases = [(1.0, 0, 1.0, 0.0), (0.7, 50, 1.0, 0.0), (1.0, 0, 0.9, 0.0), (1.5, 0, 1.0, 0.02),
+             (0.9, 200, 0.8, 0.01), (1.0, 3, 0.5, 0.0), (2.0, V, 0.999, 0.0), (1.0, 12, 1.0, 0.5)]
+    n = 256
+    for temp, k, p, mp in cases:
+        logits = torch.tensor(np.tile(base, (n, 1)), device="cuda")
+        seeds = torch.arange(n, dtype=torch.int64, device="cuda") * 7919 + 3
+        counters = torch.arange(n, dtype=torch.int64, device="cuda") % 5
+        out = torch.empty(n, dtype=torch.int32, device="cuda")
+        f = lambda v, dt=torch.float32: torch.full((n,), v, dtype=dt, device="cuda")   # noqa: E731
+        ops.sample(logits, f(temp), f(k, torch.int32), f(p), f(mp), seeds, counters, out)
+        got = out.cpu().numpy()
+        w = plain.kept_weights(base, temp, k, p, mp)
+        assert (w[got] > 0).all(), f"a dropped token was drawn with cuts {temp, k, p, mp}"
+        miss = 0
+        for i in range(n):
+            u = plain.uniform(int(seeds[i]), int(counters[i]))
+            assert ops.uniform(int(seeds[i]), int(counters[i])) == u
+            miss += int(plain.sample(base, temp, k, p, mp, u) != got[i])
+        assert miss <= 1, f"{miss} draws differ with cuts {temp, k, p, mp}"
+    # greedy rows: temperature 0 or top_k 1 pick the first largest
+    logits = torch.tensor(np.tile(base, (4, 1)), device="cuda")
+    logits[1, 3] = logits[1, 7]                                  # a tie: the lower index wins
+    out = torch.empty(4, dtype=torch.int32, device="cuda")
+    ops.sample(logits, torch.tensor([0.0, 0.0, 1.0, 1.0], device="cuda"),
+               torch.tensor([0, 0, 1, 1], dtype=torch.int32, device="cuda"), torch.ones(4, device="cuda"),
+               torch.zeros(4, device="cuda"), torch.zeros(4, dtype=torch.int64, device="cuda"),
+               torch.zeros(4, dtype=torch.int64, device="cuda"), out)
+    assert out.tolist() == [7, 3, 7, 7]
+    ops.argmax(logits, out)
+    assert out.tolist() == [7, 3, 7, 7]
+
+
+def test_penalties_match_plain(folders):
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders[("A", "float32")]
+    cfg, W = plain.load_folder(folder)
+    engine = Engine(folder, precision="f32", ctx=128, max_batch=4)
+    prompts = [tiny.prompt("A", n, salt=i) for i, n in enumerate((6, 11))]
+    sp = [SamplingParams(temperature=0.0, repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1),
+          SamplingParams(temperature=0.0, repetition_penalty=1.0, presence_penalty=0.0, frequency_penalty=0.7)]
+    res = engine.generate([GenerateRequest(p, s, 10, []) for p, s in zip(prompts, sp)])
+    for p, s, r in zip(prompts, sp, res):
+        seq, gen = list(p), []
+        for t in r.tokens:
+            logits = plain.apply_penalties(plain.forward(cfg, W, seq)[-1], p, gen, s.repetition_penalty,
+                                           s.presence_penalty, s.frequency_penalty)
+            best = int(np.argmax(logits))
+            assert t == best or abs(logits[best] - logits[t]) < 1e-5 * np.abs(logits).max()
+            seq.append(t)
+            gen.append(t)

@@ -10,11 +10,24 @@ import trace_util as tu
 
 pytestmark = pytest.mark.gpu
 
-# Largest |difference| over largest |reference logit|. float32: sums of a few hundred float32
-# products per element over at most 8 layers. bfloat16: activations and cache rounded to 8 bits
-# of mantissa between kernels.
-TOL = {"float32": 1e-5, "bfloat16": 3e-2}
-COS = {"float32": 0.999999, "bfloat16": 0.998}
+# Largest |difference| over largest |reference logit|.
+# float32: 1e-5, the build's target for the 32-bit path.
+# bfloat16: a value is rounded to 8 significant bits (relative error up to u = 2^-9) about ten times
+# a layer (normed input, projections, mixer state and output, gate/up, activation, branch output).
+# Errors of independent roundings add like a random walk, so a logit's typical error is about
+# sqrt(10 * layers) * u of the logits' scale; the largest of some 10^5 logits lies a few times
+# higher: 4 * sqrt(10 * layers) * u. The cosine bound is the reference's own for 16-bit runs
+# (tests/unit/model/model_parity.cpp:47).
+U_BF16 = 2.0 ** -9
+
+
+def tolerance(name, dtype):
+    if dtype == "float32":
+        return 1e-5
+    return 4.0 * (10.0 * tiny.CONFIGS[name]["num_hidden_layers"]) ** 0.5 * U_BF16
+
+
+COS = {"float32": 0.999999, "bfloat16": 0.995}
 LENGTHS = [1, 4, 7, 16, 23, 40, 70, 5, 9, 13, 33, 64, 65, 129]
 
 
@@ -58,7 +71,8 @@ def check(name, dtype, steps, replayers, references):
     vocab = tiny.CONFIGS[name]["vocab_size"]
     got = tu.collect(steps, tu.run_in_process(rp, steps), vocab)
     gap, where, cos = tu.worst_gap(got, references(name, dtype))
-    assert gap <= TOL[dtype], f"{name} {dtype}: gap {gap:.3e} at {where}"
+    print(f"GAP {name} {dtype} steps={len(steps)} gap={gap:.3e} at {where} cos={cos:.7f} tol={tolerance(name, dtype):.1e}")
+    assert gap <= tolerance(name, dtype), f"{name} {dtype}: gap {gap:.3e} at {where}"
     assert cos >= COS[dtype], f"{name} {dtype}: cosine {cos}"
     rp.cache.check()
     assert rp.cache.slots.held_count == 0 and rp.cache.tokens_held() == 0
@@ -108,4 +122,4 @@ def test_program_matches_in_process(folders, tmp_path):
     got = tu.collect(steps, out, vocab)
     ref = tu.plain_logits(folders[(name, dtype)], reqs)
     gap, where, _ = tu.worst_gap(got, ref)
-    assert gap <= TOL[dtype], f"gap {gap:.3e} at {where}"
+    assert gap <= tolerance(name, dtype), f"gap {gap:.3e} at {where}"

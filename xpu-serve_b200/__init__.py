@@ -16,3 +16,12 @@ def load_model(folder, dtype="bfloat16", device="cuda:0"):
     """The model that the folder's config.json names, ready to step on `device`."""
     from .engine.model import load_model as _load
     return _load(folder, dtype=dtype, device=device)
+
+from .sampling import GenerateRequest, GenerateResult, GenerateStats, SamplingParams   # noqa: E402
+
+
+def __getattr__(name):
+    if name == "Engine":
+        from .engine.engine import Engine
+        return Engine
+    raise AttributeError(name)

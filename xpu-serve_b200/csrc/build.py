@@ -130,6 +130,12 @@ def build(verbose: bool = True, force: bool = False, jobs: Optional[int] = None)
         if r.returncode != 0:
             raise BuildError(f"linking failed:\n{r.stdout}")
         os.replace(tmp, out)
+        for old in os.listdir(out_dir):     # libraries of earlier source versions
+            if old.startswith(LIB_STEM + "_") and old.endswith(".so") and os.path.join(out_dir, old) != out:
+                try:
+                    os.remove(os.path.join(out_dir, old))
+                except OSError:
+                    pass
     finally:
         for proc, _ in running.values():
             proc.kill()

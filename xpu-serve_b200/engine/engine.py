@@ -1,0 +1,151 @@
+"""The Python entry point: a model folder in, tokens out.
+
+    engine = Engine(model_dir, precision="bf16", ctx=4096)
+    results = engine.generate([GenerateRequest(prompt=[1, 2, 3], max_new_tokens=16)])
+
+The reference's entry is `EngineService::create(model_dir, options)` and
+`generate(request, on_token)` (src/service/engine_service.cpp:30-124,
+src/engine/engine.h:40); the option names `precision`, `ctx` and `prefill_chunk` are its
+command line's (src/cli/main.cpp:72-125). `ctx` is clamped to the model's
+max_position_embeddings as there (engine_service.cpp:54-58). Batching is added: `generate`
+takes a list of requests and returns their results in the same order.
+"""
+from __future__ import annotations
+
+import secrets
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..ops import lib as ops
+from ..sampling.params import GenerateRequest, GenerateResult, SamplingParams, TokenCallback, read_generation_defaults
+from .generate import generate as _generate
+from .model import Model, load_model
+
+PRECISIONS = {"bf16": "bfloat16", "bfloat16": "bfloat16", "f32": "float32", "float32": "float32"}
+
+
+def _i64(v: int) -> int:
+    """A 64-bit seed as the signed value with the same bits (torch has no unsigned 64-bit tensors)."""
+    v &= (1 << 64) - 1
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+class _Handle:
+    __slots__ = ("slot", "row", "request", "seed", "counter")
+
+    def __init__(self, slot, row, request, seed):
+        self.slot, self.row, self.request, self.seed, self.counter = slot, row, request, seed, 0
+
+
+class DeviceStepper:
+    """Runs the generation loop's steps on the device: the model's step function, then the choice of
+    the next token by the sampling kernels; only token ids cross to the host."""
+
+    def __init__(self, model: Model, max_tokens: int, max_context: int, max_slots: Optional[int] = None):
+        self.model = model
+        self.cache = model.new_cache(max_tokens, max_slots=max_slots, max_seq_tokens=max_context)
+        self.max_context = self.cache.max_seq_tokens
+        self.capacity_tokens = self.cache.max_tokens
+        self.page_size = self.cache.page_size
+        self.max_slots = self.cache.max_slots
+        self.device = model.rt.device
+        self._pen = None        # (seen uint8 [rows, V], counts int32 [rows, V]) when a batch has penalties
+        self._rows_free: List[int] = []
+
+    # ---------------------------------------------------------------- slots
+    def open(self, requests: Sequence[GenerateRequest]) -> List[_Handle]:
+        slots = self.cache.open(len(requests))
+        handles = []
+        for row, (s, r) in enumerate(zip(slots, requests)):
+            seed = r.sampling.seed if r.sampling.seed is not None else secrets.randbits(63)
+            handles.append(_Handle(s, row, r, seed))
+        if any(r.sampling.has_penalties() for r in requests):
+            V = self.model.spec.vocab
+            seen = torch.zeros((len(requests), V), dtype=torch.uint8, device=self.device)
+            counts = torch.zeros((len(requests), V), dtype=torch.int32, device=self.device)
+            toks = torch.tensor([t for r in requests for t in r.prompt], dtype=torch.int32, device=self.device)
+            rows = torch.tensor([i for i, r in enumerate(requests) for _ in r.prompt], dtype=torch.int32,
+                                device=self.device)
+            ops.note_tokens(toks, rows, seen, counts, generated=False)
+            self._pen = (seen, counts)
+        else:
+            self._pen = None
+        return handles
+
+    def close(self, handles: Sequence[_Handle]) -> None:
+        self.cache.close([h.slot for h in handles])
+
+    # ----------------------------------------------------------------- step
+    def step(self, handles: Sequence[_Handle], token_lists, want: Sequence[bool]) -> List[Optional[int]]:
+        places = [[len(t) - 1] if w else [] for t, w in zip(token_lists, want)]
+        logits = self.model.step(self.cache, [h.slot for h in handles], token_lists, places)
+        chosen = [h for h, w in zip(handles, want) if w]
+        if not chosen:
+            return [None] * len(handles)
+        n = len(chosen)
+        dev = self.device
+        out = torch.empty(n, dtype=torch.int32, device=dev)
+        params = [h.request.sampling for h in chosen]
+        if self._pen is not None:
+            rows = torch.tensor([h.row for h in chosen], dtype=torch.int32, device=dev)
+            ops.apply_penalties(logits, self._pen[0], self._pen[1], rows,
+                                torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=dev),
+                                torch.tensor([p.presence_penalty for p in params], dtype=torch.float32, device=dev),
+                                torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32, device=dev))
+        if all(p.greedy() for p in params):
+            ops.argmax(logits, out)
+        else:
+            f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=dev)   # noqa: E731
+            ops.sample(logits, f32([p.temperature for p in params]),
+                       torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev),
+                       f32([p.top_p for p in params]), f32([p.min_p for p in params]),
+                       torch.tensor([_i64(h.seed) for h in chosen], dtype=torch.int64, device=dev),
+                       torch.tensor([h.counter for h in chosen], dtype=torch.int64, device=dev), out)
+        if self._pen is not None:
+            ops.note_tokens(out, rows, self._pen[0], self._pen[1], generated=True)
+        host = out.to("cpu").tolist()       # the step's only device-to-host copy
+        for h in chosen:
+            h.counter += 1
+        it = iter(host)
+        return [next(it) if w else None for w in want]
+
+
+class Engine:
+    def __init__(self, model_dir: str, precision: str = "bf16", ctx: int = 8192, max_tokens: Optional[int] = None,
+                 max_batch: int = 64, prefill_chunk: int = 8192, device: str = "cuda:0"):
+        if precision not in PRECISIONS:
+            raise ValueError(f"precision '{precision}' is not supported (bf16, f32 are)")
+        self.model: Model = load_model(model_dir, dtype=PRECISIONS[precision], device=device)
+        self.default_sampling, gen_stops = read_generation_defaults(model_dir)
+        cfg_stops = list(getattr(self.model.config, "eos_token_id", ()) or ())
+        self.stop_token_ids: List[int] = sorted(set(gen_stops) | set(cfg_stops))
+        ctx = min(ctx, self.model.spec.max_position)
+        self.max_batch = max_batch
+        self.prefill_chunk = prefill_chunk
+        if max_tokens is None:
+            max_tokens = ctx * min(max_batch, 8)
+        self.stepper = DeviceStepper(self.model, max_tokens, ctx, max_slots=max(max_batch, 1))
+
+    @property
+    def ctx(self) -> int:
+        return self.stepper.max_context
+
+    def generate(self, requests: Sequence[GenerateRequest], on_token: Optional[TokenCallback] = None
+                 ) -> List[GenerateResult]:
+        return _generate(self.stepper, requests, on_token, max_batch=self.max_batch,
+                         prefill_chunk=self.prefill_chunk)
+
+    def generate_tokens(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 32,
+                        sampling: Optional[SamplingParams] = None, stop_token_ids: Optional[Sequence[int]] = None
+                        ) -> List[List[int]]:
+        """Token ids in, token ids out: one list of generated tokens per prompt."""
+        sampling = sampling or self.default_sampling
+        stops = list(self.stop_token_ids if stop_token_ids is None else stop_token_ids)
+        reqs = [GenerateRequest(list(p), sampling, max_new_tokens, stops) for p in prompts]
+        out = self.generate(reqs)
+        for r in out:
+            if r.finish == "error":
+                raise RuntimeError(r.error)
+        return [r.tokens for r in out]

@@ -54,6 +54,7 @@ class StepStager:
         self._host = None
         self._dev = None
         self._event = None
+        self.last_h2d_bytes = 0
         self._grow(capacity)
 
     def _grow(self, n: int) -> None:
@@ -97,6 +98,7 @@ class StepStager:
         for k, t in enumerate(tables.values()):
             buf[offs[7 + k]:offs[7 + k] + t.size] = t.reshape(-1)
         total = offs[-1]
+        self.last_h2d_bytes = 4 * total
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
         if self.device.type == "cuda":
             self._event = torch.cuda.Event()

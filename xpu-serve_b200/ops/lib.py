@@ -24,6 +24,7 @@ class KernelError(RuntimeError):
 
 
 _lib = None
+launches = 0      # kernels launched through this module since import (a graph replay counts its kernels too)
 
 
 def _signatures(lib) -> None:
@@ -71,9 +72,11 @@ def loaded_path() -> Optional[str]:
     return None if _lib is None else _lib._name
 
 
-def _check(rc: int) -> None:
+def _check(rc: int, kernels: int = 1) -> None:
+    global launches
     if rc != 0:
         raise KernelError(_lib.xs_last_error().decode("utf-8", "replace"))
+    launches += kernels
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -230,7 +233,7 @@ def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor
         _need(bias, "bias", torch.float32)
     _check(load().xs_short_conv(bcx.data_ptr(), bcx.stride(0), w_t.data_ptr(), _ptr(bias), state.data_ptr(),
                                 seq_of_token.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(),
-                                T, slots.numel(), H, K, _code(bcx), _stream()))
+                                T, slots.numel(), H, K, _code(bcx), _stream()), kernels=2)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

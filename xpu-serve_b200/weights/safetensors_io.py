@@ -14,6 +14,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Dict, Iterable, List, Optional, Tuple
 
 import numpy as np
@@ -90,8 +91,10 @@ class SafetensorsFile:
         count = int(np.prod(entry.shape, dtype=np.int64)) if entry.shape else 1
         if count == 0:
             return torch.empty(entry.shape, dtype=entry.dtype)
-        t = torch.frombuffer(self._map, dtype=entry.dtype, count=count,
-                             offset=self.data_begin + entry.begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)    # the mapping is read-only; nothing writes to it
+            t = torch.frombuffer(self._map, dtype=entry.dtype, count=count,
+                                 offset=self.data_begin + entry.begin)
         return t.reshape(entry.shape)
 
 
