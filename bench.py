@@ -209,6 +209,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run only the first N layers (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    ap.add_argument("--only", default=None, choices=["decode", "prefill"],
+                    help="time one part only and print a short line (for profiler captures)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -240,6 +242,15 @@ def main() -> int:
         folder = write_random_model(os.path.join(root, "lfm3_1_2b"), Lfm3Config.from_json(cfg), seed=0, dtype="bfloat16")
         model = load_model(folder, dtype="bfloat16")
 
+        if args.only == "decode":
+            ms, launches = time_decode(model, args.batch, args.steps, args.warmup, V)
+            print(json.dumps({"only": "decode", "batch": args.batch, "layers": n_layers, "ms_per_step": round(ms, 4),
+                              "launches_per_step": launches}))
+            return 0
+        if args.only == "prefill":
+            ms = time_prefill(model, V, warmup=args.warmup, runs=args.steps)
+            print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": PROMPT, "ms": round(ms, 4)}))
+            return 0
         prefill_ms = time_prefill(model, V, warmup=2, runs=3)
         pf = prefill_flops(cfg, nums, PROMPT)
 
