@@ -1,0 +1,408 @@
+"""Each CUDA kernel alone against a plain PyTorch float64 reference of the same operation, at
+sizes other than the tiny models': widths and vocabularies that are no power of two, head sizes
+in steps of 16, several head-group ratios, ragged batches, shuffled page tables. Where random
+inputs would hide a fault (a far key, a window's edge), one query and key are scaled so that a
+single score dominates."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# largest |difference| / largest |reference|: float32 sums of <= 4096 products; bfloat16 outputs are
+# rounded to 8 bits (2^-9 relative) on top of bfloat16 inputs that both sides share
+TOL = {"float32": 2e-6, "bfloat16": 6e-3}
+
+
+def ops():
+    from xpu_serve_b200.ops import lib
+    return lib
+
+
+def close(got, ref, dtype, factor=1.0):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all()
+    gap = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert gap <= TOL[dtype] * factor, f"gap {gap:.3e}"
+
+
+def rms_norm(x, w, eps):
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+
+# ------------------------------------------------------------------ embedding, norms, activation
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    V, H = 1003, 200
+    table = torch.randn(V, H, device=DEV).to(DT[dtype])
+    ids = torch.tensor([0, 1002, 17, 17, 500], dtype=torch.int32, device=DEV)
+    h = torch.empty(5, H, device=DEV)
+    ops().embed(table, ids, h)
+    assert torch.equal(h, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H", [96, 200, 2048, 5000])
+def test_add_rmsnorm_all_forms(dtype, H):
+    T, eps, eps_post = 7, 1e-5, 3e-6
+    h0 = torch.randn(T, H, device=DEV) * 3
+    m = torch.randn(T, H, device=DEV).to(DT[dtype])
+    w = torch.rand(H, device=DEV) + 0.5
+    pw = torch.rand(H, device=DEV) + 0.5
+    # plain norm
+    y = torch.empty(T, H, device=DEV, dtype=DT[dtype])
+    h = h0.clone()
+    ops().add_rmsnorm(h, None, None, w, y, None, eps)
+    close(y, rms_norm(h0.double(), w.double(), eps), dtype)
+    assert torch.equal(h, h0)
+    # add then norm
+    h = h0.clone()
+    ops().add_rmsnorm(h, m, None, w, y, None, eps)
+    s = h0.double() + m.double()
+    close(h, s, "float32")
+    close(y, rms_norm(s, w.double(), eps), dtype)
+    # sandwich: the branch is normed (with its own eps) before it joins the stream
+    h = h0.clone()
+    ops().add_rmsnorm(h, m, pw, w, y, None, eps, eps_post)
+    s = h0.double() + rms_norm(m.double(), pw.double(), eps_post)
+    close(h, s, "float32")
+    close(y, rms_norm(s, w.double(), eps), dtype)
+    # chosen rows only, packed
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    h = h0.clone()
+    y3 = torch.empty(3, H, device=DEV, dtype=DT[dtype])
+    ops().add_rmsnorm(h, m, None, w, y3, rows, eps)
+    close(y3, rms_norm((h0.double() + m.double())[rows.long()], w.double(), eps), dtype)
+    # flush without a norm
+    h = h0.clone()
+    ops().add_rmsnorm(h, m, pw, None, None, None, eps, eps_post)
+    close(h, h0.double() + rms_norm(m.double(), pw.double(), eps_post), "float32")
+
+
+def test_add_rmsnorm_uses_each_eps_where_it_belongs():
+    """A small branch makes its norm's eps matter; swapping the two eps must show."""
+    T, H, eps, eps_post = 4, 80, 1e-5, 3e-6
+    h0 = torch.randn(T, H, device=DEV)
+    m = torch.randn(T, H, device=DEV) * 2e-3
+    w, pw = torch.rand(H, device=DEV) + 0.5, torch.rand(H, device=DEV) + 0.5
+    y = torch.empty(T, H, device=DEV)
+    h = h0.clone()
+    ops().add_rmsnorm(h, m, pw, w, y, None, eps, eps_post)
+    right = h0.double() + rms_norm(m.double(), pw.double(), eps_post)
+    swapped = h0.double() + rms_norm(m.double(), pw.double(), eps)
+    close(h, right, "float32")
+    assert (h.double() - swapped).abs().max() > 1e-2
+
+
+def test_rmsnorm_has_no_plus_one_offset():
+    H = 64
+    h = torch.randn(3, H, device=DEV)
+    w = torch.rand(H, device=DEV)
+    y = torch.empty(3, H, device=DEV)
+    ops().add_rmsnorm(h, None, None, w, y, None, 1e-5)
+    wrong = rms_norm(h.double(), 1.0 + w.double(), 1e-5)
+    assert (y.double() - wrong).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(dtype):
+    T, F = 5, 333
+    gu = (torch.randn(T, 2 * F + 6, device=DEV) * 3).to(DT[dtype])     # a padded row stride
+    out = torch.empty(T, F, device=DEV, dtype=DT[dtype])
+    ops().silu_mul(gu[:, :2 * F], out)
+    g, u = gu[:, :F].double(), gu[:, F:2 * F].double()
+    close(out, g / (1 + torch.exp(-g)) * u, dtype)
+
+
+# ---------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 100, 96), (65, 130, 200), (200, 1000, 333), (9, 64, 4096)])
+def test_gemm_generic(dtype, M, N, K):
+    x = torch.randn(M, K, device=DEV).to(DT[dtype])
+    w = torch.randn(N, K, device=DEV).to(DT[dtype])
+    bias = torch.randn(N, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_generic(x, w, out, bias)
+    close(out, x.double() @ w.double().T + bias.double(), "float32", factor=math.sqrt(K) / 8 + 1)
+    wrong = x.double() @ w.double().flip(0).T + bias.double()
+    assert (out.double() - wrong).abs().max() > 0.1 or N == 1
+    if dtype == "bfloat16":
+        o2 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        ops().gemm_generic(x, w, o2)
+        close(o2, x.double() @ w.double().T, "bfloat16")
+
+
+def test_gemm_generic_rows_do_not_depend_on_the_batch():
+    K, N = 777, 150
+    x = torch.randn(40, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    full = torch.empty(40, N, device=DEV)
+    one = torch.empty(1, N, device=DEV)
+    ops().gemm_generic(x, w, full)
+    ops().gemm_generic(x[17:18], w, one)
+    assert torch.equal(full[17:18], one)
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (1000, 200), (2048, 8192), (333, 2056)])
+def test_gemm_small_m(M, N, K):
+    lib = ops()
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    assert lib.gemm_small_m_supports(M, K, x.stride(0), w.stride(0))
+    ref = x.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    lib.gemm_small_m(x, w, out)
+    close(out, ref, "float32", factor=4)
+    out16 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV)
+    lib.gemm_small_m(x, w, out16, bias)
+    close(out16, ref + bias.double(), "bfloat16")
+    res = torch.randn(M, N, device=DEV)
+    want = res.double() + ref
+    lib.gemm_small_m(x, w, None, None, residual=res)
+    close(res, want, "float32", factor=4)
+    one = torch.empty(1, N, device=DEV)
+    lib.gemm_small_m(x[M - 1:M], w, one)
+    assert torch.equal(one, out[M - 1:M]), "a row's result depends on the batch"
+
+
+def test_gemm_small_m_refuses_what_it_cannot_take():
+    lib = ops()
+    assert not lib.gemm_small_m_supports(17, 64, 64, 64)
+    assert not lib.gemm_small_m_supports(4, 100, 100, 100)      # K is no multiple of 8
+    x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(8, 100, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(lib.KernelError, match="not supported"):
+        lib.gemm_small_m(x, w, torch.empty(4, 8, device=DEV))
+
+
+# -------------------------------------------------------------------------------- attention
+class Paged:
+    """A ragged batch with a shuffled page table, and dense float64 copies for the reference."""
+
+    def __init__(self, starts, q_lens, Hq, Hkv, D, dtype, seed=0, page=64):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.starts, self.q_lens, self.Hq, self.Hkv, self.D, self.page = starts, q_lens, Hq, Hkv, D, page
+        n = len(starts)
+        self.kv_lens = [s + q for s, q in zip(starts, q_lens)]
+        P = max(-(-L // page) for L in self.kv_lens)
+        n_pages = n * P + 3
+        perm = torch.randperm(n_pages, generator=g)
+        self.table = perm[:n * P].reshape(n, P).to(torch.int32)
+        self.pool = (torch.randn(n_pages, 2, Hkv, page, D, generator=g) * 50).to(DT[dtype])   # stale contents are loud
+        self.k = [torch.randn(L, Hkv, D, generator=g) for L in self.kv_lens]
+        self.v = [torch.randn(L, Hkv, D, generator=g) for L in self.kv_lens]
+        T = sum(q_lens)
+        self.q = torch.randn(T, Hq, D, generator=g)
+        self.cu = np.concatenate([[0], np.cumsum(q_lens)])
+        self.seq_of = np.repeat(np.arange(n), q_lens)
+        self.pos = np.concatenate([np.arange(s, s + q) for s, q in zip(starts, q_lens)])
+
+    def fill_pool(self, upto_start_only=False):
+        for s in range(len(self.starts)):
+            L = self.starts[s] if upto_start_only else self.kv_lens[s]
+            for j in range(L):
+                pg, r = int(self.table[s, j // self.page]), j % self.page
+                self.pool[pg, 0, :, r] = self.k[s][j].to(self.pool.dtype)
+                self.pool[pg, 1, :, r] = self.v[s][j].to(self.pool.dtype)
+
+    def dev(self):
+        i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)   # noqa: E731
+        return dict(pool=self.pool.to(DEV), table=self.table.to(DEV), cu=i32(self.cu), seq_of=i32(self.seq_of),
+                    pos=i32(self.pos), kv_lens=i32(self.kv_lens), q=self.q.to(DEV).to(self.pool.dtype))
+
+    def reference(self, scale, window, gate=None):
+        q = self.q.to(self.pool.dtype).double()
+        out = torch.zeros_like(q)
+        G = self.Hq // self.Hkv
+        for t in range(q.shape[0]):
+            s, p = int(self.seq_of[t]), int(self.pos[t])
+            lo = max(0, p - window + 1) if window > 0 else 0
+            k = self.k[s].to(self.pool.dtype).double()[lo:p + 1]
+            v = self.v[s].to(self.pool.dtype).double()[lo:p + 1]
+            for h in range(self.Hq):
+                sc = scale * (k[:, h // G] @ q[t, h])
+                pr = torch.softmax(sc, 0)
+                out[t, h] = pr @ v[:, h // G]
+                if gate is not None:
+                    out[t, h] *= torch.sigmoid(gate[t, h].double())
+        return out
+
+
+ATTN_CASES = [
+    # starts, q_lens, Hq, Hkv, D, window
+    ([0], [1], 4, 2, 16, 0),
+    ([0, 0, 0], [5, 70, 129], 4, 2, 32, 0),          # prompts of unequal lengths
+    ([63, 64, 200, 0], [1, 1, 1, 1], 8, 1, 64, 0),   # decode; one sequence holds a single key
+    ([10, 100], [60, 3], 6, 3, 48, 0),               # continuing sequences with several new tokens
+    ([0, 130], [150, 1], 4, 1, 32, 37),              # a window with its edge inside and across pages
+    ([300], [1], 3, 1, 96, 64),
+    ([0], [200], 32, 8, 64, 0),                      # the 1.2B shape's heads
+    ([500, 37, 1999], [1, 1, 1], 16, 2, 128, 0),
+    ([0], [90], 5, 5, 80, 17),                       # a head size only the generic kernel takes
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+@pytest.mark.parametrize("kernel,dtype", [("generic", "float32"), ("generic", "bfloat16"), ("mma", "bfloat16")])
+def test_attention(case, kernel, dtype):
+    lib = ops()
+    starts, q_lens, Hq, Hkv, D, window = case
+    if kernel == "mma" and not lib.attention_mma_supports(D, 64, Hq // Hkv):
+        with pytest.raises(lib.KernelError, match="not supported"):
+            run_attention(lib, Paged([0], [1], Hq, Hkv, D, dtype), kernel, 0.1, 0, None, 1)
+        return
+    pg = Paged(starts, q_lens, Hq, Hkv, D, dtype, seed=len(starts) + D)
+    # plant one dominant score: the first visible key of the last query of every sequence
+    for s in range(len(starts)):
+        t = int(pg.cu[s + 1]) - 1
+        p = int(pg.pos[t])
+        j = max(0, p - window + 1) if window > 0 else 0
+        pg.k[s][j] = pg.q[t, 0] * 3.0
+        if window > 0 and j > 0:
+            pg.k[s][j - 1] = pg.q[t, 0] * 6.0          # just outside the window: must not be seen
+    pg.fill_pool()
+    scale = 1.0 / math.sqrt(D)
+    gate = torch.randn(sum(q_lens), Hq + 3).to(DT[dtype])
+    for gt in (None, gate):
+        ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
+        for splits in ([1] if kernel == "generic" else [1, 2, 5]):
+            out = run_attention(lib, pg, kernel, scale, window, gt, splits)
+            close(out, ref, dtype, factor=3 if dtype == "bfloat16" else 20)
+
+
+def run_attention(lib, pg, kernel, scale, window, gate, splits):
+    d = pg.dev()
+    T = d["q"].shape[0]
+    out = torch.full((T, pg.Hq, pg.D), float("nan"), device=DEV, dtype=d["q"].dtype)
+    gt = None if gate is None else gate.to(DEV)[:, :pg.Hq]
+    if kernel == "generic":
+        lib.attention_generic(d["q"], d["pool"], d["table"], d["seq_of"], d["pos"], gt, out, pg.Hkv, 64, scale, window)
+    else:
+        need = lib.attention_mma_scratch_bytes(T * pg.Hq, pg.D, splits)
+        scratch = torch.full((max(need, 1),), 255, dtype=torch.uint8, device=DEV) if splits > 1 else None
+        lib.attention_mma(d["q"], d["pool"], d["table"], d["cu"], d["kv_lens"], gt, out, scratch, len(pg.starts),
+                          max(pg.q_lens), pg.Hkv, 64, scale, window, splits)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D,pairs,Hq,Hkv", [(16, 8, 4, 2), (48, 12, 6, 3), (64, 32, 8, 8), (128, 20, 2, 1), (256, 128, 2, 1)])
+def test_qk_norm_rope_store(dtype, D, pairs, Hq, Hkv):
+    lib = ops()
+    pg = Paged([0, 70, 5], [9, 1, 66], Hq, Hkv, D, dtype)
+    pg.fill_pool(upto_start_only=True)
+    d = pg.dev()
+    T = sum(pg.q_lens)
+    width = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(T, width + 8, device=DEV).to(DT[dtype])
+    qw, kw = torch.rand(D, device=DEV) + 0.5, torch.rand(D, device=DEV) + 0.5
+    eps, theta = 1e-6, 10000.0
+    inv = torch.zeros(D // 2, dtype=torch.float64)
+    inv[:pairs] = (1.0 / theta ** (2.0 * torch.arange(pairs, dtype=torch.float64) / D)).float().double()
+    ang = torch.arange(256, dtype=torch.float64)[:, None] * inv[None, :]
+    rope = torch.stack([ang.cos(), ang.sin()], -1).float().to(DEV)
+    q_out = torch.empty(T, Hq, D, device=DEV, dtype=DT[dtype])
+    before = d["pool"].clone()
+    lib.qk_norm_rope_store(qkv, q_out, d["pool"], d["table"], d["seq_of"], d["pos"], qw, kw, rope, Hq, Hkv, D, 64,
+                           eps, True)
+    x = qkv.double().cpu()
+    pos = torch.tensor(pg.pos)
+
+    def norm_rope(v, w):     # v [T, heads, D]
+        v = rms_norm(v, w.double().cpu(), eps)
+        c, s = ang[pos].cos()[:, None, :], ang[pos].sin()[:, None, :]
+        a, b = v[..., :D // 2], v[..., D // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    q_ref = norm_rope(x[:, :Hq * D].reshape(T, Hq, D), qw)
+    k_ref = norm_rope(x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D), kw)
+    v_ref = x[:, (Hq + Hkv) * D:width].reshape(T, Hkv, D)
+    close(q_out, q_ref, dtype)
+    pool = d["pool"].double().cpu()
+    touched = torch.zeros(pool.shape[0], 64, dtype=torch.bool)
+    for t in range(T):
+        s, p = int(pg.seq_of[t]), int(pg.pos[t])
+        page, r = int(pg.table[s, p // 64]), p % 64
+        close(pool[page, 0, :, r], k_ref[t], dtype)
+        close(pool[page, 1, :, r], v_ref[t], dtype)
+        touched[page, r] = True
+    same = (d["pool"] == before).all(-1).all(1).all(1).cpu()       # [pages, 64]
+    assert same[~touched].all(), "a cache row of another position was written"
+    if pairs < D // 2:      # the unrotated tail passes through: pair i is (i, i + D/2), not neighbours
+        tail = rms_norm(x[:, :Hq * D].reshape(T, Hq, D), qw.double().cpu(), eps)[..., pairs:D // 2]
+        close(q_out[..., pairs:D // 2], tail, dtype)
+
+
+# ------------------------------------------------------------------------------ short convolution
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,K", [(96, 3), (200, 4), (64, 7), (40, 2)])
+def test_short_conv_in_steps_equals_one_pass(dtype, H, K):
+    """Three sequences fed in pieces of different sizes (one of them 5, 1, 1, 3, 2 as in the reference's
+    tests/unit/backend/recurrent_ops_cases.h:89-118) give what one pass over each whole sequence gives,
+    and never read a neighbour's tokens."""
+    lib = ops()
+    cuts = [[5, 1, 1, 3, 2], [1, 1, 9, 1], [12]]
+    totals = [sum(c) for c in cuts]
+    bcx_all = [(torch.randn(n, 3 * H + 8) * 2).to(DT[dtype]) for n in totals]
+    taps = torch.randn(H, K)
+    bias = torch.randn(H)
+    w_t = taps.t().contiguous().to(DEV)
+    n_slots = 5
+    slots = [3, 0, 4]
+    state = (torch.randn(n_slots, K - 1, H, device=DEV) * 40).to(DT[dtype])     # other slots' rows stay untouched
+    lib.zero_rows(state, torch.tensor(slots, dtype=torch.int32, device=DEV))
+    guard = state[[1, 2]].clone()
+
+    def reference(s):
+        x = bcx_all[s].double()
+        B, C, X = x[:, :H], x[:, H:2 * H], x[:, 2 * H:3 * H]
+        g = (B * X).to(DT[dtype]).double()                  # kept in the activation type, as the state keeps it
+        ext = torch.cat([torch.zeros(K - 1, H, dtype=torch.float64), g], 0)
+        conv = sum(taps[:, j].double()[None, :] * ext[j:j + x.shape[0]] for j in range(K)) + bias.double()
+        return C * conv
+
+    got = [torch.empty(n, H, device=DEV, dtype=DT[dtype]) for n in totals]
+    at = [0, 0, 0]
+    for step in range(max(len(c) for c in cuts)):
+        part = [s for s in range(3) if step < len(cuts[s])]
+        lens = [cuts[s][step] for s in part]
+        bcx = torch.cat([bcx_all[s][at[s]:at[s] + n] for s, n in zip(part, lens)], 0).to(DEV)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+        seq_of = torch.tensor(np.repeat(np.arange(len(part)), lens), dtype=torch.int32, device=DEV)
+        sl = torch.tensor([slots[s] for s in part], dtype=torch.int32, device=DEV)
+        out = torch.empty(sum(lens), H, device=DEV, dtype=DT[dtype])
+        lib.short_conv(bcx[:, :3 * H], w_t, bias.to(DEV), state, seq_of, cu, sl, out)
+        o = 0
+        for s, n in zip(part, lens):
+            got[s][at[s]:at[s] + n] = out[o:o + n]
+            at[s] += n
+            o += n
+    for s in range(3):
+        close(got[s], reference(s), dtype, factor=4)
+    assert torch.equal(state[[1, 2]], guard)
+    # the wrong tap order must not match: w[c, K-1] multiplies the current token
+    x = bcx_all[2].double()
+    g = (x[:, :H] * x[:, 2 * H:3 * H])
+    ext = torch.cat([torch.zeros(K - 1, H, dtype=torch.float64), g], 0)
+    flipped = x[:, H:2 * H] * (sum(taps[:, K - 1 - j].double()[None, :] * ext[j:j + 12] for j in range(K)) + bias.double())
+    assert (got[2].double().cpu() - flipped).abs().max() > 0.5
+
+
+def test_argmax_ties_and_width():
+    lib = ops()
+    V = 65536 + 77
+    logits = torch.randn(5, V, device=DEV)
+    logits[0, 40000] = 50.0
+    logits[1, V - 1] = 50.0
+    logits[2, 9] = 50.0
+    logits[2, 70] = 50.0          # a tie: the lower index wins
+    logits[3, :] = -1.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    lib.argmax(logits, out)
+    assert out.tolist()[:4] == [40000, V - 1, 9, 0] and out[4].item() == int(logits[4].argmax())

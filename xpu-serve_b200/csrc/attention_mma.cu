@@ -1,0 +1,376 @@
+// Flash-style attention over the paged bfloat16 cache on tensor cores, for prefill and decode.
+//
+// One CTA (4 warps) owns a tile of 64 query rows that share one kv head: rows are
+// (token, head of the group) pairs, row r = token r / G, head r % G with G = heads / kv_heads,
+// so keys and values are read once for the whole group. It walks the cache in blocks of
+// 64 keys (one page: 64 x head_dim contiguous elements for keys, the same for values),
+// double-buffered with cp.async, S = Q K^T and O += P V with mma.sync m16n8k16 (bfloat16 in,
+// float32 accumulate), softmax online in float32 (base-2 exponentials of scores pre-multiplied
+// by scale * log2 e). Query at position pos sees key j iff j <= pos and (window == 0 or
+// pos - j < window) (src/backend/cpu_ref/ops.cpp:567-571). Rows of keys and values past the
+// sequence's length are zero-filled in shared memory, so stale cache contents never reach
+// the arithmetic.
+//
+// When a tile's key range is split over several CTAs (decode: few tiles, long ranges), each
+// writes an unnormalised partial (O, running max, running sum) to scratch and
+// attention_combine_kernel merges them; this is the reference's attention_rows +
+// attention_combine pair (src/backend/sycl/sycl_kernels.h:223-244), and its XMX flash kernel
+// for prefill (src/backend/sycl/sycl_flash_attention.cpp:1-15), as one kernel.
+//
+// Head sizes: multiples of 16 up to 128 that are instantiated below; others are refused here
+// and served by the generic kernel.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 64;       // query rows per CTA
+constexpr int BN = 64;       // keys per block = page size
+constexpr int NTHREADS = 128;
+
+struct AttnParams {
+    const __nv_bfloat16* q;          // [T, Hq, D]
+    const __nv_bfloat16* pool;       // [pages, 2, Hkv, 64, D]
+    const int32_t* page_table;       // [n_seqs, P]
+    int P;
+    const int32_t* cu_seqlens;       // [n_seqs + 1]
+    const int32_t* kv_lens;          // [n_seqs] length after this step
+    const __nv_bfloat16* gate;       // [T, ld_gate] gate logits or null
+    int64_t ld_gate;
+    __nv_bfloat16* out;              // [T, Hq, D]
+    float* part_o;                   // [T * Hq, splits, D]
+    float* part_ml;                  // [T * Hq, splits, 2]
+    int Hq, Hkv, G, tokens_per_tile, window, splits;
+    float scale_log2;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParams p) {
+    constexpr int LD = D + 8;              // padded row: ldmatrix reads 8 rows without bank conflicts
+    constexpr int KSTEPS = D / 16;         // k-steps of Q K^T
+    constexpr int DTILES = D / 8;          // n-tiles of the output
+    constexpr int CHUNKS = D / 8;          // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* k_sm = q_sm + BM * LD;            // [2][BN][LD]
+    __nv_bfloat16* v_sm = k_sm + 2 * BN * LD;        // [2][BN][LD]
+
+    const int tile = blockIdx.x, seq = blockIdx.y;
+    const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+    const int tok_begin = p.cu_seqlens[seq];
+    const int q_len = p.cu_seqlens[seq + 1] - tok_begin;
+    const int t0 = tile * p.tokens_per_tile;
+    if (t0 >= q_len) return;
+    const int nt = min(p.tokens_per_tile, q_len - t0);
+    const int kv_len = p.kv_lens[seq];
+    const int pos0 = kv_len - q_len + t0;
+    const int hi = pos0 + nt;                                     // keys [lo, hi) matter to this tile
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int b_lo = lo / BN, nb = (hi + BN - 1) / BN - b_lo;
+    const int bs = b_lo + (int)((int64_t)nb * split / p.splits);
+    const int be = b_lo + (int)((int64_t)nb * (split + 1) / p.splits);
+    const int32_t* table = p.page_table + (int64_t)seq * p.P;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.G;
+    const int rows_valid = nt * G;
+    const bool warp_active = warp * 16 < rows_valid;
+
+    // ---- Q tile: row r = (token t0 + r / G, head kvh * G + r % G); invalid rows are zero
+    for (int c = threadIdx.x; c < BM * CHUNKS; c += NTHREADS) {
+        const int r = c / CHUNKS, ch = c % CHUNKS;
+        const bool ok = r < rows_valid;
+        const int ti = ok ? r / G : 0, g = ok ? r % G : 0;
+        const __nv_bfloat16* src = p.q + ((int64_t)(tok_begin + t0 + ti) * p.Hq + kvh * G + g) * D + ch * 8;
+        cp_async16(q_sm + r * LD + ch * 8, src, ok);
+    }
+    auto load_block = [&](int b, int stage) {
+        const int page = table[b];
+        const int page_at = max(page, 0);      // a page given back (-1) is never read: its rows are zero-filled
+        const __nv_bfloat16* kbase = p.pool + (((int64_t)page_at * 2 + 0) * p.Hkv + kvh) * BN * D;
+        const __nv_bfloat16* vbase = p.pool + (((int64_t)page_at * 2 + 1) * p.Hkv + kvh) * BN * D;
+        __nv_bfloat16* ks = k_sm + stage * BN * LD;
+        __nv_bfloat16* vs = v_sm + stage * BN * LD;
+        for (int c = threadIdx.x; c < BN * CHUNKS; c += NTHREADS) {
+            const int r = c / CHUNKS, ch = c % CHUNKS;
+            const bool ok = page >= 0 && b * BN + r < hi;
+            cp_async16(ks + r * LD + ch * 8, kbase + (ok ? r * D + ch * 8 : 0), ok);
+            cp_async16(vs + r * LD + ch * 8, vbase + (ok ? r * D + ch * 8 : 0), ok);
+        }
+    };
+    if (bs < be) load_block(bs, 0);
+    cp_async_commit();
+
+    // this thread's two rows and their positions (-1: no key is visible)
+    const int r1 = warp * 16 + (lane >> 2), r2 = r1 + 8;
+    const int pos1 = r1 < rows_valid ? pos0 + r1 / G : -1;
+    const int pos2 = r2 < rows_valid ? pos0 + r2 / G : -1;
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.0f, l2 = 0.0f;
+    unsigned qf[KSTEPS][4];
+    bool q_loaded = false;
+
+    for (int b = bs, it = 0; b < be; ++b, ++it) {
+        const int stage = it & 1;
+        if (b + 1 < be) {
+            load_block(b + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (warp_active) {
+            if (!q_loaded) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+                    ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3],
+                                q_sm + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+                q_loaded = true;
+            }
+            const __nv_bfloat16* ks = k_sm + stage * BN * LD;
+            const __nv_bfloat16* vs = v_sm + stage * BN * LD;
+            float s[BN / 8][4];
+#pragma unroll
+            for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                for (int np = 0; np < BN / 16; ++np) {
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4(b0, b1, b2, b3,
+                                ks + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma_bf16(s[2 * np], qf[kk], b0, b1);
+                    mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+                }
+            }
+            // scale, mask, running max
+            const int key0 = b * BN + (lane & 3) * 2;
+            float mx1 = -INFINITY, mx2 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key0 + i * 8 + e;
+                    const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
+                    const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
+                    s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
+                    s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
+                    mx1 = fmaxf(mx1, s[i][e]);
+                    mx2 = fmaxf(mx2, s[i][2 + e]);
+                }
+            }
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 1));
+            mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 2));
+            const float mn1 = fmaxf(m1, mx1), mn2 = fmaxf(m2, mx2);
+            const float base1 = mn1 == -INFINITY ? 0.0f : mn1, base2 = mn2 == -INFINITY ? 0.0f : mn2;
+            const float c1 = exp2f(m1 - base1), c2 = exp2f(m2 - base2);   // 0 while nothing was seen
+            m1 = mn1;
+            m2 = mn2;
+            l1 *= c1;
+            l2 *= c2;
+#pragma unroll
+            for (int i = 0; i < DTILES; ++i) {
+                o[i][0] *= c1;
+                o[i][1] *= c1;
+                o[i][2] *= c2;
+                o[i][3] *= c2;
+            }
+            unsigned pf[BN / 16][4];
+#pragma unroll
+            for (int i = 0; i < BN / 8; ++i) {
+                const float p0 = exp2f(s[i][0] - base1), p1 = exp2f(s[i][1] - base1);
+                const float p2 = exp2f(s[i][2] - base2), p3 = exp2f(s[i][3] - base2);
+                l1 += p0 + p1;
+                l2 += p2 + p3;
+                pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
+                pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+                for (int dp = 0; dp < D / 16; ++dp) {
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3,
+                                      vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + dp * 16 + (lane >> 4) * 8);
+                    mma_bf16(o[2 * dp], pf[kk], b0, b1);
+                    mma_bf16(o[2 * dp + 1], pf[kk], b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (!warp_active) return;
+
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    l2 += __shfl_xor_sync(0xffffffffu, l2, 1);
+    l2 += __shfl_xor_sync(0xffffffffu, l2, 2);
+
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = half == 0 ? r1 : r2;
+        if (r >= rows_valid) continue;
+        const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+        const float l = half == 0 ? l1 : l2, m = half == 0 ? m1 : m2;
+        const int64_t row = (int64_t)t * p.Hq + h;
+        if (p.splits == 1) {
+            float f = l > 0.0f ? 1.0f / l : 0.0f;
+            if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
+            __nv_bfloat16* dst = p.out + row * D + (lane & 3) * 2;
+#pragma unroll
+            for (int i = 0; i < DTILES; ++i)
+                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) =
+                    __floats2bfloat162_rn(o[i][half * 2] * f, o[i][half * 2 + 1] * f);
+        } else {
+            float* dst = p.part_o + (row * p.splits + split) * D + (lane & 3) * 2;
+#pragma unroll
+            for (int i = 0; i < DTILES; ++i)
+                *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][half * 2], o[i][half * 2 + 1]);
+            if ((lane & 3) == 0) {
+                p.part_ml[(row * p.splits + split) * 2 + 0] = m;
+                p.part_ml[(row * p.splits + split) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// out[row, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), times the head's gate. One warp per row.
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
+                                         __nv_bfloat16* __restrict__ out, int64_t rows, int Hq, int D, int splits) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* ml = part_ml + row * splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.0f;
+    for (int s = 0; s < splits; ++s) l += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * exp2f(ml[2 * s] - m);
+    float f = l > 0.0f ? 1.0f / l : 0.0f;
+    if (gate != nullptr) {
+        const int64_t t = row / Hq;
+        const int h = (int)(row % Hq);
+        f *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[t * ld_gate + h])));
+    }
+    for (int d = lane; d < D; d += 32) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = ml[2 * s];
+            if (ms != -INFINITY) acc += part_o[(row * splits + s) * D + d] * exp2f(ms - m);
+        }
+        out[row * D + d] = __float2bfloat16_rn(acc * f);
+    }
+}
+
+template <int D>
+int launch(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t stream) {
+    constexpr int LD = D + 8;
+    const size_t smem = (size_t)(BM + 4 * BN) * LD * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const dim3 grid(max_tiles, n_seqs, p.Hkv * p.splits);
+    attention_mma_kernel<D><<<grid, NTHREADS, smem, stream>>>(p);
+    return 0;
+}
+
+}  // namespace
+
+// Scratch the split path needs, in bytes, for `rows` = tokens * heads.
+XS_API int64_t xs_attention_mma_scratch_bytes(int64_t rows, int D, int splits) {
+    return splits <= 1 ? 0 : rows * splits * ((int64_t)D + 2) * (int64_t)sizeof(float);
+}
+
+// 1 when xs_attention_mma takes this head size and page size.
+XS_API int xs_attention_mma_supports(int D, int page_size, int G) {
+    const bool d_ok = D == 16 || D == 32 || D == 48 || D == 64 || D == 96 || D == 128;
+    return d_ok && page_size == BN && G >= 1 && G <= BM;
+}
+
+XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page_table, int P,
+                            const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate, int64_t ld_gate,
+                            void* out, void* scratch, int64_t scratch_bytes, int T, int n_seqs, int max_q_len, int Hq,
+                            int Hkv, int D, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d heads over %d kv heads", Hq, Hkv);
+    const int G = Hq / Hkv;
+    XS_REQUIRE(xs_attention_mma_supports(D, page_size, G),
+               "attention (tensor cores): head size %d, page size %d, group %d is not supported", D, page_size, G);
+    XS_REQUIRE(splits >= 1 && window >= 0 && max_q_len >= 1 && n_seqs >= 1 && P >= 1, "attention: bad sizes");
+    XS_REQUIRE(n_seqs <= 65535 && (int64_t)Hkv * splits <= 65535, "attention: grid too large");
+    const int64_t need = xs_attention_mma_scratch_bytes((int64_t)T * Hq, D, splits);
+    XS_REQUIRE(splits == 1 || (scratch != nullptr && scratch_bytes >= need),
+               "attention: %lld bytes of scratch needed for %d splits, %lld given", (long long)need, splits,
+               (long long)scratch_bytes);
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.pool = (const __nv_bfloat16*)pool;
+    p.page_table = page_table;
+    p.P = P;
+    p.cu_seqlens = cu_seqlens;
+    p.kv_lens = kv_lens;
+    p.gate = (const __nv_bfloat16*)gate;
+    p.ld_gate = ld_gate;
+    p.out = (__nv_bfloat16*)out;
+    p.part_o = (float*)scratch;
+    p.part_ml = p.part_o + (int64_t)T * Hq * splits * D;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.G = G;
+    p.tokens_per_tile = BM / G;
+    p.window = window;
+    p.splits = splits;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    const int max_tiles = ceil_div_i(max_q_len, p.tokens_per_tile);
+    switch (D) {
+        case 16: launch<16>(p, max_tiles, n_seqs, stream); break;
+        case 32: launch<32>(p, max_tiles, n_seqs, stream); break;
+        case 48: launch<48>(p, max_tiles, n_seqs, stream); break;
+        case 64: launch<64>(p, max_tiles, n_seqs, stream); break;
+        case 96: launch<96>(p, max_tiles, n_seqs, stream); break;
+        case 128: launch<128>(p, max_tiles, n_seqs, stream); break;
+        default: XS_REQUIRE(false, "attention (tensor cores): head size %d", D);
+    }
+    XS_LAUNCH_CHECK("attention_mma");
+    if (splits > 1) {
+        const int64_t rows = (int64_t)T * Hq;
+        attention_combine_kernel<<<ceil_div_i(rows, 4), 128, 0, stream>>>(p.part_o, p.part_ml, p.gate, ld_gate, p.out,
+                                                                         rows, Hq, D, splits);
+        XS_LAUNCH_CHECK("attention_combine");
+    }
+    return 0;
+}

@@ -58,8 +58,9 @@ class Runtime:
         self.shared: Dict[Tuple, object] = {}     # parts memoise what equal specs can share (tables)
         # cuBLAS may otherwise reduce split products in bfloat16
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
-        self.small_m = 8      # products with at most this many rows use this library's streaming kernel
+        self.small_m = 16     # products with at most this many rows use this library's streaming kernel
         ops.load()
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # -------------------------------------------------------------- weights
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
@@ -77,10 +78,12 @@ class Runtime:
         M, N = x.shape[0], w.shape[0]
         out_dtype = out_dtype or self.act_dtype
         out = self.ws.get(name, (M, N), out_dtype)
-        if self.mode == "float32" or bias is not None:
+        if self.mode == "float32":
             ops.gemm_generic(x, w, out, bias)
-        elif M <= self.small_m and hasattr(ops, "gemv_small_m"):
-            ops.gemv_small_m(x, w, out)
+        elif M <= self.small_m and ops.gemm_small_m_supports(M, x.shape[1], x.stride(0), w.stride(0)):
+            ops.gemm_small_m(x, w, out, bias)
+        elif bias is not None:
+            ops.gemm_generic(x, w, out, bias)
         elif out_dtype == torch.float32:
             out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
         else:

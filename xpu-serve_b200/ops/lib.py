@@ -38,6 +38,8 @@ def _signatures(lib) -> None:
         "xs_qk_norm_rope_store": [P, L, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P],
         "xs_attention_generic": [P, P, P, I, P, P, P, L, P, I, I, I, I, I, F, I, I, P],
         "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
+        "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, P],
         "xs_argmax": [P, L, I, I, P, P],
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
@@ -52,6 +54,12 @@ def _signatures(lib) -> None:
     lib.xs_uniform.restype = c_double
     lib.xs_uniform.argtypes = [c_uint64, c_uint64]
     lib.xs_abi_version.restype = c_int
+    lib.xs_attention_mma_scratch_bytes.restype = c_int64
+    lib.xs_attention_mma_scratch_bytes.argtypes = [c_int64, c_int, c_int]
+    lib.xs_attention_mma_supports.restype = c_int
+    lib.xs_attention_mma_supports.argtypes = [c_int, c_int, c_int]
+    lib.xs_gemm_small_m_supports.restype = c_int
+    lib.xs_gemm_small_m_supports.argtypes = [c_int, c_int, c_int64, c_int64]
 
 
 def load(verbose: bool = True):
@@ -143,7 +151,9 @@ def add_rmsnorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[tor
 
 
 def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
-    _need(gu, "gate_up"); _need(out, "out", gu.dtype)
+    _need(out, "out", gu.dtype)
+    if not gu.is_cuda or gu.dim() != 2 or gu.stride(1) != 1:
+        raise KernelError("gate_up must be a CUDA matrix with contiguous rows")
     T, F = out.shape
     if gu.shape[0] != T or gu.shape[1] < 2 * F:
         raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
@@ -218,6 +228,62 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Ten
         q.data_ptr(), pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], seq_of_token.data_ptr(),
         positions.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), T, heads, kv_heads, D, page_size, float(scale),
         int(window), _code(q), _stream()))
+
+
+def attention_mma_supports(head_dim: int, page_size: int, group: int) -> bool:
+    return bool(load().xs_attention_mma_supports(head_dim, page_size, group))
+
+
+def attention_mma_scratch_bytes(rows: int, head_dim: int, splits: int) -> int:
+    return int(load().xs_attention_mma_scratch_bytes(rows, head_dim, splits))
+
+
+def attention_mma(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                  kv_lens: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
+                  scratch: Optional[torch.Tensor], n_seqs: int, max_q_len: int, kv_heads: int, page_size: int,
+                  scale: float, window: int, splits: int) -> None:
+    """Tensor-core attention over the paged bfloat16 cache. `scratch`: a byte buffer of at least
+    attention_mma_scratch_bytes(tokens * heads, head_dim, splits) when splits > 1."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "cache", torch.bfloat16)
+    _need(page_table, "page table", torch.int32)
+    T, heads, D = q.shape
+    if tuple(pool.shape[1:]) != (2, kv_heads, page_size, D):
+        raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 2, {kv_heads}, {page_size}, {D}]")
+    ld_gate = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < heads:
+            raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {heads} heads")
+        ld_gate = gate.stride(0)
+    sbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _check(load().xs_attention_mma(
+        q.data_ptr(), pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
+        kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), _ptr(scratch), sbytes, T, n_seqs, max_q_len, heads,
+        kv_heads, D, page_size, float(scale), int(window), int(splits), _stream()), kernels=2 if splits > 1 else 1)
+
+
+def gemm_small_m_supports(M: int, K: int, ldx: int, ldw: int) -> bool:
+    return bool(load().xs_gemm_small_m_supports(M, K, ldx, ldw))
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product."""
+    for t, name in ((x, "x"), (w, "w")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
+            raise KernelError(f"gemm (few rows): {name} must be a bfloat16 CUDA matrix with contiguous rows")
+    M, K = x.shape
+    N = w.shape[0]
+    target = residual if residual is not None else out
+    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N) or target.stride(1) != 1:
+        raise KernelError(f"gemm (few rows): x {tuple(x.shape)}, w {tuple(w.shape)}, out "
+                          f"{None if target is None else tuple(target.shape)}")
+    if residual is not None and residual.dtype != torch.float32:
+        raise KernelError("gemm (few rows): the residual must be float32")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    _check(load().xs_gemm_small_m(x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual),
+                                  F32 if out is None else _code(out), M, N, K, x.stride(0), w.stride(0),
+                                  target.stride(0), _stream()))
 
 
 def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,

@@ -92,7 +92,23 @@ class AttentionMixer(Mixer):
         return rt.linear(o.view(T, self.q_dim), self.w_o, "mixer_out")
 
     def attend(self, q, cache, table, step, gate, o) -> None:
-        s = self.spec
+        s, rt = self.spec, self.rt
+        if rt.mode == "bfloat16" and ops.attention_mma_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
+            # Few tiles and long key ranges (decoding): split each range over several CTAs so that
+            # every SM streams a part of the cache; the partial results meet in scratch memory.
+            tokens_per_tile = 64 // (s.heads // s.kv_heads)
+            tiles = sum(-(-int(n) // tokens_per_tile) for n in step.q_lens_host) * s.kv_heads
+            blocks = -(-step.max_kv_len // step.page_size)
+            if s.window > 0:
+                blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
+            splits = max(1, min(blocks, 32, (2 * rt.sm_count) // max(tiles, 1)))
+            scratch = None
+            if splits > 1:
+                need = ops.attention_mma_scratch_bytes(q.shape[0] * s.heads, s.head_dim, splits)
+                scratch = rt.ws.get("attn_scratch", (need,), torch.uint8)
+            ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, scratch, step.n_seqs,
+                              step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, splits)
+            return
         ops.attention_generic(q, cache.storage, table, step.seq_of_token, step.positions, gate, o, s.kv_heads,
                               step.page_size, s.scale, s.window)
 
