@@ -42,7 +42,7 @@ def test_groups_by_need():
     c2 = make(window=100)
     assert [type(g).__name__ for g in c2.groups].count("KVGroup") == 3        # the window makes its own group
     assert c2.views[4].storage is None
-    assert c.views[1].storage.shape == (16, 2, 2, 64, 16) and c.views[0].storage.shape[1:] == (2, 8)
+    assert c.views[1].storage.shape == (16 + 1, 2, 2, 64, 16) and c.views[0].storage.shape[1:] == (2, 8)   # + the spare page
     assert c.views[1].storage.data_ptr() != c.views[3].storage.data_ptr()
 
 

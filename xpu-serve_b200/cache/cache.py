@@ -43,8 +43,10 @@ class KVGroup:
         self.table = np.full((max_slots, max_seq_pages), -1, dtype=np.int32)
         self.first_held = np.zeros(max_slots, dtype=np.int64)    # pages below it were given back
         self.end_held = np.zeros(max_slots, dtype=np.int64)      # pages from it on are not held yet
+        # one page more than the pool hands out: padding rows of a fixed-size batch write there
+        self.dummy_page = n_pages
         self.storage: Dict[int, torch.Tensor] = {
-            c: torch.zeros((max(n_pages, 1), 2, need.kv_heads, page_size, need.head_dim),
+            c: torch.zeros((n_pages + 1, 2, need.kv_heads, page_size, need.head_dim),
                            dtype=dtype, device=device) for c in calls}
 
     def _first_needed_page(self, start: int) -> int:
@@ -87,8 +89,9 @@ class StateGroup:
         self.need = need
         self.calls = list(calls)
         dtype = torch.float32 if need.dtype == "float32" else compute_dtype
+        # one row more than there are slots: the state of padding rows
         self.storage: Dict[int, torch.Tensor] = {
-            c: torch.zeros((max(max_slots, 1), *need.shape), dtype=dtype, device=device) for c in calls}
+            c: torch.zeros((max_slots + 1, *need.shape), dtype=dtype, device=device) for c in calls}
 
     def zero(self, slots: torch.Tensor) -> None:
         for t in self.storage.values():
@@ -123,6 +126,7 @@ class Cache:
         self.device = torch.device(device)
         self.dtype = dtype
         self.slots = IndexPool(self.max_slots, "slot")
+        self.dummy_slot = self.max_slots      # never handed out; padding rows of a fixed-size batch use it
         self.lens = np.zeros(self.max_slots, dtype=np.int64)
         self.groups: List[object] = []
         by_need: Dict[object, List[int]] = {}
@@ -219,6 +223,14 @@ class Cache:
         if width is None:
             width = max(1, int(g.end_held[list(slots)].max()))
         return g.table[list(slots), :width]
+
+    def page_table_fixed(self, group: int, slots: Sequence[int], rows: int) -> np.ndarray:
+        """[rows, max pages a sequence] int32: the slots' rows, then padding rows that name the
+        group's spare page."""
+        g = self.groups[group]
+        out = np.full((rows, g.max_seq_pages), g.dummy_page, dtype=np.int32)
+        out[:len(slots)] = g.table[list(slots)]
+        return out
 
     def tokens_held(self) -> int:
         """Positions reserved in the largest key/value group, in whole pages."""

@@ -12,6 +12,7 @@ src/models/lfm3/lfm3_model.cpp:34-44); the layer order and formulas are the same
 from __future__ import annotations
 
 import os
+from contextlib import contextmanager
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -24,8 +25,26 @@ from ..config.spec import ModelSpec
 from ..ops import lib as ops
 from ..parts.block import Block, ResidualStream
 from ..weights.loader import load_weights
-from .runtime import Runtime
+from .runtime import Runtime, Workspace
 from .step import StepContext, StepStager
+
+
+def _bucket(n: int) -> int:
+    """Batch sizes that decode graphs are captured for: exact up to 8, then multiples of 8 up to 64,
+    then multiples of 32."""
+    if n <= 8:
+        return n
+    if n <= 64:
+        return -(-n // 8) * 8
+    return -(-n // 32) * 32
+
+
+class _DecodeGraph:
+    """A captured decode step for a fixed number of rows: its own scratch buffers and its own
+    description buffer, whose addresses the graph holds."""
+
+    def __init__(self, rows: int, graph, stager: StepStager, ws: Workspace, logits: torch.Tensor, kernels: int):
+        self.rows, self.graph, self.stager, self.ws, self.logits, self.kernels = rows, graph, stager, ws, logits, kernels
 
 
 class Model:
@@ -44,7 +63,10 @@ class Model:
             own = {k[len(layer.prefix):]: v for k, v in weights.items() if k.startswith(layer.prefix)}
             self.blocks.append(Block(layer, own, rt))
         self.stager = StepStager(rt.device)
-        self.launches = 0
+        # Decode steps are launch-bound (some 150 small kernels): they are captured once per batch
+        # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
+        self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
+        self._graphs: Dict[tuple, _DecodeGraph] = {}
 
     # ----------------------------------------------------------------- cache
     def cache_needs(self):
@@ -87,10 +109,59 @@ class Model:
                     raise ValueError(f"wanted place {p} is not among the {len(toks)} tokens of the step")
         q_lens = [len(t) for t in token_lists]
         starts = cache.begin_step(slots, q_lens)
-        ctx = self.stager.stage(cache, slots, token_lists, want, starts)
-        logits = self.forward(ctx, cache)
+        if self.use_graphs and max(q_lens) == 1:
+            logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
+        else:
+            ctx = self.stager.stage(cache, slots, token_lists, want, starts)
+            logits = self.forward(ctx, cache)
         cache.end_step(slots, q_lens)
         return logits
+
+    # ---------------------------------------------------------- decode graphs
+    @contextmanager
+    def _workspace(self, ws: Workspace):
+        old, self.rt.ws = self.rt.ws, ws
+        try:
+            yield
+        finally:
+            self.rt.ws = old
+
+    def _capture(self, cache: Cache, rows: int) -> _DecodeGraph:
+        """Captures the decode step for `rows` sequences. Warm-up and capture run on padding rows only
+        (the cache's spare slot and page), so no sequence's state is touched before the first replay."""
+        rt = self.rt
+        ws = Workspace(rt.device)
+        width = sum(cache.groups[gi].max_seq_pages for gi in cache.kv_groups)
+        stager = StepStager(rt.device, capacity=8 * rows + rows * width + 64, fixed=True)
+        ctx = stager.stage_decode_fixed(cache, [], [], np.zeros(0, dtype=np.int64), rows)
+        with self._workspace(ws):
+            self.forward(ctx, cache)                     # allocates the scratch buffers, loads the kernels
+            torch.cuda.synchronize(rt.device)
+            before = ops.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.forward(ctx, cache)
+            kernels = ops.launches - before
+        ws.frozen = True
+        return _DecodeGraph(rows, graph, stager, ws, logits, kernels)
+
+    def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
+        n = len(slots)
+        rows = _bucket(n)
+        key = (id(cache), rows)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = self._capture(cache, rows)
+            cache._graph_owner = self        # graphs die with the model; the cache only marks its use
+        g.stager.stage_decode_fixed(cache, slots, [t[0] for t in token_lists], np.asarray(starts, dtype=np.int64), rows)
+        g.graph.replay()
+        ops.launches += g.kernels
+        picked = [i for i, places in enumerate(want) for _ in places]
+        if picked == list(range(n)):
+            return g.logits[:n]          # the graph's own output buffer: valid until the next step of this size
+        if not picked:
+            return g.logits[:0]
+        return g.logits[torch.tensor(picked, dtype=torch.int64, device=self.rt.device)]
 
     def forward(self, ctx: StepContext, cache: Cache) -> torch.Tensor:
         rt, spec = self.rt, self.spec

@@ -49,8 +49,9 @@ class StepContext:
 class StepStager:
     """Owns the pinned host buffer and the device buffer that a step's description goes through."""
 
-    def __init__(self, device, capacity: int = 1 << 16):
+    def __init__(self, device, capacity: int = 1 << 16, fixed: bool = False):
         self.device = torch.device(device)
+        self.fixed = fixed           # a captured graph holds this buffer's addresses: it must not be replaced
         self._host = None
         self._dev = None
         self._event = None
@@ -70,31 +71,49 @@ class StepStager:
         T = int(q_lens.sum())
         cu = np.zeros(n + 1, dtype=np.int64)
         np.cumsum(q_lens, out=cu[1:])
-        want_rows = [int(cu[i]) + int(p) for i, places in enumerate(want) for p in places]
-        W = len(want_rows)
+        want_rows = np.asarray([int(cu[i]) + int(p) for i, places in enumerate(want) for p in places], dtype=np.int64)
         tables = {gi: cache.page_table(gi, slots) for gi in cache.kv_groups}
-
-        sizes = [T, T, T, n + 1, n, n, W] + [t.size for t in tables.values()]
-        offs = [0]
-        for s in sizes:
-            offs.append(offs[-1] + _round4(s))
-        if offs[-1] > self._host.numel():
-            if self._event is not None:
-                self._event.synchronize()
-            self._grow(max(offs[-1], 2 * self._host.numel()))
-        elif self._event is not None:
-            self._event.synchronize()      # the last transfer has read the host buffer
-        buf = self._np
         flat = np.concatenate([np.asarray(t, dtype=np.int64) for t in token_lists]) if T else np.zeros(0, np.int64)
         seq_of = np.repeat(np.arange(n, dtype=np.int64), q_lens)
         pos = np.arange(T, dtype=np.int64) - cu[seq_of] + starts[seq_of]
-        buf[offs[0]:offs[0] + T] = flat
-        buf[offs[1]:offs[1] + T] = pos
-        buf[offs[2]:offs[2] + T] = seq_of
-        buf[offs[3]:offs[3] + n + 1] = cu
-        buf[offs[4]:offs[4] + n] = np.asarray(slots, dtype=np.int64)
-        buf[offs[5]:offs[5] + n] = starts + q_lens
-        buf[offs[6]:offs[6] + W] = np.asarray(want_rows, dtype=np.int64)
+        return self._emit(cache, flat, pos, seq_of, cu, np.asarray(slots, dtype=np.int64), starts + q_lens, want_rows,
+                          tables, q_lens, np.asarray(starts, dtype=np.int64), int((starts + q_lens).max()))
+
+    def stage_decode_fixed(self, cache, slots: Sequence[int], tokens: Sequence[int], starts: np.ndarray,
+                           rows: int) -> StepContext:
+        """One token for each of `slots`, laid out as a batch of exactly `rows` sequences with page
+        tables of the cache's full width, so that the layout (and every address a captured graph
+        reads) is the same from step to step. Rows past len(slots) are padding: they use the cache's
+        spare slot and page, stand at position 0 and are never read by the real rows."""
+        n = len(slots)
+        tok = np.zeros(rows, dtype=np.int64)
+        tok[:n] = np.asarray(tokens, dtype=np.int64)
+        pos = np.zeros(rows, dtype=np.int64)
+        pos[:n] = starts
+        sl = np.full(rows, cache.dummy_slot, dtype=np.int64)
+        sl[:n] = np.asarray(slots, dtype=np.int64)
+        idx = np.arange(rows, dtype=np.int64)
+        tables = {gi: cache.page_table_fixed(gi, slots, rows) for gi in cache.kv_groups}
+        q_lens = np.ones(rows, dtype=np.int64)
+        return self._emit(cache, tok, pos, idx, np.arange(rows + 1, dtype=np.int64), sl, pos + 1, idx, tables, q_lens,
+                          pos, cache.max_seq_tokens)
+
+    def _emit(self, cache, flat, pos, seq_of, cu, slots, kv_lens, want_rows, tables, q_lens, starts,
+              max_kv_len) -> StepContext:
+        T, n, W = len(flat), len(slots), len(want_rows)
+        sizes = [T, T, T, n + 1, n, n, W] + [t.size for t in tables.values()]
+        offs = [0]
+        for sz in sizes:
+            offs.append(offs[-1] + _round4(sz))
+        if self._event is not None:
+            self._event.synchronize()      # the last transfer has read the host buffer
+        if offs[-1] > self._host.numel():
+            if self.fixed:
+                raise RuntimeError("a step's description outgrew a buffer whose addresses a graph holds")
+            self._grow(max(offs[-1], 2 * self._host.numel()))
+        buf = self._np
+        for k, a in enumerate((flat, pos, seq_of, cu, slots, kv_lens, want_rows)):
+            buf[offs[k]:offs[k] + len(a)] = a
         for k, t in enumerate(tables.values()):
             buf[offs[7 + k]:offs[7 + k] + t.size] = t.reshape(-1)
         total = offs[-1]
@@ -110,11 +129,10 @@ class StepStager:
 
         ctx = StepContext(
             n_seqs=n, n_tokens=T, decode=bool((q_lens == 1).all()), max_q_len=int(q_lens.max()),
-            max_kv_len=int((starts + q_lens).max()), page_size=cache.page_size,
-            max_positions=cache.max_seq_tokens,
+            max_kv_len=int(max_kv_len), page_size=cache.page_size, max_positions=cache.max_seq_tokens,
             tokens=view(0, T), positions=view(1, T), seq_of_token=view(2, T), cu_seqlens=view(3, n + 1),
             slots=view(4, n), kv_lens=view(5, n), want_rows=view(6, W),
-            q_lens_host=q_lens, starts_host=np.asarray(starts, dtype=np.int64))
+            q_lens_host=q_lens, starts_host=starts)
         for k, (gi, t) in enumerate(tables.items()):
             ctx.page_tables[gi] = view(7 + k, t.size).view(n, t.shape[1])
         return ctx

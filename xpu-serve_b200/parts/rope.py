@@ -42,6 +42,8 @@ class RotaryTable:
         pos = torch.arange(n_positions, dtype=torch.float64, device=self.rt.device)
         angle = pos[:, None] * inv[None, :]
         table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).to(torch.float32).contiguous()
+        if have is not None:     # a captured graph may still read the shorter table: keep it alive
+            self.rt.shared.setdefault(("kept",), []).append(have)
         self.rt.shared[self.key] = table
         return table
 
