@@ -196,7 +196,7 @@ def time_e2e(folder: str, batch: int, steps: int, warmup: int, V: int):
         raise RuntimeError(bad[0])
     # request 0's token k arrives after decode step k - 1; skip the warm-up steps
     span = stamps[warmup + steps] - stamps[warmup]
-    h2d = engine.model.stager.last_h2d_bytes      # the step's description: tokens, positions, slots, page tables
+    h2d = engine.model.last_h2d_bytes      # the last decode step's description: tokens, positions, slots, page tables
     return batch * steps / span, h2d, 4 * batch
 
 

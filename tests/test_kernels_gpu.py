@@ -118,6 +118,21 @@ def test_silu_mul(dtype):
     close(out, g / (1 + torch.exp(-g)) * u, dtype)
 
 
+def test_silu_mul_interleaved_blocks_of_eight():
+    T, F = 9, 336
+    g = torch.randn(T, F, device=DEV) * 3
+    u = torch.randn(T, F, device=DEV)
+    gu = torch.stack([g.view(T, F // 8, 8), u.view(T, F // 8, 8)], 2).reshape(T, 2 * F)
+    want = g.double() / (1 + torch.exp(-g.double())) * u.double()
+    for dtype in ("float32", "bfloat16"):
+        x = gu.to(DT[dtype])
+        out = torch.empty(T, F, device=DEV, dtype=DT[dtype])
+        ops().silu_mul(x, out, interleave=8)
+        gg, uu = x.view(T, F // 8, 2, 8)[:, :, 0].reshape(T, F).double(), x.view(T, F // 8, 2, 8)[:, :, 1].reshape(T, F).double()
+        close(out, gg / (1 + torch.exp(-gg)) * uu, dtype)
+        assert (out.double() - want).abs().max() < 0.1
+
+
 # ---------------------------------------------------------------------------- matrix products
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 100, 96), (65, 130, 200), (200, 1000, 333), (9, 64, 4096)])
@@ -169,6 +184,20 @@ def test_gemm_small_m(M, N, K):
     one = torch.empty(1, N, device=DEV)
     lib.gemm_small_m(x[M - 1:M], w, one)
     assert torch.equal(one, out[M - 1:M]), "a row's result depends on the batch"
+
+
+@pytest.mark.parametrize("M", [1, 7, 8, 13])
+def test_gemm_small_m_with_fused_activation(M):
+    lib = ops()
+    F, K = 344, 200
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    gate = (torch.randn(F, K, device=DEV) / math.sqrt(K) * 3).to(torch.bfloat16)
+    up = (torch.randn(F, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    w = torch.stack([gate.view(F // 8, 8, K), up.view(F // 8, 8, K)], 1).reshape(2 * F, K).contiguous()
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    out = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    lib.gemm_small_m(x, w, out, swiglu=True)
+    close(out, g / (1 + torch.exp(-g)) * u, "bfloat16")
 
 
 def test_gemm_small_m_refuses_what_it_cannot_take():
@@ -377,7 +406,7 @@ def test_short_conv_in_steps_equals_one_pass(dtype, H, K):
         seq_of = torch.tensor(np.repeat(np.arange(len(part)), lens), dtype=torch.int32, device=DEV)
         sl = torch.tensor([slots[s] for s in part], dtype=torch.int32, device=DEV)
         out = torch.empty(sum(lens), H, device=DEV, dtype=DT[dtype])
-        lib.short_conv(bcx[:, :3 * H], w_t, bias.to(DEV), state, seq_of, cu, sl, out)
+        lib.short_conv(bcx[:, :3 * H], w_t, bias.to(DEV), state, seq_of, cu, sl, out, all_single=all(n == 1 for n in lens))
         o = 0
         for s, n in zip(part, lens):
             got[s][at[s]:at[s] + n] = out[o:o + n]

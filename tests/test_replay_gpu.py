@@ -93,7 +93,7 @@ def test_last_32_one_by_one(name, dtype, replayers, references):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(tiny.CONFIGS))
-@pytest.mark.parametrize("batch", [3, 5])
+@pytest.mark.parametrize("batch", [3, 5, 11])
 def test_unequal_batches(name, dtype, batch, replayers, references):
     check(name, dtype, tu.batch_trace(requests_for(name), batch), replayers, references)
 

@@ -37,7 +37,7 @@ template <int NT, typename TO>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                     const float* __restrict__ bias, TO* __restrict__ out, float* __restrict__ residual, int M, int N,
-                    int K, int64_t ldx, int64_t ldw, int64_t ldo) {
+                    int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -89,6 +89,26 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
         red[warp][g + 8][t * 8 + q * 2 + 1] = acc[t][3];
     }
     __syncthreads();
+    if (swiglu) {
+        // The weight's rows come in blocks of 16: 8 gate rows, then the 8 up rows of the same outputs.
+        // out[m, n0 / 2 + r] = silu(gate_r) * up_r: the activation is never written unfused.
+        for (int i = threadIdx.x; i < 8 * 8 * NT; i += WARPS * 32) {
+            const int r = i % 8, m = i / 8;
+            if (m >= M || n0 + 8 + r >= N) continue;
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < WARPS; ++wv) {
+                gate += red[wv][r][m];
+                up += red[wv][r + 8][m];
+            }
+            if (bias != nullptr) {
+                gate += bias[n0 + r];
+                up += bias[n0 + 8 + r];
+            }
+            out[(int64_t)m * ldo + (n0 >> 1) + r] = from_f32<TO>(gate / (1.0f + expf(-gate)) * up);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
         const int r = i % ROWS, m = i / ROWS;       // neighbouring threads write neighbouring columns of out
         const int n = n0 + r;
@@ -112,17 +132,21 @@ XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
 }
 
 // x, w bfloat16; out bfloat16 or float32 (out_dtype), or residual += when `residual` is given (float32, stride ldo).
+// swiglu != 0: w holds blocks of 8 gate rows and 8 up rows; out is [M, N / 2] = silu(gate) * up.
 XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void* out, float* residual, int out_dtype,
-                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, cudaStream_t stream) {
+                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
+                           cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     XS_REQUIRE(xs_gemm_small_m_supports(M, K, ldx, ldw), "gemm (few rows): M %d, K %d, strides %lld, %lld not supported",
                M, K, (long long)ldx, (long long)ldw);
     XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (few rows): operands must be 16-byte aligned");
-    XS_REQUIRE(N > 0 && K > 0 && ldo >= N && (out != nullptr || residual != nullptr), "gemm (few rows): bad sizes");
+    XS_REQUIRE(N > 0 && K > 0 && ldo >= (swiglu ? N / 2 : N) && (out != nullptr || residual != nullptr),
+               "gemm (few rows): bad sizes");
+    XS_REQUIRE(!swiglu || (N % 16 == 0 && residual == nullptr), "gemm (few rows): the fused activation needs N %% 16 == 0");
     const int blocks = ceil_div_i(N, ROWS);
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-#define XS_GO(NT, TO) gemm_small_m_kernel<NT, TO><<<blocks, WARPS * 32, 0, stream>>>(xp, wp, bias, (TO*)out, residual, M, N, K, ldx, ldw, ldo)
+#define XS_GO(NT, TO) gemm_small_m_kernel<NT, TO><<<blocks, WARPS * 32, 0, stream>>>(xp, wp, bias, (TO*)out, residual, M, N, K, ldx, ldw, ldo, swiglu)
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
     } else if (out_dtype == XS_BF16) {

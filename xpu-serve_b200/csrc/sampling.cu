@@ -89,6 +89,32 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int 
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
 
+// Wide rows, few of them: each row is cut into `parts` pieces so that more than a handful of SMs
+// read it. packed[row] = max over pieces of (ordered value bits << 32 | ~index): the largest value
+// wins, and among equals the lowest index. out[row] is decoded by argmax_finish_kernel.
+__global__ void argmax_part_kernel(const float* __restrict__ logits, int64_t ld, int V, int parts,
+                                   unsigned long long* __restrict__ packed) {
+    __shared__ ArgBest scratch[32];
+    const int row = blockIdx.y, part = blockIdx.x;
+    const int per = (V + parts - 1) / parts;
+    const int begin = min(V, part * per), count = min(V, begin + per) - begin;
+    if (count <= 0) return;
+    ArgBest r = block_argmax(logits + (int64_t)row * ld + begin, count, scratch);
+    if (threadIdx.x == 0) {
+        const float v = r.v != r.v ? -INFINITY : r.v;
+        const unsigned long long key = ((unsigned long long)ordered_bits(v) << 32) |
+                                       (unsigned long long)(0xFFFFFFFFu - (unsigned)(begin + r.i));
+        atomicMax(&packed[row], key);
+    }
+}
+__global__ void argmax_finish_kernel(unsigned long long* __restrict__ packed, int n, int32_t* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    out[i] = (int32_t)(0xFFFFFFFFu - (unsigned)(packed[i] & 0xFFFFFFFFull));
+    packed[i] = 0ull;      // ready for the next call
+}
+
+
 // Radix descent, most significant byte first, over the keys >= `floor_key`.
 // by_count: the key of rank `target_count` (1-based) in descending order.
 // else:     the largest key K such that the weight of {keys >= K} reaches `target_mass`.
@@ -269,9 +295,18 @@ __global__ void note_tokens_kernel(const int32_t* __restrict__ tokens, const int
 
 XS_API double xs_uniform(uint64_t seed, uint64_t counter) { return uniform_from(seed, counter); }
 
-XS_API int xs_argmax(const float* logits, int64_t ld, int n, int V, int32_t* out, cudaStream_t stream) {
+// `packed`: n zeroed 64-bit words of scratch for wide rows (left zeroed again), or null.
+XS_API int xs_argmax(const float* logits, int64_t ld, int n, int V, int32_t* out, unsigned long long* packed,
+                     cudaStream_t stream) {
     if (n == 0) return 0;
     XS_REQUIRE(n > 0 && V > 0 && ld >= V, "argmax: %d rows of %d", n, V);
+    if (V >= 16384 && n <= 65535 && packed != nullptr) {
+        const int parts = min(32, V / 4096);
+        argmax_part_kernel<<<dim3(parts, n), 256, 0, stream>>>(logits, ld, V, parts, packed);
+        argmax_finish_kernel<<<ceil_div_i(n, 128), 128, 0, stream>>>(packed, n, out);
+        XS_LAUNCH_CHECK("argmax");
+        return 0;
+    }
     argmax_kernel<<<n, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, ld, V, out);
     XS_LAUNCH_CHECK("argmax");
     return 0;

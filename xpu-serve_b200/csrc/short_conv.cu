@@ -61,13 +61,134 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, int64_t ld, T
     }
 }
 
+// ---- bfloat16, 8 channels a thread (16-byte loads and stores); H a multiple of 8.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 v = __bfloat1622float2(p[k]);
+        f[2 * k] = v.x;
+        f[2 * k + 1] = v.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 raw;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+    return raw;
+}
+// g = B * X of one token for 8 channels, rounded to bfloat16 as the state keeps it
+__device__ __forceinline__ void gated8(const __nv_bfloat16* __restrict__ row, int c8, int H, float (&g)[8]) {
+    float b[8], x[8];
+    unpack8(*reinterpret_cast<const uint4*>(row + c8), b);
+    unpack8(*reinterpret_cast<const uint4*>(row + 2 * H + c8), x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = __bfloat162float(__float2bfloat16_rn(b[k] * x[k]));
+}
+
+__global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, int64_t ld, const float* __restrict__ w_t,
+                                         const float* __restrict__ bias, const __nv_bfloat16* __restrict__ state,
+                                         const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ cu_seqlens,
+                                         const int32_t* __restrict__ slots, __nv_bfloat16* __restrict__ out, int Tn, int H,
+                                         int K) {
+    const int H8 = H >> 3;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)Tn * H8) return;
+    const int t = (int)(idx / H8), c8 = (int)(idx % H8) * 8;
+    const int seq = seq_of_token[t];
+    const int first = cu_seqlens[seq];
+    const int t_local = t - first;
+    const __nv_bfloat16* st = state + (int64_t)slots[seq] * (K - 1) * H;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = bias != nullptr ? bias[c8 + k] : 0.0f;
+    for (int j = 0; j < K; ++j) {
+        const int r = t_local + j;
+        float v[8];
+        if (r < K - 1) unpack8(*reinterpret_cast<const uint4*>(st + (int64_t)r * H + c8), v);
+        else gated8(bcx + ((int64_t)first + r - (K - 1)) * ld, c8, H, v);
+        const float4 w0 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8);
+        const float4 w1 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8 + 4);
+        acc[0] = fmaf(w0.x, v[0], acc[0]); acc[1] = fmaf(w0.y, v[1], acc[1]);
+        acc[2] = fmaf(w0.z, v[2], acc[2]); acc[3] = fmaf(w0.w, v[3], acc[3]);
+        acc[4] = fmaf(w1.x, v[4], acc[4]); acc[5] = fmaf(w1.y, v[5], acc[5]);
+        acc[6] = fmaf(w1.z, v[6], acc[6]); acc[7] = fmaf(w1.w, v[7], acc[7]);
+    }
+    float c[8];
+    unpack8(*reinterpret_cast<const uint4*>(bcx + (int64_t)t * ld + H + c8), c);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] *= c[k];
+    *reinterpret_cast<uint4*>(out + (int64_t)t * H + c8) = pack8(acc);
+}
+
+// Every sequence brings one token: the thread that owns (sequence, 8 channels) reads the state's
+// K-1 rows, computes the output and writes the shifted state, in one kernel.
+__global__ void short_conv_decode_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, int64_t ld,
+                                                const float* __restrict__ w_t, const float* __restrict__ bias,
+                                                __nv_bfloat16* __restrict__ state, const int32_t* __restrict__ slots,
+                                                __nv_bfloat16* __restrict__ out, int n_seqs, int H, int K) {
+    const int H8 = H >> 3;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)n_seqs * H8) return;
+    const int seq = (int)(idx / H8), c8 = (int)(idx % H8) * 8;
+    __nv_bfloat16* st = state + (int64_t)slots[seq] * (K - 1) * H;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = bias != nullptr ? bias[c8 + k] : 0.0f;
+    float g[8];
+    gated8(bcx + (int64_t)seq * ld, c8, H, g);
+    for (int j = 0; j < K; ++j) {
+        float v[8];
+        if (j < K - 1) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(st + (int64_t)j * H + c8);
+            unpack8(raw, v);
+            if (j > 0) *reinterpret_cast<uint4*>(st + (int64_t)(j - 1) * H + c8) = raw;   // row j moves to j - 1
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = g[k];
+        }
+        const float4 w0 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8);
+        const float4 w1 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8 + 4);
+        acc[0] = fmaf(w0.x, v[0], acc[0]); acc[1] = fmaf(w0.y, v[1], acc[1]);
+        acc[2] = fmaf(w0.z, v[2], acc[2]); acc[3] = fmaf(w0.w, v[3], acc[3]);
+        acc[4] = fmaf(w1.x, v[4], acc[4]); acc[5] = fmaf(w1.y, v[5], acc[5]);
+        acc[6] = fmaf(w1.z, v[6], acc[6]); acc[7] = fmaf(w1.w, v[7], acc[7]);
+    }
+    *reinterpret_cast<uint4*>(st + (int64_t)(K - 2) * H + c8) = pack8(g);
+    float c[8];
+    unpack8(*reinterpret_cast<const uint4*>(bcx + (int64_t)seq * ld + H + c8), c);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] *= c[k];
+    *reinterpret_cast<uint4*>(out + (int64_t)seq * H + c8) = pack8(acc);
+}
+
 }  // namespace
 
+// `all_single` != 0 promises that every sequence brings exactly one token (T == n_seqs).
 XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const float* bias, void* state,
                          const int32_t* seq_of_token, const int32_t* cu_seqlens, const int32_t* slots, void* out,
-                         int T, int n_seqs, int H, int K, int dtype, cudaStream_t stream) {
+                         int T, int n_seqs, int H, int K, int dtype, int all_single, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(H > 0 && K >= 2 && n_seqs > 0 && ld >= 3 * (int64_t)H, "short_conv: width %d, %d taps, %d sequences", H, K, n_seqs);
+    XS_REQUIRE(!all_single || T == n_seqs, "short_conv: %d tokens for %d sequences of one token each", T, n_seqs);
+    const bool vec = dtype == XS_BF16 && H % 8 == 0 && ld % 8 == 0 && (uintptr_t)bcx % 16 == 0 &&
+                     (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w_t % 16 == 0;
+    if (vec && all_single) {
+        short_conv_decode_bf16x8_kernel<<<ceil_div_i((int64_t)n_seqs * (H / 8), 128), 128, 0, stream>>>(
+            (const __nv_bfloat16*)bcx, ld, w_t, bias, (__nv_bfloat16*)state, slots, (__nv_bfloat16*)out, n_seqs, H, K);
+        XS_LAUNCH_CHECK("short_conv_decode");
+        return 0;
+    }
+    if (vec) {
+        short_conv_bf16x8_kernel<<<ceil_div_i((int64_t)T * (H / 8), 256), 256, 0, stream>>>(
+            (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots,
+            (__nv_bfloat16*)out, T, H, K);
+        short_conv_state_kernel<__nv_bfloat16><<<ceil_div_i((int64_t)n_seqs * H, 256), 256, 0, stream>>>(
+            (const __nv_bfloat16*)bcx, ld, (__nv_bfloat16*)state, cu_seqlens, slots, n_seqs, H, K);
+        XS_LAUNCH_CHECK("short_conv");
+        return 0;
+    }
     const int blocks = ceil_div_i((int64_t)T * H, 256);
     const int blocks2 = ceil_div_i((int64_t)n_seqs * H, 256);
     XS_DISPATCH_DTYPE(dtype, TT, {

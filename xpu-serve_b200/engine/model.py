@@ -67,6 +67,7 @@ class Model:
         # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
         self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
         self._graphs: Dict[tuple, _DecodeGraph] = {}
+        self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
 
     # ----------------------------------------------------------------- cache
     def cache_needs(self):
@@ -113,6 +114,7 @@ class Model:
             logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
         else:
             ctx = self.stager.stage(cache, slots, token_lists, want, starts)
+            self.last_h2d_bytes = self.stager.last_h2d_bytes
             logits = self.forward(ctx, cache)
         cache.end_step(slots, q_lens)
         return logits
@@ -154,6 +156,7 @@ class Model:
             g = self._graphs[key] = self._capture(cache, rows)
             cache._graph_owner = self        # graphs die with the model; the cache only marks its use
         g.stager.stage_decode_fixed(cache, slots, [t[0] for t in token_lists], np.asarray(starts, dtype=np.int64), rows)
+        self.last_h2d_bytes = g.stager.last_h2d_bytes
         g.graph.replay()
         ops.launches += g.kernels
         picked = [i for i, places in enumerate(want) for _ in places]

@@ -72,6 +72,11 @@ class Runtime:
         return t.to(device=self.device, dtype=torch.float32).contiguous()
 
     # ------------------------------------------------------ matrix products
+    def few_rows(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether this product goes to the library's own weight-streaming kernel."""
+        return (self.mode == "bfloat16" and x.shape[0] <= self.small_m
+                and ops.gemm_small_m_supports(x.shape[0], x.shape[1], x.stride(0), w.stride(0)))
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`."""
@@ -80,7 +85,7 @@ class Runtime:
         out = self.ws.get(name, (M, N), out_dtype)
         if self.mode == "float32":
             ops.gemm_generic(x, w, out, bias)
-        elif M <= self.small_m and ops.gemm_small_m_supports(M, x.shape[1], x.stride(0), w.stride(0)):
+        elif self.few_rows(x, w):
             ops.gemm_small_m(x, w, out, bias)
         elif bias is not None:
             ops.gemm_generic(x, w, out, bias)

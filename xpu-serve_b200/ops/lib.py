@@ -32,15 +32,15 @@ def _signatures(lib) -> None:
     sig = {
         "xs_embed": [P, I, P, P, I, I, P],
         "xs_add_rmsnorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
-        "xs_silu_mul": [P, P, I, I, I, L, P],
+        "xs_silu_mul": [P, P, I, I, I, L, I, P],
         "xs_zero_rows": [P, P, I, L, P],
         "xs_gemm_generic": [P, P, P, P, I, I, I, I, I, L, L, L, P],
         "xs_qk_norm_rope_store": [P, L, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P],
         "xs_attention_generic": [P, P, P, I, P, P, P, L, P, I, I, I, I, I, F, I, I, P],
-        "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
-        "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, P],
-        "xs_argmax": [P, L, I, I, P, P],
+        "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, P],
+        "xs_argmax": [P, L, I, I, P, P, P],
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
         "xs_note_tokens": [P, P, I, I, P, P, I, P],
@@ -150,14 +150,15 @@ def add_rmsnorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[tor
                                  float(eps if eps_post is None else eps_post), float(eps), _stream()))
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
+    """out = silu(gate) * up. interleave 0: a row of gu is [gate | up]; 8: blocks of 8 gate, 8 up columns."""
     _need(out, "out", gu.dtype)
     if not gu.is_cuda or gu.dim() != 2 or gu.stride(1) != 1:
         raise KernelError("gate_up must be a CUDA matrix with contiguous rows")
     T, F = out.shape
     if gu.shape[0] != T or gu.shape[1] < 2 * F:
         raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
-    _check(load().xs_silu_mul(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), _stream()))
+    _check(load().xs_silu_mul(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), int(interleave), _stream()))
 
 
 def zero_rows(state: torch.Tensor, slots: torch.Tensor) -> None:
@@ -266,15 +267,16 @@ def gemm_small_m_supports(M: int, K: int, ldx: int, ldw: int) -> bool:
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
-                 residual: Optional[torch.Tensor] = None) -> None:
-    """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product."""
+                 residual: Optional[torch.Tensor] = None, swiglu: bool = False) -> None:
+    """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product;
+    or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows."""
     for t, name in ((x, "x"), (w, "w")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
             raise KernelError(f"gemm (few rows): {name} must be a bfloat16 CUDA matrix with contiguous rows")
     M, K = x.shape
     N = w.shape[0]
     target = residual if residual is not None else out
-    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N) or target.stride(1) != 1:
+    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N // 2 if swiglu else N) or target.stride(1) != 1:
         raise KernelError(f"gemm (few rows): x {tuple(x.shape)}, w {tuple(w.shape)}, out "
                           f"{None if target is None else tuple(target.shape)}")
     if residual is not None and residual.dtype != torch.float32:
@@ -283,11 +285,13 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         _need(bias, "bias", torch.float32)
     _check(load().xs_gemm_small_m(x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual),
                                   F32 if out is None else _code(out), M, N, K, x.stride(0), w.stride(0),
-                                  target.stride(0), _stream()))
+                                  target.stride(0), 1 if swiglu else 0, _stream()))
 
 
 def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
-               seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor) -> None:
+               seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+               all_single: bool = False) -> None:
+    """`all_single`: every sequence brings exactly one token (lets one kernel also move the state)."""
     _need(out, "out", bcx.dtype); _need(state, "state", bcx.dtype); _need(w_t, "taps", torch.float32)
     T, H = out.shape
     K = w_t.shape[0]
@@ -299,13 +303,22 @@ def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor
         _need(bias, "bias", torch.float32)
     _check(load().xs_short_conv(bcx.data_ptr(), bcx.stride(0), w_t.data_ptr(), _ptr(bias), state.data_ptr(),
                                 seq_of_token.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(),
-                                T, slots.numel(), H, K, _code(bcx), _stream()), kernels=2)
+                                T, slots.numel(), H, K, _code(bcx), 1 if all_single else 0, _stream()),
+           kernels=1 if all_single and bcx.dtype == torch.bfloat16 and H % 8 == 0 else 2)
+
+
+_argmax_scratch = {}
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i] = index of the largest of row i, the lowest index among equals."""
     _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
     n, V = logits.shape
-    _check(load().xs_argmax(logits.data_ptr(), logits.stride(0), n, V, out.data_ptr(), _stream()))
+    scratch = _argmax_scratch.get(logits.device)
+    if scratch is None or scratch.numel() < n:       # zeroed words the wide-row path works in and leaves zeroed
+        scratch = _argmax_scratch[logits.device] = torch.zeros(max(n, 256), dtype=torch.int64, device=logits.device)
+    _check(load().xs_argmax(logits.data_ptr(), logits.stride(0), n, V, out.data_ptr(), scratch.data_ptr(), _stream()),
+           kernels=2 if V >= 16384 else 1)
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

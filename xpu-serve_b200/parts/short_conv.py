@@ -50,7 +50,8 @@ class ShortConvMixer(Mixer):
             raise RuntimeError("short_conv keeps its own state and cannot read another call's")
         bcx = rt.linear(x, self.w_in, "conv_bcx", self.b_in)
         y = rt.ws.get("conv_y", (x.shape[0], H), rt.act_dtype)
-        ops.short_conv(bcx, self.taps, self.b_conv, cache.storage, step.seq_of_token, step.cu_seqlens, step.slots, y)
+        ops.short_conv(bcx, self.taps, self.b_conv, cache.storage, step.seq_of_token, step.cu_seqlens, step.slots, y,
+                       all_single=step.decode)
         return rt.linear(y, self.w_out, "mixer_out", self.b_out)
 
 

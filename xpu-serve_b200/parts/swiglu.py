@@ -1,5 +1,8 @@
 """SwiGLU feed-forward: down(silu(gate y) * up y) (src/models/common/blocks.cpp:23-27). The
-gate and up weights are stacked at load so that one matrix product gives both."""
+gate and up weights are stacked at load so that one matrix product gives both. When the
+width allows (a multiple of 8, bfloat16) they are stacked in blocks of 8 gate rows and the 8
+up rows of the same outputs: the few-row product then applies the activation in its
+epilogue and writes silu(gate) * up directly."""
 from __future__ import annotations
 
 from typing import Dict
@@ -24,15 +27,24 @@ class SwiGLU(FeedForward):
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
         self.spec, self.rt = spec, rt
         n = spec.names
-        self.w_gate_up = rt.matrix(torch.cat([weights[n["gate"]].to(torch.float32),
-                                              weights[n["up"]].to(torch.float32)], 0))
+        gate, up = weights[n["gate"]].to(torch.float32), weights[n["up"]].to(torch.float32)
+        F, H = spec.intermediate, spec.hidden
+        self.interleave = 8 if (rt.mode == "bfloat16" and F % 8 == 0) else 0
+        if self.interleave:
+            stacked = torch.stack([gate.view(F // 8, 8, H), up.view(F // 8, 8, H)], 1).reshape(2 * F, H)
+        else:
+            stacked = torch.cat([gate, up], 0)
+        self.w_gate_up = rt.matrix(stacked)
         self.w_down = rt.matrix(weights[n["down"]])
 
     def forward(self, y: torch.Tensor, step) -> torch.Tensor:
         rt, F = self.rt, self.spec.intermediate
-        gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
-        ops.silu_mul(gu, act)
+        if self.interleave and rt.few_rows(y, self.w_gate_up):
+            ops.gemm_small_m(y, self.w_gate_up, act, swiglu=True)
+        else:
+            gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
+            ops.silu_mul(gu, act, self.interleave)
         return rt.linear(act, self.w_down, "ffn_out")
 
 
