@@ -2,22 +2,34 @@
 //
 // The weight is read exactly once, straight from HBM into registers with 16-byte loads, and
 // never staged: with M this small the product is bound by weight bandwidth. A CTA of 8 warps
-// owns 16 weight rows; its warps take the 32-wide k blocks in turn (warp w: blocks w, w+8, ...),
+// owns 16 weight rows and a slice of K; its warps take the slice's 32-wide k blocks in turn
+// (warp w: blocks w, w+8, ...). Each lane keeps eight blocks' worth of its own 16-byte pieces
+// in flight with cp.async into a private ring in shared memory (a lane reads back only what it
+// copied itself, so cp.async.wait_group is all the synchronisation the ring needs); the
+// compiler cannot shorten that queue the way it does with loads into registers. Warps
 // multiply on tensor cores (mma.sync m16n8k16: weight rows on the M side, the batch on the N
-// side) and their partial sums are added in shared memory in warp order, so the result does
-// not depend on timing. A lane's 16 bytes are 8 consecutive k of one row; the same
-// assignment of k to fragment slots is used for the weight and for x, which is all a
-// contraction needs. The reference has the same split: its own `gemv_t` up to 8 rows, a
-// library GEMM above (src/backend/sycl/sycl_kernels.cpp:630-714, sycl_kernels.h:280).
+// side) and add their partial sums in shared memory in warp order. A lane's 16 bytes are 8
+// consecutive k of one row; the same assignment of k to fragment slots is used for the
+// weight and for x, which is all a contraction needs.
 //
-// Optional epilogue: bias[N] added; `residual` (float32 [M, N]) += result instead of storing
-// (the branch output joining the residual stream when no norm stands between).
+// Narrow outputs with a long K (the feed-forward's down projection) would leave most SMs
+// idle, so K is cut into `ksplit` slices over blockIdx.y. Each slice's CTA writes its 16 x M
+// partial to scratch; the CTA that arrives last (a counter per row tile) adds the slices in
+// slice order, so the sum does not depend on which CTA that was, and resets the counter.
+//
+// Epilogues: bias[N]; `residual` (float32 [M, N]) += result; or SwiGLU for a weight stacked in
+// blocks of 8 gate rows and 8 up rows: out[M, N / 2] = silu(gate) * up.
+//
+// The reference has the same split of work between its own kernel and a library: `gemv_t` up
+// to 8 rows, oneMKL above (src/backend/sycl/sycl_kernels.cpp:630-714, sycl_kernels.h:280).
 #include "common.cuh"
 
 namespace {
 
 constexpr int WARPS = 8;
-constexpr int ROWS = 16;   // weight rows per CTA
+constexpr int ROWS = 16;      // weight rows per CTA
+constexpr int STAGES = 8;     // k blocks a warp keeps in flight
+constexpr int K_PER_CTA = WARPS * STAGES * 32;   // a K slice this long is one round of loads per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                                unsigned b0, unsigned b1) {
@@ -26,60 +38,123 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) {   // weights are used once: do not keep them in L1
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+// 16 bytes global -> shared, bypassing L1 (weights are used once); `valid` false writes zeros.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+struct SmallMParams {
+    const __nv_bfloat16* x;
+    const __nv_bfloat16* w;
+    const float* bias;
+    void* out;
+    float* residual;
+    float* partials;          // [tiles, ksplit, ROWS, 8 * NT] when ksplit > 1
+    unsigned int* counters;   // [tiles], zero between calls
+    int M, N, K, ksplit, swiglu;
+    int64_t ldx, ldw, ldo;
+};
+
+template <int NT, typename TO>
+__device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], int n0) {
+    TO* out = reinterpret_cast<TO*>(p.out);
+    if (p.swiglu) {
+        // rows 0..7 of the tile are gate rows, rows 8..15 the up rows of the same outputs
+        for (int i = threadIdx.x; i < 8 * 8 * NT; i += WARPS * 32) {
+            const int r = i % 8, m = i / 8;
+            if (m >= p.M || n0 + 8 + r >= p.N) continue;
+            float gate = sum[r][m], up = sum[r + 8][m];
+            if (p.bias != nullptr) {
+                gate += p.bias[n0 + r];
+                up += p.bias[n0 + 8 + r];
+            }
+            out[(int64_t)m * p.ldo + (n0 >> 1) + r] = from_f32<TO>(gate / (1.0f + expf(-gate)) * up);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
+        const int r = i % ROWS, m = i / ROWS;       // neighbouring threads write neighbouring columns of out
+        const int n = n0 + r;
+        if (m >= p.M || n >= p.N) continue;
+        float v = sum[r][m];
+        if (p.bias != nullptr) v += p.bias[n];
+        if (p.residual != nullptr) {
+            p.residual[(int64_t)m * p.ldo + n] += v;
+        } else {
+            out[(int64_t)m * p.ldo + n] = from_f32<TO>(v);
+        }
+    }
 }
 
 template <int NT, typename TO>
-__global__ void __launch_bounds__(WARPS * 32)
-gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                    const float* __restrict__ bias, TO* __restrict__ out, float* __restrict__ residual, int M, int N,
-                    int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu) {
+__global__ void __launch_bounds__(WARPS * 32) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
+    __shared__ float sum[ROWS][8 * NT + 1];
+    __shared__ bool last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
-    const int n0 = blockIdx.x * ROWS;
-    const int ra = min(n0 + g, N - 1), rb = min(n0 + g + 8, N - 1);   // clamped: out-of-range rows are not stored
-    const __nv_bfloat16* wa_p = w + (int64_t)ra * ldw + q * 8;
-    const __nv_bfloat16* wb_p = w + (int64_t)rb * ldw + q * 8;
+    const int tile = blockIdx.x, slice = blockIdx.y;
+    const int n0 = tile * ROWS;
+    const int ra = min(n0 + g, p.N - 1), rb = min(n0 + g + 8, p.N - 1);   // clamped: out-of-range rows are not stored
+    const __nv_bfloat16* wa_p = p.w + (int64_t)ra * p.ldw + q * 8;
+    const __nv_bfloat16* wb_p = p.w + (int64_t)rb * p.ldw + q * 8;
     const __nv_bfloat16* x_p[NT];
     bool x_ok[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-        x_ok[t] = t * 8 + g < M;
-        x_p[t] = x + (int64_t)(x_ok[t] ? t * 8 + g : 0) * ldx + q * 8;
+        x_ok[t] = t * 8 + g < p.M;
+        x_p[t] = p.x + (int64_t)(x_ok[t] ? t * 8 + g : 0) * p.ldx + q * 8;
     }
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
 
-    const int k_blocks = (K + 31) / 32;
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    constexpr int UNROLL = 4;
-    for (int kb = warp; kb < k_blocks; kb += WARPS * UNROLL) {
-        uint4 wa[UNROLL], wb[UNROLL], xv[UNROLL][NT];
+    // this CTA's k blocks: [kb_begin, kb_end); this warp takes every WARPS-th of them
+    const int k_blocks = (p.K + 31) / 32;
+    const int per_slice = (k_blocks + p.ksplit - 1) / p.ksplit;
+    const int kb_begin = slice * per_slice, kb_end = min(k_blocks, kb_begin + per_slice);
+    // this warp's ring: STAGES entries of (2 + NT) pieces; a piece is 32 lanes x 16 bytes, lane-major,
+    // so a warp's access to one piece covers 512 consecutive bytes (no bank conflicts)
+    extern __shared__ __align__(16) uint4 ring_all[];
+    uint4* ring = ring_all + (size_t)warp * STAGES * (2 + NT) * 32 + lane;
+    auto fetch = [&](int kb, int stage) {
+        const int k0 = kb * 32;
+        // K is a multiple of 8: a lane's 8 elements are all inside or all outside
+        const bool in = kb < kb_end && k0 + q * 8 < p.K;
+        uint4* dst = ring + stage * (2 + NT) * 32;
+        cp_async16(dst + 0 * 32, wa_p + (in ? k0 : 0), in);
+        cp_async16(dst + 1 * 32, wb_p + (in ? k0 : 0), in);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k0 = (kb + u * WARPS) * 32;
-            const bool in = k0 + q * 8 < K;      // K is a multiple of 8: a lane's 8 elements are all in or all out
-            wa[u] = in ? ld_stream(wa_p + k0) : zero;
-            wb[u] = in ? ld_stream(wb_p + k0) : zero;
+        for (int t = 0; t < NT; ++t) cp_async16(dst + (2 + t) * 32, x_p[t] + (in ? k0 : 0), in && x_ok[t]);
+    };
+    const int first = kb_begin + warp;
 #pragma unroll
-            for (int t = 0; t < NT; ++t)
-                xv[u][t] = (in && x_ok[t]) ? *reinterpret_cast<const uint4*>(x_p[t] + k0) : zero;
-        }
+    for (int s = 0; s < STAGES; ++s) {
+        fetch(first + s * WARPS, s);
+        cp_async_commit();
+    }
+    for (int kb = first, it = 0; kb < kb_end; kb += WARPS, ++it) {
+        cp_async_wait<STAGES - 1>();          // the oldest group, block kb, has landed
+        const int stage = it % STAGES;
+        const uint4* src = ring + stage * (2 + NT) * 32;
+        const uint4 wa = src[0 * 32], wb = src[1 * 32];
+        uint4 xv[NT];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int t = 0; t < NT; ++t) xv[t] = src[(2 + t) * 32];
+        fetch(kb + STAGES * WARPS, stage);    // refill the entry just read
+        cp_async_commit();
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                mma_bf16_16816(acc[t], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv[u][t].x, xv[u][t].y);
-                mma_bf16_16816(acc[t], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv[u][t].z, xv[u][t].w);
-            }
+        for (int t = 0; t < NT; ++t) {
+            mma_bf16_16816(acc[t], wa.x, wb.x, wa.y, wb.y, xv[t].x, xv[t].y);
+            mma_bf16_16816(acc[t], wa.z, wb.z, wa.w, wb.w, xv[t].z, xv[t].w);
         }
     }
+    cp_async_wait<0>();
     // c0, c1: (weight row g, batch q * 2 + {0, 1}); c2, c3: weight row g + 8
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -89,40 +164,36 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
         red[warp][g + 8][t * 8 + q * 2 + 1] = acc[t][3];
     }
     __syncthreads();
-    if (swiglu) {
-        // The weight's rows come in blocks of 16: 8 gate rows, then the 8 up rows of the same outputs.
-        // out[m, n0 / 2 + r] = silu(gate_r) * up_r: the activation is never written unfused.
-        for (int i = threadIdx.x; i < 8 * 8 * NT; i += WARPS * 32) {
-            const int r = i % 8, m = i / 8;
-            if (m >= M || n0 + 8 + r >= N) continue;
-            float gate = 0.0f, up = 0.0f;
-#pragma unroll
-            for (int wv = 0; wv < WARPS; ++wv) {
-                gate += red[wv][r][m];
-                up += red[wv][r + 8][m];
-            }
-            if (bias != nullptr) {
-                gate += bias[n0 + r];
-                up += bias[n0 + 8 + r];
-            }
-            out[(int64_t)m * ldo + (n0 >> 1) + r] = from_f32<TO>(gate / (1.0f + expf(-gate)) * up);
-        }
-        return;
-    }
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
-        const int r = i % ROWS, m = i / ROWS;       // neighbouring threads write neighbouring columns of out
-        const int n = n0 + r;
-        if (m >= M || n >= N) continue;
+        const int r = i / (8 * NT), m = i % (8 * NT);
         float v = 0.0f;
 #pragma unroll
         for (int wv = 0; wv < WARPS; ++wv) v += red[wv][r][m];
-        if (bias != nullptr) v += bias[n];
-        if (residual != nullptr) {
-            residual[(int64_t)m * ldo + n] += v;
-        } else {
-            out[(int64_t)m * ldo + n] = from_f32<TO>(v);
-        }
+        sum[r][m] = v;
     }
+    __syncthreads();
+    if (p.ksplit == 1) {
+        epilogue<NT, TO>(p, sum, n0);
+        return;
+    }
+    // ---- several K slices: leave this slice's partial, and let the last CTA to arrive add them all
+    float* mine = p.partials + ((int64_t)tile * p.ksplit + slice) * (ROWS * 8 * NT);
+    for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) mine[i] = sum[i / (8 * NT)][i % (8 * NT)];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&p.counters[tile], 1u) == (unsigned)p.ksplit - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    const float* all = p.partials + (int64_t)tile * p.ksplit * (ROWS * 8 * NT);
+    for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
+        float v = 0.0f;
+        for (int s = 0; s < p.ksplit; ++s) v += __ldcg(all + (int64_t)s * (ROWS * 8 * NT) + i);   // slice order
+        sum[i / (8 * NT)][i % (8 * NT)] = v;
+    }
+    if (threadIdx.x == 0) p.counters[tile] = 0;    // ready for the next call
+    __syncthreads();
+    epilogue<NT, TO>(p, sum, n0);
 }
 
 }  // namespace
@@ -131,11 +202,34 @@ XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
     return M >= 1 && M <= 16 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
 
+// How many K slices the kernel would like for this shape on a device with `sms` SMs, and the
+// scratch (bytes) that needs: partial sums, then one counter per row tile. 0 bytes when 1 slice.
+XS_API int xs_gemm_small_m_ksplit(int M, int N, int K, int sms) {
+    const int tiles = ceil_div_i(N, ROWS);
+    if (tiles >= 2 * sms || K < 2 * K_PER_CTA) return 1;
+    const int by_k = K / K_PER_CTA;
+    const int by_sm = ceil_div_i(4 * sms, tiles);
+    return by_k < by_sm ? (by_k < 1 ? 1 : by_k) : by_sm;
+}
+
+// Scratch layout: partial sums from the front; the last kCounterBytes hold one counter per row tile.
+constexpr int64_t kCounterBytes = 65536;
+
+XS_API int64_t xs_gemm_small_m_scratch_bytes(int M, int N, int ksplit) {
+    if (ksplit <= 1) return 0;
+    const int64_t tiles = ceil_div_i(N, ROWS);
+    const int nt = M <= 8 ? 1 : 2;
+    return tiles * ksplit * ROWS * 8 * nt * (int64_t)sizeof(float) + kCounterBytes;
+}
+
 // x, w bfloat16; out bfloat16 or float32 (out_dtype), or residual += when `residual` is given (float32, stride ldo).
 // swiglu != 0: w holds blocks of 8 gate rows and 8 up rows; out is [M, N / 2] = silu(gate) * up.
+// ksplit > 1 needs `scratch` of at least xs_gemm_small_m_scratch_bytes. Its last 64 KiB are the counters: zero
+// before the first call, and zero again whenever the kernel has run; a caller that keeps one buffer for all
+// shapes passes the whole buffer every time, so that the counters stay in the same place.
 XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void* out, float* residual, int out_dtype,
-                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
-                           cudaStream_t stream) {
+                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu, int ksplit,
+                           void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     XS_REQUIRE(xs_gemm_small_m_supports(M, K, ldx, ldw), "gemm (few rows): M %d, K %d, strides %lld, %lld not supported",
                M, K, (long long)ldx, (long long)ldw);
@@ -143,10 +237,39 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
     XS_REQUIRE(N > 0 && K > 0 && ldo >= (swiglu ? N / 2 : N) && (out != nullptr || residual != nullptr),
                "gemm (few rows): bad sizes");
     XS_REQUIRE(!swiglu || (N % 16 == 0 && residual == nullptr), "gemm (few rows): the fused activation needs N %% 16 == 0");
-    const int blocks = ceil_div_i(N, ROWS);
-    const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
-    const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-#define XS_GO(NT, TO) gemm_small_m_kernel<NT, TO><<<blocks, WARPS * 32, 0, stream>>>(xp, wp, bias, (TO*)out, residual, M, N, K, ldx, ldw, ldo, swiglu)
+    XS_REQUIRE(ksplit >= 1 && ksplit <= 64, "gemm (few rows): %d K slices", ksplit);
+    const int tiles = ceil_div_i(N, ROWS);
+    SmallMParams p;
+    p.x = (const __nv_bfloat16*)x;
+    p.w = (const __nv_bfloat16*)w;
+    p.bias = bias;
+    p.out = out;
+    p.residual = residual;
+    p.partials = nullptr;
+    p.counters = nullptr;
+    p.M = M; p.N = N; p.K = K; p.ksplit = ksplit; p.swiglu = swiglu;
+    p.ldx = ldx; p.ldw = ldw; p.ldo = ldo;
+    if (ksplit > 1) {
+        const int64_t need = xs_gemm_small_m_scratch_bytes(M, N, ksplit);
+        XS_REQUIRE(scratch != nullptr && scratch_bytes >= need && (uintptr_t)scratch % 16 == 0 && scratch_bytes % 16 == 0,
+                   "gemm (few rows): %lld bytes of scratch needed for %d K slices, %lld given", (long long)need, ksplit,
+                   (long long)scratch_bytes);
+        XS_REQUIRE((int64_t)tiles * (int64_t)sizeof(unsigned int) <= kCounterBytes, "gemm (few rows): %d row tiles", tiles);
+        p.partials = (float*)scratch;
+        p.counters = (unsigned int*)((char*)scratch + scratch_bytes - kCounterBytes);
+    }
+    const dim3 grid(tiles, ksplit);
+#define XS_GO(NT, TO)                                                                                        \
+    do {                                                                                                     \
+        const size_t smem = (size_t)WARPS * 32 * STAGES * (2 + NT) * sizeof(uint4);                          \
+        static bool opted = false;                                                                           \
+        if (!opted) {                                                                                        \
+            cudaFuncSetAttribute(gemm_small_m_kernel<NT, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 (int)smem);                                                                 \
+            opted = true;                                                                                    \
+        }                                                                                                    \
+        gemm_small_m_kernel<NT, TO><<<grid, WARPS * 32, smem, stream>>>(p);                                  \
+    } while (0)
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
     } else if (out_dtype == XS_BF16) {

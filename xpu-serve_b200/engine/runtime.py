@@ -61,6 +61,7 @@ class Runtime:
         self.small_m = 16     # products with at most this many rows use this library's streaming kernel
         ops.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
 
     # -------------------------------------------------------------- weights
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
@@ -77,6 +78,15 @@ class Runtime:
         return (self.mode == "bfloat16" and x.shape[0] <= self.small_m
                 and ops.gemm_small_m_supports(x.shape[0], x.shape[1], x.stride(0), w.stride(0)))
 
+    def few_rows_product(self, x, w, out, bias=None, swiglu: bool = False) -> None:
+        """The library's weight-streaming product, with K cut over several CTAs where the output is
+        narrow; the partial sums meet in one zero-initialised scratch buffer that lives as long as
+        the runtime (its tail holds the kernel's counters)."""
+        ksplit = ops.gemm_small_m_ksplit(x.shape[0], w.shape[0], x.shape[1], self.sm_count)
+        if ksplit > 1 and ops.gemm_small_m_scratch_bytes(x.shape[0], w.shape[0], ksplit) > self.gemm_scratch.numel():
+            ksplit = 1
+        ops.gemm_small_m(x, w, out, bias, swiglu=swiglu, ksplit=ksplit, scratch=self.gemm_scratch if ksplit > 1 else None)
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`."""
@@ -86,7 +96,7 @@ class Runtime:
         if self.mode == "float32":
             ops.gemm_generic(x, w, out, bias)
         elif self.few_rows(x, w):
-            ops.gemm_small_m(x, w, out, bias)
+            self.few_rows_product(x, w, out, bias)
         elif bias is not None:
             ops.gemm_generic(x, w, out, bias)
         elif out_dtype == torch.float32:

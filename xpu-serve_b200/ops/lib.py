@@ -39,7 +39,7 @@ def _signatures(lib) -> None:
         "xs_attention_generic": [P, P, P, I, P, P, P, L, P, I, I, I, I, I, F, I, I, P],
         "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
-        "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, P],
+        "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P],
         "xs_argmax": [P, L, I, I, P, P, P],
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
@@ -60,6 +60,10 @@ def _signatures(lib) -> None:
     lib.xs_attention_mma_supports.argtypes = [c_int, c_int, c_int]
     lib.xs_gemm_small_m_supports.restype = c_int
     lib.xs_gemm_small_m_supports.argtypes = [c_int, c_int, c_int64, c_int64]
+    lib.xs_gemm_small_m_ksplit.restype = c_int
+    lib.xs_gemm_small_m_ksplit.argtypes = [c_int, c_int, c_int, c_int]
+    lib.xs_gemm_small_m_scratch_bytes.restype = c_int64
+    lib.xs_gemm_small_m_scratch_bytes.argtypes = [c_int, c_int, c_int]
 
 
 def load(verbose: bool = True):
@@ -266,10 +270,22 @@ def gemm_small_m_supports(M: int, K: int, ldx: int, ldw: int) -> bool:
     return bool(load().xs_gemm_small_m_supports(M, K, ldx, ldw))
 
 
+def gemm_small_m_ksplit(M: int, N: int, K: int, sms: int) -> int:
+    """The number of K slices the kernel prefers for this shape on a device with `sms` SMs."""
+    return int(load().xs_gemm_small_m_ksplit(M, N, K, sms))
+
+
+def gemm_small_m_scratch_bytes(M: int, N: int, ksplit: int) -> int:
+    return int(load().xs_gemm_small_m_scratch_bytes(M, N, ksplit))
+
+
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
-                 residual: Optional[torch.Tensor] = None, swiglu: bool = False) -> None:
+                 residual: Optional[torch.Tensor] = None, swiglu: bool = False, ksplit: int = 1,
+                 scratch: Optional[torch.Tensor] = None) -> None:
     """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product;
-    or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows."""
+    or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows.
+    ksplit > 1 cuts K over several CTAs; `scratch` is then a zero-initialised byte buffer of at least
+    gemm_small_m_scratch_bytes, kept (whole) from call to call."""
     for t, name in ((x, "x"), (w, "w")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
             raise KernelError(f"gemm (few rows): {name} must be a bfloat16 CUDA matrix with contiguous rows")
@@ -285,7 +301,8 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         _need(bias, "bias", torch.float32)
     _check(load().xs_gemm_small_m(x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual),
                                   F32 if out is None else _code(out), M, N, K, x.stride(0), w.stride(0),
-                                  target.stride(0), 1 if swiglu else 0, _stream()))
+                                  target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
+                                  0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()))
 
 
 def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,

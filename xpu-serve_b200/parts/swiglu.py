@@ -41,7 +41,7 @@ class SwiGLU(FeedForward):
         rt, F = self.rt, self.spec.intermediate
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
         if self.interleave and rt.few_rows(y, self.w_gate_up):
-            ops.gemm_small_m(y, self.w_gate_up, act, swiglu=True)
+            rt.few_rows_product(y, self.w_gate_up, act, swiglu=True)
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
             ops.silu_mul(gu, act, self.interleave)
