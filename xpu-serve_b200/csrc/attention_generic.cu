@@ -21,6 +21,8 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, int64_t ld,
                                           const int32_t* __restrict__ positions, const float* __restrict__ q_w,
                                           const float* __restrict__ k_w, const float2* __restrict__ rope, int Tn,
                                           int Hq, int Hkv, int D, int page_size, float eps, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int heads_total = Hq + (write_kv ? 2 * Hkv : 0);
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (int64_t)Tn * heads_total) return;
@@ -99,6 +101,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          int64_t ld_gate, T* __restrict__ out, int Tn, int Hq, int Hkv, int D,
                                          int page_size, float scale, int window) {
     extern __shared__ float q_sm[];   // [warps][D]
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (item >= (int64_t)Tn * Hq) return;
@@ -175,7 +179,7 @@ XS_API int xs_qk_norm_rope_store(const void* qkv, int64_t ld, void* q_out, void*
     const int64_t items = (int64_t)T * (Hq + (write_kv ? 2 * Hkv : 0));
     const int blocks = ceil_div_i(items, 4);
     XS_DISPATCH_DTYPE(dtype, TT,
-                      qk_norm_rope_store_kernel<TT><<<blocks, 128, 0, stream>>>(
+                      xs_launch(qk_norm_rope_store_kernel<TT>, dim3(blocks), dim3(128), 0, stream,
                           (const TT*)qkv, ld, (TT*)q_out, (TT*)pool, page_table, P, seq_of_token, positions, q_w,
                           k_w, (const float2*)rope, T, Hq, Hkv, D, page_size, eps, write_kv));
     XS_LAUNCH_CHECK("qk_norm_rope_store");

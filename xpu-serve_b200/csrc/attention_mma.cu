@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
     __nv_bfloat16* k_sm = q_sm + BM * LD;            // [2][BN][LD]
     __nv_bfloat16* v_sm = k_sm + 2 * BN * LD;        // [2][BN][LD]
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tile = blockIdx.x, seq = blockIdx.y;
     const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
     const int tok_begin = p.cu_seqlens[seq];
@@ -273,6 +275,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
                                          __nv_bfloat16* __restrict__ out, int64_t rows, int Hq, int D, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -304,7 +308,7 @@ int launch(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t stream) 
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const dim3 grid(max_tiles, n_seqs, p.Hkv * p.splits);
-    attention_mma_kernel<D><<<grid, NTHREADS, smem, stream>>>(p);
+    xs_launch(attention_mma_kernel<D>, grid, dim3(NTHREADS), smem, stream, p);
     return 0;
 }
 
@@ -368,8 +372,8 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
     XS_LAUNCH_CHECK("attention_mma");
     if (splits > 1) {
         const int64_t rows = (int64_t)T * Hq;
-        attention_combine_kernel<<<ceil_div_i(rows, 4), 128, 0, stream>>>(p.part_o, p.part_ml, p.gate, ld_gate, p.out,
-                                                                         rows, Hq, D, splits);
+        xs_launch(attention_combine_kernel, dim3(ceil_div_i(rows, 4)), dim3(128), 0, stream, (const float*)p.part_o,
+                  (const float*)p.part_ml, p.gate, ld_gate, p.out, rows, Hq, D, splits);
         XS_LAUNCH_CHECK("attention_combine");
     }
     return 0;

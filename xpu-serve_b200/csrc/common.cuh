@@ -83,3 +83,32 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int ceil_div_i(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A decode step is a chain of some 150 short kernels, each waiting for the one before it. Launched
+// with the attribute below, a kernel may start while its predecessor is still draining: it runs up
+// to pdl_wait() (address arithmetic, and in the few-row product the first weight loads, which
+// depend on nothing), and only there waits until the predecessor has completed and its writes are
+// visible. Rules every kernel here keeps: nothing that another kernel of the step writes is read,
+// and nothing at all is written to global memory, before pdl_wait(). Without the attribute both
+// calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+
+extern int g_xs_pdl;   // 1: launches carry the attribute (xs_set_pdl)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t xs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_xs_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

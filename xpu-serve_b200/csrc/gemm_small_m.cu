@@ -3,14 +3,11 @@
 // The weight is read exactly once, straight from HBM into registers with 16-byte loads, and
 // never staged: with M this small the product is bound by weight bandwidth. A CTA of 8 warps
 // owns 16 weight rows and a slice of K; its warps take the slice's 32-wide k blocks in turn
-// (warp w: blocks w, w+8, ...). Each lane keeps eight blocks' worth of its own 16-byte pieces
-// in flight with cp.async into a private ring in shared memory (a lane reads back only what it
-// copied itself, so cp.async.wait_group is all the synchronisation the ring needs); the
-// compiler cannot shorten that queue the way it does with loads into registers. Warps
-// multiply on tensor cores (mma.sync m16n8k16: weight rows on the M side, the batch on the N
-// side) and add their partial sums in shared memory in warp order. A lane's 16 bytes are 8
-// consecutive k of one row; the same assignment of k to fragment slots is used for the
-// weight and for x, which is all a contraction needs.
+// (warp w: blocks w, w+8, ...), four blocks' loads issued together. They multiply on tensor
+// cores (mma.sync m16n8k16: weight rows on the M side, the batch on the N side) and add their
+// partial sums in shared memory in warp order. A lane's 16 bytes are 8 consecutive k of one
+// row; the same assignment of k to fragment slots is used for the weight and for x, which is
+// all a contraction needs.
 //
 // Narrow outputs with a long K (the feed-forward's down projection) would leave most SMs
 // idle, so K is cut into `ksplit` slices over blockIdx.y. Each slice's CTA writes its 16 x M
@@ -28,8 +25,8 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int ROWS = 16;      // weight rows per CTA
-constexpr int STAGES = 8;     // k blocks a warp keeps in flight
-constexpr int K_PER_CTA = WARPS * STAGES * 32;   // a K slice this long is one round of loads per warp
+constexpr int UNROLL = 4;     // k blocks whose loads a warp issues together
+constexpr int K_PER_CTA = WARPS * UNROLL * 32;   // a K slice this long is one round of loads per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                                unsigned b0, unsigned b1) {
@@ -38,15 +35,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// 16 bytes global -> shared, bypassing L1 (weights are used once); `valid` false writes zeros.
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    const int bytes = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+__device__ __forceinline__ uint4 ld_stream(const void* p) {   // weights are used once: do not keep them in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 struct SmallMParams {
     const __nv_bfloat16* x;
@@ -118,43 +112,48 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_small_m_kernel(const SmallMPa
     const int k_blocks = (p.K + 31) / 32;
     const int per_slice = (k_blocks + p.ksplit - 1) / p.ksplit;
     const int kb_begin = slice * per_slice, kb_end = min(k_blocks, kb_begin + per_slice);
-    // this warp's ring: STAGES entries of (2 + NT) pieces; a piece is 32 lanes x 16 bytes, lane-major,
-    // so a warp's access to one piece covers 512 consecutive bytes (no bank conflicts)
-    extern __shared__ __align__(16) uint4 ring_all[];
-    uint4* ring = ring_all + (size_t)warp * STAGES * (2 + NT) * 32 + lane;
-    auto fetch = [&](int kb, int stage) {
-        const int k0 = kb * 32;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    // The first round of weight loads depends on no other kernel: it is issued before pdl_wait(), so
+    // that the weights are already on their way while the previous kernel of the step finishes.
+    pdl_launch_dependents();
+    uint4 wa[UNROLL], wb[UNROLL];
+    int kb = kb_begin + warp;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int k0 = (kb + u * WARPS) * 32;
         // K is a multiple of 8: a lane's 8 elements are all inside or all outside
-        const bool in = kb < kb_end && k0 + q * 8 < p.K;
-        uint4* dst = ring + stage * (2 + NT) * 32;
-        cp_async16(dst + 0 * 32, wa_p + (in ? k0 : 0), in);
-        cp_async16(dst + 1 * 32, wb_p + (in ? k0 : 0), in);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) cp_async16(dst + (2 + t) * 32, x_p[t] + (in ? k0 : 0), in && x_ok[t]);
-    };
-    const int first = kb_begin + warp;
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-        fetch(first + s * WARPS, s);
-        cp_async_commit();
+        const bool in = kb + u * WARPS < kb_end && k0 + q * 8 < p.K;
+        wa[u] = in ? ld_stream(wa_p + k0) : zero;
+        wb[u] = in ? ld_stream(wb_p + k0) : zero;
     }
-    for (int kb = first, it = 0; kb < kb_end; kb += WARPS, ++it) {
-        cp_async_wait<STAGES - 1>();          // the oldest group, block kb, has landed
-        const int stage = it % STAGES;
-        const uint4* src = ring + stage * (2 + NT) * 32;
-        const uint4 wa = src[0 * 32], wb = src[1 * 32];
-        uint4 xv[NT];
+    pdl_wait();
+    for (; kb < kb_end; kb += WARPS * UNROLL) {
+        uint4 xv[UNROLL][NT];
 #pragma unroll
-        for (int t = 0; t < NT; ++t) xv[t] = src[(2 + t) * 32];
-        fetch(kb + STAGES * WARPS, stage);    // refill the entry just read
-        cp_async_commit();
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k0 = (kb + u * WARPS) * 32;
+            const bool in = kb + u * WARPS < kb_end && k0 + q * 8 < p.K;
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            mma_bf16_16816(acc[t], wa.x, wb.x, wa.y, wb.y, xv[t].x, xv[t].y);
-            mma_bf16_16816(acc[t], wa.z, wb.z, wa.w, wb.w, xv[t].z, xv[t].w);
+            for (int t = 0; t < NT; ++t)
+                xv[u][t] = (in && x_ok[t]) ? *reinterpret_cast<const uint4*>(x_p[t] + k0) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                mma_bf16_16816(acc[t], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv[u][t].x, xv[u][t].y);
+                mma_bf16_16816(acc[t], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv[u][t].z, xv[u][t].w);
+            }
+        }
+        const int nkb = kb + WARPS * UNROLL;      // the next round's weights
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k0 = (nkb + u * WARPS) * 32;
+            const bool in = nkb + u * WARPS < kb_end && k0 + q * 8 < p.K;
+            wa[u] = in ? ld_stream(wa_p + k0) : zero;
+            wb[u] = in ? ld_stream(wb_p + k0) : zero;
         }
     }
-    cp_async_wait<0>();
     // c0, c1: (weight row g, batch q * 2 + {0, 1}); c2, c3: weight row g + 8
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -205,11 +204,14 @@ XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
 // How many K slices the kernel would like for this shape on a device with `sms` SMs, and the
 // scratch (bytes) that needs: partial sums, then one counter per row tile. 0 bytes when 1 slice.
 XS_API int xs_gemm_small_m_ksplit(int M, int N, int K, int sms) {
+    // Measured on B200 inside a CUDA graph (M 8): N 2048, K 8192 takes 24.5 us in one slice, 15.9 in two,
+    // 11.4 in four; N 2048, K 2048 takes 7.4, 7.0, 6.1; N 16384, K 2048 gets slower with every slice.
+    (void)M;
     const int tiles = ceil_div_i(N, ROWS);
-    if (tiles >= 2 * sms || K < 2 * K_PER_CTA) return 1;
-    const int by_k = K / K_PER_CTA;
-    const int by_sm = ceil_div_i(4 * sms, tiles);
-    return by_k < by_sm ? (by_k < 1 ? 1 : by_k) : by_sm;
+    if (tiles >= 2 * sms) return 1;
+    int ks = K / 512;                 // at least 512 of K a slice
+    if (ks > 4) ks = 4;
+    return ks < 1 ? 1 : ks;
 }
 
 // Scratch layout: partial sums from the front; the last kCounterBytes hold one counter per row tile.
@@ -259,17 +261,7 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
         p.counters = (unsigned int*)((char*)scratch + scratch_bytes - kCounterBytes);
     }
     const dim3 grid(tiles, ksplit);
-#define XS_GO(NT, TO)                                                                                        \
-    do {                                                                                                     \
-        const size_t smem = (size_t)WARPS * 32 * STAGES * (2 + NT) * sizeof(uint4);                          \
-        static bool opted = false;                                                                           \
-        if (!opted) {                                                                                        \
-            cudaFuncSetAttribute(gemm_small_m_kernel<NT, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                 (int)smem);                                                                 \
-            opted = true;                                                                                    \
-        }                                                                                                    \
-        gemm_small_m_kernel<NT, TO><<<grid, WARPS * 32, smem, stream>>>(p);                                  \
-    } while (0)
+#define XS_GO(NT, TO) xs_launch(gemm_small_m_kernel<NT, TO>, grid, dim3(WARPS * 32), 0, stream, p)
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
     } else if (out_dtype == XS_BF16) {

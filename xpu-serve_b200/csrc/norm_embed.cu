@@ -20,13 +20,24 @@ void xs_set_error(const char* fmt, ...) {
 
 XS_API const char* xs_last_error() { return g_error; }
 
-XS_API int xs_abi_version() { return 3; }
+XS_API int xs_abi_version() { return 4; }
+
+int g_xs_pdl = 1;
+// 1: kernels of a step may overlap their start with the previous kernel's end (programmatic
+// dependent launch); 0: plain stream order. Returns the previous setting.
+XS_API int xs_set_pdl(int on) {
+    const int old = g_xs_pdl;
+    g_xs_pdl = on ? 1 : 0;
+    return old;
+}
 
 // ------------------------------------------------------------------ embedding
 // h[t, :] = table[ids[t], :] as float32 (no scaling: src/models/lfm3/lfm3_decoder.cpp:50).
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int32_t* __restrict__ ids,
                              float* __restrict__ h, int T, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const TW* row = table + (int64_t)ids[t] * H;
     float* out = h + (int64_t)t * H;
@@ -38,7 +49,7 @@ XS_API int xs_embed(const void* table, int table_dtype, const int32_t* ids, floa
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && H > 0, "embed: %d tokens of width %d", T, H);
     XS_DISPATCH_DTYPE(table_dtype, TW,
-                      embed_kernel<TW><<<T, 256, 0, stream>>>((const TW*)table, ids, h, T, H));
+                      xs_launch(embed_kernel<TW>, dim3(T), dim3(256), 0, stream, (const TW*)table, ids, h, T, H));
     XS_LAUNCH_CHECK("embed");
     return 0;
 }
@@ -56,6 +67,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TM* __restrict__
                                    TY* __restrict__ y, const int32_t* __restrict__ rows, int H, float eps_post, float eps) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x;
     const int64_t r = rows ? rows[i] : i;
     float* hr = h + r * H;
@@ -129,6 +142,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TM* __restri
                                        TY* __restrict__ y, const int32_t* __restrict__ rows, int H, float eps_post,
                                        float eps) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x;
     const int64_t r = rows ? rows[i] : i;
     float* hr = h + r * H;
@@ -204,8 +219,8 @@ XS_API int xs_add_rmsnorm(float* h, const void* m, int m_dtype, const float* pos
         const int threads = chunks <= 128 ? 128 : chunks <= 1024 ? 256 : chunks <= 2048 ? 512 : 1024;
         const int nv = (chunks + threads - 1) / threads;
 #define XS_VEC(TM, TY, NV)                                                                                          \
-    add_rmsnorm_vec_kernel<TM, TY, NV><<<n_rows, threads, 0, stream>>>(h, (const TM*)m, post_w, w, (TY*)y, rows, H, \
-                                                                       eps_post, eps)
+    xs_launch(add_rmsnorm_vec_kernel<TM, TY, NV>, dim3(n_rows), dim3(threads), 0, stream, h, (const TM*)m, post_w, \
+              w, (TY*)y, rows, H, eps_post, eps)
 #define XS_VEC_NV(TM, TY)                       \
     do {                                        \
         if (nv <= 1) XS_VEC(TM, TY, 1);         \
@@ -225,8 +240,8 @@ XS_API int xs_add_rmsnorm(float* h, const void* m, int m_dtype, const float* pos
         if (smem > 48 * 1024)                                                                            \
             cudaFuncSetAttribute(add_rmsnorm_kernel<TM, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem);                                                             \
-        add_rmsnorm_kernel<TM, TY><<<n_rows, threads, smem, stream>>>(h, (const TM*)m, post_w, w, (TY*)y, \
-                                                                      rows, H, eps_post, eps);           \
+        xs_launch(add_rmsnorm_kernel<TM, TY>, dim3(n_rows), dim3(threads), smem, stream, h, (const TM*)m, \
+                  post_w, w, (TY*)y, rows, H, eps_post, eps);                                            \
     } while (0)
     XS_DISPATCH_DTYPE(m_dtype, TM, XS_DISPATCH_DTYPE(y_dtype, TY, XS_GO(TM, TY)));
 #undef XS_GO
@@ -245,6 +260,8 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g));
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int F, int64_t ld,
                                 int interleave) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = i / F;
         const int f = (int)(i - t * F);
@@ -257,6 +274,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // 8 outputs a thread, 16-byte loads and stores; F a multiple of 8, rows 16-byte aligned.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                        int64_t total8, int F8, int64_t ld, int interleave) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = i / F8;
         const int j = (int)(i - t * F8);
@@ -284,14 +303,14 @@ XS_API int xs_silu_mul(const void* gu, void* out, int dtype, int T, int F, int64
     if (dtype == XS_BF16 && F % 8 == 0 && ld % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
         const int64_t total8 = (int64_t)T * (F / 8);
         const int blocks = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
-        silu_mul_bf16x8_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total8, F / 8,
-                                                           ld, interleave);
+        xs_launch(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                  (__nv_bfloat16*)out, total8, F / 8, ld, interleave);
         XS_LAUNCH_CHECK("silu_mul");
         return 0;
     }
     const int64_t total = (int64_t)T * F;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    XS_DISPATCH_DTYPE(dtype, TT, silu_mul_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, (TT*)out, total, F, ld, interleave));
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(silu_mul_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total, F, ld, interleave));
     XS_LAUNCH_CHECK("silu_mul");
     return 0;
 }

@@ -95,6 +95,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int 
 __global__ void argmax_part_kernel(const float* __restrict__ logits, int64_t ld, int V, int parts,
                                    unsigned long long* __restrict__ packed) {
     __shared__ ArgBest scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.y, part = blockIdx.x;
     const int per = (V + parts - 1) / parts;
     const int begin = min(V, part * per), count = min(V, begin + per) - begin;
@@ -108,6 +110,8 @@ __global__ void argmax_part_kernel(const float* __restrict__ logits, int64_t ld,
     }
 }
 __global__ void argmax_finish_kernel(unsigned long long* __restrict__ packed, int n, int32_t* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     out[i] = (int32_t)(0xFFFFFFFFu - (unsigned)(packed[i] & 0xFFFFFFFFull));
@@ -302,8 +306,8 @@ XS_API int xs_argmax(const float* logits, int64_t ld, int n, int V, int32_t* out
     XS_REQUIRE(n > 0 && V > 0 && ld >= V, "argmax: %d rows of %d", n, V);
     if (V >= 16384 && n <= 65535 && packed != nullptr) {
         const int parts = min(32, V / 4096);
-        argmax_part_kernel<<<dim3(parts, n), 256, 0, stream>>>(logits, ld, V, parts, packed);
-        argmax_finish_kernel<<<ceil_div_i(n, 128), 128, 0, stream>>>(packed, n, out);
+        xs_launch(argmax_part_kernel, dim3(parts, n), dim3(256), 0, stream, logits, ld, V, parts, packed);
+        xs_launch(argmax_finish_kernel, dim3(ceil_div_i(n, 128)), dim3(128), 0, stream, packed, n, out);
         XS_LAUNCH_CHECK("argmax");
         return 0;
     }

@@ -25,6 +25,8 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, int64_t ld, const f
                                   const float* __restrict__ bias, const T* __restrict__ state,
                                   const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ cu_seqlens,
                                   const int32_t* __restrict__ slots, T* __restrict__ out, int Tn, int H, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)Tn * H) return;
     const int t = (int)(idx / H), c = (int)(idx % H);
@@ -47,6 +49,8 @@ template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, int64_t ld, T* __restrict__ state,
                                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
                                         int n_seqs, int H, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)n_seqs * H) return;
     const int seq = (int)(idx / H), c = (int)(idx % H);
@@ -92,6 +96,8 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
                                          const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ cu_seqlens,
                                          const int32_t* __restrict__ slots, __nv_bfloat16* __restrict__ out, int Tn, int H,
                                          int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int H8 = H >> 3;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)Tn * H8) return;
@@ -128,6 +134,8 @@ __global__ void short_conv_decode_bf16x8_kernel(const __nv_bfloat16* __restrict_
                                                 const float* __restrict__ w_t, const float* __restrict__ bias,
                                                 __nv_bfloat16* __restrict__ state, const int32_t* __restrict__ slots,
                                                 __nv_bfloat16* __restrict__ out, int n_seqs, int H, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int H8 = H >> 3;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)n_seqs * H8) return;
@@ -175,8 +183,8 @@ XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const fl
     const bool vec = dtype == XS_BF16 && H % 8 == 0 && ld % 8 == 0 && (uintptr_t)bcx % 16 == 0 &&
                      (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w_t % 16 == 0;
     if (vec && all_single) {
-        short_conv_decode_bf16x8_kernel<<<ceil_div_i((int64_t)n_seqs * (H / 8), 128), 128, 0, stream>>>(
-            (const __nv_bfloat16*)bcx, ld, w_t, bias, (__nv_bfloat16*)state, slots, (__nv_bfloat16*)out, n_seqs, H, K);
+        xs_launch(short_conv_decode_bf16x8_kernel, dim3(ceil_div_i((int64_t)n_seqs * (H / 8), 128)), dim3(128), 0, stream,
+                  (const __nv_bfloat16*)bcx, ld, w_t, bias, (__nv_bfloat16*)state, slots, (__nv_bfloat16*)out, n_seqs, H, K);
         XS_LAUNCH_CHECK("short_conv_decode");
         return 0;
     }
