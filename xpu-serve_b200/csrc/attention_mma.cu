@@ -378,3 +378,44 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
     }
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same operation for callers that cannot allocate (xs_no_alloc.h): the scratch for the partial
+// results is a device array that is part of the library image.
+#include "xs_no_alloc.h"
+
+namespace {
+constexpr int64_t kScratchBytes = 8ll * 1024 * 1024;
+constexpr int kMaxDevices = 64;
+// In host code this name is only a handle for the runtime, not a device address; the address that
+// kernels may use comes from cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[kScratchBytes];
+void* g_static_scratch_ptr[kMaxDevices] = {};
+}  // namespace
+
+XS_API int64_t xs_attention_mma_static_capacity(void) { return kScratchBytes; }
+
+XS_API int xs_attention_mma_static(const void* q, const void* pool, const int32_t* page_table, int P,
+                                   const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate,
+                                   int64_t ld_gate, void* out, int T, int n_seqs, int max_q_len, int Hq, int Hkv,
+                                   int D, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    XS_REQUIRE(T >= 0 && Hq > 0 && D > 0 && splits >= 1, "attention (built-in scratch): bad sizes");
+    const int64_t need = xs_attention_mma_scratch_bytes((int64_t)T * Hq, D, splits);
+    XS_REQUIRE(need <= kScratchBytes,
+               "attention (built-in scratch): %d tokens x %d heads x %d splits need %lld bytes of scratch, the "
+               "built-in array holds %lld; use fewer splits or xs_attention_mma with a buffer of your own",
+               T, Hq, splits, (long long)need, (long long)kScratchBytes);
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    XS_REQUIRE(e == cudaSuccess && device >= 0 && device < kMaxDevices, "attention (built-in scratch): no usable current device (%s)",
+               cudaGetErrorString(e));
+    if (g_static_scratch_ptr[device] == nullptr) {   // first call on this device: not inside a stream capture
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        XS_REQUIRE(e == cudaSuccess && ptr != nullptr, "attention (built-in scratch): cudaGetSymbolAddress failed: %s",
+                   cudaGetErrorString(e));
+        g_static_scratch_ptr[device] = ptr;
+    }
+    return xs_attention_mma(q, pool, page_table, P, cu_seqlens, kv_lens, gate, ld_gate, out, g_static_scratch_ptr[device],
+                            kScratchBytes, T, n_seqs, max_q_len, Hq, Hkv, D, page_size, scale, window, splits, stream);
+}
