@@ -129,22 +129,27 @@ def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window:
 
 
 def self_attention(x: np.ndarray, W: Dict[str, np.ndarray], L: str, Hq: int, Hkv: int, D: int, eps: float,
-                   inv_freq: np.ndarray, window: int, head_gate: bool) -> np.ndarray:
+                   inv_freq: np.ndarray, window: int, head_gate: bool, shared_kv=None, return_kv: bool = False):
     """q/k projections -> per-head norms -> RoPE; v raw; attention; sigmoid head gate; o_proj
-    (src/models/common/blocks.cpp:143-187; src/models/lfm3/lfm3_decoder.cpp:114-141)."""
+    (src/models/common/blocks.cpp:143-187; src/models/lfm3/lfm3_decoder.cpp:114-141). With
+    `shared_kv` = (k, v) of another call, only q is computed here (blocks.cpp:165-167)."""
     T = x.shape[0]
     pos = np.arange(T)
     A = L + "self_attn."
     q = (x @ W[A + "q_proj.weight"].T).reshape(T, Hq, D)
-    k = (x @ W[A + "k_proj.weight"].T).reshape(T, Hkv, D)
-    v = (x @ W[A + "v_proj.weight"].T).reshape(T, Hkv, D)
     q = rope(rms_norm(q, W[A + "q_norm.weight"], eps), pos, inv_freq)
-    k = rope(rms_norm(k, W[A + "k_norm.weight"], eps), pos, inv_freq)
+    if shared_kv is not None:
+        k, v = shared_kv
+    else:
+        k = (x @ W[A + "k_proj.weight"].T).reshape(T, Hkv, D)
+        v = (x @ W[A + "v_proj.weight"].T).reshape(T, Hkv, D)
+        k = rope(rms_norm(k, W[A + "k_norm.weight"], eps), pos, inv_freq)
     o = attention(q, k, v, 1.0 / math.sqrt(D), window)
     if head_gate:
         z = x @ W[A + "gate_proj.weight"].T
         o = o * (1.0 / (1.0 + np.exp(-z)))[:, :, None]
-    return o.reshape(T, Hq * D) @ W[A + "o_proj.weight"].T
+    out = o.reshape(T, Hq * D) @ W[A + "o_proj.weight"].T
+    return (out, (k, v)) if return_kv else out
 
 
 def swiglu(y: np.ndarray, W: Dict[str, np.ndarray], L: str) -> np.ndarray:

@@ -1,0 +1,384 @@
+"""Each part alone against the plain functions; a toy mixer with a state of its own, defined here,
+registered, built and stepped without touching the framework; a running order that names a layer
+twice and lets a layer read another layer's cache; long decoding; the first tokens of a sequence."""
+import math
+from dataclasses import dataclass, field, replace
+from typing import Dict
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def gap_of(got, ref):
+    got = got.detach().double().cpu().numpy() if torch.is_tensor(got) else np.asarray(got, dtype=np.float64)
+    assert np.isfinite(got).all()
+    return np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+class Harness:
+    """A runtime, a cache for one layer call, and steps over a ragged batch."""
+
+    def __init__(self, dtype, need):
+        from xpu_serve_b200.cache import Cache
+        from xpu_serve_b200.engine.runtime import Runtime
+        from xpu_serve_b200.engine.step import StepStager
+        self.rt = Runtime(dtype)
+        self.cache = Cache([need], [None], 2048, dtype=self.rt.act_dtype, device=self.rt.device)
+        self.stager = StepStager(self.rt.device)
+        self.dtype = dtype
+
+    def run(self, part_forward, xs, cuts, input_dtype=None):
+        """xs: list of [T_i, H] float64 inputs; cuts: per step, how many tokens of each sequence.
+        Inputs are given in the activation type unless `input_dtype` says otherwise. Returns the
+        outputs joined per sequence."""
+        n = len(xs)
+        slots = self.cache.open(n)
+        outs = [[] for _ in range(n)]
+        at = [0] * n
+        for step in cuts:
+            part = [i for i in range(n) if step[i] > 0]
+            lens = [step[i] for i in part]
+            starts = self.cache.begin_step([slots[i] for i in part], lens)
+            ctx = self.stager.stage(self.cache, [slots[i] for i in part], [[0] * q for q in lens], [[] for _ in part], starts)
+            x = np.concatenate([xs[i][at[i]:at[i] + q] for i, q in zip(part, lens)], 0)
+            xt = torch.tensor(x, device=self.rt.device).to(input_dtype or self.rt.act_dtype)
+            y = part_forward(xt, ctx, self.cache.views[0]).detach().double().cpu().numpy()
+            self.cache.end_step([slots[i] for i in part], lens)
+            o = 0
+            for i, q in zip(part, lens):
+                outs[i].append(y[o:o + q].copy())
+                at[i] += q
+                o += q
+        self.cache.close(slots)
+        self.cache.check()
+        return [np.concatenate(o, 0) for o in outs]
+
+
+def weights_for(part_cls, spec, seed, dtype, scale=None):
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, ts in part_cls.tensors(spec).items():
+        if ts.role == "vector":
+            t = torch.rand(ts.shape, generator=g) + 0.5
+        else:
+            t = torch.randn(ts.shape, generator=g) / math.sqrt(ts.shape[-1]) * ((scale or {}).get(name.split(".")[-2], 1.0))
+            t = t.to(TORCH[dtype]).float()       # both sides see the same, representable weights
+        out[name] = t
+    return out
+
+
+def as_plain(weights, prefix):
+    return {prefix + k: v.double().numpy() for k, v in weights.items()}
+
+
+CUTS = [[5, 70, 0], [1, 1, 9], [1, 0, 1], [3, 2, 1]]      # prompts of unequal lengths, a late joiner, decoding
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,D,window,gate,pairs", [(4, 2, 16, 0, False, 8), (6, 3, 48, 11, True, 10), (8, 2, 64, 0, True, 32)])
+def test_attention_mixer_alone(dtype, Hq, Hkv, D, window, gate, pairs):
+    from xpu_serve_b200.config.spec import AttentionSpec, RopeSpec
+    from xpu_serve_b200.parts import AttentionMixer
+    H = 72
+    spec = AttentionSpec(hidden=H, heads=Hq, kv_heads=Hkv, head_dim=D, qk_norm=True, qk_norm_eps=1e-6,
+                         position=RopeSpec(D, 300.0, pairs), window=window, head_gate=gate, scale=1.0 / math.sqrt(D))
+    w = weights_for(AttentionMixer, spec, 1, dtype, scale={"q_proj": 4.0, "k_proj": 4.0})
+    hs = Harness(dtype, AttentionMixer.cache_need(spec))
+    mixer = AttentionMixer(spec, w, hs.rt)
+    rng = np.random.default_rng(0)
+    totals = [sum(c[i] for c in CUTS) for i in range(3)]
+    xs = [plain.to_bf16(rng.normal(size=(n, H))) for n in totals]
+    got = hs.run(mixer.forward, xs, CUTS)
+    W = as_plain(w, "L.")
+    inv = plain.rope_inv_freq(300.0, D, pairs)
+    for x, y in zip(xs, got):
+        ref = plain.self_attention(x, W, "L.", Hq, Hkv, D, 1e-6, inv, window, gate)
+        assert gap_of(y, ref) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,K,bias", [(72, 3, False), (40, 7, True), (64, 2, False)])
+def test_short_conv_mixer_alone(dtype, H, K, bias):
+    from xpu_serve_b200.config.spec import ShortConvSpec
+    from xpu_serve_b200.parts import ShortConvMixer
+    spec = ShortConvSpec(H, K, bias)
+    w = weights_for(ShortConvMixer, spec, 2, dtype, scale={"conv": 3.0})
+    hs = Harness(dtype, ShortConvMixer.cache_need(spec))
+    mixer = ShortConvMixer(spec, w, hs.rt)
+    rng = np.random.default_rng(1)
+    totals = [sum(c[i] for c in CUTS) for i in range(3)]
+    xs = [plain.to_bf16(rng.normal(size=(n, H))) for n in totals]
+    got = hs.run(mixer.forward, xs, CUTS)
+    W = as_plain(w, "L.")
+    for x, y in zip(xs, got):
+        assert gap_of(y, plain.short_conv(x, W, "L.", H, K, bias)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,F,T", [(72, 200, 5), (64, 192, 40), (96, 321, 3)])
+def test_swiglu_alone(dtype, H, F, T):
+    from xpu_serve_b200.config.spec import SwiGLUSpec
+    from xpu_serve_b200.engine.runtime import Runtime
+    from xpu_serve_b200.parts import SwiGLU
+    spec = SwiGLUSpec(H, F)
+    w = weights_for(SwiGLU, spec, 3, dtype, scale={"w1": 3.0})
+    rt = Runtime(dtype)
+    ffn = SwiGLU(spec, w, rt)
+    x = plain.to_bf16(np.random.default_rng(2).normal(size=(T, H)))
+    y = ffn.forward(torch.tensor(x, device=rt.device).to(rt.act_dtype), None)
+    assert gap_of(y, plain.swiglu(x, as_plain(w, "L."), "L.")) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sandwich", [False, True])
+def test_block_alone(dtype, sandwich):
+    """The layer frame: norms before, (normed) branches added to a float32 stream."""
+    from xpu_serve_b200.config.spec import LayerSpec, NormSpec, ShortConvSpec, SwiGLUSpec
+    from xpu_serve_b200.parts import Block, ResidualStream, ShortConvMixer
+    from xpu_serve_b200.weights.expected import layer_tensors
+    H, F, K, eps = 72, 136, 3, 2e-6
+    layer = LayerSpec("L.", ShortConvSpec(H, K, False), SwiGLUSpec(H, F), NormSpec(H, eps), sandwich)
+    g = torch.Generator().manual_seed(5)
+    w = {}
+    for name, ts in layer_tensors(layer).items():
+        t = (torch.rand(ts.shape, generator=g) + 0.5) if ts.role == "vector" else \
+            (torch.randn(ts.shape, generator=g) / math.sqrt(ts.shape[-1])).to(TORCH[dtype]).float()
+        w[name] = t
+    hs = Harness(dtype, ShortConvMixer.cache_need(layer.mixer))
+    block = Block(layer, w, hs.rt)
+    rng = np.random.default_rng(3)
+    totals = [sum(c[i] for c in CUTS) for i in range(3)]
+    hs_in = [rng.normal(size=(n, H)).astype(np.float32).astype(np.float64) for n in totals]
+
+    def forward(x, ctx, view):
+        stream = ResidualStream(x.contiguous(), hs.rt)
+        block.forward(stream, ctx, view)
+        stream.flush()
+        return stream.h
+
+    got = hs.run(forward, hs_in, CUTS, input_dtype=torch.float32)      # the stream is float32 in both modes
+    W = as_plain(w, "L.")
+    for h0, y in zip(hs_in, got):
+        x = plain.rms_norm(h0, W["L.operator_norm.weight"], eps)
+        m = plain.short_conv(x, W, "L.", H, K, False)
+        h1 = h0 + (plain.rms_norm(m, W["L.post_operator_norm.weight"], eps) if sandwich else m)
+        f = plain.swiglu(plain.rms_norm(h1, W["L.ffn_norm.weight"], eps), W, "L.")
+        h2 = h1 + (plain.rms_norm(f, W["L.post_ffn_norm.weight"], eps) if sandwich else f)
+        assert gap_of(y, h2) <= TOL[dtype]
+
+
+def test_rotary_table_matches_plain_angles():
+    from xpu_serve_b200.config.spec import RopeSpec
+    from xpu_serve_b200.engine.runtime import Runtime
+    from xpu_serve_b200.parts import RotaryTable
+    rt = Runtime("float32")
+    for D, theta, pairs in ((16, 10000.0, 8), (48, 77.0, 16), (64, 1e6, 32)):
+        table = RotaryTable(RopeSpec(D, theta, pairs), rt).table(3000).double().cpu().numpy()
+        inv = plain.rope_inv_freq(theta, D, pairs)
+        ang = np.arange(3000)[:, None] * inv[None, :]
+        assert np.abs(table[:3000, :, 0] - np.cos(ang)).max() < 1e-7 and np.abs(table[:3000, :, 1] - np.sin(ang)).max() < 1e-7
+        assert (table[:, pairs:, 0] == 1).all() and (table[:, pairs:, 1] == 0).all()
+
+
+# --------------------------------------------------------------------------- a toy mixer, defined here
+@dataclass(frozen=True)
+class ToyEmaSpec:
+    """out_t = s_t, s_t = decay * s_{t-1} + (1 - decay) * (x_t W^T): a state of its own, per channel."""
+    hidden: int
+    names: Dict[str, str] = field(default_factory=lambda: {"w": "toy.proj.weight", "decay": "toy.decay"})
+    kind: str = "toy_ema"
+
+
+def make_toy_class():
+    from xpu_serve_b200.parts.base import Mixer, StateNeed, TensorSpec
+
+    class ToyEma(Mixer):
+        kind = "toy_ema"
+
+        @classmethod
+        def tensors(cls, spec):
+            return {spec.names["w"]: TensorSpec((spec.hidden, spec.hidden)),
+                    spec.names["decay"]: TensorSpec((spec.hidden,), init="ones", role="vector")}
+
+        @classmethod
+        def cache_need(cls, spec):
+            return StateNeed((spec.hidden,), "float32")
+
+        def __init__(self, spec, weights, rt):
+            self.spec, self.rt = spec, rt
+            self.w = rt.matrix(weights[spec.names["w"]])
+            self.decay = torch.sigmoid(rt.vector(weights[spec.names["decay"]]))
+
+        def forward(self, x, step, cache):
+            z = (x.float() @ self.w.float().t())
+            state = cache.storage
+            slots = step.slots.long()
+            out = torch.empty_like(z)
+            if step.decode:                       # one token a sequence: no host-side loop, graph-safe
+                s = self.decay * state[slots] + (1 - self.decay) * z
+                state.index_copy_(0, slots, s)
+                return s.to(self.rt.act_dtype)
+            cu = np.concatenate([[0], np.cumsum(step.q_lens_host)])
+            for i in range(step.n_seqs):
+                s = state[slots[i]]
+                for t in range(int(cu[i]), int(cu[i + 1])):
+                    s = self.decay * s + (1 - self.decay) * z[t]
+                    out[t] = s
+                state[slots[i]] = s
+            return out.to(self.rt.act_dtype)
+
+    return ToyEma
+
+
+def toy_model(dtype):
+    """Layers: toy, attention, conv. Order: toy, attention, toy again (its own state), conv, and an
+    attention call that reads the first attention call's cache."""
+    from xpu_serve_b200 import registry
+    from xpu_serve_b200.config import Lfm3Config
+    from xpu_serve_b200.config.spec import LayerCall
+    from xpu_serve_b200.engine.model import Model
+    from xpu_serve_b200.weights import random_tensors
+    try:
+        registry.mixer_class("toy_ema")
+    except KeyError:
+        registry.register_mixer("toy_ema", make_toy_class())
+    base = Lfm3Config.from_json(tiny.CONFIG_A).model_spec()
+    attn = next(l for l in base.layers if l.mixer.kind == "attention")
+    conv = next(l for l in base.layers if l.mixer.kind == "short_conv")
+    layers = (replace(attn, prefix="layers.0.", mixer=ToyEmaSpec(base.hidden)),
+              replace(attn, prefix="layers.1."), replace(conv, prefix="layers.2."),
+              replace(attn, prefix="layers.3."))
+    order = (LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(2), LayerCall(3, cache_of=1))
+    spec = replace(base, layers=layers, order=order)
+    tensors = dict(random_tensors(spec, 7, "float32", norm_range=(0.5, 1.5), scale=tiny.LIVELY))
+    weights = {k[len("model."):]: v for k, v in tensors.items()}
+    return spec, tensors, Model(spec, weights, dtype=dtype)
+
+
+def plain_toy_forward(spec, tensors, ids):
+    W = {k: v.double().numpy() for k, v in tensors.items()}
+    cfg = tiny.CONFIG_A
+    H, Hq, Hkv, D, K, eps = 64, 4, 2, 16, 3, cfg["norm_eps"]
+    inv = plain.rope_inv_freq(cfg["rope_theta"], D, D // 2)
+    h = W["model.embed_tokens.weight"][np.asarray(ids)]
+    kv = {}
+    ema_state = {}
+    for ci, call in enumerate(spec.order):
+        L = f"model.layers.{call.layer}."
+        x = plain.rms_norm(h, W[L + "operator_norm.weight"], eps)
+        kind = spec.layers[call.layer].mixer.kind
+        if kind == "toy_ema":
+            decay = 1 / (1 + np.exp(-W[L + "toy.decay"]))
+            z = x @ W[L + "toy.proj.weight"].T
+            s = np.zeros(H)
+            m = np.zeros_like(z)
+            for t in range(len(ids)):
+                s = decay * s + (1 - decay) * z[t]
+                m[t] = s
+        elif kind == "short_conv":
+            m = plain.short_conv(x, W, L, H, K, False)
+        else:
+            shared = kv[call.cache_of] if call.cache_of is not None else None
+            m, kv[ci] = plain.self_attention(x, W, L, Hq, Hkv, D, eps, inv, 0, False, shared_kv=shared, return_kv=True)
+        h = h + m
+        y = plain.rms_norm(h, W[L + "ffn_norm.weight"], eps)
+        h = h + plain.swiglu(y, W, L)
+    return plain.rms_norm(h, W["model.embedding_norm.weight"], eps) @ W["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_order_and_shared_cache(dtype):
+    spec, tensors, model = toy_model(dtype)
+    needs, shares = model.cache_needs()
+    assert [type(n).__name__ for n in needs] == ["StateNeed", "KVNeed", "StateNeed", "StateNeed", "KVNeed"]
+    assert shares == [None, None, None, None, 1]
+    cache = model.new_cache(1024)
+    assert cache.views[4].storage.data_ptr() == cache.views[1].storage.data_ptr() and not cache.views[4].owner
+    assert cache.views[0].storage.data_ptr() != cache.views[2].storage.data_ptr()      # a layer called twice: two states
+    prompts = [tiny.prompt("A", n, salt=i) for i, n in enumerate((9, 30, 3))]
+    refs = [plain_toy_forward(spec, tensors, p) for p in prompts]
+    slots = cache.open(3)
+    heads = [6, 20, 1]
+    got = [[] for _ in prompts]
+    lg = model.step(cache, slots, [p[:h] for p, h in zip(prompts, heads)], [list(range(h)) for h in heads])
+    lg = lg.cpu().numpy()
+    o = 0
+    for i, h in enumerate(heads):
+        got[i].append(lg[o:o + h])
+        o += h
+    at = list(heads)
+    live = [0, 1, 2]
+    while live:
+        lg = model.step(cache, [slots[i] for i in live], [[prompts[i][at[i]]] for i in live]).cpu().numpy()
+        for r, i in enumerate(live):
+            got[i].append(lg[r:r + 1])
+            at[i] += 1
+        done = [i for i in live if at[i] == len(prompts[i])]
+        cache.close([slots[i] for i in done])
+        live = [i for i in live if i not in done]
+    tol = 1e-5 if dtype == "float32" else 5e-2
+    for g, r in zip(got, refs):
+        assert gap_of(np.concatenate(g, 0), r) <= tol
+    cache.check()
+    # slots are used again, and the toy's state starts from zero again
+    (s2,) = cache.open(1)
+    lg = model.step(cache, [s2], [prompts[0]], [list(range(len(prompts[0])))]).cpu().numpy()
+    assert gap_of(lg, refs[0]) <= tol
+    cache.close([s2])
+
+
+# ------------------------------------------------------------------------------ long runs, first tokens
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["R", "W"])
+def test_long_decoding(tmp_path, name, dtype):
+    """400 tokens one by one, beyond the window and across several pages, beside a second sequence that
+    starts later in a slot that another sequence has used."""
+    from xpu_serve_b200.engine.model import load_model
+    folder = tiny.make_folder(tmp_path, name, dtype)
+    cfg, W = plain.load_folder(folder)
+    model = load_model(folder, dtype=dtype)
+    cache = model.new_cache(1024)
+    toks = tiny.prompt(name, 400, salt=3)
+    ref = plain.forward(cfg, W, toks)
+    (warm,) = cache.open(1)
+    model.step(cache, [warm], [tiny.prompt(name, 70, salt=9)])
+    cache.close([warm])
+    (s,) = cache.open(1)
+    assert s == warm
+    rows = [model.step(cache, [s], [[t]]).cpu().numpy()[0] for t in toks]
+    layers = cfg["num_hidden_layers"]
+    tol = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * layers) * 2 ** -9
+    assert gap_of(np.stack(rows), ref) <= tol
+    cache.close([s])
+    cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_first_tokens(tmp_path, name, dtype):
+    """Positions 0, 1, 2: a one-token prompt, then single tokens; and prompts of 1, 2 and 3 tokens in one batch."""
+    from xpu_serve_b200.engine.model import load_model
+    folder = tiny.make_folder(tmp_path, name, dtype)
+    cfg, W = plain.load_folder(folder)
+    model = load_model(folder, dtype=dtype)
+    cache = model.new_cache(512)
+    tol = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * cfg["num_hidden_layers"]) * 2 ** -9
+    toks = tiny.prompt(name, 3, salt=1)
+    ref = plain.forward(cfg, W, toks)
+    (s,) = cache.open(1)
+    rows = [model.step(cache, [s], [[t]]).cpu().numpy()[0] for t in toks]
+    assert gap_of(np.stack(rows), ref) <= tol
+    cache.close([s])
+    slots = cache.open(3)
+    batch = [toks[:1], toks[:2], toks[:3]]
+    lg = model.step(cache, slots, batch, [[0], [0, 1], [0, 1, 2]]).cpu().numpy()
+    assert gap_of(lg, np.concatenate([ref[:1], ref[:2], ref[:3]], 0)) <= tol
+    cache.close(slots)
