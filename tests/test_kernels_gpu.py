@@ -200,6 +200,60 @@ def test_gemm_small_m_with_fused_activation(M):
     close(out, g / (1 + torch.exp(-g)) * u, "bfloat16")
 
 
+TC_SHAPES = [(1, 128, 64), (8, 256, 128), (16, 2048, 2048), (5, 100, 96), (33, 1000, 200), (64, 384, 512),
+             (130, 300, 264), (700, 1024, 2048), (2048, 512, 1024)]
+
+
+@pytest.mark.parametrize("T,N,K", TC_SHAPES)
+def test_gemm_tc_store_and_residual(T, N, K):
+    lib = ops()
+    g = torch.Generator(device="cpu").manual_seed(T + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    assert lib.gemm_tc_supports(T, N, K, x.stride(0), w.stride(0))
+    ref = x.double() @ w.double().T
+    status = lib.gemm_tc_status(DEV)
+    out = torch.full((T, N), float("nan"), device=DEV)
+    lib.gemm_tc(x, w, out)
+    torch.cuda.synchronize()
+    assert status.item() == 0, "a wait inside the kernel gave up"
+    close(out, ref, "float32", factor=4)
+    out16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV)
+    lib.gemm_tc(x, w, out16, bias)
+    close(out16, ref + bias.double(), "bfloat16")
+    res = torch.randn(T, N, device=DEV)
+    want = res.double() + ref
+    lib.gemm_tc(x, w, res, epilogue=lib.EPI_RESIDUAL)
+    close(res, want, "float32", factor=4)
+    if T > 1:
+        one = torch.empty(1, N, device=DEV)
+        lib.gemm_tc(x[T - 1:T], w, one)
+        close(one, ref[T - 1:T], "float32", factor=4)
+    assert status.item() == 0
+
+
+@pytest.mark.parametrize("T,F,K,ksplit", [(1, 344, 200, 1), (8, 1024, 2048, 1), (16, 256, 4096, 4), (40, 136, 512, 2), (300, 512, 256, 1)])
+def test_gemm_tc_swiglu_and_k_slices(T, F, K, ksplit):
+    lib = ops()
+    g = torch.Generator(device="cpu").manual_seed(F)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(F, K, generator=g) / math.sqrt(K) * 3).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    w = torch.stack([gate.view(F // 8, 8, K), up.view(F // 8, 8, K)], 1).reshape(2 * F, K).contiguous()
+    gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
+    scratch = torch.zeros(max(lib.gemm_tc_scratch_bytes(T, 2 * F, ksplit), 16), dtype=torch.uint8, device=DEV)
+    out = torch.empty(T, F, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):          # the counters must be left ready for the next call
+        out.fill_(float("nan"))
+        lib.gemm_tc(x, w, out, epilogue=lib.EPI_SWIGLU, ksplit=ksplit, scratch=scratch if ksplit > 1 else None)
+        close(out, gg / (1 + torch.exp(-gg)) * uu, "bfloat16")
+    plain_out = torch.empty(T, 2 * F, device=DEV)
+    lib.gemm_tc(x, w, plain_out, ksplit=ksplit, scratch=scratch if ksplit > 1 else None)
+    close(plain_out, x.double() @ w.double().T, "float32", factor=4)
+    assert lib.gemm_tc_status(DEV).item() == 0
+
+
 def test_gemm_small_m_refuses_what_it_cannot_take():
     lib = ops()
     assert not lib.gemm_small_m_supports(17, 64, 64, 64)

@@ -1,0 +1,395 @@
+// out[T, N] = x[T, K] . w[N, K]^T on Blackwell's fifth-generation tensor cores (tcgen05), bfloat16
+// in, float32 accumulation in tensor memory.
+//
+// Orientation: the weight's rows ride the MMA's M side (128 rows a tile) and the tokens its N side
+// (16 to 256 a tile), so the same kernel serves a prefill of thousands of tokens and a decode
+// step of one token a sequence, where the product is a stream of weights past a tiny x.
+//
+//   warp 0   TMA producer: cp.async.bulk.tensor loads of a 128 x 64 weight tile and a BN x 64 tile
+//            of x per k block into a ring of shared-memory stages (128-byte swizzle), each stage
+//            guarded by a full/empty mbarrier pair. Weight tiles depend on no other kernel, so
+//            the first ring-full of them is requested before griddepcontrol.wait.
+//   warp 1   MMA issuer: allocates tensor memory, and one lane issues four
+//            tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) per stage straight from shared
+//            memory; tcgen05.commit hands the stage back to the producer and, at the end, the
+//            accumulator to the epilogue.
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = weight row, column = token), apply the
+//            epilogue and write out[token][row]; a warp's 32 lanes write 32 neighbouring columns.
+//
+// Epilogues: store (bfloat16 or float32); residual (float32 out += result); SwiGLU for a weight
+// stacked in blocks of 8 gate rows and 8 up rows (out[T, N / 2] = silu(gate) * up, the partner row
+// sits 8 lanes away). With K cut into slices (narrow outputs in decode), every slice's CTA leaves
+// its partial tile in scratch and the CTA that arrives last adds them in slice order.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls a CTA sets an abort flag, all its
+// roles leave their loops, tensor memory is freed, and *status is set non-zero for the host.
+// Any K that is a multiple of 8, any N, any T: tiles that reach past the matrices are zero-filled
+// by the TMA unit and their results are not stored.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // weight rows per tile (MMA M)
+constexpr int BK = 64;           // k per stage: one 128-byte swizzle atom of bfloat16
+constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
+constexpr int kSpinLimit = 1 << 22;
+
+enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
+
+struct GemmTcParams {
+    void* out;                // EPI_STORE: [T, N]; EPI_RESIDUAL: float [T, N]; EPI_SWIGLU: [T, N / 2]
+    const float* bias;        // [N] or null
+    float* partials;          // [tiles_m * tiles_n, ksplit, BM * BN] when ksplit > 1
+    unsigned int* counters;   // [tiles_m * tiles_n], zero between calls
+    int* status;              // set non-zero when a wait gave up
+    int T, N, K, ksplit, epilogue, out_f32;
+    int64_t ldo;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when this CTA has given up (here or in another role).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile written by TMA with the 128-byte swizzle: rows of
+// 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), start address in 16-byte units,
+// descriptor version 1, layout type 2 (SWIZZLE_128B). The tile starts on a 1024-byte boundary.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // bits [0, 14)
+    d |= (uint64_t)1 << 16;                           // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset
+    d |= (uint64_t)1 << 46;                           // version
+    d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN>
+struct Smem {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;     // a multiple of 1024 for BN a multiple of 8
+};
+
+// One value of the accumulator, after bias, goes out through the chosen epilogue.
+template <int BN>
+__device__ __forceinline__ void emit(const GemmTcParams& p, float v, int row, int token, int lane) {
+    // SwiGLU: lanes 0-7 and 16-23 hold gate rows, the lane 8 further holds the up row of the same output
+    if (p.epilogue == EPI_SWIGLU) {
+        const float up = __shfl_xor_sync(0xffffffffu, v, 8);
+        if ((lane & 8) == 0 && row + 8 < p.N && token < p.T) {
+            const float a = v / (1.0f + __expf(-v)) * up;
+            const int64_t at = (int64_t)token * p.ldo + (row >> 4) * 8 + (row & 7);
+            if (p.out_f32) ((float*)p.out)[at] = a; else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(a);
+        }
+        return;
+    }
+    if (row >= p.N || token >= p.T) return;
+    const int64_t at = (int64_t)token * p.ldo + row;
+    if (p.epilogue == EPI_RESIDUAL) ((float*)p.out)[at] += v;
+    else if (p.out_f32) ((float*)p.out)[at] = v;
+    else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+               const GemmTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte alignment of the stage ring (the swizzle pattern is a function of the address)
+    uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bar_full[STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];
+    __shared__ __align__(8) uint64_t bar_acc;
+    __shared__ uint32_t tmem_base;
+    __shared__ int abort_flag;
+    __shared__ bool is_last;
+
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;           // a power of two >= 32
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.x, tile_n = blockIdx.y, slice = blockIdx.z;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int per_slice = (kb_total + p.ksplit - 1) / p.ksplit;
+    const int kb0 = slice * per_slice, kb1 = min(kb_total, kb0 + per_slice);
+    const int n_kb = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {    // the MMA warp owns tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    pdl_launch_dependents();
+    volatile int* abort_p = &abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const int ahead = min(STAGES, n_kb);
+            for (int i = 0; i < ahead; ++i) {        // weights first: they wait for nobody
+                const uint32_t full = smem_u32(&bar_full[i]);
+                mbar_expect_tx(full, Smem<BN>::kStageBytes);
+                tma_load_2d(smem_u32(ring + i * Smem<BN>::kStageBytes), &tmap_w, (kb0 + i) * BK, tile_m * BM, full);
+            }
+            pdl_wait();                              // x is written by the kernel before this one
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(smem_u32(ring + i * Smem<BN>::kStageBytes + Smem<BN>::kABytes), &tmap_x, (kb0 + i) * BK,
+                            tile_n * BN, smem_u32(&bar_full[i]));
+            for (int i = ahead; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / STAGES) & 1) ^ 1, abort_p)) break;
+                const uint32_t full = smem_u32(&bar_full[s]);
+                mbar_expect_tx(full, Smem<BN>::kStageBytes);
+                tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes), &tmap_w, (kb0 + i) * BK, tile_m * BM, full);
+                tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes + Smem<BN>::kABytes), &tmap_x, (kb0 + i) * BK,
+                            tile_n * BN, full);
+            }
+        } else {
+            pdl_wait();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        pdl_wait();
+        if (lane == 0) {
+            const uint32_t acc = tmem_base;
+            constexpr uint32_t idesc = instr_desc(BN < 16 ? 16 : BN);
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(smem_u32(&bar_full[s]), (i / STAGES) & 1, abort_p)) break;
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(ring + s * Smem<BN>::kStageBytes);
+                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + Smem<BN>::kABytes);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)      // 16 k = 32 bytes further along the swizzled row
+                    umma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tcgen05_commit(smem_u32(&bar_empty[s]));      // the stage is free when these MMAs have read it
+            }
+            tcgen05_commit(smem_u32(&bar_acc));               // the accumulator is complete
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        pdl_wait();
+        const int quarter = warp & 3;                          // the tensor-memory lanes this warp may read
+        const int row = tile_m * BM + quarter * 32 + lane;     // weight row = output column
+        bool ok = n_kb == 0 || mbar_wait(smem_u32(&bar_acc), 0, abort_p);
+        tcgen05_fence_after();
+        if (ok) {
+            const float b = (p.bias != nullptr && row < p.N && slice == 0) ? p.bias[row] : 0.0f;
+            const int64_t tile = (int64_t)tile_m * gridDim.y + tile_n;
+            float* mine = p.ksplit > 1 ? p.partials + (tile * p.ksplit + slice) * (int64_t)(BM * BN) : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                if (n_kb > 0) {
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float v = __uint_as_float(r[j]) + b;
+                    if (p.ksplit > 1) mine[(c + j) * BM + quarter * 32 + lane] = v;      // [token][row]: coalesced
+                    else emit<BN>(p, v, row, tile_n * BN + c + j, lane);
+                }
+            }
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (p.ksplit > 1 && !abort_flag) {
+        // the last slice's CTA to arrive adds all slices in slice order
+        const int64_t tile = (int64_t)tile_m * gridDim.y + tile_n;
+        __threadfence();
+        if (threadIdx.x == 0) is_last = atomicAdd(&p.counters[tile], 1u) == (unsigned)p.ksplit - 1;
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            if (warp >= 2) {
+                const int quarter = warp & 3;
+                const int row = tile_m * BM + quarter * 32 + lane;
+                const float* all = p.partials + tile * p.ksplit * (int64_t)(BM * BN);
+                for (int c = 0; c < BN; ++c) {
+                    float v = 0.0f;
+                    for (int s = 0; s < p.ksplit; ++s) v += __ldcg(all + (int64_t)s * (BM * BN) + c * BM + quarter * 32 + lane);
+                    emit<BN>(p, v, row, tile_n * BN + c, lane);
+                }
+            }
+            if (threadIdx.x == 0) p.counters[tile] = 0;
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+}
+
+// ---- tensor maps -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    });
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with `ld` elements between rows, read in boxes of box_rows x 64.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcParams& p, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * Smem<BN>::kStageBytes + 1024;
+    static bool opted = false;
+    if (!opted) {
+        cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        opted = true;
+    }
+    const dim3 grid(ceil_div_i(p.N, BM), ceil_div_i(p.T, BN), p.ksplit);
+    return xs_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(kThreads), smem, stream, mw, mx, p) == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace
+
+XS_API int xs_gemm_tc_supports(int T, int N, int K, int64_t ldx, int64_t ldw) {
+    return T >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && encode_fn() != nullptr;
+}
+
+// The token tile the kernel uses for T tokens.
+XS_API int xs_gemm_tc_tile_n(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128; }
+
+XS_API int64_t xs_gemm_tc_scratch_bytes(int T, int N, int ksplit) {
+    if (ksplit <= 1) return 0;
+    const int bn = xs_gemm_tc_tile_n(T);
+    const int64_t tiles = (int64_t)ceil_div_i(N, BM) * ceil_div_i(T, bn);
+    return tiles * ksplit * BM * bn * (int64_t)sizeof(float) + 65536;
+}
+
+// epilogue: 0 store (out_dtype), 1 residual (out is float32 [T, N], += result), 2 SwiGLU (out is [T, N / 2]).
+// ksplit > 1: scratch of xs_gemm_tc_scratch_bytes; its last 64 KiB are counters that are zero between calls.
+// status: one device int that the kernel sets non-zero if a wait inside it gave up (the result is then invalid).
+XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int epilogue, int T, int N,
+                      int K, int64_t ldx, int64_t ldw, int64_t ldo, int ksplit, void* scratch, int64_t scratch_bytes,
+                      int* status, cudaStream_t stream) {
+    if (T == 0 || N == 0) return 0;
+    XS_REQUIRE(xs_gemm_tc_supports(T, N, K, ldx, ldw), "gemm (tcgen05): T %d, N %d, K %d, strides %lld, %lld not supported", T,
+               N, K, (long long)ldx, (long long)ldw);
+    XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (tcgen05): operands must be 16-byte aligned");
+    XS_REQUIRE(epilogue >= 0 && epilogue <= 2 && status != nullptr && out != nullptr, "gemm (tcgen05): bad arguments");
+    XS_REQUIRE(epilogue != EPI_SWIGLU || N % 16 == 0, "gemm (tcgen05): the fused activation needs N %% 16 == 0");
+    XS_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == XS_F32, "gemm (tcgen05): the residual is float32");
+    XS_REQUIRE(ksplit >= 1 && ksplit <= 64, "gemm (tcgen05): %d K slices", ksplit);
+    const int bn = xs_gemm_tc_tile_n(T);
+    GemmTcParams p;
+    p.out = out;
+    p.bias = bias;
+    p.partials = nullptr;
+    p.counters = nullptr;
+    p.status = status;
+    p.T = T; p.N = N; p.K = K; p.ksplit = ksplit; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
+    p.ldo = ldo;
+    if (ksplit > 1) {
+        const int64_t need = xs_gemm_tc_scratch_bytes(T, N, ksplit);
+        const int64_t tiles = (int64_t)ceil_div_i(N, BM) * ceil_div_i(T, bn);
+        XS_REQUIRE(scratch != nullptr && scratch_bytes >= need && (uintptr_t)scratch % 16 == 0 && tiles * 4 <= 65536,
+                   "gemm (tcgen05): %lld bytes of scratch needed for %d K slices, %lld given", (long long)need, ksplit,
+                   (long long)scratch_bytes);
+        p.partials = (float*)scratch;
+        p.counters = (unsigned int*)((char*)scratch + scratch_bytes - 65536);
+    }
+    alignas(64) CUtensorMap mw, mx;
+    XS_REQUIRE(make_map(&mw, w, N, K, ldw, BM), "gemm (tcgen05): the weight's tensor map could not be made");
+    XS_REQUIRE(make_map(&mx, x, T, K, ldx, bn), "gemm (tcgen05): the input's tensor map could not be made");
+    int rc;
+    switch (bn) {
+        case 16: rc = launch<16, 8>(mw, mx, p, stream); break;
+        case 32: rc = launch<32, 8>(mw, mx, p, stream); break;
+        case 64: rc = launch<64, 6>(mw, mx, p, stream); break;
+        default: rc = launch<128, 3>(mw, mx, p, stream); break;
+    }
+    XS_REQUIRE(rc == 0, "gemm (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}

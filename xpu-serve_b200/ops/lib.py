@@ -40,6 +40,7 @@ def _signatures(lib) -> None:
         "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
         "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P],
+        "xs_gemm_tc": [P, P, P, P, I, I, I, I, I, L, L, L, I, P, L, P, P],
         "xs_argmax": [P, L, I, I, P, P, P],
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
@@ -60,6 +61,12 @@ def _signatures(lib) -> None:
     lib.xs_attention_mma_supports.argtypes = [c_int, c_int, c_int]
     lib.xs_gemm_small_m_supports.restype = c_int
     lib.xs_gemm_small_m_supports.argtypes = [c_int, c_int, c_int64, c_int64]
+    lib.xs_gemm_tc_supports.restype = c_int
+    lib.xs_gemm_tc_supports.argtypes = [c_int, c_int, c_int, c_int64, c_int64]
+    lib.xs_gemm_tc_tile_n.restype = c_int
+    lib.xs_gemm_tc_tile_n.argtypes = [c_int]
+    lib.xs_gemm_tc_scratch_bytes.restype = c_int64
+    lib.xs_gemm_tc_scratch_bytes.argtypes = [c_int, c_int, c_int]
     lib.xs_gemm_small_m_ksplit.restype = c_int
     lib.xs_gemm_small_m_ksplit.argtypes = [c_int, c_int, c_int, c_int]
     lib.xs_gemm_small_m_scratch_bytes.restype = c_int64
@@ -303,6 +310,47 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
                                   F32 if out is None else _code(out), M, N, K, x.stride(0), w.stride(0),
                                   target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
                                   0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()))
+
+
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+_tc_status = {}
+
+
+def gemm_tc_supports(T: int, N: int, K: int, ldx: int, ldw: int) -> bool:
+    return bool(load().xs_gemm_tc_supports(T, N, K, ldx, ldw))
+
+
+def gemm_tc_scratch_bytes(T: int, N: int, ksplit: int) -> int:
+    return int(load().xs_gemm_tc_scratch_bytes(T, N, ksplit))
+
+
+def gemm_tc_status(device) -> torch.Tensor:
+    """The device word that the tcgen05 kernels set non-zero when one of their waits gave up."""
+    device = torch.device(device)
+    if device not in _tc_status:
+        _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[device]
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            epilogue: int = EPI_STORE, ksplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """x[T, K] . w[N, K]^T on tcgen05 tensor cores (bfloat16 operands). epilogue EPI_STORE: out[T, N] bfloat16 or
+    float32; EPI_RESIDUAL: out float32 += product; EPI_SWIGLU: out[T, N / 2] = silu(gate) * up for a weight stacked
+    in blocks of 8 gate and 8 up rows."""
+    for t, name in ((x, "x"), (w, "w")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
+            raise KernelError(f"gemm (tcgen05): {name} must be a bfloat16 CUDA matrix with contiguous rows")
+    T, K = x.shape
+    N = w.shape[0]
+    cols = N // 2 if epilogue == EPI_SWIGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (T, cols) or out.stride(1) != 1:
+        raise KernelError(f"gemm (tcgen05): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    _check(load().xs_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), _code(out), int(epilogue), T, N, K,
+                             x.stride(0), w.stride(0), out.stride(0), int(ksplit), _ptr(scratch),
+                             0 if scratch is None else scratch.numel() * scratch.element_size(),
+                             gemm_tc_status(x.device).data_ptr(), _stream()))
 
 
 def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
