@@ -123,3 +123,21 @@ def test_program_matches_in_process(folders, tmp_path):
     ref = tu.plain_logits(folders[(name, dtype)], reqs)
     gap, where, _ = tu.worst_gap(got, ref)
     assert gap <= tolerance(name, dtype), f"gap {gap:.3e} at {where}"
+
+
+@pytest.mark.parametrize("name", ["A", "W"])
+def test_tcgen05_products_on_the_model_path(name, folders, references, monkeypatch):
+    """The same batches with every many-row product on the tcgen05 kernel (and SwiGLU in its epilogue)."""
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.ops import lib as ops
+    monkeypatch.setenv("XS_MANY_ROWS_GEMM", "tcgen05")
+    rp = Replayer(load_model(folders[(name, "bfloat16")], dtype="bfloat16"), 1024, None)
+    assert rp.model.rt.many_rows == "tcgen05"
+    reqs = requests_for(name)
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    for steps in (tu.whole_trace(reqs), tu.batch_trace(reqs, 5)):
+        got = tu.collect(steps, tu.run_in_process(rp, steps), vocab)
+        gap, where, cos = tu.worst_gap(got, references(name, "bfloat16"))
+        assert gap <= tolerance(name, "bfloat16") and cos >= COS["bfloat16"], f"gap {gap:.3e} at {where}"
+    assert ops.gemm_tc_status(rp.model.rt.device).item() == 0

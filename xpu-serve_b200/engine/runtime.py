@@ -13,6 +13,7 @@ src/backend/sycl/sycl_matmul.cpp:44-110; cuBLAS through torch.mm here).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -59,6 +60,11 @@ class Runtime:
         # cuBLAS may otherwise reduce split products in bfloat16
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self.small_m = 16     # products with at most this many rows use this library's streaming kernel
+        # Products with more rows: "library" (cuBLAS, the faster one today) or "tcgen05" (this library's
+        # TMA + tensor-memory kernel, with the SwiGLU activation fused into its epilogue).
+        self.many_rows = os.environ.get("XS_MANY_ROWS_GEMM", "library")
+        if self.many_rows not in ("library", "tcgen05"):
+            raise ValueError("XS_MANY_ROWS_GEMM must be 'library' or 'tcgen05'")
         ops.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
@@ -77,6 +83,11 @@ class Runtime:
         """Whether this product goes to the library's own weight-streaming kernel."""
         return (self.mode == "bfloat16" and x.shape[0] <= self.small_m
                 and ops.gemm_small_m_supports(x.shape[0], x.shape[1], x.stride(0), w.stride(0)))
+
+    def tensor_core_product(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether this product goes to the library's tcgen05 kernel."""
+        return (self.mode == "bfloat16" and self.many_rows == "tcgen05"
+                and ops.gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0)))
 
     def few_rows_product(self, x, w, out, bias=None, swiglu: bool = False) -> None:
         """The library's weight-streaming product, with K cut over several CTAs where the output is
@@ -97,6 +108,8 @@ class Runtime:
             ops.gemm_generic(x, w, out, bias)
         elif self.few_rows(x, w):
             self.few_rows_product(x, w, out, bias)
+        elif self.tensor_core_product(x, w):
+            ops.gemm_tc(x, w, out, bias)
         elif bias is not None:
             ops.gemm_generic(x, w, out, bias)
         elif out_dtype == torch.float32:

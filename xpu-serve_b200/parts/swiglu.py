@@ -42,6 +42,8 @@ class SwiGLU(FeedForward):
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
         if self.interleave and rt.few_rows(y, self.w_gate_up):
             rt.few_rows_product(y, self.w_gate_up, act, swiglu=True)
+        elif self.interleave and rt.tensor_core_product(y, self.w_gate_up):
+            ops.gemm_tc(y, self.w_gate_up, act, epilogue=ops.EPI_SWIGLU)
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
             ops.silu_mul(gu, act, self.interleave)
