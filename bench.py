@@ -91,6 +91,24 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(mhz)}
 
 
+def copy_bandwidth_here() -> float:
+    """GB/s of a device-to-device copy of 1 GiB (read + write counted) on this GPU, now: context for the
+    roofline fraction when the driver's measured peaks are absent."""
+    import torch
+    a = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")
+    b = torch.empty_like(a)
+    for _ in range(2):
+        b.copy_(a)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(10):
+        b.copy_(a)
+    e.record()
+    torch.cuda.synchronize()
+    return 10 * 2 * (1 << 30) / (s.elapsed_time(e) * 1e-3) / 1e9
+
+
 def model_numbers(cfg: dict, n_layers_run: int):
     """Bytes a decode step must read and flops of a prefill, from the configuration."""
     H, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
@@ -245,7 +263,7 @@ def main() -> int:
         if args.only == "decode":
             ms, launches = time_decode(model, args.batch, args.steps, args.warmup, V)
             print(json.dumps({"only": "decode", "batch": args.batch, "layers": n_layers, "ms_per_step": round(ms, 4),
-                              "launches_per_step": launches}))
+                              "launches_per_step": launches, "copy_gbs_here": round(copy_bandwidth_here(), 1)}))
             return 0
         if args.only == "prefill":
             ms = time_prefill(model, V, warmup=args.warmup, runs=args.steps)
@@ -266,6 +284,7 @@ def main() -> int:
                 points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
         del model
         torch.cuda.empty_cache()
+        copy_here = copy_bandwidth_here()
         e2e_value, h2d, d2h = time_e2e(folder, args.batch, min(args.steps, 32), args.warmup, V)
 
     value = args.batch * 1000.0 / ms
@@ -289,7 +308,7 @@ def main() -> int:
                     "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes,
-                     "peaks": pk["source"]},
+                     "peaks": pk["source"], "copy_gbs_here": round(copy_here, 1)},
         "points": points,
         "clocks": clocks,
         "gpu_launches": int(round(launches * args.steps)),

@@ -72,7 +72,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
-template <int D>
+template <int D, int NST>
 __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParams p) {
     constexpr int LD = D + 8;              // padded row: ldmatrix reads 8 rows without bank conflicts
     constexpr int KSTEPS = D / 16;         // k-steps of Q K^T
@@ -80,8 +80,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
     constexpr int CHUNKS = D / 8;          // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* k_sm = q_sm + BM * LD;            // [2][BN][LD]
-    __nv_bfloat16* v_sm = k_sm + 2 * BN * LD;        // [2][BN][LD]
+    __nv_bfloat16* k_sm = q_sm + BM * LD;            // [NST][BN][LD]
+    __nv_bfloat16* v_sm = k_sm + NST * BN * LD;      // [NST][BN][LD]
 
     pdl_launch_dependents();
     pdl_wait();
@@ -128,8 +128,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
             cp_async16(vs + r * LD + ch * 8, vbase + (ok ? r * D + ch * 8 : 0), ok);
         }
     };
-    if (bs < be) load_block(bs, 0);
-    cp_async_commit();
+    // NST - 1 blocks are requested before the first is used; one commit group per block, empty ones too,
+    // so that "all but the newest NST - 2 groups have landed" always means "block b is here"
+#pragma unroll
+    for (int s = 0; s < NST - 1; ++s) {
+        if (bs + s < be) load_block(bs + s, s);
+        cp_async_commit();
+    }
 
     // this thread's two rows and their positions (-1: no key is visible)
     const int r1 = warp * 16 + (lane >> 2), r2 = r1 + 8;
@@ -144,15 +149,11 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
     bool q_loaded = false;
 
     for (int b = bs, it = 0; b < be; ++b, ++it) {
-        const int stage = it & 1;
-        if (b + 1 < be) {
-            load_block(b + 1, stage ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int stage = it % NST;
+        cp_async_wait<NST - 2>();
+        __syncthreads();            // block b has landed for everyone, and everyone is done with block b - 1
+        if (b + NST - 1 < be) load_block(b + NST - 1, (it + NST - 1) % NST);   // into the stage block b - 1 used
+        cp_async_commit();
         if (warp_active) {
             if (!q_loaded) {
 #pragma unroll
@@ -233,7 +234,6 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
                 }
             }
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
     if (!warp_active) return;
@@ -271,7 +271,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
     }
 }
 
-// out[row, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), times the head's gate. One warp per row.
+// out[row, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), times the head's gate. One warp per row; lane s holds
+// split s's (max, sum) and weight (splits <= 32), and the partial outputs are read with independent loads.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
                                          __nv_bfloat16* __restrict__ out, int64_t rows, int Hq, int D, int splits) {
@@ -281,38 +282,63 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
     const float* ml = part_ml + row * splits * 2;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
-    float l = 0.0f;
-    for (int s = 0; s < splits; ++s) l += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * exp2f(ml[2 * s] - m);
+    const float ms = lane < splits ? ml[2 * lane] : -INFINITY;
+    const float ls = lane < splits ? ml[2 * lane + 1] : 0.0f;
+    const float m = warp_max(ms);
+    const float wgt = ms == -INFINITY ? 0.0f : exp2f(ms - m);     // this split's weight
+    const float l = warp_sum(ls * wgt);
     float f = l > 0.0f ? 1.0f / l : 0.0f;
     if (gate != nullptr) {
         const int64_t t = row / Hq;
         const int h = (int)(row % Hq);
         f *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[t * ld_gate + h])));
     }
-    for (int d = lane; d < D; d += 32) {
+    const float* po = part_o + row * splits * D;
+    for (int d0 = 0; d0 < D; d0 += 32) {       // every lane stays in the loop: the shuffles need the whole warp
+        const int d = d0 + lane;
         float acc = 0.0f;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float ms = ml[2 * s];
-            if (ms != -INFINITY) acc += part_o[(row * splits + s) * D + d] * exp2f(ms - m);
+            const float w = __shfl_sync(0xffffffffu, wgt, s);
+            acc = fmaf(w, (w == 0.0f || d >= D) ? 0.0f : po[s * D + d], acc);
         }
-        out[row * D + d] = __float2bfloat16_rn(acc * f);
+        if (d < D) out[row * D + d] = __float2bfloat16_rn(acc * f);
     }
 }
 
-template <int D>
-int launch(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t stream) {
+template <int D, int NST>
+int launch_stages(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t stream) {
     constexpr int LD = D + 8;
-    const size_t smem = (size_t)(BM + 4 * BN) * LD * sizeof(__nv_bfloat16);
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = (size_t)(BM + 2 * NST * BN) * LD * sizeof(__nv_bfloat16);
+    static bool opted = false;
+    if (smem > 48 * 1024 && !opted) {
+        cudaFuncSetAttribute(attention_mma_kernel<D, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        opted = true;
+    }
     const dim3 grid(max_tiles, n_seqs, p.Hkv * p.splits);
-    xs_launch(attention_mma_kernel<D>, grid, dim3(NTHREADS), smem, stream, p);
+    xs_launch(attention_mma_kernel<D, NST>, grid, dim3(NTHREADS), smem, stream, p);
     return 0;
 }
 
+// Prompts (many query tiles, compute-bound): two stages. Decoding (one tile a sequence, bound by the latency of the
+// cache reads): four stages, so that three 64-key blocks are on their way while one is used.
+int g_attn_decode_stages = 4;
+
+template <int D>
+int launch(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t stream) {
+    if (max_tiles == 1 && D <= 64 && g_attn_decode_stages >= 4) return launch_stages<D, 4>(p, max_tiles, n_seqs, stream);
+    if (max_tiles == 1 && g_attn_decode_stages >= 3) return launch_stages<D, 3>(p, max_tiles, n_seqs, stream);
+    return launch_stages<D, 2>(p, max_tiles, n_seqs, stream);
+}
+
 }  // namespace
+
+// How many cp.async stages decoding uses (2, 3 or 4); returns the previous value.
+XS_API int xs_attention_mma_set_decode_stages(int n) {
+    const int old = g_attn_decode_stages;
+    g_attn_decode_stages = n;
+    return old;
+}
 
 // Scratch the split path needs, in bytes, for `rows` = tokens * heads.
 XS_API int64_t xs_attention_mma_scratch_bytes(int64_t rows, int D, int splits) {

@@ -26,6 +26,7 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int ROWS = 16;      // weight rows per CTA
 constexpr int UNROLL = 4;     // k blocks whose loads a warp issues together
+constexpr bool kBlocked = true;   // measured on B200: 3 % faster than interleaved on the wide shapes
 constexpr int K_PER_CTA = WARPS * UNROLL * 32;   // a K slice this long is one round of loads per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -50,7 +51,7 @@ struct SmallMParams {
     float* residual;
     float* partials;          // [tiles, ksplit, ROWS, 8 * NT] when ksplit > 1
     unsigned int* counters;   // [tiles], zero between calls
-    int M, N, K, ksplit, swiglu, blocked;
+    int M, N, K, ksplit, swiglu;
     int64_t ldx, ldw, ldo;
 };
 
@@ -86,7 +87,7 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
 }
 
 template <int NT, typename TO>
-__global__ void __launch_bounds__(WARPS * 32) gemm_small_m_kernel(const SmallMParams p) {
+__global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
     __shared__ bool last;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_small_m_kernel(const SmallMPa
     uint4 wa[UNROLL], wb[UNROLL];
     // k blocks of a round: warp w takes blocks w*ws + u*us. blocked (ws = UNROLL, us = 1): a warp's four loads
     // cover 256 consecutive bytes of a row; interleaved (ws = 1, us = WARPS): the CTA's warps cover them together.
-    const int ws = p.blocked ? UNROLL : 1, us = p.blocked ? 1 : WARPS;
+    constexpr int ws = kBlocked ? UNROLL : 1, us = kBlocked ? 1 : WARPS;
     int kb = kb_begin + warp * ws;
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -200,9 +201,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_small_m_kernel(const SmallMPa
 
 }  // namespace
 
-int g_small_m_blocked = 1;   // measured on B200: 3 % faster than interleaved on the wide shapes
-XS_API int xs_gemm_small_m_set_blocked(int on) { const int old = g_small_m_blocked; g_small_m_blocked = on; return old; }
-
 XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
     return M >= 1 && M <= 16 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
@@ -256,7 +254,6 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
     p.partials = nullptr;
     p.counters = nullptr;
     p.M = M; p.N = N; p.K = K; p.ksplit = ksplit; p.swiglu = swiglu;
-    p.blocked = g_small_m_blocked;
     p.ldx = ldx; p.ldw = ldw; p.ldo = ldo;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_small_m_scratch_bytes(M, N, ksplit);

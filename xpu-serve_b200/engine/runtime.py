@@ -59,6 +59,8 @@ class Runtime:
         self.shared: Dict[Tuple, object] = {}     # parts memoise what equal specs can share (tables)
         # cuBLAS may otherwise reduce split products in bfloat16
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        # decode attention cuts each sequence's keys over enough CTAs to fill this many CTA slots an SM
+        self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "2"))
         self.small_m = 16     # products with at most this many rows use this library's streaming kernel
         # Products with more rows: "library" (cuBLAS, the faster one today) or "tcgen05" (this library's
         # TMA + tensor-memory kernel, with the SwiGLU activation fused into its epilogue).

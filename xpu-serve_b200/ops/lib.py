@@ -8,6 +8,7 @@ be captured in a CUDA graph.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_double, c_float, c_int, c_int64, c_uint64, c_void_p
 from typing import Optional
 
@@ -83,6 +84,11 @@ def load(verbose: bool = True):
         except OSError as e:
             raise KernelError(f"the CUDA library {path} cannot be loaded: {e}") from None
         _signatures(lib)
+        # tuning switches, read once (defaults are what measured best on B200)
+        if "XS_ATTN_DECODE_STAGES" in os.environ:
+            lib.xs_attention_mma_set_decode_stages(int(os.environ["XS_ATTN_DECODE_STAGES"]))
+        if os.environ.get("XS_NO_PDL", "0") == "1":
+            lib.xs_set_pdl(0)
         _lib = lib
     return _lib
 

@@ -101,7 +101,7 @@ class AttentionMixer(Mixer):
             blocks = -(-step.max_kv_len // step.page_size)
             if s.window > 0:
                 blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
-            splits = max(1, min(blocks, 32, (2 * rt.sm_count) // max(tiles, 1)))
+            splits = max(1, min(blocks, 32, (rt.attn_split_factor * rt.sm_count) // max(tiles, 1)))
             scratch = None
             if splits > 1:
                 need = ops.attention_mma_scratch_bytes(q.shape[0] * s.heads, s.head_dim, splits)
