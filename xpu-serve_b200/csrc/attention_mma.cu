@@ -40,6 +40,7 @@ struct AttnParams {
     float* part_o;                   // [T * Hq, splits, D]
     float* part_ml;                  // [T * Hq, splits, 2]
     int Hq, Hkv, G, tokens_per_tile, window, splits;
+    int decode_rows;                 // every tile has at most 16 rows: the warps split the keys instead
     float scale_log2;
 };
 
@@ -271,6 +272,240 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
     }
 }
 
+// Decoding (at most 16 query rows a tile: one token's group of heads): the rows would keep a single warp
+// busy, so here the four warps split every 64-key block instead, 16 keys each, each with its own
+// running maximum, sum and output; they are merged through shared memory at the end. Everything else
+// (paging, masks, splits, zero-filled tails) is as in the kernel above.
+template <int D, int NST>
+__global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const AttnParams p) {
+    constexpr int LD = D + 8;
+    constexpr int KSTEPS = D / 16;
+    constexpr int DTILES = D / 8;
+    constexpr int CHUNKS = D / 8;
+    constexpr int QROWS = 16;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(smem_raw);    // [16][LD]
+    __nv_bfloat16* k_sm = q_sm + QROWS * LD;                             // [NST][BN][LD]
+    __nv_bfloat16* v_sm = k_sm + NST * BN * LD;                          // [NST][BN][LD]
+    __shared__ float sm_m[4][QROWS], sm_l[4][QROWS];
+    __shared__ int pages_sm[64];
+
+    pdl_launch_dependents();
+    // The step's description (lengths, page table) was copied to the device before the step began, and cached
+    // keys and values of earlier positions do not change during a step: this CTA's whole share of the cache is
+    // asked into L2 before waiting for the kernel that writes the current position's keys and values.
+    const int seq = blockIdx.y;
+    const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+    const int tok_begin = p.cu_seqlens[seq];
+    const int q_len = p.cu_seqlens[seq + 1] - tok_begin;
+    const int t0 = blockIdx.x * p.tokens_per_tile;
+    if (t0 >= q_len) return;
+    const int nt = min(p.tokens_per_tile, q_len - t0);
+    const int kv_len = p.kv_lens[seq];
+    const int pos0 = kv_len - q_len + t0;
+    const int hi = pos0 + nt;
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int b_lo = lo / BN, nb = (hi + BN - 1) / BN - b_lo;
+    const int bs = b_lo + (int)((int64_t)nb * split / p.splits);
+    const int be = b_lo + (int)((int64_t)nb * (split + 1) / p.splits);
+    const int32_t* table = p.page_table + (int64_t)seq * p.P;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.G;
+    const int rows_valid = nt * G;          // <= 16
+    {
+        constexpr int kLines = BN * D * 2 / 128;          // 128-byte lines of one block of keys (or values)
+        for (int b = bs; b < be; ++b) {
+            const int page = table[b];
+            if (page < 0) continue;
+            const __nv_bfloat16* kbase = p.pool + (((int64_t)page * 2 + 0) * p.Hkv + kvh) * BN * D;
+            const __nv_bfloat16* vbase = p.pool + (((int64_t)page * 2 + 1) * p.Hkv + kvh) * BN * D;
+            for (int i = threadIdx.x; i < 2 * kLines; i += NTHREADS) {
+                const __nv_bfloat16* at = (i < kLines ? kbase : vbase) + (i % kLines) * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(at));
+            }
+        }
+    }
+    pdl_wait();
+
+    // this CTA's page numbers in one coalesced read (in pieces of 64 blocks)
+    auto load_pages = [&](int from) {
+        __syncthreads();
+        if (threadIdx.x < 64 && from + (int)threadIdx.x < be) pages_sm[threadIdx.x] = table[from + threadIdx.x];
+        __syncthreads();
+    };
+    int pages_from = bs;
+    load_pages(pages_from);
+
+    for (int c = threadIdx.x; c < QROWS * CHUNKS; c += NTHREADS) {
+        const int r = c / CHUNKS, ch = c % CHUNKS;
+        const bool ok = r < rows_valid;
+        const int ti = ok ? r / G : 0, g = ok ? r % G : 0;
+        const __nv_bfloat16* src = p.q + ((int64_t)(tok_begin + t0 + ti) * p.Hq + kvh * G + g) * D + ch * 8;
+        cp_async16(q_sm + r * LD + ch * 8, src, ok);
+    }
+    auto load_block = [&](int b, int stage) {
+        const int page = pages_sm[b - pages_from];
+        const int page_at = max(page, 0);
+        const __nv_bfloat16* kbase = p.pool + (((int64_t)page_at * 2 + 0) * p.Hkv + kvh) * BN * D;
+        const __nv_bfloat16* vbase = p.pool + (((int64_t)page_at * 2 + 1) * p.Hkv + kvh) * BN * D;
+        __nv_bfloat16* ks = k_sm + stage * BN * LD;
+        __nv_bfloat16* vs = v_sm + stage * BN * LD;
+        for (int c = threadIdx.x; c < BN * CHUNKS; c += NTHREADS) {
+            const int r = c / CHUNKS, ch = c % CHUNKS;
+            const bool ok = page >= 0 && b * BN + r < hi;
+            cp_async16(ks + r * LD + ch * 8, kbase + (ok ? r * D + ch * 8 : 0), ok);
+            cp_async16(vs + r * LD + ch * 8, vbase + (ok ? r * D + ch * 8 : 0), ok);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < NST - 1; ++s) {
+        if (bs + s < be) load_block(bs + s, s);
+        cp_async_commit();
+    }
+
+    const int r1 = lane >> 2, r2 = r1 + 8;
+    const int pos1 = r1 < rows_valid ? pos0 + r1 / G : -1;
+    const int pos2 = r2 < rows_valid ? pos0 + r2 / G : -1;
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.0f, l2 = 0.0f;
+    unsigned qf[KSTEPS][4];
+    bool q_loaded = false;
+
+    for (int b = bs, it = 0; b < be; ++b, ++it) {
+        const int stage = it % NST;
+        cp_async_wait<NST - 2>();
+        __syncthreads();
+        const int nxt = b + NST - 1;
+        if (nxt < be) {
+            if (nxt - pages_from >= 64) {          // the page numbers held do not reach that far: refill (rare: > 4,096 keys a split)
+                cp_async_wait<0>();
+                pages_from = b;
+                load_pages(pages_from);
+            }
+            load_block(nxt, (it + NST - 1) % NST);
+        }
+        cp_async_commit();
+        if (!q_loaded) {
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk)
+                ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_sm + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+            q_loaded = true;
+        }
+        const __nv_bfloat16* ks = k_sm + stage * BN * LD + warp * 16 * LD;     // this warp's 16 keys of the block
+        const __nv_bfloat16* vs = v_sm + stage * BN * LD + warp * 16 * LD;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, ks + ((lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[0], qf[kk], b0, b1);
+            mma_bf16(s[1], qf[kk], b2, b3);
+        }
+        const int key0 = b * BN + warp * 16 + (lane & 3) * 2;
+        float mx1 = -INFINITY, mx2 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + i * 8 + e;
+                const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
+                const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
+                s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
+                s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
+                mx1 = fmaxf(mx1, s[i][e]);
+                mx2 = fmaxf(mx2, s[i][2 + e]);
+            }
+        }
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 1));
+        mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 2));
+        const float mn1 = fmaxf(m1, mx1), mn2 = fmaxf(m2, mx2);
+        const float base1 = mn1 == -INFINITY ? 0.0f : mn1, base2 = mn2 == -INFINITY ? 0.0f : mn2;
+        const float c1 = exp2f(m1 - base1), c2 = exp2f(m2 - base2);
+        m1 = mn1;
+        m2 = mn2;
+        l1 *= c1;
+        l2 *= c2;
+#pragma unroll
+        for (int i = 0; i < DTILES; ++i) {
+            o[i][0] *= c1;
+            o[i][1] *= c1;
+            o[i][2] *= c2;
+            o[i][3] *= c2;
+        }
+        unsigned pf[4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float p0 = exp2f(s[i][0] - base1), p1 = exp2f(s[i][1] - base1);
+            const float p2 = exp2f(s[i][2] - base2), p3 = exp2f(s[i][3] - base2);
+            l1 += p0 + p1;
+            l2 += p2 + p3;
+            pf[i * 2 + 0] = pack_bf16(p0, p1);
+            pf[i * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, vs + (((lane >> 3) & 1) * 8 + (lane & 7)) * LD + dp * 16 + (lane >> 4) * 8);
+            mma_bf16(o[2 * dp], pf, b0, b1);
+            mma_bf16(o[2 * dp + 1], pf, b2, b3);
+        }
+    }
+    cp_async_wait<0>();
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    l2 += __shfl_xor_sync(0xffffffffu, l2, 1);
+    l2 += __shfl_xor_sync(0xffffffffu, l2, 2);
+
+    // ---- merge the four warps: their outputs go through the (now idle) key stages
+    __syncthreads();
+    float* sm_o = reinterpret_cast<float*>(k_sm);          // [4][16][D]
+    if ((lane & 3) == 0) {
+        sm_m[warp][r1] = m1;
+        sm_l[warp][r1] = l1;
+        sm_m[warp][r2] = m2;
+        sm_l[warp][r2] = l2;
+    }
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+        float* d1 = sm_o + ((warp * QROWS + r1) * D) + i * 8 + (lane & 3) * 2;
+        float* d2 = sm_o + ((warp * QROWS + r2) * D) + i * 8 + (lane & 3) * 2;
+        d1[0] = o[i][0];
+        d1[1] = o[i][1];
+        d2[0] = o[i][2];
+        d2[1] = o[i][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows_valid * D; idx += NTHREADS) {
+        const int r = idx / D, d = idx % D;
+        float m = fmaxf(fmaxf(sm_m[0][r], sm_m[1][r]), fmaxf(sm_m[2][r], sm_m[3][r]));
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = sm_m[w][r] == -INFINITY ? 0.0f : exp2f(sm_m[w][r] - m);
+            l += sm_l[w][r] * f;
+            acc += sm_o[(w * QROWS + r) * D + d] * f;
+        }
+        const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+        const int64_t row = (int64_t)t * p.Hq + h;
+        if (p.splits == 1) {
+            float f = l > 0.0f ? 1.0f / l : 0.0f;
+            if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
+            p.out[row * D + d] = __float2bfloat16_rn(acc * f);
+        } else {
+            p.part_o[(row * p.splits + split) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[(row * p.splits + split) * 2 + 0] = m;
+                p.part_ml[(row * p.splits + split) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
 // out[row, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), times the head's gate. One warp per row; lane s holds
 // split s's (max, sum) and weight (splits <= 32), and the partial outputs are read with independent loads.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -324,8 +559,24 @@ int launch_stages(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t s
 // cache reads): four stages, so that three 64-key blocks are on their way while one is used.
 int g_attn_decode_stages = 4;
 
+template <int D, int NST>
+int launch_decode(const AttnParams& p, int n_seqs, cudaStream_t stream) {
+    constexpr int LD = D + 8;
+    const size_t smem = (size_t)(16 + 2 * NST * BN) * LD * sizeof(__nv_bfloat16);
+    static bool opted = false;
+    if (smem > 48 * 1024 && !opted) {
+        cudaFuncSetAttribute(attention_decode_mma_kernel<D, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        opted = true;
+    }
+    const dim3 grid(1, n_seqs, p.Hkv * p.splits);
+    xs_launch(attention_decode_mma_kernel<D, NST>, grid, dim3(NTHREADS), smem, stream, p);
+    return 0;
+}
+
 template <int D>
 int launch(const AttnParams& p, int max_tiles, int n_seqs, cudaStream_t stream) {
+    if (p.decode_rows && g_attn_decode_stages >= 3) return launch_decode<D, 3>(p, n_seqs, stream);
+    if (p.decode_rows) return launch_decode<D, 2>(p, n_seqs, stream);
     if (max_tiles == 1 && D <= 64 && g_attn_decode_stages >= 4) return launch_stages<D, 4>(p, max_tiles, n_seqs, stream);
     if (max_tiles == 1 && g_attn_decode_stages >= 3) return launch_stages<D, 3>(p, max_tiles, n_seqs, stream);
     return launch_stages<D, 2>(p, max_tiles, n_seqs, stream);
@@ -382,6 +633,7 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
     p.Hkv = Hkv;
     p.G = G;
     p.tokens_per_tile = BM / G;
+    p.decode_rows = (max_q_len == 1 && G <= 16) ? 1 : 0;
     p.window = window;
     p.splits = splits;
     p.scale_log2 = scale * 1.4426950408889634f;

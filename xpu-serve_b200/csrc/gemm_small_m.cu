@@ -51,7 +51,7 @@ struct SmallMParams {
     float* residual;
     float* partials;          // [tiles, ksplit, ROWS, 8 * NT] when ksplit > 1
     unsigned int* counters;   // [tiles], zero between calls
-    int M, N, K, ksplit, swiglu;
+    int M, N, K, ksplit, swiglu, wave;
     int64_t ldx, ldw, ldo;
 };
 
@@ -130,6 +130,27 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         wa[u] = in ? ld_stream(wa_p + k0) : zero;
         wb[u] = in ? ld_stream(wb_p + k0) : zero;
     }
+    if (kBlocked) {
+        // The rounds after the first are asked into L2 now (a hint, no registers held): when their loads are
+        // issued after the first round's multiplies they find the lines on the chip. A warp's round is 256
+        // consecutive bytes of each of its 16 rows: lane -> (row, which 128-byte line).
+        const int prow = min(n0 + (lane & 15), p.N - 1);
+        const __nv_bfloat16* pbase = p.w + (int64_t)prow * p.ldw + (lane >> 4) * 64;
+#pragma unroll 1
+        for (int r = 1; r <= 3; ++r) {
+            const int pkb = kb + r * WARPS * UNROLL;
+            if (pkb < kb_end && pkb * 32 + (lane >> 4) * 64 < p.K)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pbase + (int64_t)pkb * 32));
+        }
+        // More row tiles than CTAs that fit on the chip at once: also ask for the first round of the tile
+        // that will take this CTA's place (CTAs start in index order, `wave` of them at a time).
+        const int later = tile + p.wave;
+        if (p.wave > 0 && later < (int)gridDim.x) {
+            const int lrow = min(later * ROWS + (lane & 15), p.N - 1);
+            if (kb < kb_end && kb * 32 + (lane >> 4) * 64 < p.K)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + (int64_t)lrow * p.ldw + (lane >> 4) * 64 + (int64_t)kb * 32));
+        }
+    }
     pdl_wait();
     for (; kb - warp * ws < kb_end; kb += WARPS * UNROLL) {
         uint4 xv[UNROLL][NT];
@@ -201,6 +222,9 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
 
 }  // namespace
 
+// CTAs of this kernel that are resident on the device at once (4 an SM); 0 until the first launch asks the device.
+int g_small_m_wave = 0;
+
 XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
     return M >= 1 && M <= 16 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
@@ -210,10 +234,12 @@ XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
 XS_API int xs_gemm_small_m_ksplit(int M, int N, int K, int sms) {
     // Measured on B200 inside a CUDA graph (M 8): N 2048, K 8192 takes 24.5 us in one slice, 15.9 in two,
     // 11.4 in four; N 2048, K 2048 takes 7.4, 7.0, 6.1; N 16384, K 2048 gets slower with every slice.
+    // In the whole decode step (1.2B shape, batch 8): slicing K 2048 products makes the step slower, the
+    // K 8192 one is best in four slices.
     (void)M;
     const int tiles = ceil_div_i(N, ROWS);
     if (tiles >= 2 * sms) return 1;
-    int ks = K / 512;                 // at least 512 of K a slice
+    int ks = K / 2048;                // at least 2048 of K a slice
     if (ks > 4) ks = 4;
     return ks < 1 ? 1 : ks;
 }
@@ -245,6 +271,12 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
     XS_REQUIRE(!swiglu || (N % 16 == 0 && residual == nullptr), "gemm (few rows): the fused activation needs N %% 16 == 0");
     XS_REQUIRE(ksplit >= 1 && ksplit <= 64, "gemm (few rows): %d K slices", ksplit);
     const int tiles = ceil_div_i(N, ROWS);
+    if (g_small_m_wave == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        g_small_m_wave = sms > 0 ? 4 * sms : 592;
+    }
     SmallMParams p;
     p.x = (const __nv_bfloat16*)x;
     p.w = (const __nv_bfloat16*)w;
@@ -254,6 +286,7 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
     p.partials = nullptr;
     p.counters = nullptr;
     p.M = M; p.N = N; p.K = K; p.ksplit = ksplit; p.swiglu = swiglu;
+    p.wave = g_small_m_wave / ksplit;
     p.ldx = ldx; p.ldw = ldw; p.ldo = ldo;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_small_m_scratch_bytes(M, N, ksplit);
