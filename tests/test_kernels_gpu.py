@@ -30,6 +30,11 @@ def close(got, ref, dtype, factor=1.0):
     assert gap <= TOL[dtype] * factor, f"gap {gap:.3e}"
 
 
+def gap_ok(got, ref, rel=2e-2):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return (got - ref).abs().max().item() <= rel * ref.abs().max().item()
+
+
 def rms_norm(x, w, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
@@ -130,7 +135,7 @@ def test_silu_mul_interleaved_blocks_of_eight():
         ops().silu_mul(x, out, interleave=8)
         gg, uu = x.view(T, F // 8, 2, 8)[:, :, 0].reshape(T, F).double(), x.view(T, F // 8, 2, 8)[:, :, 1].reshape(T, F).double()
         close(out, gg / (1 + torch.exp(-gg)) * uu, dtype)
-        assert (out.double() - want).abs().max() < 0.1
+        assert gap_ok(out, want)            # and the layout is the intended one: close to the unrounded values too
 
 
 # ---------------------------------------------------------------------------- matrix products
