@@ -68,13 +68,19 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (2 ulp; -inf gives 0): the softmax weights are rounded to bfloat16 anyway
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
 template <int D, int NST>
-__global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2)) attention_mma_kernel(const AttnParams p) {
     constexpr int LD = D + 8;              // padded row: ldmatrix reads 8 rows without bank conflicts
     constexpr int KSTEPS = D / 16;         // k-steps of Q K^T
     constexpr int DTILES = D / 8;          // n-tiles of the output
@@ -86,7 +92,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
 
     pdl_launch_dependents();
     pdl_wait();
-    const int tile = blockIdx.x, seq = blockIdx.y;
+    // later tiles see more keys: they are started first, so that the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x, seq = blockIdx.y;
     const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
     const int tok_begin = p.cu_seqlens[seq];
     const int q_len = p.cu_seqlens[seq + 1] - tok_begin;
@@ -179,20 +186,35 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
                     mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
                 }
             }
-            // scale, mask, running max
+            // scale, mask, running max. A block that every row of the tile sees whole (all of it at or before
+            // the tile's first position and inside every row's window) needs no per-element test.
             const int key0 = b * BN + (lane & 3) * 2;
+            const bool whole = b * BN + BN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - b * BN < p.window);
             float mx1 = -INFINITY, mx2 = -INFINITY;
+            if (whole) {
 #pragma unroll
-            for (int i = 0; i < BN / 8; ++i) {
+                for (int i = 0; i < BN / 8; ++i) {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = key0 + i * 8 + e;
-                    const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
-                    const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
-                    s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
-                    s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
-                    mx1 = fmaxf(mx1, s[i][e]);
-                    mx2 = fmaxf(mx2, s[i][2 + e]);
+                    for (int e = 0; e < 2; ++e) {
+                        s[i][e] = pos1 >= 0 ? s[i][e] * p.scale_log2 : -INFINITY;
+                        s[i][2 + e] = pos2 >= 0 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
+                        mx1 = fmaxf(mx1, s[i][e]);
+                        mx2 = fmaxf(mx2, s[i][2 + e]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = key0 + i * 8 + e;
+                        const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
+                        const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
+                        s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
+                        s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
+                        mx1 = fmaxf(mx1, s[i][e]);
+                        mx2 = fmaxf(mx2, s[i][2 + e]);
+                    }
                 }
             }
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -201,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
             mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 2));
             const float mn1 = fmaxf(m1, mx1), mn2 = fmaxf(m2, mx2);
             const float base1 = mn1 == -INFINITY ? 0.0f : mn1, base2 = mn2 == -INFINITY ? 0.0f : mn2;
-            const float c1 = exp2f(m1 - base1), c2 = exp2f(m2 - base2);   // 0 while nothing was seen
+            const float c1 = fast_exp2(m1 - base1), c2 = fast_exp2(m2 - base2);   // 0 while nothing was seen
             m1 = mn1;
             m2 = mn2;
             l1 *= c1;
@@ -216,8 +238,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const AttnParam
             unsigned pf[BN / 16][4];
 #pragma unroll
             for (int i = 0; i < BN / 8; ++i) {
-                const float p0 = exp2f(s[i][0] - base1), p1 = exp2f(s[i][1] - base1);
-                const float p2 = exp2f(s[i][2] - base2), p3 = exp2f(s[i][3] - base2);
+                const float p0 = fast_exp2(s[i][0] - base1), p1 = fast_exp2(s[i][1] - base1);
+                const float p2 = fast_exp2(s[i][2] - base2), p3 = fast_exp2(s[i][3] - base2);
                 l1 += p0 + p1;
                 l2 += p2 + p3;
                 pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -425,7 +447,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
         mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 2));
         const float mn1 = fmaxf(m1, mx1), mn2 = fmaxf(m2, mx2);
         const float base1 = mn1 == -INFINITY ? 0.0f : mn1, base2 = mn2 == -INFINITY ? 0.0f : mn2;
-        const float c1 = exp2f(m1 - base1), c2 = exp2f(m2 - base2);
+        const float c1 = fast_exp2(m1 - base1), c2 = fast_exp2(m2 - base2);
         m1 = mn1;
         m2 = mn2;
         l1 *= c1;
@@ -440,8 +462,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
         unsigned pf[4];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const float p0 = exp2f(s[i][0] - base1), p1 = exp2f(s[i][1] - base1);
-            const float p2 = exp2f(s[i][2] - base2), p3 = exp2f(s[i][3] - base2);
+            const float p0 = fast_exp2(s[i][0] - base1), p1 = fast_exp2(s[i][1] - base1);
+            const float p2 = fast_exp2(s[i][2] - base2), p3 = fast_exp2(s[i][3] - base2);
             l1 += p0 + p1;
             l2 += p2 + p3;
             pf[i * 2 + 0] = pack_bf16(p0, p1);
@@ -486,7 +508,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
         float l = 0.0f, acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float f = sm_m[w][r] == -INFINITY ? 0.0f : exp2f(sm_m[w][r] - m);
+            const float f = sm_m[w][r] == -INFINITY ? 0.0f : fast_exp2(sm_m[w][r] - m);
             l += sm_l[w][r] * f;
             acc += sm_o[(w * QROWS + r) * D + d] * f;
         }
@@ -520,7 +542,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     const float ms = lane < splits ? ml[2 * lane] : -INFINITY;
     const float ls = lane < splits ? ml[2 * lane + 1] : 0.0f;
     const float m = warp_max(ms);
-    const float wgt = ms == -INFINITY ? 0.0f : exp2f(ms - m);     // this split's weight
+    const float wgt = ms == -INFINITY ? 0.0f : fast_exp2(ms - m);     // this split's weight
     const float l = warp_sum(ls * wgt);
     float f = l > 0.0f ? 1.0f / l : 0.0f;
     if (gate != nullptr) {
