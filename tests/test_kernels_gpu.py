@@ -206,7 +206,8 @@ def test_gemm_small_m_with_fused_activation(M):
 
 
 TC_SHAPES = [(1, 128, 64), (8, 256, 128), (16, 2048, 2048), (5, 100, 96), (33, 1000, 200), (64, 384, 512),
-             (130, 300, 264), (700, 1024, 2048), (2048, 512, 1024)]
+             (130, 300, 264), (700, 1024, 2048), (2048, 512, 1024), (100, 300, 256), (128, 128, 64),
+             (257, 2048, 2048), (1000, 6144, 512)]
 
 
 @pytest.mark.parametrize("T,N,K", TC_SHAPES)

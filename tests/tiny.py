@@ -5,7 +5,8 @@ option (layers, widths that are no power of two, heads and groups, head size, ta
 theta, eps, tied or untied head). R is the layout the reference's own loader reads:
 sandwich norms, a gate per head, partly rotated heads, a sliding layer whose window is
 shorter than the test prompts, 7 taps (tests/parity/model/make_tiny.py:113-140 of the
-reference). W adds to B's options a sliding layer with an odd window and two rope bases.
+reference). W adds to B's options a sliding layer with an odd window and two rope bases. X has
+widths that are no multiple of 8 and a head size that only the generic attention kernel takes.
 """
 import os
 
@@ -52,8 +53,18 @@ CONFIG_W = {
                         "sliding_attention": {"rope_theta": 77.0, "partial_rotary_factor": 0.67}},
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "R": CONFIG_R, "W": CONFIG_W}
-SEEDS = {"A": 0, "B": 1, "R": 2, "W": 3}
+# widths that are no multiple of 8 (none of the 16-byte vector paths applies), a vocabulary that is odd
+CONFIG_X = {
+    "model_type": "lfm3", "vocab_size": 1001, "hidden_size": 100, "intermediate_size": 250,
+    "num_hidden_layers": 3, "layer_types": ["conv", "full_attention", "conv"],
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 80,
+    "conv_L_cache": 5, "conv_bias": True, "norm_eps": 1e-5, "max_position_embeddings": 512,
+    "tie_word_embeddings": True, "use_sandwich_norm": False, "attn_head_gate": True,
+    "rope_parameters": {"full_attention": {"rope_theta": 5000.0, "partial_rotary_factor": 0.25}},
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "R": CONFIG_R, "W": CONFIG_W, "X": CONFIG_X}
+SEEDS = {"A": 0, "B": 1, "R": 2, "W": 3, "X": 4}
 # Plain N(0, sigma) weights give near-uniform attention and near-linear layers. These factors make the
 # parts matter: q and k large enough for peaked scores, taps and gates of order one.
 LIVELY = {"q_proj.weight": 6.0, "k_proj.weight": 6.0, "conv.conv.weight": 12.0, "gate_proj.weight": 8.0,

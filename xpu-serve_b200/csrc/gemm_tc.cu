@@ -289,6 +289,125 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Many tokens: a persistent kernel, one CTA an SM, each walking over output tiles (token tile fastest, so
+// that the CTAs running at one time share weight tiles in L2). Two accumulators in tensor memory: while the
+// epilogue warps drain tile i, the MMA warp already works on tile i + 1. The stage ring runs on across tiles.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                          const GemmTcParams p, int tiles_m, int tiles_n) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bar_full[STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base;
+    __shared__ int abort_flag;
+
+    constexpr uint32_t kTmemCols = 2 * BN;                       // 256 or 512: a power of two
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (p.K + BK - 1) / BK;
+    const int total = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4);           // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    pdl_launch_dependents();
+    pdl_wait();
+    volatile int* abort_p = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int t = blockIdx.x; t < total && !*abort_p; t += gridDim.x) {
+                const int tile_m = t / tiles_n, tile_n = t % tiles_n;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(smem_u32(&bar_empty[s]), ((it / STAGES) & 1) ^ 1, abort_p)) break;
+                    const uint32_t full = smem_u32(&bar_full[s]);
+                    mbar_expect_tx(full, Smem<BN>::kStageBytes);
+                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes), &tmap_w, kb * BK, tile_m * BM, full);
+                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes + Smem<BN>::kABytes), &tmap_x, kb * BK,
+                                tile_n * BN, full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            int it = 0, lt = 0;
+            for (int t = blockIdx.x; t < total && !*abort_p; t += gridDim.x, ++lt) {
+                const int buf = lt & 1;
+                // the epilogue must have drained this accumulator's previous tile
+                if (lt >= 2 && !mbar_wait(smem_u32(&bar_acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_p)) break;
+                tcgen05_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                bool ok = true;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&bar_full[s]), (it / STAGES) & 1, abort_p)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(ring + s * Smem<BN>::kStageBytes);
+                    const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + Smem<BN>::kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tcgen05_commit(smem_u32(&bar_empty[s]));
+                }
+                if (!ok) break;
+                tcgen05_commit(smem_u32(&bar_acc_full[buf]));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int lt = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
+            const int tile_m = t / tiles_n, tile_n = t % tiles_n, buf = lt & 1;
+            if (!mbar_wait(smem_u32(&bar_acc_full[buf]), (lt >> 1) & 1, abort_p)) break;
+            tcgen05_fence_after();
+            const int row = tile_m * BM + quarter * 32 + lane;
+            const float b = (p.bias != nullptr && row < p.N) ? p.bias[row] : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) emit<BN>(p, __uint_as_float(r[j]) + b, row, tile_n * BN + c + j, lane);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+}
+
 // ---- tensor maps -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -332,6 +451,24 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcParams& p, 
     return xs_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(kThreads), smem, stream, mw, mx, p) == cudaSuccess ? 0 : -1;
 }
 
+template <int BN, int STAGES>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcParams& p, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * Smem<BN>::kStageBytes + 1024;
+    static bool opted = false;
+    static int sms = 0;
+    if (!opted) {
+        cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        opted = true;
+    }
+    const int tiles_m = ceil_div_i(p.N, BM), tiles_n = ceil_div_i(p.T, BN);
+    const int grid = tiles_m * tiles_n < sms ? tiles_m * tiles_n : sms;
+    return xs_launch(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(kThreads), smem, stream, mw, mx, p, tiles_m,
+                     tiles_n) == cudaSuccess ? 0 : -1;
+}
+
 }  // namespace
 
 XS_API int xs_gemm_tc_supports(int T, int N, int K, int64_t ldx, int64_t ldw) {
@@ -339,7 +476,7 @@ XS_API int xs_gemm_tc_supports(int T, int N, int K, int64_t ldx, int64_t ldw) {
 }
 
 // The token tile the kernel uses for T tokens.
-XS_API int xs_gemm_tc_tile_n(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128; }
+XS_API int xs_gemm_tc_tile_n(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 XS_API int64_t xs_gemm_tc_scratch_bytes(int T, int N, int ksplit) {
     if (ksplit <= 1) return 0;
@@ -384,11 +521,13 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
     XS_REQUIRE(make_map(&mw, w, N, K, ldw, BM), "gemm (tcgen05): the weight's tensor map could not be made");
     XS_REQUIRE(make_map(&mx, x, T, K, ldx, bn), "gemm (tcgen05): the input's tensor map could not be made");
     int rc;
+    if (bn >= 128) XS_REQUIRE(ksplit == 1, "gemm (tcgen05): K slices are for at most 64 tokens");
     switch (bn) {
         case 16: rc = launch<16, 8>(mw, mx, p, stream); break;
         case 32: rc = launch<32, 8>(mw, mx, p, stream); break;
         case 64: rc = launch<64, 6>(mw, mx, p, stream); break;
-        default: rc = launch<128, 3>(mw, mx, p, stream); break;
+        case 128: rc = launch_persistent<128, 6>(mw, mx, p, stream); break;
+        default: rc = launch_persistent<256, 4>(mw, mx, p, stream); break;
     }
     XS_REQUIRE(rc == 0, "gemm (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return 0;
