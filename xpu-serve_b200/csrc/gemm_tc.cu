@@ -48,6 +48,7 @@ struct GemmTcParams {
     unsigned int* counters;   // [tiles_m * tiles_n], zero between calls
     int* status;              // set non-zero when a wait gave up
     int T, N, K, ksplit, epilogue, out_f32;
+    int vec;                  // rows of out start on 16-byte boundaries: the many-token epilogue may store vectors
     int64_t ldo;
 };
 
@@ -144,6 +145,94 @@ __device__ __forceinline__ void emit(const GemmTcParams& p, float v, int row, in
     if (p.epilogue == EPI_RESIDUAL) ((float*)p.out)[at] += v;
     else if (p.out_f32) ((float*)p.out)[at] = v;
     else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// The many-token kernels keep tokens on the MMA's M side (lane = token, column = weight row), so a thread
+// holds neighbouring outputs of one token and stores them as vectors. Sixteen of them, starting at weight
+// row f0 (a multiple of 16), leave here through the chosen epilogue.
+__device__ __forceinline__ void emit16(const GemmTcParams& p, const uint32_t* r, int token, int f0) {
+    if (token >= p.T || f0 >= p.N) return;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+    const bool full = f0 + 16 <= p.N;
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (full || f0 + j < p.N) v[j] += __ldg(p.bias + f0 + j);
+    }
+    if (p.epilogue == EPI_SWIGLU) {   // rows f0..f0+7 are gates, f0+8..f0+15 their up rows; N is a multiple of 16
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = v[j] / (1.0f + __expf(-v[j])) * v[j + 8];
+        const int64_t at = (int64_t)token * p.ldo + (f0 >> 1);
+        if (p.out_f32) {
+            float* o = (float*)p.out + at;
+            if (p.vec) {
+                ((float4*)o)[0] = make_float4(a[0], a[1], a[2], a[3]);
+                ((float4*)o)[1] = make_float4(a[4], a[5], a[6], a[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = a[j];
+            }
+        } else {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + at;
+            if (p.vec) {
+                *(uint4*)o = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(a[j]);
+            }
+        }
+        return;
+    }
+    const int64_t at = (int64_t)token * p.ldo + f0;
+    if (p.epilogue == EPI_RESIDUAL || p.out_f32) {
+        float* o = (float*)p.out + at;
+        const bool add = p.epilogue == EPI_RESIDUAL;
+        if (p.vec && full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 w = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                if (add) {
+                    const float4 old = ((const float4*)o)[q];
+                    w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
+                }
+                ((float4*)o)[q] = w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (f0 + j < p.N) o[j] = add ? o[j] + v[j] : v[j];
+        }
+        return;
+    }
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + at;
+    if (p.vec && full) {
+        ((uint4*)o)[0] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        ((uint4*)o)[1] = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]), pack_bf16(v[14], v[15]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (f0 + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+    }
 }
 
 template <int BN, int STAGES>
@@ -294,12 +383,14 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // Many tokens: a persistent kernel, one CTA an SM, each walking over output tiles (token tile fastest, so
-// that the CTAs running at one time share weight tiles in L2). Two accumulators in tensor memory: while the
-// epilogue warps drain tile i, the MMA warp already works on tile i + 1. The stage ring runs on across tiles.
+// that the CTAs running at one time share weight tiles in L2). Here the tokens ride the M side (128 a tile)
+// and the weight's rows the N side (BN a tile): a thread of the epilogue then holds neighbouring outputs of
+// one token and stores 16 bytes at a time. Two accumulators in tensor memory: while the epilogue warps drain
+// tile i, the MMA warp already works on tile i + 1. The stage ring runs on across tiles.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                          const GemmTcParams p, int tiles_m, int tiles_n) {
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                          const GemmTcParams p, int tiles_tok, int tiles_f) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -312,7 +403,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     constexpr uint32_t kTmemCols = 2 * BN;                       // 256 or 512: a power of two
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (p.K + BK - 1) / BK;
-    const int total = tiles_m * tiles_n;
+    const int total = tiles_tok * tiles_f;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -341,15 +432,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         if (lane == 0) {
             int it = 0;
             for (int t = blockIdx.x; t < total && !*abort_p; t += gridDim.x) {
-                const int tile_m = t / tiles_n, tile_n = t % tiles_n;
+                const int tile_f = t / tiles_tok, tile_tok = t % tiles_tok;
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(smem_u32(&bar_empty[s]), ((it / STAGES) & 1) ^ 1, abort_p)) break;
                     const uint32_t full = smem_u32(&bar_full[s]);
                     mbar_expect_tx(full, Smem<BN>::kStageBytes);
-                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes), &tmap_w, kb * BK, tile_m * BM, full);
-                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes + Smem<BN>::kABytes), &tmap_x, kb * BK,
-                                tile_n * BN, full);
+                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes), &tmap_x, kb * BK, tile_tok * BM, full);
+                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes + Smem<BN>::kABytes), &tmap_w, kb * BK,
+                                tile_f * BN, full);
                 }
             }
         }
@@ -383,17 +474,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         const int quarter = warp & 3;
         int lt = 0;
         for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
-            const int tile_m = t / tiles_n, tile_n = t % tiles_n, buf = lt & 1;
+            const int tile_f = t / tiles_tok, tile_tok = t % tiles_tok, buf = lt & 1;
             if (!mbar_wait(smem_u32(&bar_acc_full[buf]), (lt >> 1) & 1, abort_p)) break;
             tcgen05_fence_after();
-            const int row = tile_m * BM + quarter * 32 + lane;
-            const float b = (p.bias != nullptr && row < p.N) ? p.bias[row] : 0.0f;
+            const int token = tile_tok * BM + quarter * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) emit<BN>(p, __uint_as_float(r[j]) + b, row, tile_n * BN + c + j, lane);
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                emit16(p, r, token, tile_f * BN + c);
+                emit16(p, r + 16, token, tile_f * BN + c + 16);
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -404,6 +494,202 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+}
+
+// ---- CTA pairs (cta_group::2) ---------------------------------------------------------------------------
+// Two CTAs of a cluster, on neighbouring SMs, work on one 256 x 256 output tile: each loads 128 of its
+// tokens and 128 of its weight rows per k block (32 KB instead of the 48 KB a lone CTA loads for a 128 x 256
+// tile: a third less traffic from L2, and fewer TMA rows, per flop), the leader's MMA thread issues
+// tcgen05.mma.cta_group::2 with M = 256, which reads both CTAs' shared memory and writes rows 0-127 of the
+// accumulator to the leader's tensor memory and rows 128-255 to its peer's. Barriers: both producers' loads
+// complete on the leader's full barrier; tcgen05.commit with multicast hands a stage back to both producers
+// and the accumulator to both CTAs' epilogue warps; the epilogue warps of both CTAs arrive on the leader's
+// accumulator-empty barrier. No load is multicast.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// The shared::cluster address of `addr` (a shared::cta address here) in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// A load into this CTA's shared memory whose bytes are counted on a barrier that may be the peer's.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+// Arrives, once the MMAs issued so far are complete, on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Instruction descriptor of the pair's MMA: M = 256 over both CTAs, N = 256.
+__host__ __device__ constexpr uint32_t instr_desc_pair() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+constexpr int kPairTile = 256;                               // weight rows and tokens of a pair's tile
+constexpr int kPairStageBytes = 2 * BM * BK * 2;             // per CTA: 128 weight rows and 128 tokens, 64 k each
+
+template <int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                    const GemmTcParams p, int tiles_tok, int tiles_f) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bar_full[STAGES];       // used in the leader only
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];      // one set per CTA, signalled by the leader's commits
+    __shared__ __align__(8) uint64_t bar_acc_full[2];        // one set per CTA
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];       // used in the leader only: 8 epilogue warps arrive
+    __shared__ uint32_t tmem_base;
+    __shared__ int abort_flag;
+
+    constexpr uint32_t kTmemCols = 512;                      // two accumulators of 256 columns
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int n_kb = (p.K + BK - 1) / BK;
+    const int total = tiles_tok * tiles_f;
+    const int first = (int)cluster_id_x(), step = (int)cluster_count_x();
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 8);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                      // the peer's barriers exist before anything signals them
+    tcgen05_fence_after();
+    pdl_launch_dependents();
+    pdl_wait();
+    volatile int* abort_p = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int t = first; t < total && !*abort_p; t += step) {
+                const int tile_f = t / tiles_tok, tile_tok = t % tiles_tok;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait_cluster(smem_u32(&bar_empty[s]), ((it / STAGES) & 1) ^ 1, abort_p)) break;
+                    if (leader) mbar_expect_tx(smem_u32(&bar_full[s]), 2 * kPairStageBytes);
+                    const uint32_t full = map_to_rank(smem_u32(&bar_full[s]), 0);
+                    const uint32_t dst = smem_u32(ring + s * kPairStageBytes);
+                    tma_load_2d_pair(dst, &tmap_x, kb * BK, tile_tok * kPairTile + (int)rank * BM, full);
+                    tma_load_2d_pair(dst + BM * BK * 2, &tmap_w, kb * BK, tile_f * kPairTile + (int)rank * BM, full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = instr_desc_pair();
+            int it = 0, lt = 0;
+            for (int t = first; t < total && !*abort_p; t += step, ++lt) {
+                const int buf = lt & 1;
+                // both CTAs' epilogue warps must have drained this accumulator's previous tile
+                if (lt >= 2 && !mbar_wait_cluster(smem_u32(&bar_acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_p)) break;
+                tcgen05_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * kPairTile);
+                bool ok = true;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_cluster(smem_u32(&bar_full[s]), (it / STAGES) & 1, abort_p)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(ring + s * kPairStageBytes);
+                    const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16_pair(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tcgen05_commit_pair(smem_u32(&bar_empty[s]));
+                }
+                if (!ok) break;
+                tcgen05_commit_pair(smem_u32(&bar_acc_full[buf]));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int lt = 0;
+        for (int t = first; t < total; t += step, ++lt) {
+            const int tile_f = t / tiles_tok, tile_tok = t % tiles_tok, buf = lt & 1;
+            if (!mbar_wait_cluster(smem_u32(&bar_acc_full[buf]), (lt >> 1) & 1, abort_p)) break;
+            tcgen05_fence_after();
+            const int token = tile_tok * kPairTile + (int)rank * BM + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < kPairTile; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kPairTile + c), r);
+                emit16(p, r, token, tile_f * kPairTile + c);
+                emit16(p, r + 16, token, tile_f * kPairTile + c + 16);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bar_acc_empty[buf]), 0));
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    cluster_sync_all();                                      // neither CTA frees or leaves while its peer still works
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
 }
@@ -452,7 +738,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcParams& p, 
 }
 
 template <int BN, int STAGES>
-int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcParams& p, cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTcParams& p, cudaStream_t stream) {
     const size_t smem = (size_t)STAGES * Smem<BN>::kStageBytes + 1024;
     static bool opted = false;
     static int sms = 0;
@@ -463,13 +749,61 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         opted = true;
     }
-    const int tiles_m = ceil_div_i(p.N, BM), tiles_n = ceil_div_i(p.T, BN);
-    const int grid = tiles_m * tiles_n < sms ? tiles_m * tiles_n : sms;
-    return xs_launch(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(kThreads), smem, stream, mw, mx, p, tiles_m,
-                     tiles_n) == cudaSuccess ? 0 : -1;
+    const int tiles_tok = ceil_div_i(p.T, BM), tiles_f = ceil_div_i(p.N, BN);
+    const int grid = tiles_tok * tiles_f < sms ? tiles_tok * tiles_f : sms;
+    return xs_launch(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(kThreads), smem, stream, mx, mw, p, tiles_tok,
+                     tiles_f) == cudaSuccess ? 0 : -1;
+}
+
+int g_pair = 1;   // CTA pairs for more than 128 tokens (xs_gemm_tc_set_pair)
+
+template <int STAGES>
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTcParams& p, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * kPairStageBytes + 1024;
+    static bool opted = false;
+    static int max_pairs = 0;
+    if (!opted) {
+        cudaFuncSetAttribute(gemm_tc_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        // how many pairs can run at one time: SMs pair up inside a GPC only
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(2 * (sms / 2));
+        probe.blockDim = dim3(kThreads);
+        probe.dynamicSmemBytes = smem;
+        cudaLaunchAttribute a[1];
+        a[0].id = cudaLaunchAttributeClusterDimension;
+        a[0].val.clusterDim.x = 2; a[0].val.clusterDim.y = 1; a[0].val.clusterDim.z = 1;
+        probe.attrs = a;
+        probe.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<STAGES>, &probe) != cudaSuccess || clusters < 1)
+            clusters = sms / 2;
+        max_pairs = clusters < sms / 2 ? clusters : sms / 2;
+        cudaGetLastError();
+        opted = true;
+    }
+    const int tiles_tok = ceil_div_i(p.T, kPairTile), tiles_f = ceil_div_i(p.N, kPairTile);
+    const int pairs = tiles_tok * tiles_f < max_pairs ? tiles_tok * tiles_f : max_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_xs_pdl ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<STAGES>, mx, mw, p, tiles_tok, tiles_f) == cudaSuccess ? 0 : -1;
 }
 
 }  // namespace
+
+XS_API void xs_gemm_tc_set_pair(int on) { g_pair = on ? 1 : 0; }
 
 XS_API int xs_gemm_tc_supports(int T, int N, int K, int64_t ldx, int64_t ldw) {
     return T >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && encode_fn() != nullptr;
@@ -508,6 +842,7 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
     p.status = status;
     p.T = T; p.N = N; p.K = K; p.ksplit = ksplit; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
     p.ldo = ldo;
+    p.vec = 0;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_tc_scratch_bytes(T, N, ksplit);
         const int64_t tiles = (int64_t)ceil_div_i(N, BM) * ceil_div_i(T, bn);
@@ -518,16 +853,28 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
         p.counters = (unsigned int*)((char*)scratch + scratch_bytes - 65536);
     }
     alignas(64) CUtensorMap mw, mx;
-    XS_REQUIRE(make_map(&mw, w, N, K, ldw, BM), "gemm (tcgen05): the weight's tensor map could not be made");
-    XS_REQUIRE(make_map(&mx, x, T, K, ldx, bn), "gemm (tcgen05): the input's tensor map could not be made");
     int rc;
-    if (bn >= 128) XS_REQUIRE(ksplit == 1, "gemm (tcgen05): K slices are for at most 64 tokens");
-    switch (bn) {
-        case 16: rc = launch<16, 8>(mw, mx, p, stream); break;
-        case 32: rc = launch<32, 8>(mw, mx, p, stream); break;
-        case 64: rc = launch<64, 6>(mw, mx, p, stream); break;
-        case 128: rc = launch_persistent<128, 6>(mw, mx, p, stream); break;
-        default: rc = launch_persistent<256, 4>(mw, mx, p, stream); break;
+    if (T <= 64) {
+        // few tokens: the weight's rows on the M side, the tokens a narrow N
+        XS_REQUIRE(make_map(&mw, w, N, K, ldw, BM), "gemm (tcgen05): the weight's tensor map could not be made");
+        XS_REQUIRE(make_map(&mx, x, T, K, ldx, bn), "gemm (tcgen05): the input's tensor map could not be made");
+        switch (bn) {
+            case 16: rc = launch<16, 8>(mw, mx, p, stream); break;
+            case 32: rc = launch<32, 8>(mw, mx, p, stream); break;
+            default: rc = launch<64, 6>(mw, mx, p, stream); break;
+        }
+    } else {
+        // many tokens: the tokens on the M side, 128 or 256 weight rows on the N side; pairs of CTAs beyond 128 tokens
+        XS_REQUIRE(ksplit == 1, "gemm (tcgen05): K slices are for at most 64 tokens");
+        const int esz = p.out_f32 ? 4 : 2;
+        p.vec = ((uintptr_t)out % 16 == 0) && ((ldo * esz) % 16 == 0);
+        const bool pair = T > 128 && g_pair;
+        const int box_w = (pair || N <= 128) ? 128 : 256;
+        XS_REQUIRE(make_map(&mx, x, T, K, ldx, BM), "gemm (tcgen05): the input's tensor map could not be made");
+        XS_REQUIRE(make_map(&mw, w, N, K, ldw, box_w), "gemm (tcgen05): the weight's tensor map could not be made");
+        if (pair) rc = launch_pair<6>(mx, mw, p, stream);
+        else if (box_w == 128) rc = launch_persistent<128, 6>(mx, mw, p, stream);
+        else rc = launch_persistent<256, 4>(mx, mw, p, stream);
     }
     XS_REQUIRE(rc == 0, "gemm (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return 0;

@@ -89,6 +89,8 @@ def load(verbose: bool = True):
             lib.xs_attention_mma_set_decode_stages(int(os.environ["XS_ATTN_DECODE_STAGES"]))
         if os.environ.get("XS_NO_PDL", "0") == "1":
             lib.xs_set_pdl(0)
+        if os.environ.get("XS_TC_NO_PAIR", "0") == "1":
+            lib.xs_gemm_tc_set_pair(0)
         _lib = lib
     return _lib
 
