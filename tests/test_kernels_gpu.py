@@ -381,7 +381,7 @@ def run_attention(lib, pg, kernel, scale, window, gate, splits):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("D,pairs,Hq,Hkv", [(16, 8, 4, 2), (48, 12, 6, 3), (64, 32, 8, 8), (128, 20, 2, 1), (256, 128, 2, 1)])
+@pytest.mark.parametrize("D,pairs,Hq,Hkv", [(16, 8, 4, 2), (32, 16, 3, 1), (48, 12, 6, 3), (64, 32, 8, 8), (128, 20, 2, 1), (256, 128, 2, 1)])
 def test_qk_norm_rope_store(dtype, D, pairs, Hq, Hkv):
     lib = ops()
     pg = Paged([0, 70, 5], [9, 1, 66], Hq, Hkv, D, dtype)
@@ -481,6 +481,43 @@ def test_short_conv_in_steps_equals_one_pass(dtype, H, K):
     ext = torch.cat([torch.zeros(K - 1, H, dtype=torch.float64), g], 0)
     flipped = x[:, H:2 * H] * (sum(taps[:, K - 1 - j].double()[None, :] * ext[j:j + 12] for j in range(K)) + bias.double())
     assert (got[2].double().cpu() - flipped).abs().max() > 0.5
+
+
+@pytest.mark.parametrize("K", [2, 3, 4, 5])
+def test_short_conv_long_prompts(K):
+    """Long ragged prompts take the kernel in which a thread walks several tokens: sequences that start inside
+    a thread's run, a run that ends past the last token, and a second step that continues from the state."""
+    lib = ops()
+    H = 1024
+    steps = [[900, 3, 1, 1499], [1201, 2, 6, 1000]]
+    totals = [sum(st[s] for st in steps) for s in range(4)]
+    bcx_all = [(torch.randn(n, 3 * H) * 2).to(torch.bfloat16) for n in totals]
+    taps, bias = torch.randn(H, K), torch.randn(H)
+    w_t = taps.t().contiguous().to(DEV)
+    slots = [2, 0, 5, 3]
+    state = (torch.randn(6, K - 1, H, device=DEV) * 40).to(torch.bfloat16)
+    lib.zero_rows(state, torch.tensor(slots, dtype=torch.int32, device=DEV))
+    guard = state[[1, 4]].clone()
+    got = [torch.empty(n, H, device=DEV, dtype=torch.bfloat16) for n in totals]
+    at = [0, 0, 0, 0]
+    for lens in steps:
+        bcx = torch.cat([bcx_all[s][at[s]:at[s] + n] for s, n in enumerate(lens)], 0).to(DEV)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+        seq_of = torch.tensor(np.repeat(np.arange(4), lens), dtype=torch.int32, device=DEV)
+        out = torch.full((sum(lens), H), float("nan"), device=DEV, dtype=torch.bfloat16)
+        lib.short_conv(bcx, w_t, bias.to(DEV), state, seq_of, cu, torch.tensor(slots, dtype=torch.int32, device=DEV), out)
+        o = 0
+        for s, n in enumerate(lens):
+            got[s][at[s]:at[s] + n] = out[o:o + n]
+            at[s] += n
+            o += n
+    for s in range(4):
+        x = bcx_all[s].double()
+        g = (x[:, :H] * x[:, 2 * H:]).to(torch.bfloat16).double()
+        ext = torch.cat([torch.zeros(K - 1, H, dtype=torch.float64), g], 0)
+        conv = sum(taps[:, j].double()[None, :] * ext[j:j + x.shape[0]] for j in range(K)) + bias.double()
+        close(got[s], x[:, H:2 * H] * conv, "bfloat16", factor=4)
+    assert torch.equal(state[[1, 4]], guard)
 
 
 def test_argmax_ties_and_width():

@@ -92,6 +92,95 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, int64_t ld,
     }
 }
 
+// bfloat16, head sizes 16, 32, 64, 128, 256: a thread owns 8 neighbouring channels (one 16-byte load and
+// store), the D / 8 threads of a head are neighbours in a warp; the sum of squares and the partner channels
+// (i and i + D / 2 sit D / 16 lanes apart) travel by shuffles.
+template <int D>
+__global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int64_t ld, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ pool,
+    const int32_t* __restrict__ page_table, int P, const int32_t* __restrict__ seq_of_token,
+    const int32_t* __restrict__ positions, const float* __restrict__ q_w, const float* __restrict__ k_w,
+    const float2* __restrict__ rope, int Tn, int Hq, int Hkv, int page_size, float eps, int write_kv) {
+    constexpr int G = D / 8;        // threads of a head
+    constexpr int half = D / 2;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int heads_total = Hq + (write_kv ? 2 * Hkv : 0);
+    const int64_t thread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = thread / G;
+    const int part = (int)(thread % G);
+    const bool live = item < (int64_t)Tn * heads_total;     // dead threads still take part in the shuffles
+    const int t = live ? (int)(item / heads_total) : 0;
+    const int hh = live ? (int)(item % heads_total) : 0;
+    const int pos = positions[t];
+    const int c0 = part * 8;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(qkv + (int64_t)t * ld + (int64_t)hh * D + c0);
+
+    __nv_bfloat16* dst;
+    const float* w;
+    bool rotate;
+    if (hh < Hq) {
+        dst = q_out + ((int64_t)t * Hq + hh) * D + c0;
+        w = q_w;
+        rotate = true;
+    } else {
+        const int kvh = (hh - Hq) % Hkv;
+        const int which = (hh - Hq) / Hkv;
+        const int seq = seq_of_token[t];
+        const int page = page_table[(int64_t)seq * P + pos / page_size];
+        dst = pool + ((((int64_t)page * 2 + which) * Hkv + kvh) * page_size + pos % page_size) * D + c0;
+        w = which == 0 ? k_w : nullptr;
+        rotate = which == 0;
+    }
+    float x[8];
+    {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            x[2 * j] = f.x;
+            x[2 * j + 1] = f.y;
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (rotate && w != nullptr) {
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        const float4 w0 = *reinterpret_cast<const float4*>(w + c0), w1 = *reinterpret_cast<const float4*>(w + c0 + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * wv[j];
+    }
+    // the partner's 8 channels: i + D/2 for the lower half, i - D/2 for the upper half
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = G > 1 ? __shfl_xor_sync(0xffffffffu, x[j], G / 2) : 0.0f;
+    if (rotate && rope != nullptr) {
+        const bool low = c0 < half;
+        const float2* cs = rope + (int64_t)pos * half + (low ? c0 : c0 - half);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float2 a = cs[j];
+            // low: x1 cos - x2 sin with x1 = x, x2 = y; high: x2 cos + x1 sin with x2 = x, x1 = y
+            x[j] = low ? x[j] * a.x - y[j] * a.y : x[j] * a.x + y[j] * a.y;
+        }
+    }
+    if (!live) return;
+    if (rotate) {
+        uint4 o;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+        *reinterpret_cast<uint4*>(dst) = o;
+    } else {
+        *reinterpret_cast<uint4*>(dst) = raw;     // values: a plain copy
+    }
+}
+
 // One warp per (token, q head). Scores with lanes over keys, weighted sum with lanes over channels.
 template <typename T>
 __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ pool,
@@ -177,6 +266,27 @@ XS_API int xs_qk_norm_rope_store(const void* qkv, int64_t ld, void* q_out, void*
     XS_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "qk_norm_rope: %d heads over %d kv heads", Hq, Hkv);
     XS_REQUIRE(!write_kv || (pool != nullptr && page_table != nullptr && P > 0), "qk_norm_rope: no cache to write to");
     const int64_t items = (int64_t)T * (Hq + (write_kv ? 2 * Hkv : 0));
+    // bfloat16 with 16-byte rows everywhere and a head size whose halves sit a power of two of lanes apart
+    const bool vec = dtype == XS_BF16 && (D == 16 || D == 32 || D == 64 || D == 128 || D == 256) && ld % 8 == 0 &&
+                     (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (!write_kv || (uintptr_t)pool % 16 == 0) &&
+                     (q_w == nullptr || (uintptr_t)q_w % 16 == 0) && (k_w == nullptr || (uintptr_t)k_w % 16 == 0);
+    if (vec) {
+        const int vblocks = ceil_div_i(items * (D / 8), 256);
+#define XS_ROPE_VEC(DD)                                                                                            \
+    xs_launch(qk_norm_rope_store_vec_kernel<DD>, dim3(vblocks), dim3(256), 0, stream, (const __nv_bfloat16*)qkv, ld, \
+              (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, page_table, P, seq_of_token, positions, q_w, k_w,        \
+              (const float2*)rope, T, Hq, Hkv, page_size, eps, write_kv)
+        switch (D) {
+            case 16: XS_ROPE_VEC(16); break;
+            case 32: XS_ROPE_VEC(32); break;
+            case 64: XS_ROPE_VEC(64); break;
+            case 128: XS_ROPE_VEC(128); break;
+            default: XS_ROPE_VEC(256); break;
+        }
+#undef XS_ROPE_VEC
+        XS_LAUNCH_CHECK("qk_norm_rope_store");
+        return 0;
+    }
     const int blocks = ceil_div_i(items, 4);
     XS_DISPATCH_DTYPE(dtype, TT,
                       xs_launch(qk_norm_rope_store_kernel<TT>, dim3(blocks), dim3(128), 0, stream,

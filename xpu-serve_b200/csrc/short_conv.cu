@@ -128,6 +128,70 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
     *reinterpret_cast<uint4*>(out + (int64_t)t * H + c8) = pack8(acc);
 }
 
+// Long prompts: a thread walks RUN neighbouring tokens of its 8 channels with the last KT-1 gated inputs in
+// registers, so that B, C and X of a token are read once (not once per tap) and the taps once per thread.
+// At the run's first token, and wherever a sequence starts inside the run, the history is fetched as the
+// plain kernel does (state rows, or earlier tokens of the same sequence).
+template <int KT, int RUN>
+__global__ void __launch_bounds__(256) short_conv_bf16x8_run_kernel(
+    const __nv_bfloat16* __restrict__ bcx, int64_t ld, const float* __restrict__ w_t, const float* __restrict__ bias,
+    const __nv_bfloat16* __restrict__ state, const int32_t* __restrict__ seq_of_token,
+    const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots, __nv_bfloat16* __restrict__ out, int Tn,
+    int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int H8 = H >> 3;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int run = (int)(idx / H8), c8 = (int)(idx % H8) * 8;
+    const int t0 = run * RUN;
+    if (t0 >= Tn) return;
+    float w[KT][8], b0[8];
+#pragma unroll
+    for (int j = 0; j < KT; ++j) {
+        const float4 w0 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8);
+        const float4 w1 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8 + 4);
+        w[j][0] = w0.x; w[j][1] = w0.y; w[j][2] = w0.z; w[j][3] = w0.w;
+        w[j][4] = w1.x; w[j][5] = w1.y; w[j][6] = w1.z; w[j][7] = w1.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) b0[k] = bias != nullptr ? bias[c8 + k] : 0.0f;
+    float hist[KT - 1][8];
+#pragma unroll
+    for (int i = 0; i < RUN; ++i) {
+        const int t = t0 + i;
+        if (t >= Tn) break;
+        const int seq = seq_of_token[t];
+        const int first = cu_seqlens[seq];
+        const int t_local = t - first;
+        if (i == 0 || t_local == 0) {
+            const __nv_bfloat16* st = state + (int64_t)slots[seq] * (KT - 1) * H;
+#pragma unroll
+            for (int j = 0; j < KT - 1; ++j) {
+                const int r = t_local + j;
+                if (r < KT - 1) unpack8(*reinterpret_cast<const uint4*>(st + (int64_t)r * H + c8), hist[j]);
+                else gated8(bcx + ((int64_t)first + r - (KT - 1)) * ld, c8, H, hist[j]);
+            }
+        }
+        float g[8], acc[8], c[8];
+        gated8(bcx + (int64_t)t * ld, c8, H, g);
+        unpack8(*reinterpret_cast<const uint4*>(bcx + (int64_t)t * ld + H + c8), c);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float a = b0[k];
+#pragma unroll
+            for (int j = 0; j < KT - 1; ++j) a = fmaf(w[j][k], hist[j][k], a);   // taps in the plain kernel's order
+            acc[k] = fmaf(w[KT - 1][k], g[k], a) * c[k];
+        }
+        *reinterpret_cast<uint4*>(out + (int64_t)t * H + c8) = pack8(acc);
+#pragma unroll
+        for (int j = 0; j + 1 < KT - 1; ++j)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) hist[j][k] = hist[j + 1][k];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) hist[KT - 2][k] = g[k];
+    }
+}
+
 // Every sequence brings one token: the thread that owns (sequence, 8 channels) reads the state's
 // K-1 rows, computes the output and writes the shifted state, in one kernel.
 __global__ void short_conv_decode_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, int64_t ld,
@@ -189,9 +253,26 @@ XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const fl
         return 0;
     }
     if (vec) {
-        short_conv_bf16x8_kernel<<<ceil_div_i((int64_t)T * (H / 8), 256), 256, 0, stream>>>(
-            (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots,
-            (__nv_bfloat16*)out, T, H, K);
+        constexpr int RUN = 4;
+        const int64_t run_threads = (int64_t)ceil_div_i(T, RUN) * (H / 8);
+        if (K >= 2 && K <= 5 && run_threads >= 64 * 1024) {    // enough runs to fill the device
+            const dim3 grid(ceil_div_i(run_threads, 256));
+#define XS_CONV_RUN(KT)                                                                                              \
+    short_conv_bf16x8_run_kernel<KT, RUN><<<grid, 256, 0, stream>>>(                                                  \
+        (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots,       \
+        (__nv_bfloat16*)out, T, H)
+            switch (K) {
+                case 2: XS_CONV_RUN(2); break;
+                case 3: XS_CONV_RUN(3); break;
+                case 4: XS_CONV_RUN(4); break;
+                default: XS_CONV_RUN(5); break;
+            }
+#undef XS_CONV_RUN
+        } else {
+            short_conv_bf16x8_kernel<<<ceil_div_i((int64_t)T * (H / 8), 256), 256, 0, stream>>>(
+                (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots,
+                (__nv_bfloat16*)out, T, H, K);
+        }
         short_conv_state_kernel<__nv_bfloat16><<<ceil_div_i((int64_t)n_seqs * H, 256), 256, 0, stream>>>(
             (const __nv_bfloat16*)bcx, ld, (__nv_bfloat16*)state, cu_seqlens, slots, n_seqs, H, K);
         XS_LAUNCH_CHECK("short_conv");
