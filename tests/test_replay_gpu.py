@@ -4,6 +4,7 @@ requests end earlier, one batch after another so that slots and pages are used a
 float32 and in bfloat16, for every tiny configuration."""
 import numpy as np
 import pytest
+import torch
 
 import tiny
 import trace_util as tu
@@ -141,3 +142,29 @@ def test_tcgen05_products_on_the_model_path(name, folders, references, monkeypat
         gap, where, cos = tu.worst_gap(got, references(name, "bfloat16"))
         assert gap <= tolerance(name, "bfloat16") and cos >= COS["bfloat16"], f"gap {gap:.3e} at {where}"
     assert ops.gemm_tc_status(rp.model.rt.device).item() == 0
+
+
+def test_long_prompts_take_the_fused_gate_up_product(folders):
+    """A batch of prompts with more than 512 tokens between them: by default the gate/up product then runs on
+    the tcgen05 kernel with the activation in its epilogue, everything else as for short prompts."""
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.ops import lib as ops
+    name = "A"
+    model = load_model(folders[(name, "bfloat16")], dtype="bfloat16")
+    rt = model.rt
+    assert rt.many_rows == "auto"
+    reqs = {"long": tiny.prompt(name, 300, salt=50), "mid": tiny.prompt(name, 251, salt=51), "short": tiny.prompt(name, 77, salt=52)}
+    ffn = model.blocks[0].ffn
+    probe = torch.empty(sum(len(v) for v in reqs.values()), ffn.spec.hidden, dtype=torch.bfloat16, device=rt.device)
+    assert ffn.interleave and rt.tensor_core_product(probe, ffn.w_gate_up, fused=True)
+    assert not rt.tensor_core_product(probe[:400], ffn.w_gate_up, fused=True)
+    rp = Replayer(model, 1024, None)
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": v, "want": [0, len(v) // 2, len(v) - 1]} for k, v in reqs.items()],
+              "end": list(reqs)}]
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    got = tu.collect(steps, tu.run_in_process(rp, steps), vocab)
+    ref = tu.plain_logits(folders[(name, "bfloat16")], reqs)
+    gap, where, cos = tu.worst_gap(got, {k: ref[k] for k in got})
+    assert gap <= tolerance(name, "bfloat16") and cos >= COS["bfloat16"], f"gap {gap:.3e} at {where}"
+    assert ops.gemm_tc_status(rt.device).item() == 0

@@ -62,11 +62,16 @@ class Runtime:
         # decode attention cuts each sequence's keys over enough CTAs to fill this many CTA slots an SM
         self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "2"))
         self.small_m = 16     # products with at most this many rows use this library's streaming kernel
-        # Products with more rows: "library" (cuBLAS, the faster one today) or "tcgen05" (this library's
-        # TMA + tensor-memory kernel, with the SwiGLU activation fused into its epilogue).
-        self.many_rows = os.environ.get("XS_MANY_ROWS_GEMM", "library")
-        if self.many_rows not in ("library", "tcgen05"):
-            raise ValueError("XS_MANY_ROWS_GEMM must be 'library' or 'tcgen05'")
+        # Products with more rows. "auto": this library's tcgen05 kernel where it fuses an epilogue that the
+        # library product cannot (the gate/up product with its activation, from 512 tokens on: measured on
+        # B200 at 2,048 tokens, 99 us against 95 us + 22 us for the separate activation), cuBLAS elsewhere
+        # (in_proj, out_proj, qkv and the down projection run 12 to 45 % faster there at 2,048 tokens, mostly
+        # because it cuts the last, partly filled wave of tiles finer). "tcgen05": every such product on this
+        # library's kernel. "library": none.
+        self.many_rows = os.environ.get("XS_MANY_ROWS_GEMM", "auto")
+        if self.many_rows not in ("auto", "library", "tcgen05"):
+            raise ValueError("XS_MANY_ROWS_GEMM must be 'auto', 'library' or 'tcgen05'")
+        self.fused_from_rows = 512
         ops.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
@@ -86,10 +91,14 @@ class Runtime:
         return (self.mode == "bfloat16" and x.shape[0] <= self.small_m
                 and ops.gemm_small_m_supports(x.shape[0], x.shape[1], x.stride(0), w.stride(0)))
 
-    def tensor_core_product(self, x: torch.Tensor, w: torch.Tensor) -> bool:
-        """Whether this product goes to the library's tcgen05 kernel."""
-        return (self.mode == "bfloat16" and self.many_rows == "tcgen05"
-                and ops.gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0)))
+    def tensor_core_product(self, x: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
+        """Whether this product goes to the library's tcgen05 kernel. `fused`: the caller would use an
+        epilogue of that kernel that saves a pass over the output."""
+        if self.mode != "bfloat16" or self.many_rows == "library":
+            return False
+        if self.many_rows == "auto" and not (fused and x.shape[0] >= self.fused_from_rows):
+            return False
+        return ops.gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))
 
     def few_rows_product(self, x, w, out, bias=None, swiglu: bool = False) -> None:
         """The library's weight-streaming product, with K cut over several CTAs where the output is

@@ -1,8 +1,8 @@
 """SwiGLU feed-forward: down(silu(gate y) * up y) (src/models/common/blocks.cpp:23-27). The
 gate and up weights are stacked at load so that one matrix product gives both. When the
 width allows (a multiple of 8, bfloat16) they are stacked in blocks of 8 gate rows and the 8
-up rows of the same outputs: the few-row product then applies the activation in its
-epilogue and writes silu(gate) * up directly."""
+up rows of the same outputs: the few-row product and, for long prompts, the tcgen05 product
+then apply the activation in their epilogue and write silu(gate) * up directly."""
 from __future__ import annotations
 
 from typing import Dict
@@ -42,7 +42,7 @@ class SwiGLU(FeedForward):
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
         if self.interleave and rt.few_rows(y, self.w_gate_up):
             rt.few_rows_product(y, self.w_gate_up, act, swiglu=True)
-        elif self.interleave and rt.tensor_core_product(y, self.w_gate_up):
+        elif self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
             ops.gemm_tc(y, self.w_gate_up, act, epilogue=ops.EPI_SWIGLU)
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
