@@ -205,6 +205,50 @@ def test_gemm_small_m_with_fused_activation(M):
     close(out, g / (1 + torch.exp(-g)) * u, "bfloat16")
 
 
+@pytest.mark.parametrize("M,H,N2,K1,ks1,ks2", [(8, 2048, 512, 1024, 2, 1), (3, 200, 96, 64, 1, 1), (13, 2304, 256, 512, 4, 2),
+                                                (1, 64, 48, 4096, 4, 1)])
+def test_gemm_small_m_carries_the_norm(M, H, N2, K1, ks1, ks2):
+    """Two products with an RMSNorm between them and no norm kernel: the first adds to the float32 stream and
+    leaves stream * weight and per-tile sums of squares, the second scales its rows by 1 / rms. Widths that
+    are no multiple of 16, more tiles than the kernel stages in shared memory (2304 / 16 = 144), K slices on
+    either side, and a row whose stream is a thousand times larger than its neighbours'."""
+    lib = ops()
+    g = torch.Generator(device="cpu").manual_seed(M * H)
+    act = torch.randn(M, K1, generator=g).to(torch.bfloat16).to(DEV)
+    w1 = (torch.randn(H, K1, generator=g) / math.sqrt(K1)).to(torch.bfloat16).to(DEV)
+    h0 = torch.randn(M, H, generator=g).to(DEV)
+    h0[M // 2] *= 1000.0
+    nw = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    bias1 = torch.randn(H, generator=g).to(DEV)
+    w2 = (torch.randn(N2, H, generator=g) / math.sqrt(H)).to(torch.bfloat16).to(DEV)
+    bias2 = torch.randn(N2, generator=g).to(DEV)
+    eps = 1e-5
+    scratch = torch.zeros(8 << 20, dtype=torch.uint8, device=DEV)
+    h = h0.clone()
+    nx = torch.full((M, H), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ssq = torch.full(((H + 15) // 16, 16), float("nan"), device=DEV)
+    lib.gemm_small_m(act, w1, None, bias1, residual=h, ksplit=ks1, scratch=scratch if ks1 > 1 else None,
+                     next_w=nw, next_x=nx, out_ssq=ssq)
+    h_ref = h0.double() + act.double() @ w1.double().T + bias1.double()
+    close(h, h_ref, "float32", factor=4)
+    close(nx, h_ref * nw.double(), "bfloat16")
+    close(ssq[:, :M].sum(0), (h_ref ** 2).sum(1), "float32", factor=4)
+    normed = h_ref / torch.sqrt((h_ref ** 2).mean(1, keepdim=True) + eps) * nw.double()
+    ref = normed @ w2.double().T + bias2.double()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N2), float("nan"), device=DEV, dtype=out_dtype)
+        lib.gemm_small_m(nx, w2, out, bias2, ksplit=ks2, scratch=scratch if ks2 > 1 else None, in_ssq=ssq, in_width=H,
+                         in_eps=eps)
+        close(out, ref, "bfloat16", factor=2)
+    if N2 % 16 == 0:       # the same through the fused activation: w2's rows as 8 gates, 8 ups
+        F = N2 // 2
+        o = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+        lib.gemm_small_m(nx, w2, o, swiglu=True, in_ssq=ssq, in_width=H, in_eps=eps)
+        pre = (normed @ w2.double().T).view(M, F // 8, 2, 8)
+        gate, up = pre[:, :, 0].reshape(M, F), pre[:, :, 1].reshape(M, F)
+        close(o, gate / (1 + torch.exp(-gate)) * up, "bfloat16", factor=2)
+
+
 TC_SHAPES = [(1, 128, 64), (8, 256, 128), (16, 2048, 2048), (5, 100, 96), (33, 1000, 200), (64, 384, 512),
              (130, 300, 264), (700, 1024, 2048), (2048, 512, 1024), (100, 300, 256), (128, 128, 64),
              (257, 2048, 2048), (1000, 6144, 512)]

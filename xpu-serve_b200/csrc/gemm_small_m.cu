@@ -17,6 +17,13 @@
 // Epilogues: bias[N]; `residual` (float32 [M, N]) += result; or SwiGLU for a weight stacked in
 // blocks of 8 gate rows and 8 up rows: out[M, N / 2] = silu(gate) * up.
 //
+// RMSNorm across the product (decode): a norm between two products is a kernel of its own only to wait in,
+// so it is taken apart. The product that ends a branch adds its result to the float32 stream, and beside it
+// leaves x~ = bfloat16(stream * next norm's weight) and, per row tile, the sum of squares of its 16 stream
+// values per batch row (`next_*`, `out_ssq`). The product that follows reads x~, adds the tiles' sums in tile
+// order and multiplies its result by 1 / sqrt(mean square + eps) per batch row (`in_ssq`): the scale is a
+// factor per row of x, so it commutes with the contraction.
+//
 // The reference has the same split of work between its own kernel and a library: `gemv_t` up
 // to 8 rows, oneMKL above (src/backend/sycl/sycl_kernels.cpp:630-714, sycl_kernels.h:280).
 #include "common.cuh"
@@ -27,6 +34,7 @@ constexpr int WARPS = 8;
 constexpr int ROWS = 16;      // weight rows per CTA
 constexpr int UNROLL = 4;     // k blocks whose loads a warp issues together
 constexpr bool kBlocked = true;   // measured on B200: 3 % faster than interleaved on the wide shapes
+constexpr int kSsqStaged = 128;  // producer tiles whose sums of squares are staged in shared memory
 constexpr int K_PER_CTA = WARPS * UNROLL * 32;   // a K slice this long is one round of loads per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -53,17 +61,25 @@ struct SmallMParams {
     unsigned int* counters;   // [tiles], zero between calls
     int M, N, K, ksplit, swiglu, wave;
     int64_t ldx, ldw, ldo;
+    // RMSNorm across the product (null / 0 when unused)
+    const float* in_ssq;      // [in_tiles, 16]: sums of squares of x's stream rows, one row per producer tile
+    int in_tiles, in_width;   // the stream's width (the mean's divisor)
+    float in_eps;
+    const float* next_w;      // [N]: the weight of the norm that reads the stream next
+    __nv_bfloat16* next_x;    // [M, N]: bfloat16(stream * next_w)
+    int64_t ld_next;
+    float* out_ssq;           // [tiles, 16]
 };
 
 template <int NT, typename TO>
-__device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], int n0) {
+__device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0) {
     TO* out = reinterpret_cast<TO*>(p.out);
     if (p.swiglu) {
         // rows 0..7 of the tile are gate rows, rows 8..15 the up rows of the same outputs
         for (int i = threadIdx.x; i < 8 * 8 * NT; i += WARPS * 32) {
             const int r = i % 8, m = i / 8;
             if (m >= p.M || n0 + 8 + r >= p.N) continue;
-            float gate = sum[r][m], up = sum[r + 8][m];
+            float gate = sum[r][m] * inv[m], up = sum[r + 8][m] * inv[m];
             if (p.bias != nullptr) {
                 gate += p.bias[n0 + r];
                 up += p.bias[n0 + 8 + r];
@@ -72,16 +88,28 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
         }
         return;
     }
+    // ROWS * 8 * NT is 128 or 256: whole warps enter, once
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
         const int r = i % ROWS, m = i / ROWS;       // neighbouring threads write neighbouring columns of out
         const int n = n0 + r;
-        if (m >= p.M || n >= p.N) continue;
-        float v = sum[r][m];
-        if (p.bias != nullptr) v += p.bias[n];
-        if (p.residual != nullptr) {
-            p.residual[(int64_t)m * p.ldo + n] += v;
-        } else {
-            out[(int64_t)m * p.ldo + n] = from_f32<TO>(v);
+        const bool live = m < p.M && n < p.N;
+        float v = sum[r][m] * inv[m];
+        if (live && p.bias != nullptr) v += p.bias[n];
+        float sq = 0.0f;
+        if (live) {
+            if (p.residual != nullptr) {
+                const float h = p.residual[(int64_t)m * p.ldo + n] + v;
+                p.residual[(int64_t)m * p.ldo + n] = h;
+                if (p.next_x != nullptr) p.next_x[(int64_t)m * p.ld_next + n] = __float2bfloat16_rn(h * p.next_w[n]);
+                sq = h * h;
+            } else {
+                out[(int64_t)m * p.ldo + n] = from_f32<TO>(v);
+            }
+        }
+        if (p.out_ssq != nullptr) {     // the tile's 16 columns of batch row m sit in 16 neighbouring lanes
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (r == 0) p.out_ssq[(int64_t)blockIdx.x * 16 + m] = sq;
         }
     }
 }
@@ -90,6 +118,9 @@ template <int NT, typename TO>
 __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
+    __shared__ __align__(16) float ssq_in[kSsqStaged][16];
+    __shared__ float ssq_red[16][17];
+    __shared__ float inv[16];
     __shared__ bool last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -152,6 +183,18 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         }
     }
     pdl_wait();
+    // the producer's per-tile sums of squares travel to shared memory beside the main loop (no registers held,
+    // nothing waits for them until the loop is done)
+    if (p.in_ssq != nullptr) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = threadIdx.x + WARPS * 32 * u;          // 16-byte chunk: tile c / 4, batch rows (c % 4) * 4 ...
+            if ((c >> 2) < p.in_tiles)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(&ssq_in[c >> 2][(c & 3) * 4])),
+                             "l"(p.in_ssq + (int64_t)c * 4) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (; kb - warp * ws < kb_end; kb += WARPS * UNROLL) {
         uint4 xv[UNROLL][NT];
 #pragma unroll
@@ -187,7 +230,20 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         red[warp][g + 8][t * 8 + q * 2] = acc[t][2];
         red[warp][g + 8][t * 8 + q * 2 + 1] = acc[t][3];
     }
+    if (p.in_ssq != nullptr) asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
+    if (p.in_ssq != nullptr) {
+        // thread (j, m): tiles j * 8 .. j * 8 + 7 of batch row m, then every 128th tile beyond the staged ones
+        const int sm_ = threadIdx.x & 15, sj_ = threadIdx.x >> 4;
+        float v = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int t = sj_ * 8 + u;
+            v += t < p.in_tiles ? ssq_in[t][sm_] : 0.0f;
+        }
+        for (int t = kSsqStaged + sj_; t < p.in_tiles; t += 16) v += __ldcg(p.in_ssq + (int64_t)t * 16 + sm_);
+        ssq_red[sj_][sm_] = v;
+    }
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
         const int r = i / (8 * NT), m = i % (8 * NT);
         float v = 0.0f;
@@ -196,8 +252,19 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         sum[r][m] = v;
     }
     __syncthreads();
+    if (threadIdx.x < 16) {
+        float v = 1.0f;
+        if (p.in_ssq != nullptr) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ss += ssq_red[j][threadIdx.x];
+            v = 1.0f / sqrtf(ss / (float)p.in_width + p.in_eps);
+        }
+        inv[threadIdx.x] = v;
+    }
+    __syncthreads();
     if (p.ksplit == 1) {
-        epilogue<NT, TO>(p, sum, n0);
+        epilogue<NT, TO>(p, sum, inv, n0);
         return;
     }
     // ---- several K slices: leave this slice's partial, and let the last CTA to arrive add them all
@@ -217,7 +284,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
     }
     if (threadIdx.x == 0) p.counters[tile] = 0;    // ready for the next call
     __syncthreads();
-    epilogue<NT, TO>(p, sum, n0);
+    epilogue<NT, TO>(p, sum, inv, n0);
 }
 
 }  // namespace
@@ -259,10 +326,23 @@ XS_API int64_t xs_gemm_small_m_scratch_bytes(int M, int N, int ksplit) {
 // ksplit > 1 needs `scratch` of at least xs_gemm_small_m_scratch_bytes. Its last 64 KiB are the counters: zero
 // before the first call, and zero again whenever the kernel has run; a caller that keeps one buffer for all
 // shapes passes the whole buffer every time, so that the counters stay in the same place.
-XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void* out, float* residual, int out_dtype,
-                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu, int ksplit,
-                           void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+//
+// RMSNorm across the product (see the top of this file), all optional:
+//   in_ssq [in_tiles, 16], in_width, in_eps: x is x~ of a stream whose rows' sums of squares a producer left per
+//     tile; the result is scaled by 1 / sqrt(sum / in_width + in_eps) per batch row (before the bias).
+//   next_w [N], next_x [M, N] bfloat16 (stride ld_next), out_ssq [ceil(N / 16), 16]: with `residual`, also leave
+//     bfloat16(stream * next_w) and this product's per-tile sums of squares of the new stream values.
+XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bias, void* out, float* residual,
+                                  int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
+                                  int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
+                                  int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
+                                  float* out_ssq, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    XS_REQUIRE(in_ssq == nullptr || (in_tiles > 0 && in_width > 0 && (uintptr_t)in_ssq % 16 == 0),
+               "gemm (few rows): %d tiles of sums over a width of %d", in_tiles, in_width);
+    XS_REQUIRE((next_x == nullptr) == (next_w == nullptr) && (next_x == nullptr || (out_ssq != nullptr && ld_next >= N)),
+               "gemm (few rows): the next norm's weight, its input and the sums of squares come together");
+    XS_REQUIRE(out_ssq == nullptr || residual != nullptr, "gemm (few rows): sums of squares are of the residual stream");
     XS_REQUIRE(xs_gemm_small_m_supports(M, K, ldx, ldw), "gemm (few rows): M %d, K %d, strides %lld, %lld not supported",
                M, K, (long long)ldx, (long long)ldw);
     XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (few rows): operands must be 16-byte aligned");
@@ -288,6 +368,8 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
     p.M = M; p.N = N; p.K = K; p.ksplit = ksplit; p.swiglu = swiglu;
     p.wave = g_small_m_wave / ksplit;
     p.ldx = ldx; p.ldw = ldw; p.ldo = ldo;
+    p.in_ssq = in_ssq; p.in_tiles = in_tiles; p.in_width = in_width; p.in_eps = in_eps;
+    p.next_w = next_w; p.next_x = (__nv_bfloat16*)next_x; p.ld_next = ld_next; p.out_ssq = out_ssq;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_small_m_scratch_bytes(M, N, ksplit);
         XS_REQUIRE(scratch != nullptr && scratch_bytes >= need && (uintptr_t)scratch % 16 == 0 && scratch_bytes % 16 == 0,
@@ -309,4 +391,11 @@ XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void
 #undef XS_GO
     XS_LAUNCH_CHECK("gemm_small_m");
     return 0;
+}
+
+XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void* out, float* residual, int out_dtype,
+                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu, int ksplit,
+                           void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    return xs_gemm_small_m_normed(x, w, bias, out, residual, out_dtype, M, N, K, ldx, ldw, ldo, swiglu, ksplit, scratch,
+                                  scratch_bytes, nullptr, 0, 0, 0.0f, nullptr, nullptr, 0, nullptr, stream);
 }

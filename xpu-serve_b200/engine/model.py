@@ -171,12 +171,18 @@ class Model:
         h = rt.ws.get("stream", (ctx.n_tokens, spec.hidden), torch.float32)
         ops.embed(self.embed, ctx.tokens, h)
         stream = ResidualStream(h, rt)
+        last = len(spec.order) - 1
         for i, call in enumerate(spec.order):
-            self.blocks[call.layer].forward(stream, ctx, cache.views[i])
+            # the norm that reads the stream after this block, for products that carry the norm with them
+            next_w = self.blocks[spec.order[i + 1].layer].w_pre_mixer if i < last else self.final_norm
+            self.blocks[call.layer].forward(stream, ctx, cache.views[i], next_w)
         if ctx.want_rows.numel() == 0:
             stream.flush()
             return torch.empty((0, spec.vocab), dtype=torch.float32, device=rt.device)
-        y = stream.norm(self.final_norm, spec.final_norm.eps, ctx.want_rows)
+        if ctx.want_all and stream.fuses():
+            y = stream.norm_input(self.final_norm, spec.final_norm.eps, lazy=True)
+        else:
+            y = stream.norm(self.final_norm, spec.final_norm.eps, ctx.want_rows)
         return rt.linear(y, self.head, "logits", out_dtype=torch.float32)
 
 

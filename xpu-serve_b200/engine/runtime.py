@@ -62,6 +62,8 @@ class Runtime:
         # decode attention cuts each sequence's keys over enough CTAs to fill this many CTA slots an SM
         self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "2"))
         self.small_m = 16     # products with at most this many rows use this library's streaming kernel
+        # decode: RMSNorm carried by the products on either side of it instead of a kernel of its own
+        self.fuse_norms = os.environ.get("XS_NO_NORM_FUSION", "0") != "1"
         # Products with more rows. "auto": this library's tcgen05 kernel where it fuses an epilogue that the
         # library product cannot (the gate/up product with its activation, from 512 tokens on: measured on
         # B200 at 2,048 tokens, 99 us against 95 us + 22 us for the separate activation), cuBLAS elsewhere
@@ -86,33 +88,45 @@ class Runtime:
         return t.to(device=self.device, dtype=torch.float32).contiguous()
 
     # ------------------------------------------------------ matrix products
-    def few_rows(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+    def few_rows(self, x, w: torch.Tensor) -> bool:
         """Whether this product goes to the library's own weight-streaming kernel."""
+        x = getattr(x, "x", x)      # a Prenormed input counts as its tensor
         return (self.mode == "bfloat16" and x.shape[0] <= self.small_m
                 and ops.gemm_small_m_supports(x.shape[0], x.shape[1], x.stride(0), w.stride(0)))
 
     def tensor_core_product(self, x: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
         """Whether this product goes to the library's tcgen05 kernel. `fused`: the caller would use an
         epilogue of that kernel that saves a pass over the output."""
-        if self.mode != "bfloat16" or self.many_rows == "library":
+        if self.mode != "bfloat16" or self.many_rows == "library" or hasattr(x, "ssq"):
             return False
         if self.many_rows == "auto" and not (fused and x.shape[0] >= self.fused_from_rows):
             return False
         return ops.gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))
 
-    def few_rows_product(self, x, w, out, bias=None, swiglu: bool = False) -> None:
+    def few_rows_product(self, x, w, out, bias=None, swiglu: bool = False, residual=None, next_w=None, next_x=None,
+                         out_ssq=None) -> None:
         """The library's weight-streaming product, with K cut over several CTAs where the output is
         narrow; the partial sums meet in one zero-initialised scratch buffer that lives as long as
-        the runtime (its tail holds the kernel's counters)."""
+        the runtime (its tail holds the kernel's counters). `x` may be a Prenormed input; `residual`
+        (the float32 stream) takes the result instead of `out`, with `next_*` / `out_ssq` as in
+        ops.gemm_small_m."""
+        norm = {}
+        if hasattr(x, "ssq"):
+            norm = dict(in_ssq=x.ssq, in_width=x.width, in_eps=x.eps)
+            x = x.x
         ksplit = ops.gemm_small_m_ksplit(x.shape[0], w.shape[0], x.shape[1], self.sm_count)
         if ksplit > 1 and ops.gemm_small_m_scratch_bytes(x.shape[0], w.shape[0], ksplit) > self.gemm_scratch.numel():
             ksplit = 1
-        ops.gemm_small_m(x, w, out, bias, swiglu=swiglu, ksplit=ksplit, scratch=self.gemm_scratch if ksplit > 1 else None)
+        ops.gemm_small_m(x, w, out, bias, residual=residual, swiglu=swiglu, ksplit=ksplit,
+                         scratch=self.gemm_scratch if ksplit > 1 else None, next_w=next_w, next_x=next_x, out_ssq=out_ssq,
+                         **norm)
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`."""
+        """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`. x may be a Prenormed input."""
         M, N = x.shape[0], w.shape[0]
+        if hasattr(x, "ssq") and not self.few_rows(x, w):
+            raise RuntimeError("a Prenormed input needs the few-row product")
         out_dtype = out_dtype or self.act_dtype
         out = self.ws.get(name, (M, N), out_dtype)
         if self.mode == "float32":

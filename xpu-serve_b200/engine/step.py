@@ -41,6 +41,7 @@ class StepContext:
     slots: torch.Tensor
     kv_lens: torch.Tensor        # length of each sequence after this step
     want_rows: torch.Tensor
+    want_all: bool = False       # want_rows is every row, in order
     page_tables: Dict[int, torch.Tensor] = field(default_factory=dict)
     q_lens_host: Optional[np.ndarray] = None
     starts_host: Optional[np.ndarray] = None
@@ -132,6 +133,7 @@ class StepStager:
             max_kv_len=int(max_kv_len), page_size=cache.page_size, max_positions=cache.max_seq_tokens,
             tokens=view(0, T), positions=view(1, T), seq_of_token=view(2, T), cu_seqlens=view(3, n + 1),
             slots=view(4, n), kv_lens=view(5, n), want_rows=view(6, W),
+            want_all=bool(W == T and np.array_equal(np.asarray(want_rows, dtype=np.int64), np.arange(T, dtype=np.int64))),
             q_lens_host=q_lens, starts_host=starts)
         for k, (gi, t) in enumerate(tables.items()):
             ctx.page_tables[gi] = view(7 + k, t.size).view(n, t.shape[1])

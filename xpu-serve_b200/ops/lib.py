@@ -41,6 +41,7 @@ def _signatures(lib) -> None:
         "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
         "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P],
+        "xs_gemm_small_m_normed": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P, P],
         "xs_gemm_tc": [P, P, P, P, I, I, I, I, I, L, L, L, I, P, L, P, P],
         "xs_argmax": [P, L, I, I, P, P, P],
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
@@ -296,11 +297,19 @@ def gemm_small_m_scratch_bytes(M: int, N: int, ksplit: int) -> int:
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
                  residual: Optional[torch.Tensor] = None, swiglu: bool = False, ksplit: int = 1,
-                 scratch: Optional[torch.Tensor] = None) -> None:
+                 scratch: Optional[torch.Tensor] = None, in_ssq: Optional[torch.Tensor] = None, in_width: int = 0,
+                 in_eps: float = 0.0, next_w: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None,
+                 out_ssq: Optional[torch.Tensor] = None) -> None:
     """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product;
     or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows.
     ksplit > 1 cuts K over several CTAs; `scratch` is then a zero-initialised byte buffer of at least
-    gemm_small_m_scratch_bytes, kept (whole) from call to call."""
+    gemm_small_m_scratch_bytes, kept (whole) from call to call.
+
+    RMSNorm across the product: with `residual`, `next_w` [N] and `next_x` [M, N] bfloat16, the kernel also
+    leaves next_x = bfloat16(residual * next_w) and, in `out_ssq` [ceil(N / 16), 16] float32, each tile's
+    sums of squares of the new residual values per row. A product given that `out_ssq` as `in_ssq` (with the
+    residual's width and the norm's eps) and that `next_x` as x scales its result by each row's
+    1 / sqrt(mean square + eps): together they are norm(residual) . w^T without a norm kernel between."""
     for t, name in ((x, "x"), (w, "w")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
             raise KernelError(f"gemm (few rows): {name} must be a bfloat16 CUDA matrix with contiguous rows")
@@ -314,10 +323,27 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         raise KernelError("gemm (few rows): the residual must be float32")
     if bias is not None:
         _need(bias, "bias", torch.float32)
-    _check(load().xs_gemm_small_m(x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual),
-                                  F32 if out is None else _code(out), M, N, K, x.stride(0), w.stride(0),
-                                  target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
-                                  0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()))
+    in_tiles = 0
+    if in_ssq is not None:
+        _need(in_ssq, "in_ssq", torch.float32)
+        if in_ssq.dim() != 2 or in_ssq.shape[1] != 16 or not in_ssq.is_contiguous() or in_width <= 0:
+            raise KernelError(f"gemm (few rows): sums of squares {tuple(in_ssq.shape)} over a width of {in_width}")
+        in_tiles = in_ssq.shape[0]
+    ld_next = 0
+    if next_x is not None or next_w is not None or out_ssq is not None:
+        if next_x is not None:
+            _need(next_w, "next_w", torch.float32); _need(next_x, "next_x", torch.bfloat16)
+            if tuple(next_x.shape) != (M, N) or next_x.stride(1) != 1 or next_w.numel() != N or not next_w.is_contiguous():
+                raise KernelError(f"gemm (few rows): next_x {tuple(next_x.shape)}, next_w {tuple(next_w.shape)} for [{M}, {N}]")
+            ld_next = next_x.stride(0)
+        _need(out_ssq, "out_ssq", torch.float32)
+        if tuple(out_ssq.shape) != ((N + 15) // 16, 16) or not out_ssq.is_contiguous():
+            raise KernelError(f"gemm (few rows): out_ssq is {tuple(out_ssq.shape)}, expected [{(N + 15) // 16}, 16]")
+    _check(load().xs_gemm_small_m_normed(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual), F32 if out is None else _code(out), M, N, K,
+        x.stride(0), w.stride(0), target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
+        0 if scratch is None else scratch.numel() * scratch.element_size(), _ptr(in_ssq), in_tiles, int(in_width),
+        float(in_eps), _ptr(next_w), _ptr(next_x), ld_next, _ptr(out_ssq), _stream()))
 
 
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2

@@ -20,6 +20,7 @@ from .base import KVNeed, Mixer, TensorSpec
 
 class AttentionMixer(Mixer):
     kind = "attention"
+    fuses_norm = True
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
@@ -67,7 +68,7 @@ class AttentionMixer(Mixer):
         self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
                          if spec.position is not None else None)
 
-    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+    def forward(self, x, step, cache, into=None) -> torch.Tensor:
         s, rt = self.spec, self.rt
         T = x.shape[0]
         if cache is None or cache.storage is None:
@@ -89,6 +90,8 @@ class AttentionMixer(Mixer):
         o = rt.ws.get("attn_o", (T, s.heads, s.head_dim), rt.act_dtype)
         gate = proj[:, gate_at:] if s.head_gate else None
         self.attend(q, cache, table, step, gate, o)
+        if into is not None:
+            return into.product(o.view(T, self.q_dim), self.w_o)
         return rt.linear(o.view(T, self.q_dim), self.w_o, "mixer_out")
 
     def attend(self, q, cache, table, step, gate, o) -> None:

@@ -13,6 +13,12 @@ Mixer:        tensors(spec) -> {relative name: TensorSpec}
 FeedForward:  tensors(spec); __init__(spec, weights, rt); forward(y, step) -> [tokens, hidden]
 Position:     __init__(spec, rt, max_position); table() -> device tensors the mixer passes
               to its kernels
+Optional, for decode steps (few rows): a part whose class sets `fuses_norm = True` takes
+`forward(x, step, cache, into=None)` (feed-forward: `forward(y, step, into=None)`). Its x may then be
+a parts.block.Prenormed (the stream times the norm's weight, with the row scale still to apply),
+which it may hand to `rt.linear` / `rt.few_rows_product` only; and when `into` is given it sends its
+last product through `into.product(act, w, bias)` (which adds it to the stream inside the product's
+kernel) and returns None. Parts without the flag get the normed tensor and return their branch.
 `step` is engine.step.StepContext (which tokens belong to which sequence, where each
 sequence stands), `cache` the view of this call's storage (cache/views.py).
 """
@@ -46,6 +52,7 @@ class StateNeed:
 
 class Part:
     kind: str = ""
+    fuses_norm: bool = False    # see the module text: takes a Prenormed input and an `into` sink
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:

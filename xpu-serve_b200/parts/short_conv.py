@@ -15,6 +15,7 @@ from .base import Mixer, StateNeed, TensorSpec
 
 class ShortConvMixer(Mixer):
     kind = "short_conv"
+    fuses_norm = True
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
@@ -44,7 +45,7 @@ class ShortConvMixer(Mixer):
         self.b_conv = rt.vector(weights[n["conv_bias"]]) if spec.bias else None
         self.b_out = rt.vector(weights[n["out_bias"]]) if spec.bias else None
 
-    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+    def forward(self, x, step, cache, into=None) -> torch.Tensor:
         rt, H = self.rt, self.spec.hidden
         if cache is None or cache.storage is None or not cache.owner:
             raise RuntimeError("short_conv keeps its own state and cannot read another call's")
@@ -52,6 +53,8 @@ class ShortConvMixer(Mixer):
         y = rt.ws.get("conv_y", (x.shape[0], H), rt.act_dtype)
         ops.short_conv(bcx, self.taps, self.b_conv, cache.storage, step.seq_of_token, step.cu_seqlens, step.slots, y,
                        all_single=step.decode)
+        if into is not None:
+            return into.product(y, self.w_out, self.b_out)
         return rt.linear(y, self.w_out, "mixer_out", self.b_out)
 
 

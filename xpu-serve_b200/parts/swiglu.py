@@ -16,6 +16,7 @@ from .base import FeedForward, TensorSpec
 
 class SwiGLU(FeedForward):
     kind = "swiglu"
+    fuses_norm = True
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
@@ -37,7 +38,7 @@ class SwiGLU(FeedForward):
         self.w_gate_up = rt.matrix(stacked)
         self.w_down = rt.matrix(weights[n["down"]])
 
-    def forward(self, y: torch.Tensor, step) -> torch.Tensor:
+    def forward(self, y, step, into=None) -> torch.Tensor:
         rt, F = self.rt, self.spec.intermediate
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
         if self.interleave and rt.few_rows(y, self.w_gate_up):
@@ -47,6 +48,8 @@ class SwiGLU(FeedForward):
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
             ops.silu_mul(gu, act, self.interleave)
+        if into is not None:
+            return into.product(act, self.w_down)
         return rt.linear(act, self.w_down, "ffn_out")
 
 
