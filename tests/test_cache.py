@@ -173,3 +173,42 @@ def test_random_traffic_keeps_the_books():
     c.close(sorted(live))
     c.check()
     assert c.tokens_held() == 0 and c.slots.held_count == 0
+
+
+@pytest.mark.parametrize("window", [0, 100])
+def test_decoding_the_same_batch_step_after_step(window):
+    """The short cut for "the last step's batch again, one token each" reserves pages exactly where the full
+    path would, notices a sequence that ends, a slot that is closed, and the context's end."""
+    c = make(max_tokens=2048, window=window, max_slots=4, max_seq=400)
+    slots = c.open(3)
+    first = [5, 64, 190]
+    c.begin_step(slots, first)
+    c.end_step(slots, first)
+    lens = list(first)
+    versions = c.tables_version()
+    for step in range(150):
+        starts = c.begin_step(slots, [1, 1, 1])
+        assert list(starts) == lens
+        for gi in c.kv_groups:
+            g = c.groups[gi]
+            for s, n in zip(slots, lens):
+                assert int(g.end_held[s]) == -(-(n + 1) // 64)         # the page the new position lies in is held
+                assert g.table[s, n // 64] >= 0
+        crossed = any(n % 64 == 0 for n in lens)
+        assert (c.tables_version() != versions) == crossed or window > 0
+        c.end_step(slots, [1, 1, 1])
+        versions = c.tables_version()
+        lens = [n + 1 for n in lens]
+        c.check()
+    # the third sequence stands at 340: 60 more positions fit, the 61st does not
+    for _ in range(60):
+        c.begin_step(slots, [1, 1, 1])
+        c.end_step(slots, [1, 1, 1])
+    with pytest.raises(CacheError, match="exceed the limit"):
+        c.begin_step(slots, [1, 1, 1])
+    c.close([slots[2]])
+    with pytest.raises(CacheError, match="not held"):
+        c.begin_step(slots, [1, 1, 1])
+    c.begin_step(slots[:2], [1, 1])
+    c.end_step(slots[:2], [1, 1])
+    c.check()

@@ -43,6 +43,7 @@ class KVGroup:
         self.table = np.full((max_slots, max_seq_pages), -1, dtype=np.int32)
         self.first_held = np.zeros(max_slots, dtype=np.int64)    # pages below it were given back
         self.end_held = np.zeros(max_slots, dtype=np.int64)      # pages from it on are not held yet
+        self.version = 0      # grows whenever a row of `table` changes (a staged copy of the table is then stale)
         # one page more than the pool hands out: padding rows of a fixed-size batch write there
         self.dummy_page = n_pages
         self.storage: Dict[int, torch.Tensor] = {
@@ -67,6 +68,7 @@ class KVGroup:
             raise CacheError(f"a sequence of {new_len} positions exceeds the cache's {self.max_seq_pages} pages a sequence")
         self.table[slot, end:end + want] = self.pages.take(want)
         self.end_held[slot] = end + want
+        self.version += 1
 
     def trim(self, slot: int, length: int) -> None:
         first = min(self._first_needed_page(length), int(self.end_held[slot]))
@@ -75,6 +77,7 @@ class KVGroup:
             self.pages.give_back(int(p) for p in self.table[slot, lo:first])
             self.table[slot, lo:first] = -1
             self.first_held[slot] = first
+            self.version += 1
 
     def release(self, slot: int) -> None:
         lo, hi = int(self.first_held[slot]), int(self.end_held[slot])
@@ -82,6 +85,7 @@ class KVGroup:
         self.table[slot, :] = -1
         self.first_held[slot] = 0
         self.end_held[slot] = 0
+        self.version += 1
 
 
 class StateGroup:
@@ -153,12 +157,16 @@ class Cache:
             else:
                 self.views.append(CallView(call, -1, None, None, True))
         self.kv_groups = [i for i, g in enumerate(self.groups) if isinstance(g, KVGroup)]
+        self._any_window = any(self.groups[i].need.window > 0 for i in self.kv_groups)
+        self._last_slots: Optional[tuple] = None       # the batch of the last finished step (decode fast path)
+        self._last_slots_arr: Optional[np.ndarray] = None
 
     # ------------------------------------------------------------ sequences
     def open(self, n: int) -> List[int]:
         """n free slots, their fixed-size state zeroed and their length 0."""
         slots = self.slots.take(n)
         self.lens[slots] = 0
+        self._last_slots = None
         state_groups = [g for g in self.groups if isinstance(g, StateGroup)]
         if state_groups and slots:
             idx = torch.tensor(slots, dtype=torch.int64, device=self.device)
@@ -168,6 +176,7 @@ class Cache:
 
     def close(self, slots: Sequence[int]) -> None:
         slots = list(slots)
+        self._last_slots = None
         for s in slots:
             if not self.slots.is_held(s):
                 raise CacheError(f"slot {s} is freed twice or was never held")
@@ -187,6 +196,10 @@ class Cache:
         max_seq_tokens, or pages run out."""
         if len(slots) != len(q_lens) or len(slots) == 0:
             raise CacheError("a step needs one token count per slot, and at least one slot")
+        if self._same_decode_batch(slots, q_lens):
+            # the batch of the last step again, one token each, no sequence at a page's or the context's end:
+            # nothing to reserve, nothing that can fail
+            return self.lens[self._last_slots_arr].copy()
         if len(set(slots)) != len(slots):
             raise CacheError("a slot appears twice in one step")
         for s, q in zip(slots, q_lens):
@@ -209,7 +222,26 @@ class Cache:
                 g.reserve(s, int(self.lens[s]) + q)
         return starts
 
+    def _same_decode_batch(self, slots: Sequence[int], q_lens: Sequence[int]) -> bool:
+        """Whether this is the batch that `end_step` last saw, each sequence with one token that fits the pages
+        it holds (so every check of `begin_step` would pass and no table would change)."""
+        if self._last_slots is None or len(slots) != len(self._last_slots) or tuple(slots) != self._last_slots:
+            return False
+        if any(q != 1 for q in q_lens):
+            return False
+        lens = self.lens[self._last_slots_arr]
+        if int(lens.max()) + 1 > self.max_seq_tokens or (lens % self.page_size == 0).any():
+            return False
+        return all(self.slots.is_held(s) for s in slots)
+
     def end_step(self, slots: Sequence[int], q_lens: Sequence[int]) -> None:
+        key = tuple(slots)
+        if key != self._last_slots:
+            self._last_slots = key
+            self._last_slots_arr = np.asarray(slots, dtype=np.int64)
+        if not self._any_window and len(set(q_lens)) == 1:
+            self.lens[self._last_slots_arr] += q_lens[0]
+            return
         for s, q in zip(slots, q_lens):
             self.lens[s] += q
             for gi in self.kv_groups:
@@ -231,6 +263,10 @@ class Cache:
         out = np.full((rows, g.max_seq_pages), g.dummy_page, dtype=np.int32)
         out[:len(slots)] = g.table[list(slots)]
         return out
+
+    def tables_version(self) -> int:
+        """Changes whenever any key/value group's page table does."""
+        return sum(self.groups[gi].version for gi in self.kv_groups)
 
     def tokens_held(self) -> int:
         """Positions reserved in the largest key/value group, in whole pages."""

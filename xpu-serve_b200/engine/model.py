@@ -45,6 +45,7 @@ class _DecodeGraph:
 
     def __init__(self, rows: int, graph, stager: StepStager, ws: Workspace, logits: torch.Tensor, kernels: int):
         self.rows, self.graph, self.stager, self.ws, self.logits, self.kernels = rows, graph, stager, ws, logits, kernels
+        self.batch_key = None      # (slots, version of the cache's page tables) of the step staged last
 
 
 class Model:
@@ -155,7 +156,12 @@ class Model:
         if g is None:
             g = self._graphs[key] = self._capture(cache, rows)
             cache._graph_owner = self        # graphs die with the model; the cache only marks its use
-        g.stager.stage_decode_fixed(cache, slots, [t[0] for t in token_lists], np.asarray(starts, dtype=np.int64), rows)
+        tokens = [t[0] for t in token_lists]
+        batch_key = (tuple(slots), cache.tables_version())
+        # the same sequences as in this graph's last step and no page table changed: rewrite tokens and positions only
+        if not (g.batch_key == batch_key and g.stager.restage_next_token(tokens, starts)):
+            g.stager.stage_decode_fixed(cache, slots, tokens, np.asarray(starts, dtype=np.int64), rows)
+            g.batch_key = batch_key
         self.last_h2d_bytes = g.stager.last_h2d_bytes
         g.graph.replay()
         ops.launches += g.kernels

@@ -56,6 +56,7 @@ class StepStager:
         self._host = None
         self._dev = None
         self._event = None
+        self._fixed_layout = None     # set by stage_decode_fixed: what restage_next_token may rewrite
         self.last_h2d_bytes = 0
         self._grow(capacity)
 
@@ -96,12 +97,39 @@ class StepStager:
         idx = np.arange(rows, dtype=np.int64)
         tables = {gi: cache.page_table_fixed(gi, slots, rows) for gi in cache.kv_groups}
         q_lens = np.ones(rows, dtype=np.int64)
-        return self._emit(cache, tok, pos, idx, np.arange(rows + 1, dtype=np.int64), sl, pos + 1, idx, tables, q_lens,
-                          pos, cache.max_seq_tokens)
+        ctx = self._emit(cache, tok, pos, idx, np.arange(rows + 1, dtype=np.int64), sl, pos + 1, idx, tables, q_lens,
+                         pos, cache.max_seq_tokens)
+        r4 = _round4(rows)
+        # (sequences, offsets of tokens, positions and lengths, words up to the end of the lengths)
+        self._fixed_layout = (n, 0, r4, 3 * r4 + _round4(rows + 1) + r4, 3 * r4 + _round4(rows + 1) + 2 * r4)
+        return ctx
+
+    def restage_next_token(self, tokens: Sequence[int], starts: np.ndarray) -> bool:
+        """The step after a `stage_decode_fixed` of the same sequences, whose page tables have not changed:
+        only the tokens, the positions and the lengths differ, so only those are rewritten and copied.
+        False (nothing done) when the last staging was not such a step or the positions do not follow on."""
+        lay = self._fixed_layout
+        n = len(tokens)
+        if lay is None or n != lay[0]:
+            return False
+        _, o_tok, o_pos, o_kv, head = lay
+        buf = self._np
+        if not np.array_equal(buf[o_pos:o_pos + n] + 1, starts):
+            return False
+        if self._event is not None:
+            self._event.synchronize()
+        buf[o_tok:o_tok + n] = tokens
+        buf[o_pos:o_pos + n] += 1
+        buf[o_kv:o_kv + n] += 1
+        self.last_h2d_bytes = 4 * head
+        self._dev[:head].copy_(self._host[:head], non_blocking=True)
+        self._event.record()
+        return True
 
     def _emit(self, cache, flat, pos, seq_of, cu, slots, kv_lens, want_rows, tables, q_lens, starts,
               max_kv_len) -> StepContext:
         T, n, W = len(flat), len(slots), len(want_rows)
+        self._fixed_layout = None
         sizes = [T, T, T, n + 1, n, n, W] + [t.size for t in tables.values()]
         offs = [0]
         for sz in sizes:
@@ -121,7 +149,8 @@ class StepStager:
         self.last_h2d_bytes = 4 * total
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
         if self.device.type == "cuda":
-            self._event = torch.cuda.Event()
+            if self._event is None:
+                self._event = torch.cuda.Event()
             self._event.record()
         d = self._dev
 
