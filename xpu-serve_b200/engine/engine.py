@@ -53,6 +53,7 @@ class DeviceStepper:
         self.device = model.rt.device
         self._pen = None        # (seen uint8 [rows, V], counts int32 [rows, V]) when a batch has penalties
         self._rows_free: List[int] = []
+        self._host_tokens: Optional[torch.Tensor] = None      # pinned: where the chosen tokens land
 
     # ---------------------------------------------------------------- slots
     def open(self, requests: Sequence[GenerateRequest]) -> List[_Handle]:
@@ -86,8 +87,10 @@ class DeviceStepper:
             return [None] * len(handles)
         n = len(chosen)
         dev = self.device
-        out = torch.empty(n, dtype=torch.int32, device=dev)
         params = [h.request.sampling for h in chosen]
+        if self._pen is None and n == len(handles) and self.model.last_greedy is not None and all(p.greedy() for p in params):
+            return self._to_host(self.model.last_greedy, chosen, want)     # the decode graph has chosen already
+        out = torch.empty(n, dtype=torch.int32, device=dev)
         if self._pen is not None:
             rows = torch.tensor([h.row for h in chosen], dtype=torch.int32, device=dev)
             ops.apply_penalties(logits, self._pen[0], self._pen[1], rows,
@@ -105,9 +108,20 @@ class DeviceStepper:
                        torch.tensor([h.counter for h in chosen], dtype=torch.int64, device=dev), out)
         if self._pen is not None:
             ops.note_tokens(out, rows, self._pen[0], self._pen[1], generated=True)
-        host = out.to("cpu").tolist()       # the step's only device-to-host copy
+        return self._to_host(out, chosen, want)
+
+    def _to_host(self, out: torch.Tensor, chosen, want) -> List[Optional[int]]:
+        """The step's only device-to-host copy: the chosen tokens, through pinned memory."""
+        n = out.numel()
+        if self._host_tokens is None or self._host_tokens.numel() < n:
+            self._host_tokens = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True)
+        self._host_tokens[:n].copy_(out, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        host = self._host_tokens[:n].tolist()
         for h in chosen:
             h.counter += 1
+        if len(host) == len(want):
+            return host
         it = iter(host)
         return [next(it) if w else None for w in want]
 

@@ -43,8 +43,10 @@ class _DecodeGraph:
     """A captured decode step for a fixed number of rows: its own scratch buffers and its own
     description buffer, whose addresses the graph holds."""
 
-    def __init__(self, rows: int, graph, stager: StepStager, ws: Workspace, logits: torch.Tensor, kernels: int):
+    def __init__(self, rows: int, graph, stager: StepStager, ws: Workspace, logits: torch.Tensor, greedy: torch.Tensor,
+                 kernels: int):
         self.rows, self.graph, self.stager, self.ws, self.logits, self.kernels = rows, graph, stager, ws, logits, kernels
+        self.greedy = greedy       # int32 [rows]: each row's most likely token, found inside the graph
         self.batch_key = None      # (slots, version of the cache's page tables) of the step staged last
 
 
@@ -67,6 +69,7 @@ class Model:
         # Decode steps are launch-bound (some 150 small kernels): they are captured once per batch
         # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
         self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
+        self.last_greedy: Optional[torch.Tensor] = None
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
 
@@ -110,6 +113,7 @@ class Model:
                 if not 0 <= int(p) < len(toks):
                     raise ValueError(f"wanted place {p} is not among the {len(toks)} tokens of the step")
         q_lens = [len(t) for t in token_lists]
+        self.last_greedy = None      # set by a decode graph: argmax of the returned rows, already on the device
         starts = cache.begin_step(slots, q_lens)
         if self.use_graphs and max(q_lens) == 1:
             logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
@@ -137,16 +141,18 @@ class Model:
         width = sum(cache.groups[gi].max_seq_pages for gi in cache.kv_groups)
         stager = StepStager(rt.device, capacity=8 * rows + rows * width + 64, fixed=True)
         ctx = stager.stage_decode_fixed(cache, [], [], np.zeros(0, dtype=np.int64), rows)
+        greedy = torch.empty(rows, dtype=torch.int32, device=rt.device)
         with self._workspace(ws):
-            self.forward(ctx, cache)                     # allocates the scratch buffers, loads the kernels
+            ops.argmax(self.forward(ctx, cache), greedy)     # allocates the scratch buffers, loads the kernels
             torch.cuda.synchronize(rt.device)
             before = ops.launches
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.forward(ctx, cache)
+                ops.argmax(logits, greedy)               # greedy decoding needs no launch after the graph
             kernels = ops.launches - before
         ws.frozen = True
-        return _DecodeGraph(rows, graph, stager, ws, logits, kernels)
+        return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels)
 
     def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
         n = len(slots)
@@ -167,6 +173,7 @@ class Model:
         ops.launches += g.kernels
         picked = [i for i, places in enumerate(want) for _ in places]
         if picked == list(range(n)):
+            self.last_greedy = g.greedy[:n]
             return g.logits[:n]          # the graph's own output buffer: valid until the next step of this size
         if not picked:
             return g.logits[:0]
