@@ -172,3 +172,54 @@ def test_penalties_match_plain(folders):
             assert t == best or abs(logits[best] - logits[t]) < 1e-5 * np.abs(logits).max()
             seq.append(t)
             gen.append(t)
+
+
+def test_running_ahead_changes_no_token(folders, monkeypatch):
+    """Greedy batches decode with the next step already started on the device. Stop tokens that end one
+    sequence in the middle, unequal lengths, a page boundary (64) crossed while running ahead, a sequence
+    that reaches the context's end, a callback that cancels: the same tokens as without running ahead."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders[("A", "float32")]
+    greedy = SamplingParams(temperature=0.0)
+    prompts = [tiny.prompt("A", n, salt=40 + i) for i, n in enumerate((60, 3, 17, 100))]
+
+    def run(ahead, stops, cancel_at=None):
+        monkeypatch.setenv("XS_NO_RUN_AHEAD", "0" if ahead else "1")
+        engine = Engine(folder, precision="f32", ctx=128, max_batch=8)
+        assert engine.stepper.run_ahead == ahead
+        seen = []
+
+        def on_token(i, t):
+            seen.append((i, t))
+            return not (cancel_at is not None and i == 2 and sum(1 for j, _ in seen if j == 2) >= cancel_at)
+
+        reqs = [GenerateRequest(p, greedy, n, list(stops)) for p, n in zip(prompts, (40, 30, 25, 60))]
+        res = engine.generate(reqs, on_token)
+        engine.stepper.cache.check()
+        assert engine.stepper.cache.slots.held_count == 0
+        return [(r.finish, r.tokens) for r in res]
+
+    plain_run = run(False, [])
+    assert plain_run[3][0] == "length" and len(plain_run[3][1]) == 28        # 100 + 28 = the context of 128
+    assert run(True, []) == plain_run
+    # a stop token that sequence 1 meets in the middle of its run
+    stop = plain_run[1][1][7]
+    with_stop = run(False, [stop])
+    assert any(f == "stop" for f, _ in with_stop)
+    assert run(True, [stop]) == with_stop
+    assert run(True, [], cancel_at=5) == run(False, [], cancel_at=5)
+
+
+def test_running_ahead_refuses_another_token(folders):
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    engine = Engine(folders[("A", "float32")], precision="f32", ctx=128, max_batch=4)
+    st = engine.stepper
+    reqs = [GenerateRequest(tiny.prompt("A", 5, salt=1), SamplingParams(temperature=0.0), 8, [])]
+    hs = st.open(reqs)
+    (t0,) = st.step(hs, [reqs[0].prompt], [True])
+    (t1,) = st.step(hs, [[t0]], [True])           # from here on the next step is already running
+    with pytest.raises(RuntimeError, match="one decode step ahead"):
+        st.step(hs, [[(t1 + 1) % 512]], [True])
+    st.close(hs)

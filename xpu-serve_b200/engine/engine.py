@@ -12,6 +12,7 @@ takes a list of requests and returns their results in the same order.
 """
 from __future__ import annotations
 
+import os
 import secrets
 from typing import List, Optional, Sequence
 
@@ -39,9 +40,25 @@ class _Handle:
         self.slot, self.row, self.request, self.seed, self.counter = slot, row, request, seed, 0
 
 
+class _Ahead:
+    """A decode step that was started before the loop asked for it."""
+    __slots__ = ("row_of", "fed", "event", "host")
+
+    def __init__(self, row_of, fed, event, host):
+        self.row_of, self.fed, self.event, self.host = row_of, fed, event, host
+
+
 class DeviceStepper:
     """Runs the generation loop's steps on the device: the model's step function, then the choice of
-    the next token by the sampling kernels; only token ids cross to the host."""
+    the next token by the sampling kernels; only token ids cross to the host.
+
+    Running ahead. A generation loop feeds every live sequence the token the last step chose for it, so
+    while greedy sequences decode, the step after the one being asked for is started at once, fed on the
+    device from the graph's own choice; by the time the loop has looked at a step's tokens the next step is
+    already running. A sequence that the loop ends (a stop token, its length, a callback) has then run one
+    step too many: a row of work that nobody reads, in a slot that the loop closes. The promise the loop
+    makes in return (`generate` keeps it): after decoding has begun, a sequence's next call brings the token
+    the last call returned for it. A call that breaks it is refused."""
 
     def __init__(self, model: Model, max_tokens: int, max_context: int, max_slots: Optional[int] = None):
         self.model = model
@@ -53,15 +70,21 @@ class DeviceStepper:
         self.device = model.rt.device
         self._pen = None        # (seen uint8 [rows, V], counts int32 [rows, V]) when a batch has penalties
         self._rows_free: List[int] = []
-        self._host_tokens: Optional[torch.Tensor] = None      # pinned: where the chosen tokens land
+        self._host_bufs: List[torch.Tensor] = []              # pinned: where the chosen tokens land, in turns
+        self._turn = 0
+        self.run_ahead = os.environ.get("XS_NO_RUN_AHEAD", "0") != "1"
+        self._ahead: Optional[_Ahead] = None
+        self._live = set()          # handles that hold a slot
 
     # ---------------------------------------------------------------- slots
     def open(self, requests: Sequence[GenerateRequest]) -> List[_Handle]:
+        self._ahead = None          # what ran ahead for an earlier batch is nobody's any more
         slots = self.cache.open(len(requests))
         handles = []
         for row, (s, r) in enumerate(zip(slots, requests)):
             seed = r.sampling.seed if r.sampling.seed is not None else secrets.randbits(63)
             handles.append(_Handle(s, row, r, seed))
+        self._live.update(handles)
         if any(r.sampling.has_penalties() for r in requests):
             V = self.model.spec.vocab
             seen = torch.zeros((len(requests), V), dtype=torch.uint8, device=self.device)
@@ -77,9 +100,17 @@ class DeviceStepper:
 
     def close(self, handles: Sequence[_Handle]) -> None:
         self.cache.close([h.slot for h in handles])
+        self._live.difference_update(handles)
 
     # ----------------------------------------------------------------- step
     def step(self, handles: Sequence[_Handle], token_lists, want: Sequence[bool]) -> List[Optional[int]]:
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            if any(h in ahead.row_of for h in handles):
+                return self._take_ahead(ahead, handles, token_lists, want)
+            if any(h in self._live for h in ahead.row_of):
+                raise RuntimeError("this stepper runs one decode step ahead for sequences that are still open; "
+                                   "their step has to be taken before other sequences are stepped")
         places = [[len(t) - 1] if w else [] for t, w in zip(token_lists, want)]
         logits = self.model.step(self.cache, [h.slot for h in handles], token_lists, places)
         chosen = [h for h, w in zip(handles, want) if w]
@@ -89,7 +120,16 @@ class DeviceStepper:
         dev = self.device
         params = [h.request.sampling for h in chosen]
         if self._pen is None and n == len(handles) and self.model.last_greedy is not None and all(p.greedy() for p in params):
-            return self._to_host(self.model.last_greedy, chosen, want)     # the decode graph has chosen already
+            # the decode graph has chosen already; start the next step before waiting for this one's tokens
+            host, event = self._copy_out(self.model.last_greedy)
+            self._start_ahead(handles)
+            event.synchronize()
+            tokens = host[:n].tolist()
+            if self._ahead is not None:
+                self._ahead.fed = tokens
+            for h in chosen:
+                h.counter += 1
+            return tokens
         out = torch.empty(n, dtype=torch.int32, device=dev)
         if self._pen is not None:
             rows = torch.tensor([h.row for h in chosen], dtype=torch.int32, device=dev)
@@ -110,20 +150,62 @@ class DeviceStepper:
             ops.note_tokens(out, rows, self._pen[0], self._pen[1], generated=True)
         return self._to_host(out, chosen, want)
 
-    def _to_host(self, out: torch.Tensor, chosen, want) -> List[Optional[int]]:
-        """The step's only device-to-host copy: the chosen tokens, through pinned memory."""
+    def _copy_out(self, out: torch.Tensor):
+        """Starts the step's only device-to-host copy (the chosen tokens, into pinned memory) and returns the
+        host buffer and the event that says it has landed. Two buffers take turns: a step that runs ahead
+        copies out while the one before it is still being read."""
         n = out.numel()
-        if self._host_tokens is None or self._host_tokens.numel() < n:
-            self._host_tokens = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True)
-        self._host_tokens[:n].copy_(out, non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
-        host = self._host_tokens[:n].tolist()
+        self._turn ^= 1
+        while len(self._host_bufs) < 2:
+            self._host_bufs.append(torch.empty(64, dtype=torch.int32, pin_memory=True))
+        if self._host_bufs[self._turn].numel() < n:
+            self._host_bufs[self._turn] = torch.empty(2 * n, dtype=torch.int32, pin_memory=True)
+        host = self._host_bufs[self._turn]
+        host[:n].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return host, event
+
+    def _to_host(self, out: torch.Tensor, chosen, want) -> List[Optional[int]]:
+        host, event = self._copy_out(out)
+        event.synchronize()
+        tokens = host[:out.numel()].tolist()
         for h in chosen:
             h.counter += 1
-        if len(host) == len(want):
-            return host
-        it = iter(host)
+        if len(tokens) == len(want):
+            return tokens
+        it = iter(tokens)
         return [next(it) if w else None for w in want]
+
+    # ----------------------------------------------------------- running ahead
+    def _start_ahead(self, handles: Sequence[_Handle]) -> None:
+        """Starts the decode step after the last one for the same sequences, fed on the device, if the last
+        step was a greedy graph step of exactly these sequences and the cache has room."""
+        if not self.run_ahead or self._pen is not None or not all(h.request.sampling.greedy() for h in handles):
+            return
+        out = self.model.step_from_last_greedy(self.cache, [h.slot for h in handles])
+        if out is None:
+            return
+        host, event = self._copy_out(out)
+        self._ahead = _Ahead({h: i for i, h in enumerate(handles)}, None, event, host)
+
+    def _take_ahead(self, ahead: _Ahead, handles, token_lists, want) -> List[Optional[int]]:
+        """The loop now asks for (a part of) the step that already runs."""
+        for h, toks, w in zip(handles, token_lists, want):
+            i = ahead.row_of.get(h)
+            if i is None or not w or len(toks) != 1 or int(toks[0]) != ahead.fed[i]:
+                raise RuntimeError("this stepper runs one decode step ahead: after decoding has begun, a sequence's "
+                                   "next step must bring the token that the last step returned for it")
+        if len(handles) == len(ahead.row_of):
+            self._start_ahead(handles)          # the same sequences go on: keep the device busy
+        ahead.event.synchronize()
+        tokens = ahead.host[:len(ahead.row_of)].tolist()
+        got = [tokens[ahead.row_of[h]] for h in handles]
+        if self._ahead is not None:
+            self._ahead.fed = got
+        for h in handles:
+            h.counter += 1
+        return got
 
 
 class Engine:

@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from .. import registry
-from ..cache import Cache
+from ..cache import Cache, CacheError
 from ..config.json_util import ConfigError, read_json
 from ..config.spec import ModelSpec
 from ..ops import lib as ops
@@ -70,6 +70,7 @@ class Model:
         # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
         self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
         self.last_greedy: Optional[torch.Tensor] = None
+        self._last_graph: Optional[_DecodeGraph] = None
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
 
@@ -114,6 +115,7 @@ class Model:
                     raise ValueError(f"wanted place {p} is not among the {len(toks)} tokens of the step")
         q_lens = [len(t) for t in token_lists]
         self.last_greedy = None      # set by a decode graph: argmax of the returned rows, already on the device
+        self._last_graph = None
         starts = cache.begin_step(slots, q_lens)
         if self.use_graphs and max(q_lens) == 1:
             logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
@@ -174,10 +176,35 @@ class Model:
         picked = [i for i, places in enumerate(want) for _ in places]
         if picked == list(range(n)):
             self.last_greedy = g.greedy[:n]
+            self._last_graph = g
             return g.logits[:n]          # the graph's own output buffer: valid until the next step of this size
         if not picked:
             return g.logits[:0]
         return g.logits[torch.tensor(picked, dtype=torch.int64, device=self.rt.device)]
+
+    def step_from_last_greedy(self, cache: Cache, slots: Sequence[int]) -> Optional[torch.Tensor]:
+        """One more decode step of exactly the sequences of the last step, each fed the token that step's graph
+        chose, which never leaves the device. Returns the new choices (int32 [n] on the device, the graph's
+        own buffer), or None, with nothing changed, when the last step was no graph step of these sequences
+        with all rows wanted, or the cache cannot take another token for every one of them."""
+        g = self._last_graph
+        n = len(slots)
+        if g is None or self.last_greedy is None or g.batch_key is None or g.batch_key[0] != tuple(slots):
+            return None
+        try:
+            starts = cache.begin_step(slots, [1] * n)
+        except CacheError:
+            return None
+        batch_key = (tuple(slots), cache.tables_version())
+        if not (g.batch_key == batch_key and g.stager.restage_fed(g.greedy, n, starts)):
+            g.stager.stage_decode_fixed(cache, slots, [0] * n, np.asarray(starts, dtype=np.int64), g.rows)
+            g.stager.feed_tokens(g.greedy, n)
+            g.batch_key = batch_key
+        self.last_h2d_bytes = g.stager.last_h2d_bytes
+        g.graph.replay()
+        ops.launches += g.kernels
+        cache.end_step(slots, [1] * n)
+        return self.last_greedy
 
     def forward(self, ctx: StepContext, cache: Cache) -> torch.Tensor:
         rt, spec = self.rt, self.spec

@@ -126,6 +126,30 @@ class StepStager:
         self._event.record()
         return True
 
+    def feed_tokens(self, tokens_dev: torch.Tensor, n: int) -> None:
+        """The first n tokens of the staged step are taken from a device tensor (int32) instead of the host's."""
+        self._dev[:n].copy_(tokens_dev[:n])
+
+    def restage_fed(self, tokens_dev: torch.Tensor, n: int, starts: np.ndarray) -> bool:
+        """`restage_next_token` with the tokens coming from the device: positions and lengths advance on the
+        host and are copied; the tokens never leave the device."""
+        lay = self._fixed_layout
+        if lay is None or n != lay[0]:
+            return False
+        _, o_tok, o_pos, o_kv, head = lay
+        buf = self._np
+        if not np.array_equal(buf[o_pos:o_pos + n] + 1, starts):
+            return False
+        if self._event is not None:
+            self._event.synchronize()
+        buf[o_pos:o_pos + n] += 1
+        buf[o_kv:o_kv + n] += 1
+        self.last_h2d_bytes = 4 * (head - o_pos)
+        self._dev[o_pos:head].copy_(self._host[o_pos:head], non_blocking=True)
+        self._event.record()
+        self.feed_tokens(tokens_dev, n)
+        return True
+
     def _emit(self, cache, flat, pos, seq_of, cu, slots, kv_lens, want_rows, tables, q_lens, starts,
               max_kv_len) -> StepContext:
         T, n, W = len(flat), len(slots), len(want_rows)
