@@ -66,7 +66,7 @@ class Runtime:
         self.fuse_norms = os.environ.get("XS_NO_NORM_FUSION", "0") != "1"
         # Products with more rows. "auto": this library's tcgen05 kernel where it fuses an epilogue that the
         # library product cannot (the gate/up product with its activation, from 512 tokens on: measured on
-        # B200 at 2,048 tokens, 99 us against 95 us + 22 us for the separate activation), cuBLAS elsewhere
+        # B200 at 2,048 tokens, 99 us against 95 us and a separate activation pass over 100 MB), cuBLAS elsewhere
         # (in_proj, out_proj, qkv and the down projection run 12 to 45 % faster there at 2,048 tokens, mostly
         # because it cuts the last, partly filled wave of tiles finer). "tcgen05": every such product on this
         # library's kernel. "library": none.
