@@ -335,6 +335,188 @@ def test_toy_mixer_order_and_shared_cache(dtype):
     cache.close([s2])
 
 
+# ------------------------------------------- a toy feed-forward with routing and a toy position encoding, defined here
+@dataclass(frozen=True)
+class ToyExpertsSpec:
+    """out = sum over the 2 best of E experts of p_e * W2_e relu(W1_e y), p = softmax of the router's logits
+    over those 2 (router in float32)."""
+    hidden: int
+    experts: int
+    inner: int
+    names: Dict[str, str] = field(default_factory=lambda: {"router": "toy_moe.router.weight", "w1": "toy_moe.w1", "w2": "toy_moe.w2"})
+    kind: str = "toy_experts"
+
+
+@dataclass(frozen=True)
+class ToyInterpolatedRopeSpec:
+    """Rotary encoding at position / stretch (position interpolation): another table, the same kernels."""
+    head_dim: int
+    theta: float
+    pairs: int
+    stretch: float
+    kind: str = "toy_interpolated_rope"
+
+
+def make_toy_experts_class():
+    from xpu_serve_b200.parts.base import FeedForward, TensorSpec
+
+    class ToyExperts(FeedForward):
+        kind = "toy_experts"
+
+        @classmethod
+        def tensors(cls, spec):
+            n = spec.names
+            return {n["router"]: TensorSpec((spec.experts, spec.hidden)),
+                    n["w1"]: TensorSpec((spec.experts * spec.inner, spec.hidden)),
+                    n["w2"]: TensorSpec((spec.experts * spec.hidden, spec.inner))}
+
+        def __init__(self, spec, weights, rt):
+            self.spec, self.rt = spec, rt
+            n = spec.names
+            self.router = weights[n["router"]].to(rt.device, torch.float32)
+            self.w1 = rt.matrix(weights[n["w1"]]).view(spec.experts, spec.inner, spec.hidden)
+            self.w2 = rt.matrix(weights[n["w2"]]).view(spec.experts, spec.hidden, spec.inner)
+
+        def forward(self, y, step):       # dense over the experts with a mask: no host sync, graph-safe
+            logits = y.float() @ self.router.t()
+            top = logits.topk(2, dim=-1)
+            p = torch.zeros_like(logits).scatter_(1, top.indices, torch.softmax(top.values, -1))
+            hid = torch.relu(torch.einsum("th,eih->tei", y.float(), self.w1.float()))
+            out = torch.einsum("tei,ehi->teh", hid, self.w2.float())
+            return (out * p[:, :, None]).sum(1).to(self.rt.act_dtype)
+
+    return ToyExperts
+
+
+def make_toy_position_class():
+    from xpu_serve_b200.parts.rope import RotaryTable
+
+    class ToyInterpolatedRope(RotaryTable):
+        kind = "toy_interpolated_rope"
+
+        def __init__(self, spec, rt):
+            super().__init__(spec, rt)
+            self.key = ("toy_interpolated_rope", spec.head_dim, float(spec.theta), spec.pairs, float(spec.stretch))
+
+        def inv_freq(self):
+            return super().inv_freq() / self.spec.stretch
+
+    return ToyInterpolatedRope
+
+
+def routed_model(dtype):
+    """Layer 0: attention with the toy position encoding, toy experts; layer 1: short conv, SwiGLU; layer 2:
+    attention (plain RoPE), toy experts."""
+    from xpu_serve_b200 import registry
+    from xpu_serve_b200.config import Lfm3Config
+    from xpu_serve_b200.engine.model import Model
+    from xpu_serve_b200.weights import random_tensors
+    try:
+        registry.ffn_class("toy_experts")
+    except KeyError:
+        registry.register_ffn("toy_experts", make_toy_experts_class())
+    try:
+        registry.position_class("toy_interpolated_rope")
+    except KeyError:
+        registry.register_position("toy_interpolated_rope", make_toy_position_class())
+    base = Lfm3Config.from_json(tiny.CONFIG_A).model_spec()
+    attn = next(l for l in base.layers if l.mixer.kind == "attention")
+    conv = next(l for l in base.layers if l.mixer.kind == "short_conv")
+    rp = attn.mixer.position
+    moe = ToyExpertsSpec(base.hidden, 4, 24)
+    stretched = replace(attn.mixer, position=ToyInterpolatedRopeSpec(rp.head_dim, rp.theta, rp.pairs, 4.0))
+    layers = (replace(attn, prefix="layers.0.", mixer=stretched, ffn=moe), replace(conv, prefix="layers.1."),
+              replace(attn, prefix="layers.2.", ffn=moe))
+    from xpu_serve_b200.config.spec import LayerCall
+    spec = replace(base, layers=layers, order=(LayerCall(0), LayerCall(1), LayerCall(2)))
+    tensors = dict(random_tensors(spec, 11, "float32", norm_range=(0.5, 1.5), scale=tiny.LIVELY))
+    weights = {k[len("model."):]: v for k, v in tensors.items()}
+    return spec, tensors, Model(spec, weights, dtype=dtype)
+
+
+def plain_routed_forward(spec, tensors, ids):
+    W = {k: v.double().numpy() for k, v in tensors.items()}
+    cfg = tiny.CONFIG_A
+    H, Hq, Hkv, D, K, eps = 64, 4, 2, 16, 3, cfg["norm_eps"]
+    inv = plain.rope_inv_freq(cfg["rope_theta"], D, D // 2)
+    h = W["model.embed_tokens.weight"][np.asarray(ids)]
+    margins = []
+    for call in spec.order:
+        layer = spec.layers[call.layer]
+        L = f"model.layers.{call.layer}."
+        x = plain.rms_norm(h, W[L + "operator_norm.weight"], eps)
+        if layer.mixer.kind == "short_conv":
+            m = plain.short_conv(x, W, L, H, K, False)
+        else:
+            stretch = getattr(layer.mixer.position, "stretch", 1.0)
+            m = plain.self_attention(x, W, L, Hq, Hkv, D, eps, inv / stretch, 0, False)
+        h = h + m
+        y = plain.rms_norm(h, W[L + "ffn_norm.weight"], eps)
+        if layer.ffn.kind == "toy_experts":
+            E, I = layer.ffn.experts, layer.ffn.inner
+            logits = y @ W[L + "toy_moe.router.weight"].T
+            w1 = W[L + "toy_moe.w1"].reshape(E, I, H)
+            w2 = W[L + "toy_moe.w2"].reshape(E, H, I)
+            f = np.zeros_like(y)
+            for t in range(len(ids)):
+                order = np.argsort(-logits[t])
+                margins.append(logits[t, order[1]] - logits[t, order[2]])
+                best = order[:2]
+                pe = np.exp(logits[t, best] - logits[t, best].max())
+                pe /= pe.sum()
+                for e, pw in zip(best, pe):
+                    f[t] += pw * (w2[e] @ np.maximum(w1[e] @ y[t], 0.0))
+        else:
+            f = plain.swiglu(y, W, L)
+        h = h + f
+    return plain.rms_norm(h, W["model.embedding_norm.weight"], eps) @ W["model.embed_tokens.weight"].T, min(margins)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_ffn_and_toy_position_encoding(dtype):
+    """A feed-forward with routing and another position encoding are registered from here, built into a model
+    beside the library's parts and stepped (prompts in one step, then token by token through the decode
+    graphs, where the toy feed-forward takes the plain norm between the fused products around it)."""
+    spec, tensors, model = routed_model(dtype)
+    cache = model.new_cache(1024)
+    prompts = [tiny.prompt("A", n, salt=20 + i) for i, n in enumerate((12, 40, 5))]
+    refs = []
+    for p in prompts:
+        ref, margin = plain_routed_forward(spec, tensors, p)
+        assert margin > 1e-4, "the test's own routing is near a tie for float32; pick another prompt"
+        refs.append(ref)
+    # the stretch matters: without it the logits are others
+    flat, _ = plain_routed_forward(replace(spec, layers=(replace(spec.layers[0], mixer=replace(
+        spec.layers[0].mixer, position=replace(spec.layers[0].mixer.position, stretch=1.0))),) + spec.layers[1:]),
+        tensors, prompts[1])
+    assert gap_of(flat, refs[1]) > 1e-3
+    slots = cache.open(3)
+    heads = [7, 25, 1]
+    got = [[] for _ in prompts]
+    lg = model.step(cache, slots, [p[:h] for p, h in zip(prompts, heads)], [list(range(h)) for h in heads]).cpu().numpy()
+    o = 0
+    for i, h in enumerate(heads):
+        got[i].append(lg[o:o + h])
+        o += h
+    at = list(heads)
+    live = [0, 1, 2]
+    while live:
+        lg = model.step(cache, [slots[i] for i in live], [[prompts[i][at[i]]] for i in live]).cpu().numpy()
+        for r, i in enumerate(live):
+            got[i].append(lg[r:r + 1])
+            at[i] += 1
+        done = [i for i in live if at[i] == len(prompts[i])]
+        cache.close([slots[i] for i in done])
+        live = [i for i in live if i not in done]
+    gaps = [np.abs(np.concatenate(g, 0) - r).max(1) / np.abs(r).max() for g, r in zip(got, refs)]
+    if dtype == "float32":
+        assert max(g.max() for g in gaps) <= 1e-5
+    else:
+        # bfloat16 noise can turn a routing decision that float64 makes by a hair; most positions must agree
+        assert np.median(np.concatenate(gaps)) <= 5e-2 and np.isfinite(np.concatenate(gaps)).all()
+    cache.check()
+
+
 # ------------------------------------------------------------------------------ long runs, first tokens
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["R", "W"])
