@@ -168,7 +168,8 @@ def test_gemm_generic_rows_do_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (1000, 200), (2048, 8192), (333, 2056)])
+# the two widest: more row tiles than CTAs fit on the device at once; (2048, 8192), (4096, 1024): no edge anywhere
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (1000, 200), (2048, 8192), (333, 2056), (10007, 200), (20000, 1096), (4096, 1024)])
 def test_gemm_small_m(M, N, K):
     lib = ops()
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -191,10 +192,11 @@ def test_gemm_small_m(M, N, K):
     assert torch.equal(one, out[M - 1:M]), "a row's result depends on the batch"
 
 
+@pytest.mark.parametrize("F", [344, 10400])
 @pytest.mark.parametrize("M", [1, 7, 8, 13])
-def test_gemm_small_m_with_fused_activation(M):
+def test_gemm_small_m_with_fused_activation(M, F):
     lib = ops()
-    F, K = 344, 200
+    K = 200
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     gate = (torch.randn(F, K, device=DEV) / math.sqrt(K) * 3).to(torch.bfloat16)
     up = (torch.randn(F, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
@@ -206,7 +208,7 @@ def test_gemm_small_m_with_fused_activation(M):
 
 
 @pytest.mark.parametrize("M,H,N2,K1,ks1,ks2", [(8, 2048, 512, 1024, 2, 1), (3, 200, 96, 64, 1, 1), (13, 2304, 256, 512, 4, 2),
-                                                (1, 64, 48, 4096, 4, 1)])
+                                                (1, 64, 48, 4096, 4, 1), (8, 2048, 16384, 1024, 2, 1), (5, 96, 9616, 64, 1, 1)])
 def test_gemm_small_m_carries_the_norm(M, H, N2, K1, ks1, ks2):
     """Two products with an RMSNorm between them and no norm kernel: the first adds to the float32 stream and
     leaves stream * weight and per-tile sums of squares, the second scales its rows by 1 / rms. Widths that

@@ -114,7 +114,9 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
     }
 }
 
-template <int NT, typename TO>
+// EXACT: N is a multiple of 16 and every K slice a multiple of 1,024 (8 warps x 4 blocks x 32), so no row is
+// clamped and no load is predicated: a third fewer instructions in the loop that feeds the memory system.
+template <int NT, typename TO, bool EXACT>
 __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
@@ -126,7 +128,8 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
     const int g = lane >> 2, q = lane & 3;
     const int tile = blockIdx.x, slice = blockIdx.y;
     const int n0 = tile * ROWS;
-    const int ra = min(n0 + g, p.N - 1), rb = min(n0 + g + 8, p.N - 1);   // clamped: out-of-range rows are not stored
+    // clamped: out-of-range rows are not stored
+    const int ra = EXACT ? n0 + g : min(n0 + g, p.N - 1), rb = EXACT ? n0 + g + 8 : min(n0 + g + 8, p.N - 1);
     const __nv_bfloat16* wa_p = p.w + (int64_t)ra * p.ldw + q * 8;
     const __nv_bfloat16* wb_p = p.w + (int64_t)rb * p.ldw + q * 8;
     const __nv_bfloat16* x_p[NT];
@@ -157,7 +160,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
     for (int u = 0; u < UNROLL; ++u) {
         const int k0 = (kb + u * us) * 32;
         // K is a multiple of 8: a lane's 8 elements are all inside or all outside
-        const bool in = kb + u * us < kb_end && k0 + q * 8 < p.K;
+        const bool in = EXACT || (kb + u * us < kb_end && k0 + q * 8 < p.K);
         wa[u] = in ? ld_stream(wa_p + k0) : zero;
         wb[u] = in ? ld_stream(wb_p + k0) : zero;
     }
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k0 = (kb + u * us) * 32;
-            const bool in = kb + u * us < kb_end && k0 + q * 8 < p.K;
+            const bool in = EXACT || (kb + u * us < kb_end && k0 + q * 8 < p.K);
 #pragma unroll
             for (int t = 0; t < NT; ++t)
                 xv[u][t] = (in && x_ok[t]) ? *reinterpret_cast<const uint4*>(x_p[t] + k0) : zero;
@@ -214,12 +217,22 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
             }
         }
         const int nkb = kb + WARPS * UNROLL;      // the next round's weights
+        if (EXACT) {
+            if (nkb - warp * ws < kb_end) {       // the same for the whole CTA
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k0 = (nkb + u * us) * 32;
-            const bool in = nkb + u * us < kb_end && k0 + q * 8 < p.K;
-            wa[u] = in ? ld_stream(wa_p + k0) : zero;
-            wb[u] = in ? ld_stream(wb_p + k0) : zero;
+                for (int u = 0; u < UNROLL; ++u) {
+                    wa[u] = ld_stream(wa_p + (nkb + u * us) * 32);
+                    wb[u] = ld_stream(wb_p + (nkb + u * us) * 32);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int k0 = (nkb + u * us) * 32;
+                const bool in = nkb + u * us < kb_end && k0 + q * 8 < p.K;
+                wa[u] = in ? ld_stream(wa_p + k0) : zero;
+                wb[u] = in ? ld_stream(wb_p + k0) : zero;
+            }
         }
     }
     // c0, c1: (weight row g, batch q * 2 + {0, 1}); c2, c3: weight row g + 8
@@ -380,7 +393,11 @@ XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bia
         p.counters = (unsigned int*)((char*)scratch + scratch_bytes - kCounterBytes);
     }
     const dim3 grid(tiles, ksplit);
-#define XS_GO(NT, TO) xs_launch(gemm_small_m_kernel<NT, TO>, grid, dim3(WARPS * 32), 0, stream, p)
+    // (up to 8 rows: with 16 the unpredicated loop spills registers)
+    const bool exact = M <= 8 && N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0;
+#define XS_GO(NT, TO)                                                                                       \
+    ((exact && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true>, grid, dim3(WARPS * 32), 0, stream, p)  \
+                        : xs_launch(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, p))
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
     } else if (out_dtype == XS_BF16) {
