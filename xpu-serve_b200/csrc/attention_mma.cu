@@ -613,6 +613,38 @@ XS_API int xs_attention_mma_set_decode_stages(int n) {
     return old;
 }
 
+namespace {
+template <int D, int NST>
+int decode_ctas_per_sm() {
+    constexpr int LD = D + 8;
+    const size_t smem = (size_t)(16 + 2 * NST * BN) * LD * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(attention_decode_mma_kernel<D, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_mma_kernel<D, NST>, NTHREADS, smem) != cudaSuccess)
+        n = 0;
+    return n;
+}
+template <int D>
+int decode_ctas_per_sm_d() {
+    return g_attn_decode_stages >= 3 ? decode_ctas_per_sm<D, 3>() : decode_ctas_per_sm<D, 2>();
+}
+}  // namespace
+
+// CTAs of the decode kernel (one token a sequence) that fit an SM at once, for this head size and the current
+// number of stages; 0 when the head size is not supported. The caller sizes its key splits by it.
+XS_API int xs_attention_mma_decode_ctas_per_sm(int D) {
+    switch (D) {
+        case 16: return decode_ctas_per_sm_d<16>();
+        case 32: return decode_ctas_per_sm_d<32>();
+        case 48: return decode_ctas_per_sm_d<48>();
+        case 64: return decode_ctas_per_sm_d<64>();
+        case 96: return decode_ctas_per_sm_d<96>();
+        case 128: return decode_ctas_per_sm_d<128>();
+        default: return 0;
+    }
+}
+
 // Scratch the split path needs, in bytes, for `rows` = tokens * heads.
 XS_API int64_t xs_attention_mma_scratch_bytes(int64_t rows, int D, int splits) {
     return splits <= 1 ? 0 : rows * splits * ((int64_t)D + 2) * (int64_t)sizeof(float);

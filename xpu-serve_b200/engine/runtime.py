@@ -60,7 +60,8 @@ class Runtime:
         # cuBLAS may otherwise reduce split products in bfloat16
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         # decode attention cuts each sequence's keys over enough CTAs to fill this many CTA slots an SM
-        self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "2"))
+        # (0: sized by rounds of CTAs, parts/attention.py decode_splits; n > 0: n CTAs an SM, the earlier rule)
+        self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "0"))
         self.small_m = 16     # products with at most this many rows use this library's streaming kernel
         # decode: RMSNorm carried by the products on either side of it instead of a kernel of its own
         self.fuse_norms = os.environ.get("XS_NO_NORM_FUSION", "0") != "1"

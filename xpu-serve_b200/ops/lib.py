@@ -61,6 +61,8 @@ def _signatures(lib) -> None:
     lib.xs_attention_mma_scratch_bytes.argtypes = [c_int64, c_int, c_int]
     lib.xs_attention_mma_supports.restype = c_int
     lib.xs_attention_mma_supports.argtypes = [c_int, c_int, c_int]
+    lib.xs_attention_mma_decode_ctas_per_sm.restype = c_int
+    lib.xs_attention_mma_decode_ctas_per_sm.argtypes = [c_int]
     lib.xs_gemm_small_m_supports.restype = c_int
     lib.xs_gemm_small_m_supports.argtypes = [c_int, c_int, c_int64, c_int64]
     lib.xs_gemm_tc_supports.restype = c_int
@@ -253,6 +255,16 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Ten
 
 def attention_mma_supports(head_dim: int, page_size: int, group: int) -> bool:
     return bool(load().xs_attention_mma_supports(head_dim, page_size, group))
+
+
+_decode_ctas = {}
+
+
+def attention_mma_decode_ctas_per_sm(head_dim: int) -> int:
+    """CTAs of the decode attention kernel that fit an SM at once (asked of the device once per head size)."""
+    if head_dim not in _decode_ctas:
+        _decode_ctas[head_dim] = int(load().xs_attention_mma_decode_ctas_per_sm(head_dim))
+    return _decode_ctas[head_dim]
 
 
 def attention_mma_scratch_bytes(rows: int, head_dim: int, splits: int) -> int:

@@ -18,6 +18,21 @@ from ..ops import lib as ops
 from .base import KVNeed, Mixer, TensorSpec
 
 
+def decode_splits(tiles: int, blocks: int, slots: int) -> int:
+    """Into how many parts to cut each sequence's keys when every sequence brings one token: `tiles` CTAs
+    (sequences x kv heads) would each walk `blocks` 64-key blocks; `slots` CTAs run at one time. The cost of a
+    choice is its number of rounds of CTAs times a CTA's length (its blocks and a fixed cost worth about two),
+    plus the combine kernel when there is more than one part. 64 sequences of 2,048 keys over 444 slots: one part
+    is 2 rounds of 34, four parts are 5 rounds of 10."""
+    best, best_cost = 1, None
+    for parts in range(1, max(1, min(blocks, 32)) + 1):
+        rounds = -(-tiles * parts // slots)
+        cost = rounds * (-(-blocks // parts) + 2) + (1.5 if parts > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = parts, cost
+    return best
+
+
 class AttentionMixer(Mixer):
     kind = "attention"
     fuses_norm = True
@@ -104,7 +119,10 @@ class AttentionMixer(Mixer):
             blocks = -(-step.max_kv_len // step.page_size)
             if s.window > 0:
                 blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
-            splits = max(1, min(blocks, 32, (rt.attn_split_factor * rt.sm_count) // max(tiles, 1)))
+            if step.decode and s.heads // s.kv_heads <= 16 and rt.attn_split_factor == 0:
+                splits = decode_splits(tiles, blocks, rt.sm_count * max(1, ops.attention_mma_decode_ctas_per_sm(s.head_dim)))
+            else:
+                splits = max(1, min(blocks, 32, (max(rt.attn_split_factor, 1) * rt.sm_count) // max(tiles, 1)))
             scratch = None
             if splits > 1:
                 need = ops.attention_mma_scratch_bytes(q.shape[0] * s.heads, s.head_dim, splits)
