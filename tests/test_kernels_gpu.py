@@ -411,12 +411,57 @@ def test_attention(case, kernel, dtype):
             close(out, ref, dtype, factor=3 if dtype == "bfloat16" else 20)
 
 
+ATTN_TC_CASES = [
+    # starts, q_lens, Hq, Hkv, window (head size 64)
+    ([0], [200], 32, 8, 0),                          # the 1.2B shape's heads: 32 tokens a tile
+    ([63, 64, 200, 0], [1, 1, 1, 1], 8, 1, 0),       # single tokens; a sequence that holds one key; a page's first row
+    ([0, 0, 0], [5, 70, 300], 4, 2, 0),              # prompts of unequal lengths, several tiles and blocks
+    ([10, 100, 700], [60, 3, 130], 4, 4, 0),         # continuing sequences, one head a group
+    ([0, 130], [150, 1], 4, 1, 37),                  # a window with its edge inside and across pages
+    ([500], [200], 16, 1, 100),                      # 16 heads a group, a window that has left whole blocks behind
+    ([0], [129], 2, 2, 0),                           # one row into the second tile, one key into the second block
+]
+
+
+@pytest.mark.parametrize("case", ATTN_TC_CASES)
+def test_attention_tc(case):
+    """The tcgen05 kernel for prompts against the float64 reference, with a dominant score planted at the first
+    visible key of each sequence's last query (a far key; with a window: its very edge) and a larger one just
+    outside the window. The cache holds loud stale values wherever the sequences do not."""
+    lib = ops()
+    starts, q_lens, Hq, Hkv, window = case
+    D = 64
+    assert lib.attention_tc_supports(D, 64, Hq // Hkv)
+    assert not lib.attention_tc_supports(128, 64, 4) and not lib.attention_tc_supports(64, 64, 3)
+    pg = Paged(starts, q_lens, Hq, Hkv, D, "bfloat16", seed=len(starts) + Hq)
+    for s in range(len(starts)):
+        t = int(pg.cu[s + 1]) - 1
+        p = int(pg.pos[t])
+        j = max(0, p - window + 1) if window > 0 else 0
+        pg.k[s][j] = pg.q[t, 0] * 3.0
+        if window > 0 and j > 0:
+            pg.k[s][j - 1] = pg.q[t, 0] * 6.0
+    pg.fill_pool()
+    scale = 1.0 / math.sqrt(D)
+    gate = torch.randn(sum(q_lens), Hq + 3).to(torch.bfloat16)
+    for gt in (None, gate):
+        ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
+        out = run_attention(lib, pg, "tc", scale, window, gt, 1)
+        close(out, ref, "bfloat16", factor=3)
+        same = run_attention(lib, pg, "mma", scale, window, gt, 1)
+        close(out, same.double(), "bfloat16", factor=3)
+
+
 def run_attention(lib, pg, kernel, scale, window, gate, splits):
     d = pg.dev()
     T = d["q"].shape[0]
     out = torch.full((T, pg.Hq, pg.D), float("nan"), device=DEV, dtype=d["q"].dtype)
     gt = None if gate is None else gate.to(DEV)[:, :pg.Hq]
-    if kernel == "generic":
+    if kernel == "tc":
+        lib.attention_tc(d["q"], d["pool"], d["table"], d["cu"], d["kv_lens"], gt, out, len(pg.starts), max(pg.q_lens),
+                         pg.Hkv, 64, scale, window)
+        assert lib.gemm_tc_status(DEV).item() == 0, "a wait inside the kernel gave up"
+    elif kernel == "generic":
         lib.attention_generic(d["q"], d["pool"], d["table"], d["seq_of"], d["pos"], gt, out, pg.Hkv, 64, scale, window)
     else:
         need = lib.attention_mma_scratch_bytes(T * pg.Hq, pg.D, splits)

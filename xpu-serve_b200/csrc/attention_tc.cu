@@ -1,0 +1,398 @@
+// Prefill attention over the paged bfloat16 cache on Blackwell's fifth-generation tensor cores.
+//
+// One CTA owns a tile of 128 query rows that share one kv head (row r = token r / G, head r % G of the
+// group, G = heads / kv_heads) and walks the cache in blocks of 128 keys (two pages). Per block:
+//
+//   warp 0   TMA producer: the block's K and V pages (64 x 64 elements each, 128-byte swizzle) into a
+//            ring of three stages. Pages past the sequence's end, pages a window has given back, and the
+//            rows of the last page past the sequence's length are zeroed in shared memory (V only: a
+//            masked score becomes a weight of exactly 0, and 0 times stale bits must stay 0).
+//   warp 1   one thread issues S = Q K^T (tcgen05.mma, M 128, N 128, K 16 x D / 16, Q and K K-major) into
+//            one of two S buffers in tensor memory, and O_j = P V (M 128, N D, K 16 x 8, P K-major from
+//            shared memory, V MN-major: the pages' own layout) into one of two O buffers.
+//   warps 2-5 softmax, one thread a query row: tcgen05.ld of S, mask (causal, window), running maximum
+//            and sum in float32 with base-2 exponentials, P as bfloat16 into shared memory (swizzled by
+//            hand as TMA would have); then tcgen05.ld of the block's O_j, added to the row's output in
+//            registers, which is rescaled when the maximum moves.
+//
+// S of block j + 1 is issued before P V of block j, so the tensor pipe works while the softmax of block j
+// runs. Every mbarrier wait is bounded (see tc_common.cuh); a CTA that gives up frees its tensor memory and
+// sets *status. Head size 64, groups that divide 128, one key split; other cases take the mma.sync kernel.
+// The reference's counterpart is its XMX flash kernel for prefill (src/backend/sycl/sycl_flash_attention.cpp:1-15).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int TM = 128;           // query rows a CTA
+constexpr int TN = 128;           // keys a block
+constexpr int PAGE = 64;          // keys a page
+constexpr int kAttnThreads = 192;
+constexpr int KV_STAGES = 3;
+
+struct AttnTcParams {
+    const __nv_bfloat16* q;          // [T, Hq, D]
+    const int32_t* page_table;       // [n_seqs, P]
+    int P;
+    const int32_t* cu_seqlens;
+    const int32_t* kv_lens;
+    const __nv_bfloat16* gate;       // [T, ld_gate] or null
+    int64_t ld_gate;
+    __nv_bfloat16* out;              // [T, Hq, D]
+    int* status;
+    int Hq, Hkv, G, tokens_per_tile, window;
+    float scale_log2;
+};
+
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Writes of this thread to shared memory become visible to the tensor core's and the TMA unit's reads.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Descriptor of an MN-major operand with the 128-byte swizzle: 64 elements of N contiguous (128 bytes), rows of
+// K 128 bytes apart, groups of 8 rows of K 1024 bytes apart (stride byte offset). One 64-wide chunk of N only,
+// so the leading byte offset is not used.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p) {
+    static_assert(D == 64, "one 128-byte swizzle atom a row");
+    constexpr int kPageBytes = PAGE * D * 2;                   // 8 KB
+    constexpr int kStageBytes = 4 * kPageBytes;                // K (two pages), V (two pages)
+    constexpr int kPBytes = TM * TN * 2;                       // 32 KB: two halves of 64 keys
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_sm = base;
+    uint8_t* kv_sm = q_sm + TM * D * 2;
+    uint8_t* p_sm = kv_sm + KV_STAGES * kStageBytes;
+    __shared__ __align__(8) uint64_t bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_fix[KV_STAGES];
+    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_o_full[2], bar_o_empty[2];
+    __shared__ uint32_t tmem_base;
+    __shared__ int abort_flag;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    // later tiles see more keys: they are started first, so that the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x, seq = blockIdx.y, kvh = blockIdx.z;
+    const int tok_begin = p.cu_seqlens[seq];
+    const int q_len = p.cu_seqlens[seq + 1] - tok_begin;
+    const int t0 = tile * p.tokens_per_tile;
+    if (t0 >= q_len) return;                                   // the whole CTA, before anything is set up
+    const int nt = min(p.tokens_per_tile, q_len - t0);
+    const int kv_len = p.kv_lens[seq];
+    const int pos0 = kv_len - q_len + t0;
+    const int hi = pos0 + nt;                                  // keys [lo, hi) matter to this tile
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int b_lo = lo / TN, nb = (hi + TN - 1) / TN - b_lo;
+    const int32_t* table = p.page_table + (int64_t)seq * p.P;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.G;
+    const int rows_valid = nt * G;
+    constexpr uint32_t kTmemCols = 512;                        // S0, S1 (128 each), O0, O1 (D each)
+    constexpr uint32_t kColO = 2 * TN;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(smem_u32(&bar_kv_full[s]), 1);
+            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+            mbar_init(smem_u32(&bar_fix[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_s_full[b]), 1);
+            mbar_init(smem_u32(&bar_s_empty[b]), 4);           // one arrival per softmax warp
+            mbar_init(smem_u32(&bar_p_full[b]), 4);
+            mbar_init(smem_u32(&bar_o_full[b]), 1);
+            mbar_init(smem_u32(&bar_o_empty[b]), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp >= 2) {
+        // ---- Q tile: row r = (token t0 + r / G, head kvh * G + r % G), zero beyond the tile's rows; chunk c of a
+        // row sits at chunk c ^ (r % 8), which is where the 128-byte swizzle looks for it
+        const int r = (warp & 3) * 32 + lane;
+        const bool ok = r < rows_valid;
+        const __nv_bfloat16* src = p.q + ((int64_t)(tok_begin + t0 + (ok ? r / G : 0)) * p.Hq + kvh * G + (ok ? r % G : 0)) * D;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const uint4 v = ok ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(q_sm + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+        }
+        fence_async_smem();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    volatile int* abort_p = &abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        int fixes[KV_STAGES];
+#pragma unroll
+        for (int s = 0; s < KV_STAGES; ++s) fixes[s] = 0;
+        for (int j = 0; j < nb && !*abort_p; ++j) {
+            const int s = j % KV_STAGES;
+            if (j >= KV_STAGES && !mbar_wait(smem_u32(&bar_kv_empty[s]), ((j / KV_STAGES) & 1) ^ 1, abort_p)) break;
+            uint8_t* stage = kv_sm + s * kStageBytes;
+            int page[2], valid[2];                             // physical page (-1: none), rows of it inside the sequence
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int lp = 2 * (b_lo + j) + h;
+                const int rows = min(PAGE, kv_len - lp * PAGE);
+                page[h] = (rows > 0 && lp < p.P) ? table[lp] : -1;
+                valid[h] = page[h] >= 0 ? rows : 0;
+            }
+            const bool fix = valid[0] < PAGE || valid[1] < PAGE;
+            const uint32_t bytes = (uint32_t)((page[0] >= 0) + (page[1] >= 0)) * 2u * kPageBytes;
+            const uint32_t bar = smem_u32(fix ? &bar_fix[s] : &bar_kv_full[s]);
+            if (lane == 0) {
+                if (bytes > 0) mbar_expect_tx(bar, bytes); else mbar_arrive_cta(bar);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (page[h] < 0) continue;
+                    const int y = ((page[h] * 2 + 0) * p.Hkv + kvh) * PAGE;
+                    tma_load_2d(smem_u32(stage + h * kPageBytes), &tmap_kv, 0, y, bar);
+                    tma_load_2d(smem_u32(stage + 2 * kPageBytes + h * kPageBytes), &tmap_kv, 0, y + p.Hkv * PAGE, bar);
+                }
+            }
+            if (fix) {
+                // wait for what was loaded, zero V's rows that hold no key of this sequence, hand the stage over
+                if (!mbar_wait(smem_u32(&bar_fix[s]), fixes[s] & 1, abort_p)) break;
+                ++fixes[s];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint8_t* v_page = stage + 2 * kPageBytes + h * kPageBytes;
+                    for (int i = valid[h] * 8 + lane; i < PAGE * 8; i += 32)      // 16-byte chunks from row valid[h] on
+                        *reinterpret_cast<uint4*>(v_page + i * 16) = make_uint4(0, 0, 0, 0);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cta(smem_u32(&bar_kv_full[s]));
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc_mn(TM, TN);
+            constexpr uint32_t idesc_o = instr_desc_mn(TM, D, true);
+            const uint64_t dq = smem_desc_sw128(smem_u32(q_sm));
+            for (int j = 0; j <= nb && !*abort_p; ++j) {
+                if (j < nb) {
+                    const int s = j % KV_STAGES, buf = j & 1;
+                    if (!mbar_wait(smem_u32(&bar_kv_full[s]), (j / KV_STAGES) & 1, abort_p)) break;
+                    if (j >= 2 && !mbar_wait(smem_u32(&bar_s_empty[buf]), ((j >> 1) & 1) ^ 1, abort_p)) break;
+                    tcgen05_fence_after();
+                    const uint64_t dk = smem_desc_sw128(smem_u32(kv_sm + s * kStageBytes));
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k)
+                        umma_bf16(tmem_base + (uint32_t)(buf * TN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k > 0 ? 1u : 0u);
+                    tcgen05_commit(smem_u32(&bar_s_full[buf]));
+                }
+                if (j >= 1) {
+                    const int jj = j - 1, s = jj % KV_STAGES, buf = jj & 1;
+                    if (!mbar_wait(smem_u32(&bar_p_full[buf]), (jj >> 1) & 1, abort_p)) break;
+                    if (jj >= 2 && !mbar_wait(smem_u32(&bar_o_empty[buf]), ((jj >> 1) & 1) ^ 1, abort_p)) break;
+                    tcgen05_fence_after();
+                    const uint32_t p_addr = smem_u32(p_sm + buf * kPBytes);
+                    const uint32_t v_addr = smem_u32(kv_sm + s * kStageBytes + 2 * kPageBytes);
+#pragma unroll
+                    for (int k = 0; k < TN / 16; ++k) {
+                        // P: K-major, 16 keys = 32 bytes along a row, the second 64 keys in the second half tile
+                        const uint64_t da = smem_desc_sw128(p_addr + (k >> 2) * (TM * 128) + (k & 3) * 32);
+                        // V: MN-major, 16 keys = 16 rows of 128 bytes
+                        const uint64_t db = smem_desc_sw128_mn(v_addr + k * 16 * 128);
+                        umma_bf16(tmem_base + kColO + (uint32_t)(buf * D), da, db, idesc_o, k > 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(smem_u32(&bar_o_full[buf]));
+                    tcgen05_commit(smem_u32(&bar_kv_empty[s]));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax, one thread a row
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int pos = r < rows_valid ? pos0 + r / G : -1;       // -1: the row sees nothing
+        float o[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) o[d] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < nb; ++j) {
+            const int buf = j & 1;
+            if (!mbar_wait(smem_u32(&bar_s_full[buf]), (j >> 1) & 1, abort_p)) { ok = false; break; }
+            tcgen05_fence_after();
+            const int key0 = (b_lo + j) * TN;
+            // a block that every row of the tile sees whole needs no per-element test
+            const bool whole = key0 + TN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - key0 < p.window);
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < TN; c += 32) {
+                uint32_t raw[32];
+                tmem_ld32(lane_base + (uint32_t)(buf * TN + c), raw);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int key = key0 + c + e;
+                    const bool see = pos >= 0 && (whole || (key <= pos && (p.window == 0 || pos - key < p.window)));
+                    mx = fmaxf(mx, see ? __uint_as_float(raw[e]) * p.scale_log2 : -INFINITY);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float mb = m_new == -INFINITY ? 0.0f : m_new;
+            const float alpha = ex2(m - mb);                      // 0 while nothing was seen
+            m = m_new;
+            float add = 0.0f;
+            uint8_t* p_row = p_sm + buf * kPBytes + r * 128;
+#pragma unroll 1
+            for (int c = 0; c < TN; c += 32) {
+                uint32_t raw[32];
+                tmem_ld32(lane_base + (uint32_t)(buf * TN + c), raw);
+                float w[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int key = key0 + c + e;
+                    const bool see = pos >= 0 && (whole || (key <= pos && (p.window == 0 || pos - key < p.window)));
+                    w[e] = see ? ex2(__uint_as_float(raw[e]) * p.scale_log2 - mb) : 0.0f;
+                    add += w[e];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int kc = (c >> 3) + i;                   // 8-key chunk of the block, 0..15
+                    const uint4 v = make_uint4(pack_bf16(w[8 * i], w[8 * i + 1]), pack_bf16(w[8 * i + 2], w[8 * i + 3]),
+                                               pack_bf16(w[8 * i + 4], w[8 * i + 5]), pack_bf16(w[8 * i + 6], w[8 * i + 7]));
+                    *reinterpret_cast<uint4*>(p_row + (kc >> 3) * (TM * 128) + (((kc & 7) ^ (r & 7)) << 4)) = v;
+                }
+            }
+            l = l * alpha + add;
+            fence_async_smem();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cta(smem_u32(&bar_p_full[buf]));
+                mbar_arrive_cta(smem_u32(&bar_s_empty[buf]));
+            }
+            if (j >= 1) {
+                // the block before: its P V has had the time of this block's softmax
+                const int jb = (j - 1) & 1;
+                if (!mbar_wait(smem_u32(&bar_o_full[jb]), ((j - 1) >> 1) & 1, abort_p)) { ok = false; break; }
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t raw[32];
+                    tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + c), raw);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[c + e] += __uint_as_float(raw[e]);
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cta(smem_u32(&bar_o_empty[jb]));
+            }
+#pragma unroll
+            for (int d = 0; d < D; ++d) o[d] *= alpha;            // now relative to this block's maximum
+        }
+        if (ok && nb > 0) {
+            const int jb = (nb - 1) & 1;
+            if (mbar_wait(smem_u32(&bar_o_full[jb]), ((nb - 1) >> 1) & 1, abort_p)) {
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t raw[32];
+                    tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + c), raw);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[c + e] += __uint_as_float(raw[e]);
+                }
+                if (r < rows_valid) {
+                    const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+                    float f = l > 0.0f ? 1.0f / l : 0.0f;
+                    if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)t * p.Hq + h) * D);
+#pragma unroll
+                    for (int c = 0; c < D / 8; ++c)
+                        dst[c] = make_uint4(pack_bf16(o[8 * c] * f, o[8 * c + 1] * f), pack_bf16(o[8 * c + 2] * f, o[8 * c + 3] * f),
+                                            pack_bf16(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf16(o[8 * c + 6] * f, o[8 * c + 7] * f));
+                }
+            }
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+}
+
+}  // namespace
+
+// 1 when xs_attention_tc takes this problem: head size 64, pages of 64 keys, a group that divides 128.
+XS_API int xs_attention_tc_supports(int D, int page_size, int G) {
+    return D == 64 && page_size == PAGE && G >= 1 && G <= TM && TM % G == 0 && encode_fn() != nullptr;
+}
+
+// The same operation as xs_attention_mma with one key split, for prompts. pool: [pool_pages, 2, Hkv, 64, D].
+// status: one device int that the kernel sets non-zero if a wait inside it gave up (the result is then invalid).
+XS_API int xs_attention_tc(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table, int P,
+                           const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate, int64_t ld_gate, void* out,
+                           int T, int n_seqs, int max_q_len, int Hq, int Hkv, int D, int page_size, float scale, int window,
+                           int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d heads over %d kv heads", Hq, Hkv);
+    const int G = Hq / Hkv;
+    XS_REQUIRE(xs_attention_tc_supports(D, page_size, G),
+               "attention (tcgen05): head size %d, page size %d, group %d is not supported", D, page_size, G);
+    XS_REQUIRE(window >= 0 && max_q_len >= 1 && n_seqs >= 1 && P >= 1 && pool_pages >= 1 && status != nullptr,
+               "attention (tcgen05): bad sizes");
+    XS_REQUIRE(n_seqs <= 65535 && Hkv <= 65535, "attention (tcgen05): grid too large");
+    XS_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)pool % 16 == 0 && (uintptr_t)out % 16 == 0,
+               "attention (tcgen05): operands must be 16-byte aligned");
+    alignas(64) CUtensorMap map;
+    XS_REQUIRE(make_map(&map, pool, pool_pages * 2 * Hkv * PAGE, D, D, PAGE), "attention (tcgen05): the cache's tensor map could not be made");
+    AttnTcParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.page_table = page_table;
+    p.P = P;
+    p.cu_seqlens = cu_seqlens;
+    p.kv_lens = kv_lens;
+    p.gate = (const __nv_bfloat16*)gate;
+    p.ld_gate = ld_gate;
+    p.out = (__nv_bfloat16*)out;
+    p.status = status;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.G = G;
+    p.tokens_per_tile = TM / G;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    const int max_tiles = ceil_div_i(max_q_len, p.tokens_per_tile);
+    const size_t smem = (size_t)TM * D * 2 + (size_t)KV_STAGES * 4 * PAGE * D * 2 + 2 * (size_t)TM * TN * 2 + 1024;
+    static bool opted = false;
+    if (!opted) {
+        cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        opted = true;
+    }
+    const dim3 grid(max_tiles, n_seqs, Hkv);
+    XS_REQUIRE(xs_launch(attention_tc_kernel<64>, grid, dim3(kAttnThreads), smem, stream, map, p) == cudaSuccess,
+               "attention (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}

@@ -40,6 +40,7 @@ def _signatures(lib) -> None:
         "xs_attention_generic": [P, P, P, I, P, P, P, L, P, I, I, I, I, I, F, I, I, P],
         "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
+        "xs_attention_tc": [P, P, L, P, I, P, P, P, L, P, I, I, I, I, I, I, I, F, I, P, P],
         "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P],
         "xs_gemm_small_m_normed": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P, P],
         "xs_gemm_tc": [P, P, P, P, I, I, I, I, I, L, L, L, I, P, L, P, P],
@@ -61,6 +62,8 @@ def _signatures(lib) -> None:
     lib.xs_attention_mma_scratch_bytes.argtypes = [c_int64, c_int, c_int]
     lib.xs_attention_mma_supports.restype = c_int
     lib.xs_attention_mma_supports.argtypes = [c_int, c_int, c_int]
+    lib.xs_attention_tc_supports.restype = c_int
+    lib.xs_attention_tc_supports.argtypes = [c_int, c_int, c_int]
     lib.xs_attention_mma_decode_ctas_per_sm.restype = c_int
     lib.xs_attention_mma_decode_ctas_per_sm.argtypes = [c_int]
     lib.xs_gemm_small_m_supports.restype = c_int
@@ -292,6 +295,31 @@ def attention_mma(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
         q.data_ptr(), pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
         kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), _ptr(scratch), sbytes, T, n_seqs, max_q_len, heads,
         kv_heads, D, page_size, float(scale), int(window), int(splits), _stream()), kernels=2 if splits > 1 else 1)
+
+
+def attention_tc_supports(head_dim: int, page_size: int, group: int) -> bool:
+    return bool(load().xs_attention_tc_supports(head_dim, page_size, group))
+
+
+def attention_tc(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                 kv_lens: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, n_seqs: int, max_q_len: int,
+                 kv_heads: int, page_size: int, scale: float, window: int) -> None:
+    """Attention for prompts on the tcgen05 tensor cores (head size 64): the same operation as attention_mma with
+    one key split. A wait that gives up inside the kernel sets gemm_tc_status(device)."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "cache", torch.bfloat16)
+    _need(page_table, "page table", torch.int32)
+    T, heads, D = q.shape
+    if tuple(pool.shape[1:]) != (2, kv_heads, page_size, D):
+        raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 2, {kv_heads}, {page_size}, {D}]")
+    ld_gate = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < heads:
+            raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {heads} heads")
+        ld_gate = gate.stride(0)
+    _check(load().xs_attention_tc(
+        q.data_ptr(), pool.data_ptr(), pool.shape[0], page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
+        kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), T, n_seqs, max_q_len, heads, kv_heads, D, page_size,
+        float(scale), int(window), gemm_tc_status(q.device).data_ptr(), _stream()))
 
 
 def gemm_small_m_supports(M: int, K: int, ldx: int, ldw: int) -> bool:
