@@ -246,36 +246,52 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             const int key0 = (b_lo + j) * TN;
             // a block that every row of the tile sees whole needs no per-element test
             const bool whole = key0 + TN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - key0 < p.window);
-            float mx = -INFINITY;
+            // A row that sees the whole block (most blocks of a long prompt) needs no test per key. The maximum
+            // and the sum run in four independent chains each, so that a thread's own instructions overlap.
+            const bool plain = whole && pos >= 0;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
             for (int c = 0; c < TN; c += 32) {
                 uint32_t raw[32];
                 tmem_ld32(lane_base + (uint32_t)(buf * TN + c), raw);
+                if (plain) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int key = key0 + c + e;
-                    const bool see = pos >= 0 && (whole || (key <= pos && (p.window == 0 || pos - key < p.window)));
-                    mx = fmaxf(mx, see ? __uint_as_float(raw[e]) * p.scale_log2 : -INFINITY);
+                    for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int key = key0 + c + e;
+                        const bool see = key <= pos && (p.window == 0 || pos - key < p.window);   // pos -1: nothing
+                        mx4[e & 3] = fmaxf(mx4[e & 3], see ? __uint_as_float(raw[e]) : -INFINITY);
+                    }
                 }
             }
+            // the scale is positive: the largest scaled score is the scaled largest score
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             const float m_new = fmaxf(m, mx);
             const float mb = m_new == -INFINITY ? 0.0f : m_new;
             const float alpha = ex2(m - mb);                      // 0 while nothing was seen
             m = m_new;
-            float add = 0.0f;
+            float add4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint8_t* p_row = p_sm + buf * kPBytes + r * 128;
 #pragma unroll 1
             for (int c = 0; c < TN; c += 32) {
                 uint32_t raw[32];
                 tmem_ld32(lane_base + (uint32_t)(buf * TN + c), raw);
                 float w[32];
+                if (plain) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int key = key0 + c + e;
-                    const bool see = pos >= 0 && (whole || (key <= pos && (p.window == 0 || pos - key < p.window)));
-                    w[e] = see ? ex2(__uint_as_float(raw[e]) * p.scale_log2 - mb) : 0.0f;
-                    add += w[e];
+                    for (int e = 0; e < 32; ++e) w[e] = ex2(fmaf(__uint_as_float(raw[e]), p.scale_log2, -mb));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int key = key0 + c + e;
+                        const bool see = key <= pos && (p.window == 0 || pos - key < p.window);
+                        w[e] = see ? ex2(fmaf(__uint_as_float(raw[e]), p.scale_log2, -mb)) : 0.0f;
+                    }
                 }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) add4[e & 3] += w[e];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int kc = (c >> 3) + i;                   // 8-key chunk of the block, 0..15
@@ -284,6 +300,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                     *reinterpret_cast<uint4*>(p_row + (kc >> 3) * (TM * 128) + (((kc & 7) ^ (r & 7)) << 4)) = v;
                 }
             }
+            const float add = (add4[0] + add4[1]) + (add4[2] + add4[3]);
             l = l * alpha + add;
             fence_async_smem();
             tcgen05_fence_before();
@@ -308,8 +325,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cta(smem_u32(&bar_o_empty[jb]));
             }
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {         // the maximum of most later blocks does not move
 #pragma unroll
-            for (int d = 0; d < D; ++d) o[d] *= alpha;            // now relative to this block's maximum
+                for (int d = 0; d < D; ++d) o[d] *= alpha;        // now relative to this block's maximum
+            }
         }
         if (ok && nb > 0) {
             const int jb = (nb - 1) & 1;
