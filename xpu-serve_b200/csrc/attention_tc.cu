@@ -10,10 +10,10 @@
 //   warp 1   one thread issues S = Q K^T (tcgen05.mma, M 128, N 128, K 16 x D / 16, Q and K K-major) into
 //            one of two S buffers in tensor memory, and O_j = P V (M 128, N D, K 16 x 8, P K-major from
 //            shared memory, V MN-major: the pages' own layout) into one of two O buffers.
-//   warps 2-5 softmax, one thread a query row: tcgen05.ld of S, mask (causal, window), running maximum
-//            and sum in float32 with base-2 exponentials, P as bfloat16 into shared memory (swizzled by
-//            hand as TMA would have); then tcgen05.ld of the block's O_j, added to the row's output in
-//            registers, which is rescaled when the maximum moves.
+//   warps 2-9 softmax, two threads a query row (64 keys of the block each): tcgen05.ld of S, mask (causal,
+//            window), running maximum and sum in float32 with base-2 exponentials, P as bfloat16 into
+//            shared memory (swizzled by hand as TMA would have); then tcgen05.ld of half of the block's
+//            O_j, added to the row's output in registers, which is rescaled when the maximum moves.
 //
 // S of block j + 1 is issued before P V of block j, so the tensor pipe works while the softmax of block j
 // runs. Every mbarrier wait is bounded (see tc_common.cuh); a CTA that gives up frees its tensor memory and
@@ -29,7 +29,7 @@ namespace {
 constexpr int TM = 128;           // query rows a CTA
 constexpr int TN = 128;           // keys a block
 constexpr int PAGE = 64;          // keys a page
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;   // TMA warp, MMA warp, eight softmax warps
 constexpr int KV_STAGES = 3;
 
 struct AttnTcParams {
@@ -56,6 +56,18 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// tcgen05.ld of 32 columns without waiting for them: several can be in flight before one tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Descriptor of an MN-major operand with the 128-byte swizzle: 64 elements of N contiguous (128 bytes), rows of
 // K 128 bytes apart, groups of 8 rows of K 1024 bytes apart (stride byte offset). One 64-wide chunk of N only,
 // so the leading byte offset is not used.
@@ -82,6 +94,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
     uint8_t* p_sm = kv_sm + KV_STAGES * kStageBytes;
     __shared__ __align__(8) uint64_t bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_fix[KV_STAGES];
     __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_o_full[2], bar_o_empty[2];
+    __shared__ float mx_sm[2][2][TM];                          // [block parity][half of the keys][row]
+    __shared__ float l_sm[2][TM];
     __shared__ uint32_t tmem_base;
     __shared__ int abort_flag;
 
@@ -115,10 +129,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_s_full[b]), 1);
-            mbar_init(smem_u32(&bar_s_empty[b]), 4);           // one arrival per softmax warp
-            mbar_init(smem_u32(&bar_p_full[b]), 4);
+            mbar_init(smem_u32(&bar_s_empty[b]), 8);           // one arrival per softmax warp
+            mbar_init(smem_u32(&bar_p_full[b]), 8);
             mbar_init(smem_u32(&bar_o_full[b]), 1);
-            mbar_init(smem_u32(&bar_o_empty[b]), 4);
+            mbar_init(smem_u32(&bar_o_empty[b]), 8);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -126,7 +140,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
         // ---- Q tile: row r = (token t0 + r / G, head kvh * G + r % G), zero beyond the tile's rows; chunk c of a
         // row sits at chunk c ^ (r % 8), which is where the 128-byte swizzle looks for it
         const int r = (warp & 3) * 32 + lane;
@@ -151,7 +165,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
         for (int s = 0; s < KV_STAGES; ++s) fixes[s] = 0;
         for (int j = 0; j < nb && !*abort_p; ++j) {
             const int s = j % KV_STAGES;
-            if (j >= KV_STAGES && !mbar_wait(smem_u32(&bar_kv_empty[s]), ((j / KV_STAGES) & 1) ^ 1, abort_p)) break;
+            // (the warp decides together: its lanes poll the same barrier but may give up at different polls)
+            if (j >= KV_STAGES && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_kv_empty[s]), ((j / KV_STAGES) & 1) ^ 1, abort_p))) break;
             uint8_t* stage = kv_sm + s * kStageBytes;
             int page[2], valid[2];                             // physical page (-1: none), rows of it inside the sequence
 #pragma unroll
@@ -176,7 +191,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             }
             if (fix) {
                 // wait for what was loaded, zero V's rows that hold no key of this sequence, hand the stage over
-                if (!mbar_wait(smem_u32(&bar_fix[s]), fixes[s] & 1, abort_p)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_fix[s]), fixes[s] & 1, abort_p))) break;
                 ++fixes[s];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -229,79 +244,78 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax, one thread a row
-        const int quarter = warp & 3;
+        // ------------------------------------------------------------------ softmax, two threads a row
+        // Warps 2-5 take the first 64 keys of every block and the first half of the output's channels, warps
+        // 6-9 the second halves, for the same 128 rows (a warp reaches the 32 lanes of tensor memory of its
+        // number modulo 4): two warps a scheduler hide each other's latencies. The two threads of a row
+        // exchange their maxima through shared memory once a block; their sums meet at the end.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int pos = r < rows_valid ? pos0 + r / G : -1;       // -1: the row sees nothing
-        float o[D];
+        constexpr int HN = TN / 2, HD = D / 2;
+        float o[HD];
 #pragma unroll
-        for (int d = 0; d < D; ++d) o[d] = 0.0f;
+        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
         float m = -INFINITY, l = 0.0f;
-        bool ok = true;
+        bool bad = false;                                         // a wait gave up: leave at the next common point
         for (int j = 0; j < nb; ++j) {
             const int buf = j & 1;
-            if (!mbar_wait(smem_u32(&bar_s_full[buf]), (j >> 1) & 1, abort_p)) { ok = false; break; }
+            bad |= !mbar_wait(smem_u32(&bar_s_full[buf]), (j >> 1) & 1, abort_p);
             tcgen05_fence_after();
-            const int key0 = (b_lo + j) * TN;
-            // a block that every row of the tile sees whole needs no per-element test
-            const bool whole = key0 + TN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - key0 < p.window);
-            // A row that sees the whole block (most blocks of a long prompt) needs no test per key. The maximum
-            // and the sum run in four independent chains each, so that a thread's own instructions overlap.
-            const bool plain = whole && pos >= 0;
+            const int key0 = (b_lo + j) * TN + half * HN;
+            // a block that every row of the tile sees whole needs no test per key
+            const bool plain = pos >= 0 && (b_lo + j) * TN + TN - 1 <= pos0 &&
+                               (p.window == 0 || pos0 + nt - 1 - (b_lo + j) * TN < p.window);
+            // this thread's 64 scores of the block, read once and kept through both passes
+            uint32_t raw[HN];
+            tmem_ld32_nowait(lane_base + (uint32_t)(buf * TN + half * HN), raw);
+            tmem_ld32_nowait(lane_base + (uint32_t)(buf * TN + half * HN + 32), raw + 32);
+            tmem_ld_wait();
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int c = 0; c < TN; c += 32) {
-                uint32_t raw[32];
-                tmem_ld32(lane_base + (uint32_t)(buf * TN + c), raw);
-                if (plain) {
+            if (plain) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
-                } else {
+                for (int e = 0; e < HN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
+            } else {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int key = key0 + c + e;
-                        const bool see = key <= pos && (p.window == 0 || pos - key < p.window);   // pos -1: nothing
-                        mx4[e & 3] = fmaxf(mx4[e & 3], see ? __uint_as_float(raw[e]) : -INFINITY);
-                    }
+                for (int e = 0; e < HN; ++e) {
+                    const int key = key0 + e;
+                    const bool see = key <= pos && (p.window == 0 || pos - key < p.window);   // pos -1: nothing
+                    if (!see) raw[e] = 0xff800000u;                // -inf: its weight will be exactly 0
+                    mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
                 }
             }
             // the scale is positive: the largest scaled score is the scaled largest score
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            mx_sm[buf][half][r] = mx;
+            // all 256 softmax threads meet; the barrier also tells everyone whether anyone's wait gave up
+            int any_bad;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.b32 q, %1, 0;\n\t"
+                "bar.red.or.pred p, 1, 256, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(any_bad) : "r"((int)bad) : "memory");
+            if (any_bad) { bad = true; break; }
+            mx = fmaxf(mx, mx_sm[buf][half ^ 1][r]);
             const float m_new = fmaxf(m, mx);
             const float mb = m_new == -INFINITY ? 0.0f : m_new;
             const float alpha = ex2(m - mb);                      // 0 while nothing was seen
             m = m_new;
             float add4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint8_t* p_row = p_sm + buf * kPBytes + r * 128;
-#pragma unroll 1
-            for (int c = 0; c < TN; c += 32) {
-                uint32_t raw[32];
-                tmem_ld32(lane_base + (uint32_t)(buf * TN + c), raw);
-                float w[32];
-                if (plain) {
+            uint8_t* p_row = p_sm + buf * kPBytes + half * (TM * 128) + r * 128;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) w[e] = ex2(fmaf(__uint_as_float(raw[e]), p.scale_log2, -mb));
-                } else {
+            for (int i = 0; i < HN / 8; ++i) {                     // 8-key chunks of this half of the block
+                float w[8];
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int key = key0 + c + e;
-                        const bool see = key <= pos && (p.window == 0 || pos - key < p.window);
-                        w[e] = see ? ex2(fmaf(__uint_as_float(raw[e]), p.scale_log2, -mb)) : 0.0f;
-                    }
+                for (int e = 0; e < 8; ++e) {
+                    w[e] = ex2(fmaf(__uint_as_float(raw[8 * i + e]), p.scale_log2, -mb));   // ex2(-inf) = 0
+                    add4[e & 3] += w[e];
                 }
-#pragma unroll
-                for (int e = 0; e < 32; ++e) add4[e & 3] += w[e];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int kc = (c >> 3) + i;                   // 8-key chunk of the block, 0..15
-                    const uint4 v = make_uint4(pack_bf16(w[8 * i], w[8 * i + 1]), pack_bf16(w[8 * i + 2], w[8 * i + 3]),
-                                               pack_bf16(w[8 * i + 4], w[8 * i + 5]), pack_bf16(w[8 * i + 6], w[8 * i + 7]));
-                    *reinterpret_cast<uint4*>(p_row + (kc >> 3) * (TM * 128) + (((kc & 7) ^ (r & 7)) << 4)) = v;
-                }
+                *reinterpret_cast<uint4*>(p_row + ((i ^ (r & 7)) << 4)) =
+                    make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
             }
-            const float add = (add4[0] + add4[1]) + (add4[2] + add4[3]);
-            l = l * alpha + add;
+            l = l * alpha + ((add4[0] + add4[1]) + (add4[2] + add4[3]));
             fence_async_smem();
             tcgen05_fence_before();
             __syncwarp();
@@ -312,45 +326,51 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             if (j >= 1) {
                 // the block before: its P V has had the time of this block's softmax
                 const int jb = (j - 1) & 1;
-                if (!mbar_wait(smem_u32(&bar_o_full[jb]), ((j - 1) >> 1) & 1, abort_p)) { ok = false; break; }
+                bad |= !mbar_wait(smem_u32(&bar_o_full[jb]), ((j - 1) >> 1) & 1, abort_p);
                 tcgen05_fence_after();
+                uint32_t raw[32];
+                tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + half * HD), raw);
 #pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t raw[32];
-                    tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + c), raw);
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[c + e] += __uint_as_float(raw[e]);
-                }
+                for (int e = 0; e < HD; ++e) o[e] += __uint_as_float(raw[e]);
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cta(smem_u32(&bar_o_empty[jb]));
             }
             if (__any_sync(0xffffffffu, alpha != 1.0f)) {         // the maximum of most later blocks does not move
 #pragma unroll
-                for (int d = 0; d < D; ++d) o[d] *= alpha;        // now relative to this block's maximum
+                for (int d = 0; d < HD; ++d) o[d] *= alpha;       // now relative to this block's maximum
             }
         }
-        if (ok && nb > 0) {
+        {
+            // the last block's P V; then the row's sum: this thread's keys and its partner's (both relative to
+            // the same maximum). Every softmax thread comes to the barrier, whatever happened before.
             const int jb = (nb - 1) & 1;
-            if (mbar_wait(smem_u32(&bar_o_full[jb]), ((nb - 1) >> 1) & 1, abort_p)) {
+            const bool fin = !bad && mbar_wait(smem_u32(&bar_o_full[jb]), ((nb - 1) >> 1) & 1, abort_p);
+            if (fin) {
                 tcgen05_fence_after();
+                uint32_t raw[32];
+                tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + half * HD), raw);
 #pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t raw[32];
-                    tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + c), raw);
+                for (int e = 0; e < HD; ++e) o[e] += __uint_as_float(raw[e]);
+            }
+            l_sm[half][r] = l;
+            int any_bad;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.b32 q, %1, 0;\n\t"
+                "bar.red.or.pred p, 1, 256, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(any_bad) : "r"((int)!fin) : "memory");
+            if (!any_bad && r < rows_valid) {
+                l += l_sm[half ^ 1][r];
+                const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+                float f = l > 0.0f ? 1.0f / l : 0.0f;
+                if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
+                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)t * p.Hq + h) * D + half * HD);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) o[c + e] += __uint_as_float(raw[e]);
-                }
-                if (r < rows_valid) {
-                    const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
-                    float f = l > 0.0f ? 1.0f / l : 0.0f;
-                    if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)t * p.Hq + h) * D);
-#pragma unroll
-                    for (int c = 0; c < D / 8; ++c)
-                        dst[c] = make_uint4(pack_bf16(o[8 * c] * f, o[8 * c + 1] * f), pack_bf16(o[8 * c + 2] * f, o[8 * c + 3] * f),
-                                            pack_bf16(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf16(o[8 * c + 6] * f, o[8 * c + 7] * f));
-                }
+                for (int c = 0; c < HD / 8; ++c)
+                    dst[c] = make_uint4(pack_bf16(o[8 * c] * f, o[8 * c + 1] * f), pack_bf16(o[8 * c + 2] * f, o[8 * c + 3] * f),
+                                        pack_bf16(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf16(o[8 * c + 6] * f, o[8 * c + 7] * f));
             }
         }
         tcgen05_fence_before();
