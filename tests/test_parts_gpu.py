@@ -564,3 +564,32 @@ def test_first_tokens(tmp_path, name, dtype):
     lg = model.step(cache, slots, batch, [[0], [0, 1], [0, 1, 2]]).cpu().numpy()
     assert gap_of(lg, np.concatenate([ref[:1], ref[:2], ref[:3]], 0)) <= tol
     cache.close(slots)
+
+
+def test_prompts_of_head_size_64_take_the_tcgen05_attention(tmp_path, monkeypatch):
+    """Configuration H's prompts run on the tcgen05 attention kernel (counted here), its single tokens do not;
+    with XS_PROMPT_ATTENTION=mma neither does, and the logits of the two agree."""
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.ops import lib as ops
+    folder = tiny.make_folder(tmp_path, "H", "bfloat16")
+    prompt = tiny.prompt("H", 150, salt=3)
+    calls = []
+    real = ops.attention_tc
+    monkeypatch.setattr(ops, "attention_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    out = {}
+    for mode in ("tcgen05", "mma"):
+        monkeypatch.setenv("XS_PROMPT_ATTENTION", mode)
+        model = load_model(folder, dtype="bfloat16")
+        cache = model.new_cache(512)
+        (slot,) = cache.open(1)
+        before = len(calls)
+        first = model.step(cache, [slot], [prompt[:140]], [[0, 139]]).float().cpu()
+        in_prompt = len(calls) - before
+        more = model.step(cache, [slot], [prompt[140:141]]).float().cpu()
+        assert len(calls) - before == in_prompt, "a single token took the kernel for prompts"
+        assert in_prompt == (2 if mode == "tcgen05" else 0)          # H has two attention layers
+        out[mode] = torch.cat([first, more], 0)
+        cache.close([slot])
+    assert ops.gemm_tc_status(model.rt.device).item() == 0
+    gap = (out["tcgen05"] - out["mma"]).abs().max().item() / out["mma"].abs().max().item()
+    assert gap <= 2e-2

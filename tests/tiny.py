@@ -6,7 +6,8 @@ theta, eps, tied or untied head). R is the layout the reference's own loader rea
 sandwich norms, a gate per head, partly rotated heads, a sliding layer whose window is
 shorter than the test prompts, 7 taps (tests/parity/model/make_tiny.py:113-140 of the
 reference). W adds to B's options a sliding layer with an odd window and two rope bases. X has
-widths that are no multiple of 8 and a head size that only the generic attention kernel takes.
+widths that are no multiple of 8 and a head size that only the generic attention kernel takes. H has
+the head size (64) that the tcgen05 attention kernel takes.
 """
 import os
 
@@ -63,8 +64,20 @@ CONFIG_X = {
     "rope_parameters": {"full_attention": {"rope_theta": 5000.0, "partial_rotary_factor": 0.25}},
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "R": CONFIG_R, "W": CONFIG_W, "X": CONFIG_X}
-SEEDS = {"A": 0, "B": 1, "R": 2, "W": 3, "X": 4}
+# head size 64 with two heads a group: in bfloat16 its prompts take the tcgen05 attention kernel (full and
+# sliding layers, a gate per head), its single tokens the mma.sync decode kernel
+CONFIG_H = {
+    "model_type": "lfm3", "vocab_size": 400, "hidden_size": 128, "intermediate_size": 256,
+    "num_hidden_layers": 3, "layer_types": ["full_attention", "conv", "sliding_attention"],
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "conv_L_cache": 3, "conv_bias": False, "norm_eps": 1e-5, "max_position_embeddings": 1024,
+    "sliding_window": 50, "tie_word_embeddings": True, "use_sandwich_norm": False, "attn_head_gate": True,
+    "rope_parameters": {"full_attention": {"rope_theta": 10000.0, "partial_rotary_factor": 1.0},
+                        "sliding_attention": {"rope_theta": 300.0, "partial_rotary_factor": 0.5}},
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "R": CONFIG_R, "W": CONFIG_W, "X": CONFIG_X, "H": CONFIG_H}
+SEEDS = {"A": 0, "B": 1, "R": 2, "W": 3, "X": 4, "H": 5}
 # Plain N(0, sigma) weights give near-uniform attention and near-linear layers. These factors make the
 # parts matter: q and k large enough for peaked scores, taps and gates of order one.
 LIVELY = {"q_proj.weight": 6.0, "k_proj.weight": 6.0, "conv.conv.weight": 12.0, "gate_proj.weight": 8.0,

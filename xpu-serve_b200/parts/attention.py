@@ -123,7 +123,9 @@ class AttentionMixer(Mixer):
                 splits = decode_splits(tiles, blocks, rt.sm_count * max(1, ops.attention_mma_decode_ctas_per_sm(s.head_dim)))
             else:
                 splits = max(1, min(blocks, 32, (max(rt.attn_split_factor, 1) * rt.sm_count) // max(tiles, 1)))
-            if (splits == 1 and not step.decode and rt.prompt_attention == "tcgen05"
+            # prompts: the tcgen05 kernel, unless few tiles face many keys (a short piece of a long sequence), where
+            # cutting the keys over more CTAs is worth more
+            if ((splits == 1 or step.max_kv_len <= 512) and not step.decode and rt.prompt_attention == "tcgen05"
                     and ops.attention_tc_supports(s.head_dim, step.page_size, s.heads // s.kv_heads)):
                 ops.attention_tc(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, step.n_seqs,
                                  step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window)
