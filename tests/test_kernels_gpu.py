@@ -192,6 +192,30 @@ def test_gemm_small_m(M, N, K):
     assert torch.equal(one, out[M - 1:M]), "a row's result depends on the batch"
 
 
+@pytest.mark.parametrize("M,N,K,ksplit", [(8, 2048, 8192, 4), (3, 100, 4104, 3), (16, 256, 2048, 8), (1, 48, 512, 2), (5, 2048, 2048, 7)])
+def test_gemm_small_m_k_slices(M, N, K, ksplit):
+    """K cut into slices over several CTAs: the last CTA of a tile to arrive adds the slices in slice order, so
+    the bits do not depend on which one that was; a second and third call find the counters reset."""
+    lib = ops()
+    g = torch.Generator(device="cpu").manual_seed(N + ksplit)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    ref = x.double() @ w.double().T + bias.double()
+    scratch = torch.zeros(lib.gemm_small_m_scratch_bytes(M, N, ksplit), dtype=torch.uint8, device=DEV)
+    outs = []
+    for _ in range(3):
+        out = torch.full((M, N), float("nan"), device=DEV)
+        lib.gemm_small_m(x, w, out, bias, ksplit=ksplit, scratch=scratch)
+        close(out, ref, "float32", factor=4)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    res = torch.randn(M, N, generator=g).to(DEV)
+    want = res.double() + ref
+    lib.gemm_small_m(x, w, None, bias, residual=res, ksplit=ksplit, scratch=scratch)
+    close(res, want, "float32", factor=4)
+
+
 @pytest.mark.parametrize("F", [344, 10400])
 @pytest.mark.parametrize("M", [1, 7, 8, 13])
 def test_gemm_small_m_with_fused_activation(M, F):
