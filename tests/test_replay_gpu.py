@@ -168,3 +168,39 @@ def test_long_prompts_take_the_fused_gate_up_product(folders):
     gap, where, cos = tu.worst_gap(got, {k: ref[k] for k in got})
     assert gap <= tolerance(name, "bfloat16") and cos >= COS["bfloat16"], f"gap {gap:.3e} at {where}"
     assert ops.gemm_tc_status(rt.device).item() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_the_1_2b_shape(tmp_path, dtype):
+    """Three layers (conv, conv, attention) at the sizes of the 1.2B shape that the benchmark runs: hidden 2,048,
+    32 heads over 8 of size 64, feed-forward 8,192, vocabulary 65,536. A prompt in one step and in pieces, then
+    tokens one by one and a second, shorter sequence beside it, against the plain implementation. The real
+    widths take the kernels' fast paths (16-byte accesses, K slices, unpredicated loops, the tcgen05 attention
+    and gate/up product for the long piece) that the tiny configurations cannot reach."""
+    import bench
+    from xpu_serve_b200.config import Lfm3Config
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.weights import write_random_model
+    cfg = dict(bench.SHAPE_1_2B)
+    cfg["num_hidden_layers"] = 3
+    cfg["layer_types"] = cfg["layer_types"][:3]
+    folder = write_random_model(str(tmp_path / "m"), Lfm3Config.from_json(cfg), seed=3, dtype=dtype, scale=tiny.LIVELY)
+    V = cfg["vocab_size"]
+    reqs = {"a": [(7 * i * i + 3 * i + 11) % V for i in range(600)], "b": [(5 * i + 2) % V for i in range(9)]}
+    want_a = [0, 1, 63, 64, 127, 128, 300, 511, 512, 575]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": reqs["a"][:576], "want": want_a},
+                                     {"id": "b", "tokens": reqs["b"][:5], "want": [4]}], "end": []}]
+    for k in range(4):
+        steps.append({"step": 1 + k, "entries": [{"id": "a", "tokens": [reqs["a"][576 + k]], "want": [0]},
+                                                 {"id": "b", "tokens": [reqs["b"][5 + k]], "want": [0]}],
+                      "end": ["b"] if k == 3 else []})
+    for k in range(4, 24):
+        steps.append({"step": 1 + k, "entries": [{"id": "a", "tokens": [reqs["a"][576 + k]], "want": [0]}],
+                      "end": ["a"] if k == 23 else []})
+    rp = Replayer(load_model(folder, dtype=dtype), 1024, None)
+    got = tu.collect(steps, tu.run_in_process(rp, steps), V)
+    ref = tu.plain_logits(folder, reqs)
+    gap, where, cos = tu.worst_gap(got, {k: ref[k] for k in got})
+    bound = 1e-5 if dtype == "float32" else 4.0 * (10.0 * 3) ** 0.5 * U_BF16
+    assert gap <= bound and cos >= COS[dtype], f"gap {gap:.3e} at {where}, cosine {cos}"
