@@ -8,12 +8,13 @@
 //            rows of the last page past the sequence's length are zeroed in shared memory (V only: a
 //            masked score becomes a weight of exactly 0, and 0 times stale bits must stay 0).
 //   warp 1   one thread issues S = Q K^T (tcgen05.mma, M 128, N 128, K 16 x D / 16, Q and K K-major) into
-//            one of two S buffers in tensor memory, and O_j = P V (M 128, N D, K 16 x 8, P K-major from
-//            shared memory, V MN-major: the pages' own layout) into one of two O buffers.
+//            one of two S buffers in tensor memory, and O += P V (M 128, N D, K 16 x 8, P K-major from
+//            shared memory, V MN-major: the pages' own layout) into the output, which stays in tensor memory.
 //   warps 2-9 softmax, two threads a query row (64 keys of the block each): tcgen05.ld of S, mask (causal,
 //            window), running maximum and sum in float32 with base-2 exponentials, P as bfloat16 into
-//            shared memory (swizzled by hand as TMA would have); then tcgen05.ld of half of the block's
-//            O_j, added to the row's output in registers, which is rescaled when the maximum moves.
+//            shared memory (swizzled by hand as TMA would have). When a row's maximum moves, its threads
+//            rescale their halves of its output in tensor memory (tcgen05.ld, multiply, tcgen05.st) before
+//            they hand the block's P over; the output is read once, at the end.
 //
 // S of block j + 1 is issued before P V of block j, so the tensor pipe works while the softmax of block j
 // runs. Every mbarrier wait is bounded (see tc_common.cuh); a CTA that gives up frees its tensor memory and
@@ -68,6 +69,18 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t* r) {
         : "r"(addr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// tcgen05.st of 32 columns of this thread's lane, and the wait for it
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        :: "r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // Descriptor of an MN-major operand with the 128-byte swizzle: 64 elements of N contiguous (128 bytes), rows of
 // K 128 bytes apart, groups of 8 rows of K 1024 bytes apart (stride byte offset). One 64-wide chunk of N only,
 // so the leading byte offset is not used.
@@ -93,7 +106,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
     uint8_t* kv_sm = q_sm + TM * D * 2;
     uint8_t* p_sm = kv_sm + KV_STAGES * kStageBytes;
     __shared__ __align__(8) uint64_t bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_fix[KV_STAGES];
-    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_o_full[2], bar_o_empty[2];
+    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_o_done;
     __shared__ float mx_sm[2][2][TM];                          // [block parity][half of the keys][row]
     __shared__ float l_sm[2][TM];
     __shared__ uint32_t tmem_base;
@@ -117,7 +130,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.G;
     const int rows_valid = nt * G;
-    constexpr uint32_t kTmemCols = 512;                        // S0, S1 (128 each), O0, O1 (D each)
+    constexpr uint32_t kTmemCols = 512;                        // S0, S1 (128 each), O (D): 320 of the 512 are used
     constexpr uint32_t kColO = 2 * TN;
 
     if (threadIdx.x == 0) {
@@ -127,12 +140,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             mbar_init(smem_u32(&bar_kv_empty[s]), 1);
             mbar_init(smem_u32(&bar_fix[s]), 1);
         }
+        mbar_init(smem_u32(&bar_o_done), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_s_full[b]), 1);
             mbar_init(smem_u32(&bar_s_empty[b]), 8);           // one arrival per softmax warp
             mbar_init(smem_u32(&bar_p_full[b]), 8);
-            mbar_init(smem_u32(&bar_o_full[b]), 1);
-            mbar_init(smem_u32(&bar_o_empty[b]), 8);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -226,7 +238,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                 if (j >= 1) {
                     const int jj = j - 1, s = jj % KV_STAGES, buf = jj & 1;
                     if (!mbar_wait(smem_u32(&bar_p_full[buf]), (jj >> 1) & 1, abort_p)) break;
-                    if (jj >= 2 && !mbar_wait(smem_u32(&bar_o_empty[buf]), ((jj >> 1) & 1) ^ 1, abort_p)) break;
                     tcgen05_fence_after();
                     const uint32_t p_addr = smem_u32(p_sm + buf * kPBytes);
                     const uint32_t v_addr = smem_u32(kv_sm + s * kStageBytes + 2 * kPageBytes);
@@ -236,9 +247,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                         const uint64_t da = smem_desc_sw128(p_addr + (k >> 2) * (TM * 128) + (k & 3) * 32);
                         // V: MN-major, 16 keys = 16 rows of 128 bytes
                         const uint64_t db = smem_desc_sw128_mn(v_addr + k * 16 * 128);
-                        umma_bf16(tmem_base + kColO + (uint32_t)(buf * D), da, db, idesc_o, k > 0 ? 1u : 0u);
+                        umma_bf16(tmem_base + kColO, da, db, idesc_o, (jj > 0 || k > 0) ? 1u : 0u);   // O adds up over the blocks
                     }
-                    tcgen05_commit(smem_u32(&bar_o_full[buf]));
+                    tcgen05_commit(smem_u32(&bar_o_done));
                     tcgen05_commit(smem_u32(&bar_kv_empty[s]));
                 }
             }
@@ -254,9 +265,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int pos = r < rows_valid ? pos0 + r / G : -1;       // -1: the row sees nothing
         constexpr int HN = TN / 2, HD = D / 2;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
         float m = -INFINITY, l = 0.0f;
         bool bad = false;                                         // a wait gave up: leave at the next common point
         for (int j = 0; j < nb; ++j) {
@@ -302,6 +310,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             const float mb = m_new == -INFINITY ? 0.0f : m_new;
             const float alpha = ex2(m - mb);                      // 0 while nothing was seen
             m = m_new;
+            if (j >= 1 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                // The output so far lives in tensor memory, relative to the old maximum: rescale this thread's half
+                // of its row before this block's P V adds to it. That product waits for this warp's arrival below,
+                // the one before it is waited for here. The maximum of most later blocks does not move.
+                bad |= !mbar_wait(smem_u32(&bar_o_done), (j - 1) & 1, abort_p);
+                tcgen05_fence_after();
+                uint32_t acc[HD];
+                tmem_ld32(lane_base + kColO + (uint32_t)(half * HD), acc);
+#pragma unroll
+                for (int e = 0; e < HD; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                tmem_st32(lane_base + kColO + (uint32_t)(half * HD), acc);
+            }
             float add4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint8_t* p_row = p_sm + buf * kPBytes + half * (TM * 128) + r * 128;
 #pragma unroll
@@ -323,35 +343,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                 mbar_arrive_cta(smem_u32(&bar_p_full[buf]));
                 mbar_arrive_cta(smem_u32(&bar_s_empty[buf]));
             }
-            if (j >= 1) {
-                // the block before: its P V has had the time of this block's softmax
-                const int jb = (j - 1) & 1;
-                bad |= !mbar_wait(smem_u32(&bar_o_full[jb]), ((j - 1) >> 1) & 1, abort_p);
-                tcgen05_fence_after();
-                uint32_t raw[32];
-                tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + half * HD), raw);
-#pragma unroll
-                for (int e = 0; e < HD; ++e) o[e] += __uint_as_float(raw[e]);
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cta(smem_u32(&bar_o_empty[jb]));
-            }
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {         // the maximum of most later blocks does not move
-#pragma unroll
-                for (int d = 0; d < HD; ++d) o[d] *= alpha;       // now relative to this block's maximum
-            }
         }
         {
             // the last block's P V; then the row's sum: this thread's keys and its partner's (both relative to
             // the same maximum). Every softmax thread comes to the barrier, whatever happened before.
-            const int jb = (nb - 1) & 1;
-            const bool fin = !bad && mbar_wait(smem_u32(&bar_o_full[jb]), ((nb - 1) >> 1) & 1, abort_p);
+            const bool fin = !bad && mbar_wait(smem_u32(&bar_o_done), (nb - 1) & 1, abort_p);
+            float o[HD];
             if (fin) {
                 tcgen05_fence_after();
-                uint32_t raw[32];
-                tmem_ld32(lane_base + kColO + (uint32_t)(jb * D + half * HD), raw);
+                uint32_t acc[HD];
+                tmem_ld32(lane_base + kColO + (uint32_t)(half * HD), acc);
 #pragma unroll
-                for (int e = 0; e < HD; ++e) o[e] += __uint_as_float(raw[e]);
+                for (int e = 0; e < HD; ++e) o[e] = __uint_as_float(acc[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < HD; ++e) o[e] = 0.0f;
             }
             l_sm[half][r] = l;
             int any_bad;
