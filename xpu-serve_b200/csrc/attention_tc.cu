@@ -7,6 +7,7 @@
 //            ring of three stages. Pages past the sequence's end, pages a window has given back, and the
 //            rows of the last page past the sequence's length are zeroed in shared memory (V only: a
 //            masked score becomes a weight of exactly 0, and 0 times stale bits must stay 0).
+//   warp 1 and warp 10: one thread each issues S = Q K^T and O += P V:
 //   warp 1   one thread issues S = Q K^T (tcgen05.mma, M 128, N 128, K 16 x D / 16, Q and K K-major) into
 //            one of two S buffers in tensor memory, and O += P V (M 128, N D, K 16 x 8, P K-major from
 //            shared memory, V MN-major: the pages' own layout) into the output, which stays in tensor memory.
@@ -30,7 +31,7 @@ namespace {
 constexpr int TM = 128;           // query rows a CTA
 constexpr int TN = 128;           // keys a block
 constexpr int PAGE = 64;          // keys a page
-constexpr int kAttnThreads = 320;   // TMA warp, MMA warp, eight softmax warps
+constexpr int kAttnThreads = 352;   // TMA warp, S issuer warp, eight softmax warps, P V issuer warp
 constexpr int KV_STAGES = 3;
 
 struct AttnTcParams {
@@ -218,40 +219,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             __syncwarp();
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ issuer of S = Q K^T
+        // (two issuing threads, this one and warp 10's: one thread's descriptor arithmetic and waits for both
+        // products of a block took longer than the block's softmax)
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc_mn(TM, TN);
-            constexpr uint32_t idesc_o = instr_desc_mn(TM, D, true);
             const uint64_t dq = smem_desc_sw128(smem_u32(q_sm));
-            for (int j = 0; j <= nb && !*abort_p; ++j) {
-                if (j < nb) {
-                    const int s = j % KV_STAGES, buf = j & 1;
-                    if (!mbar_wait(smem_u32(&bar_kv_full[s]), (j / KV_STAGES) & 1, abort_p)) break;
-                    if (j >= 2 && !mbar_wait(smem_u32(&bar_s_empty[buf]), ((j >> 1) & 1) ^ 1, abort_p)) break;
-                    tcgen05_fence_after();
-                    const uint64_t dk = smem_desc_sw128(smem_u32(kv_sm + s * kStageBytes));
+            const uint64_t dk0 = smem_desc_sw128(smem_u32(kv_sm));
+            for (int j = 0; j < nb && !*abort_p; ++j) {
+                const int s = j % KV_STAGES, buf = j & 1;
+                if (!mbar_wait(smem_u32(&bar_kv_full[s]), (j / KV_STAGES) & 1, abort_p)) break;
+                if (j >= 2 && !mbar_wait(smem_u32(&bar_s_empty[buf]), ((j >> 1) & 1) ^ 1, abort_p)) break;
+                tcgen05_fence_after();
+                const uint64_t dk = dk0 + (uint64_t)(s * (kStageBytes >> 4));      // start addresses count 16 bytes
 #pragma unroll
-                    for (int k = 0; k < D / 16; ++k)
-                        umma_bf16(tmem_base + (uint32_t)(buf * TN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k > 0 ? 1u : 0u);
-                    tcgen05_commit(smem_u32(&bar_s_full[buf]));
-                }
-                if (j >= 1) {
-                    const int jj = j - 1, s = jj % KV_STAGES, buf = jj & 1;
-                    if (!mbar_wait(smem_u32(&bar_p_full[buf]), (jj >> 1) & 1, abort_p)) break;
-                    tcgen05_fence_after();
-                    const uint32_t p_addr = smem_u32(p_sm + buf * kPBytes);
-                    const uint32_t v_addr = smem_u32(kv_sm + s * kStageBytes + 2 * kPageBytes);
+                for (int k = 0; k < D / 16; ++k)
+                    umma_bf16(tmem_base + (uint32_t)(buf * TN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k > 0 ? 1u : 0u);
+                tcgen05_commit(smem_u32(&bar_s_full[buf]));
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ issuer of O += P V
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = instr_desc_mn(TM, D, true);
+            const uint64_t dp0 = smem_desc_sw128(smem_u32(p_sm));
+            const uint64_t dv0 = smem_desc_sw128_mn(smem_u32(kv_sm + 2 * kPageBytes));
+            for (int j = 0; j < nb && !*abort_p; ++j) {
+                const int s = j % KV_STAGES, buf = j & 1;
+                if (!mbar_wait(smem_u32(&bar_kv_full[s]), (j / KV_STAGES) & 1, abort_p)) break;
+                if (!mbar_wait(smem_u32(&bar_p_full[buf]), (j >> 1) & 1, abort_p)) break;
+                tcgen05_fence_after();
+                const uint64_t dp = dp0 + (uint64_t)(buf * (kPBytes >> 4));
+                const uint64_t dv = dv0 + (uint64_t)(s * (kStageBytes >> 4));
 #pragma unroll
-                    for (int k = 0; k < TN / 16; ++k) {
-                        // P: K-major, 16 keys = 32 bytes along a row, the second 64 keys in the second half tile
-                        const uint64_t da = smem_desc_sw128(p_addr + (k >> 2) * (TM * 128) + (k & 3) * 32);
-                        // V: MN-major, 16 keys = 16 rows of 128 bytes
-                        const uint64_t db = smem_desc_sw128_mn(v_addr + k * 16 * 128);
-                        umma_bf16(tmem_base + kColO, da, db, idesc_o, (jj > 0 || k > 0) ? 1u : 0u);   // O adds up over the blocks
-                    }
-                    tcgen05_commit(smem_u32(&bar_o_done));
-                    tcgen05_commit(smem_u32(&bar_kv_empty[s]));
+                for (int k = 0; k < TN / 16; ++k) {
+                    // P: K-major, 16 keys = 32 bytes along a row, the second 64 keys in the second half tile;
+                    // V: MN-major, 16 keys = 16 rows of 128 bytes
+                    umma_bf16(tmem_base + kColO, dp + (uint64_t)((k >> 2) * ((TM * 128) >> 4) + (k & 3) * 2),
+                              dv + (uint64_t)(k * ((16 * 128) >> 4)), idesc_o, (j > 0 || k > 0) ? 1u : 0u);   // O adds up over the blocks
                 }
+                tcgen05_commit(smem_u32(&bar_o_done));
+                tcgen05_commit(smem_u32(&bar_kv_empty[s]));
             }
         }
     } else {
