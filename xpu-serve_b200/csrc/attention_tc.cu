@@ -70,6 +70,20 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t* r) {
         : "r"(addr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16w(uint32_t addr, uint32_t* r) {     // 16 columns, waited for
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st16w(uint32_t addr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 :: "r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // tcgen05.st of 32 columns of this thread's lane, and the wait for it
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
     asm volatile(
@@ -107,9 +121,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
     uint8_t* kv_sm = q_sm + TM * D * 2;
     uint8_t* p_sm = kv_sm + KV_STAGES * kStageBytes;
     __shared__ __align__(8) uint64_t bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_fix[KV_STAGES];
-    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_o_done;
-    __shared__ float mx_sm[2][2][TM];                          // [block parity][half of the keys][row]
-    __shared__ float l_sm[2][TM];
+    __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_o_done[2];
     __shared__ uint32_t tmem_base;
     __shared__ int abort_flag;
 
@@ -141,11 +153,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             mbar_init(smem_u32(&bar_kv_empty[s]), 1);
             mbar_init(smem_u32(&bar_fix[s]), 1);
         }
-        mbar_init(smem_u32(&bar_o_done), 1);
         for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_o_done[b]), 1);
             mbar_init(smem_u32(&bar_s_full[b]), 1);
-            mbar_init(smem_u32(&bar_s_empty[b]), 8);           // one arrival per softmax warp
-            mbar_init(smem_u32(&bar_p_full[b]), 8);
+            mbar_init(smem_u32(&bar_s_empty[b]), 4);           // one arrival per softmax warp of the buffer's group
+            mbar_init(smem_u32(&bar_p_full[b]), 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -255,46 +267,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                 for (int k = 0; k < TN / 16; ++k) {
                     // P: K-major, 16 keys = 32 bytes along a row, the second 64 keys in the second half tile;
                     // V: MN-major, 16 keys = 16 rows of 128 bytes
-                    umma_bf16(tmem_base + kColO, dp + (uint64_t)((k >> 2) * ((TM * 128) >> 4) + (k & 3) * 2),
-                              dv + (uint64_t)(k * ((16 * 128) >> 4)), idesc_o, (j > 0 || k > 0) ? 1u : 0u);   // O adds up over the blocks
+                    umma_bf16(tmem_base + kColO + (uint32_t)(buf * D), dp + (uint64_t)((k >> 2) * ((TM * 128) >> 4) + (k & 3) * 2),
+                              dv + (uint64_t)(k * ((16 * 128) >> 4)), idesc_o, (j >= 2 || k > 0) ? 1u : 0u);   // adds up over the group's blocks
                 }
-                tcgen05_commit(smem_u32(&bar_o_done));
+                tcgen05_commit(smem_u32(&bar_o_done[buf]));
                 tcgen05_commit(smem_u32(&bar_kv_empty[s]));
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax, two threads a row
-        // Warps 2-5 take the first 64 keys of every block and the first half of the output's channels, warps
-        // 6-9 the second halves, for the same 128 rows (a warp reaches the 32 lanes of tensor memory of its
-        // number modulo 4): two warps a scheduler hide each other's latencies. The two threads of a row
-        // exchange their maxima through shared memory once a block; their sums meet at the end.
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // Warps 2-5 take the even blocks of keys, warps 6-9 the odd ones, for the same 128 rows (a warp reaches
+        // the 32 lanes of tensor memory of its number modulo 4). Each group has its own S buffer, P buffer and
+        // output accumulator in tensor memory and its own running maximum and sum, so the groups never wait for
+        // each other: while one computes exponentials (16 a cycle an SM: the scarce unit) the other reads scores,
+        // finds maxima or waits for its product. The two partial results of a row are merged once, at the end,
+        // as key splits are merged in decoding.
+        const int quarter = warp & 3, grp = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_col = (uint32_t)(grp * TN), o_col = kColO + (uint32_t)(grp * D);
         const int pos = r < rows_valid ? pos0 + r / G : -1;       // -1: the row sees nothing
-        constexpr int HN = TN / 2, HD = D / 2;
         float m = -INFINITY, l = 0.0f;
-        bool bad = false;                                         // a wait gave up: leave at the next common point
-        for (int j = 0; j < nb; ++j) {
-            const int buf = j & 1;
-            bad |= !mbar_wait(smem_u32(&bar_s_full[buf]), (j >> 1) & 1, abort_p);
+        bool bad = false;                                         // a wait gave up: nothing more is waited for
+        int done = 0;                                             // blocks this group has finished
+        for (int j = grp; j < nb; j += 2, ++done) {
+            if (!mbar_wait(smem_u32(&bar_s_full[grp]), done & 1, abort_p)) { bad = true; break; }
             tcgen05_fence_after();
-            const int key0 = (b_lo + j) * TN + half * HN;
+            const int key0 = (b_lo + j) * TN;
             // a block that every row of the tile sees whole needs no test per key
-            const bool plain = pos >= 0 && (b_lo + j) * TN + TN - 1 <= pos0 &&
-                               (p.window == 0 || pos0 + nt - 1 - (b_lo + j) * TN < p.window);
-            // this thread's 64 scores of the block, read once and kept through both passes
-            uint32_t raw[HN];
-            tmem_ld32_nowait(lane_base + (uint32_t)(buf * TN + half * HN), raw);
-            tmem_ld32_nowait(lane_base + (uint32_t)(buf * TN + half * HN + 32), raw + 32);
+            const bool plain = pos >= 0 && key0 + TN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - key0 < p.window);
+            // this row's 128 scores of the block, read once and kept through both passes
+            uint32_t raw[TN];
+#pragma unroll
+            for (int c = 0; c < TN; c += 32) tmem_ld32_nowait(lane_base + s_col + (uint32_t)c, raw + c);
             tmem_ld_wait();
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (plain) {
 #pragma unroll
-                for (int e = 0; e < HN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
+                for (int e = 0; e < TN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
             } else {
 #pragma unroll
-                for (int e = 0; e < HN; ++e) {
+                for (int e = 0; e < TN; ++e) {
                     const int key = key0 + e;
                     const bool see = key <= pos && (p.window == 0 || pos - key < p.window);   // pos -1: nothing
                     if (!see) raw[e] = 0xff800000u;                // -inf: its weight will be exactly 0
@@ -302,45 +315,37 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
                 }
             }
             // the scale is positive: the largest scaled score is the scaled largest score
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-            mx_sm[buf][half][r] = mx;
-            // all 256 softmax threads meet; the barrier also tells everyone whether anyone's wait gave up
-            int any_bad;
-            asm volatile(
-                "{\n\t.reg .pred p, q;\n\t"
-                "setp.ne.b32 q, %1, 0;\n\t"
-                "bar.red.or.pred p, 1, 256, q;\n\t"
-                "selp.u32 %0, 1, 0, p;\n\t}"
-                : "=r"(any_bad) : "r"((int)bad) : "memory");
-            if (any_bad) { bad = true; break; }
-            mx = fmaxf(mx, mx_sm[buf][half ^ 1][r]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             const float m_new = fmaxf(m, mx);
             const float mb = m_new == -INFINITY ? 0.0f : m_new;
             const float alpha = ex2(m - mb);                      // 0 while nothing was seen
             m = m_new;
-            if (j >= 1 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-                // The output so far lives in tensor memory, relative to the old maximum: rescale this thread's half
-                // of its row before this block's P V adds to it. That product waits for this warp's arrival below,
-                // the one before it is waited for here. The maximum of most later blocks does not move.
-                bad |= !mbar_wait(smem_u32(&bar_o_done), (j - 1) & 1, abort_p);
+            if (done >= 1 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                // The group's output so far lives in tensor memory, relative to the old maximum: rescale this row
+                // before this block's P V adds to it. That product waits for this warp's arrival below, the one
+                // before it is waited for here. The maximum of most later blocks does not move.
+                if (!mbar_wait(smem_u32(&bar_o_done[grp]), (done - 1) & 1, abort_p)) { bad = true; break; }
                 tcgen05_fence_after();
-                uint32_t acc[HD];
-                tmem_ld32(lane_base + kColO + (uint32_t)(half * HD), acc);
+#pragma unroll 1
+                for (int c = 0; c < D; c += 16) {                  // 16 columns at a time: the scores stay in registers
+                    uint32_t acc[16];
+                    tmem_ld16w(lane_base + o_col + (uint32_t)c, acc);
 #pragma unroll
-                for (int e = 0; e < HD; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
-                tmem_st32(lane_base + kColO + (uint32_t)(half * HD), acc);
+                    for (int e = 0; e < 16; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                    tmem_st16w(lane_base + o_col + (uint32_t)c, acc);
+                }
             }
             float add4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint8_t* p_row = p_sm + buf * kPBytes + half * (TM * 128) + r * 128;
+            uint8_t* p_row = p_sm + grp * kPBytes + r * 128;
 #pragma unroll
-            for (int i = 0; i < HN / 8; ++i) {                     // 8-key chunks of this half of the block
+            for (int i = 0; i < TN / 8; ++i) {                     // 8-key chunks; the second 64 keys in the second half tile
                 float w[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     w[e] = ex2(fmaf(__uint_as_float(raw[8 * i + e]), p.scale_log2, -mb));   // ex2(-inf) = 0
                     add4[e & 3] += w[e];
                 }
-                *reinterpret_cast<uint4*>(p_row + ((i ^ (r & 7)) << 4)) =
+                *reinterpret_cast<uint4*>(p_row + (i >> 3) * (TM * 128) + (((i & 7) ^ (r & 7)) << 4)) =
                     make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
             }
             l = l * alpha + ((add4[0] + add4[1]) + (add4[2] + add4[3]));
@@ -348,43 +353,61 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive_cta(smem_u32(&bar_p_full[buf]));
-                mbar_arrive_cta(smem_u32(&bar_s_empty[buf]));
+                mbar_arrive_cta(smem_u32(&bar_p_full[grp]));
+                mbar_arrive_cta(smem_u32(&bar_s_empty[grp]));
             }
         }
-        {
-            // the last block's P V; then the row's sum: this thread's keys and its partner's (both relative to
-            // the same maximum). Every softmax thread comes to the barrier, whatever happened before.
-            const bool fin = !bad && mbar_wait(smem_u32(&bar_o_done), (nb - 1) & 1, abort_p);
-            float o[HD];
-            if (fin) {
+        // the group's output, once its last product is in
+        float o[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) o[d] = 0.0f;
+        if (!bad && done > 0) {
+            if (mbar_wait(smem_u32(&bar_o_done[grp]), (done - 1) & 1, abort_p)) {
                 tcgen05_fence_after();
-                uint32_t acc[HD];
-                tmem_ld32(lane_base + kColO + (uint32_t)(half * HD), acc);
+                uint32_t acc[D];
+                tmem_ld32_nowait(lane_base + o_col, acc);
+                tmem_ld32_nowait(lane_base + o_col + 32, acc + 32);
+                tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < HD; ++e) o[e] = __uint_as_float(acc[e]);
+                for (int e = 0; e < D; ++e) o[e] = __uint_as_float(acc[e]);
             } else {
-#pragma unroll
-                for (int e = 0; e < HD; ++e) o[e] = 0.0f;
+                bad = true;
             }
-            l_sm[half][r] = l;
-            int any_bad;
-            asm volatile(
-                "{\n\t.reg .pred p, q;\n\t"
-                "setp.ne.b32 q, %1, 0;\n\t"
-                "bar.red.or.pred p, 1, 256, q;\n\t"
-                "selp.u32 %0, 1, 0, p;\n\t}"
-                : "=r"(any_bad) : "r"((int)!fin) : "memory");
-            if (!any_bad && r < rows_valid) {
-                l += l_sm[half ^ 1][r];
-                const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
-                float f = l > 0.0f ? 1.0f / l : 0.0f;
-                if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
-                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)t * p.Hq + h) * D + half * HD);
+        }
+        // Every softmax thread comes here, whatever happened before, and learns whether anyone's wait gave up.
+        // Past this barrier both groups' products are complete: P's memory is free for the merge.
+        int any_bad;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "bar.red.or.pred p, 1, 256, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(any_bad) : "r"((int)bad) : "memory");
+        float* merge = reinterpret_cast<float*>(p_sm);            // [D + 2][TM]: a thread's row is a column
+        if (!any_bad && grp == 1) {
 #pragma unroll
-                for (int c = 0; c < HD / 8; ++c)
-                    dst[c] = make_uint4(pack_bf16(o[8 * c] * f, o[8 * c + 1] * f), pack_bf16(o[8 * c + 2] * f, o[8 * c + 3] * f),
-                                        pack_bf16(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf16(o[8 * c + 6] * f, o[8 * c + 7] * f));
+            for (int d = 0; d < D; ++d) merge[d * TM + r] = o[d];
+            merge[D * TM + r] = m;                                // -inf and 0 when the group had no block
+            merge[(D + 1) * TM + r] = l;
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (!any_bad && grp == 0 && r < rows_valid) {
+            const float m1 = merge[D * TM + r], l1 = merge[(D + 1) * TM + r];
+            const float mm = fmaxf(m, m1);
+            const float mb = mm == -INFINITY ? 0.0f : mm;
+            const float a0 = ex2(m - mb), a1 = ex2(m1 - mb);
+            l = l * a0 + l1 * a1;
+            const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+            float f = l > 0.0f ? 1.0f / l : 0.0f;
+            if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
+            const float f0 = a0 * f, f1 = a1 * f;
+            uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)t * p.Hq + h) * D);
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = o[8 * c + e] * f0 + merge[(8 * c + e) * TM + r] * f1;
+                dst[c] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
             }
         }
         tcgen05_fence_before();
