@@ -63,8 +63,8 @@ class Runtime:
         # (0: sized by rounds of CTAs, parts/attention.py decode_splits; n > 0: n CTAs an SM, the earlier rule)
         self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "0"))
         # attention of prompts: "tcgen05" (head size 64 and groups that divide 128; everything else takes the
-        # mma.sync kernel anyway) or "mma". Measured on B200, 32 heads over 8: 2,048 tokens 72 against 97 us,
-        # 2,048 tokens after 30,000: 1.36 against 1.86 ms.
+        # mma.sync kernel anyway) or "mma". Measured on B200, 32 heads over 8: 2,048 tokens 67 against 97 us,
+        # 2,048 tokens after 30,000: 1.01 against 1.87 ms.
         self.prompt_attention = os.environ.get("XS_PROMPT_ATTENTION", "tcgen05")
         if self.prompt_attention not in ("tcgen05", "mma"):
             raise ValueError("XS_PROMPT_ATTENTION must be 'tcgen05' or 'mma'")
