@@ -198,6 +198,24 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    // The sums of squares are added up (first level: thread (j, m) takes tiles j * 8 .. j * 8 + 7 of batch row m,
+    // then every 16th tile beyond the staged ones) after the first round's multiplies, while the second round's
+    // weights are on their way, not in the CTA's tail, where its place on the SM streams nothing.
+    bool ssq_done = p.in_ssq == nullptr;
+    auto ssq_first_level = [&]() {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        const int sm_ = threadIdx.x & 15, sj_ = threadIdx.x >> 4;
+        float v = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int t = sj_ * 8 + u;
+            v += t < p.in_tiles ? ssq_in[t][sm_] : 0.0f;
+        }
+        for (int t = kSsqStaged + sj_; t < p.in_tiles; t += 16) v += __ldcg(p.in_ssq + (int64_t)t * 16 + sm_);
+        ssq_red[sj_][sm_] = v;
+        ssq_done = true;
+    };
     for (; kb - warp * ws < kb_end; kb += WARPS * UNROLL) {
         uint4 xv[UNROLL][NT];
 #pragma unroll
@@ -234,7 +252,11 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
                 wb[u] = in ? ld_stream(wb_p + k0) : zero;
             }
         }
+        // (every warp runs the same number of rounds: the barrier inside is safe; with 16 batch rows the registers
+        // do not allow it, and it happens after the loop)
+        if (NT == 1 && !ssq_done) ssq_first_level();
     }
+    if (!ssq_done) ssq_first_level();
     // c0, c1: (weight row g, batch q * 2 + {0, 1}); c2, c3: weight row g + 8
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -243,20 +265,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         red[warp][g + 8][t * 8 + q * 2] = acc[t][2];
         red[warp][g + 8][t * 8 + q * 2 + 1] = acc[t][3];
     }
-    if (p.in_ssq != nullptr) asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
-    if (p.in_ssq != nullptr) {
-        // thread (j, m): tiles j * 8 .. j * 8 + 7 of batch row m, then every 128th tile beyond the staged ones
-        const int sm_ = threadIdx.x & 15, sj_ = threadIdx.x >> 4;
-        float v = 0.0f;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int t = sj_ * 8 + u;
-            v += t < p.in_tiles ? ssq_in[t][sm_] : 0.0f;
-        }
-        for (int t = kSsqStaged + sj_; t < p.in_tiles; t += 16) v += __ldcg(p.in_ssq + (int64_t)t * 16 + sm_);
-        ssq_red[sj_][sm_] = v;
-    }
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
         const int r = i / (8 * NT), m = i % (8 * NT);
         float v = 0.0f;
@@ -264,16 +273,16 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         for (int wv = 0; wv < WARPS; ++wv) v += red[wv][r][m];
         sum[r][m] = v;
     }
-    __syncthreads();
-    if (threadIdx.x < 16) {
+    if (threadIdx.x >= WARPS * 32 - 16) {      // the last 16 threads (idle above for up to 8 rows): each batch row's 1 / rms
+        const int m = threadIdx.x - (WARPS * 32 - 16);
         float v = 1.0f;
         if (p.in_ssq != nullptr) {
             float ss = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ss += ssq_red[j][threadIdx.x];
+            for (int j = 0; j < 16; ++j) ss += ssq_red[j][m];
             v = 1.0f / sqrtf(ss / (float)p.in_width + p.in_eps);
         }
-        inv[threadIdx.x] = v;
+        inv[m] = v;
     }
     __syncthreads();
     if (p.ksplit == 1) {
