@@ -28,7 +28,7 @@ LENGTHS = [1, 5, 13, 23, 40]
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="a checkout of v1k22/xpu-serve (it is configured with CMake, not changed)")
     ap.add_argument("--build-dir", default=None)
     args = ap.parse_args()
     import tiny
