@@ -404,6 +404,7 @@ ATTN_CASES = [
     ([0], [200], 32, 8, 64, 0),                      # the 1.2B shape's heads
     ([500, 37, 1999], [1, 1, 1], 16, 2, 128, 0),
     ([0], [90], 5, 5, 80, 17),                       # a head size only the generic kernel takes
+    ([4100, 30], [1, 1], 8, 2, 64, 0),               # more than 32 blocks of keys: 40 splits all hold some
 ]
 
 
@@ -430,9 +431,15 @@ def test_attention(case, kernel, dtype):
     gate = torch.randn(sum(q_lens), Hq + 3).to(DT[dtype])
     for gt in (None, gate):
         ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
-        for splits in ([1] if kernel == "generic" else [1, 2, 5]):
+        for splits in ([1] if kernel == "generic" else [1, 2, 5, 40]):
             out = run_attention(lib, pg, kernel, scale, window, gt, splits)
             close(out, ref, dtype, factor=3 if dtype == "bfloat16" else 20)
+
+
+def test_attention_refuses_more_splits_than_it_combines():
+    lib = ops()
+    with pytest.raises(lib.KernelError, match="1 to 64 key splits"):
+        run_attention(lib, Paged([100], [1], 4, 2, 64, "bfloat16"), "mma", 0.1, 0, None, 65)
 
 
 ATTN_TC_CASES = [

@@ -529,7 +529,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
 }
 
 // out[row, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), times the head's gate. One warp per row; lane s holds
-// split s's (max, sum) and weight (splits <= 32), and the partial outputs are read with independent loads.
+// splits s and s + 32's (max, sum) and weights (splits <= 64), and the partial outputs are read with independent loads.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
                                          __nv_bfloat16* __restrict__ out, int64_t rows, int Hq, int D, int splits) {
@@ -539,11 +539,13 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
     const float* ml = part_ml + row * splits * 2;
-    const float ms = lane < splits ? ml[2 * lane] : -INFINITY;
-    const float ls = lane < splits ? ml[2 * lane + 1] : 0.0f;
-    const float m = warp_max(ms);
-    const float wgt = ms == -INFINITY ? 0.0f : fast_exp2(ms - m);     // this split's weight
-    const float l = warp_sum(ls * wgt);
+    // lane s holds splits s and s + 32
+    const float ms0 = lane < splits ? ml[2 * lane] : -INFINITY, ms1 = lane + 32 < splits ? ml[2 * (lane + 32)] : -INFINITY;
+    const float ls0 = lane < splits ? ml[2 * lane + 1] : 0.0f, ls1 = lane + 32 < splits ? ml[2 * (lane + 32) + 1] : 0.0f;
+    const float m = warp_max(fmaxf(ms0, ms1));
+    const float wgt0 = ms0 == -INFINITY ? 0.0f : fast_exp2(ms0 - m);     // the splits' weights
+    const float wgt1 = ms1 == -INFINITY ? 0.0f : fast_exp2(ms1 - m);
+    const float l = warp_sum(ls0 * wgt0 + ls1 * wgt1);
     float f = l > 0.0f ? 1.0f / l : 0.0f;
     if (gate != nullptr) {
         const int64_t t = row / Hq;
@@ -556,7 +558,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
         float acc = 0.0f;
 #pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float w = __shfl_sync(0xffffffffu, wgt, s);
+            const float w = __shfl_sync(0xffffffffu, s < 32 ? wgt0 : wgt1, s & 31);
             acc = fmaf(w, (w == 0.0f || d >= D) ? 0.0f : po[s * D + d], acc);
         }
         if (d < D) out[row * D + d] = __float2bfloat16_rn(acc * f);
@@ -665,7 +667,8 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
     const int G = Hq / Hkv;
     XS_REQUIRE(xs_attention_mma_supports(D, page_size, G),
                "attention (tensor cores): head size %d, page size %d, group %d is not supported", D, page_size, G);
-    XS_REQUIRE(splits >= 1 && window >= 0 && max_q_len >= 1 && n_seqs >= 1 && P >= 1, "attention: bad sizes");
+    XS_REQUIRE(splits >= 1 && splits <= 64 && window >= 0 && max_q_len >= 1 && n_seqs >= 1 && P >= 1,
+               "attention: bad sizes (1 to 64 key splits)");
     XS_REQUIRE(n_seqs <= 65535 && (int64_t)Hkv * splits <= 65535, "attention: grid too large");
     const int64_t need = xs_attention_mma_scratch_bytes((int64_t)T * Hq, D, splits);
     XS_REQUIRE(splits == 1 || (scratch != nullptr && scratch_bytes >= need),

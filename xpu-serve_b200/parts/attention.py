@@ -25,7 +25,7 @@ def decode_splits(tiles: int, blocks: int, slots: int) -> int:
     plus the combine kernel when there is more than one part. 64 sequences of 2,048 keys over 444 slots: one part
     is 2 rounds of 34, four parts are 5 rounds of 10."""
     best, best_cost = 1, None
-    for parts in range(1, max(1, min(blocks, 32)) + 1):
+    for parts in range(1, max(1, min(blocks, 64)) + 1):
         rounds = -(-tiles * parts // slots)
         cost = rounds * (-(-blocks // parts) + 2) + (1.5 if parts > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
