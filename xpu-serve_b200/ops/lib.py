@@ -93,6 +93,8 @@ def load(verbose: bool = True):
         # tuning switches, read once (defaults are what measured best on B200)
         if "XS_ATTN_DECODE_STAGES" in os.environ:
             lib.xs_attention_mma_set_decode_stages(int(os.environ["XS_ATTN_DECODE_STAGES"]))
+        if "XS_ATTN_PREFETCH_BLOCKS" in os.environ:
+            lib.xs_attention_mma_set_prefetch_blocks(int(os.environ["XS_ATTN_PREFETCH_BLOCKS"]))
         if os.environ.get("XS_NO_PDL", "0") == "1":
             lib.xs_set_pdl(0)
         if os.environ.get("XS_TC_NO_PAIR", "0") == "1":
