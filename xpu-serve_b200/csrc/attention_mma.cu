@@ -557,15 +557,17 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
         f *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[t * ld_gate + h])));
     }
     const float* po = part_o + row * splits * D;
-    for (int d0 = 0; d0 < D; d0 += 32) {       // every lane stays in the loop: the shuffles need the whole warp
-        const int d = d0 + lane;
-        float acc = 0.0f;
-#pragma unroll 8
+    for (int d0 = 0; d0 < D; d0 += 64) {       // every lane stays in the loop: the shuffles need the whole warp
+        const int d = d0 + 2 * lane;           // D is a multiple of 16: a lane's two channels are both inside or both outside
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 16
         for (int s = 0; s < splits; ++s) {
             const float w = __shfl_sync(0xffffffffu, s < 32 ? wgt0 : wgt1, s & 31);
-            acc = fmaf(w, (w == 0.0f || d >= D) ? 0.0f : po[s * D + d], acc);
+            const float2 v = (w == 0.0f || d >= D) ? make_float2(0.0f, 0.0f) : *reinterpret_cast<const float2*>(po + s * D + d);
+            a0 = fmaf(w, v.x, a0);
+            a1 = fmaf(w, v.y, a1);
         }
-        if (d < D) out[row * D + d] = __float2bfloat16_rn(acc * f);
+        if (d < D) *reinterpret_cast<__nv_bfloat162*>(out + row * D + d) = __floats2bfloat162_rn(a0 * f, a1 * f);
     }
 }
 
@@ -684,6 +686,7 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
                "attention: bad sizes (1 to 64 key splits)");
     XS_REQUIRE(n_seqs <= 65535 && (int64_t)Hkv * splits <= 65535, "attention: grid too large");
     const int64_t need = xs_attention_mma_scratch_bytes((int64_t)T * Hq, D, splits);
+    XS_REQUIRE((uintptr_t)out % 4 == 0 && (splits == 1 || (uintptr_t)scratch % 16 == 0), "attention: out or scratch is misaligned");
     XS_REQUIRE(splits == 1 || (scratch != nullptr && scratch_bytes >= need),
                "attention: %lld bytes of scratch needed for %d splits, %lld given", (long long)need, splits,
                (long long)scratch_bytes);
