@@ -37,6 +37,21 @@ SHAPE_1_2B = {
 }
 PROMPT = 2048
 CONTEXT = 4096
+
+
+def family_shape(layers, hidden, heads, ffn, context, attn_at):
+    cfg = dict(SHAPE_1_2B)
+    at = set(attn_at)
+    cfg.update(num_hidden_layers=layers, layer_types=["attn" if i in at else "conv" for i in range(layers)],
+               hidden_size=hidden, num_attention_heads=heads, intermediate_size=ffn, max_position_embeddings=context)
+    return cfg
+
+
+# BASELINE.json configs[3] and configs[4]: (shape, batch, prompt lengths uniform in [lo, hi], decode steps)
+WORKLOADS = {
+    "ragged_2.6b": (family_shape(30, 2048, 32, 10752, 8192, range(2, 30, 3)), 16, (256, 4096), 512),
+    "long_350m": (family_shape(16, 1024, 16, 6656, 32768, (2, 5, 8, 10, 12, 14)), 64, (1024, 24576), 256),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -66,7 +81,7 @@ class ClockSampler:
     def start(self):
         try:
             self._proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                           "--format=csv,noheader,nounits", "-lms", "100"],
+                                           "--format=csv,noheader,nounits", "-lms", "20"],
                                           stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -219,17 +234,81 @@ def time_e2e(folder: str, batch: int, steps: int, warmup: int, V: int):
     return batch * steps / span, h2d, 4 * batch
 
 
+def run_workload(name: str, layers=None, batch=None, new=None) -> int:
+    """A batch of unequal prompts through Engine.generate (host token ids in and out): the prompts with one new
+    token first (prefill), then the whole workload; decode time is the difference. Second of two runs."""
+    import random
+    import torch
+    from xpu_serve_b200 import Engine, GenerateRequest, SamplingParams
+    from xpu_serve_b200.config import Lfm3Config
+    from xpu_serve_b200.weights import write_random_model
+    cfg, full_batch, (lo, hi), full_new = WORKLOADS[name]
+    cfg = dict(cfg)
+    full_layers = cfg["num_hidden_layers"]
+    if layers is not None:                       # a smaller case of the same kernels, for profiler captures
+        cfg["num_hidden_layers"] = max(1, min(layers, full_layers))
+        cfg["layer_types"] = cfg["layer_types"][:cfg["num_hidden_layers"]]
+    batch, new = batch or full_batch, new or full_new
+    rng = random.Random(3)
+    lens = [rng.randint(lo, hi) for _ in range(batch)]
+    V = cfg["vocab_size"]
+    nums = model_numbers(cfg, cfg["num_hidden_layers"])
+    with tempfile.TemporaryDirectory() as root:
+        folder = write_random_model(os.path.join(root, name), Lfm3Config.from_json(cfg), seed=0, dtype="bfloat16")
+        total = sum(-(-(n + new) // 64) * 64 for n in lens)
+        engine = Engine(folder, precision="bf16", ctx=cfg["max_position_embeddings"], max_tokens=total + 64 * batch,
+                        max_batch=batch)
+    prompts = [synthetic_prompt(V, n, i) for i, n in enumerate(lens)]
+    greedy = SamplingParams(temperature=0.0)
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first = engine.generate([GenerateRequest(p, greedy, 1, []) for p in prompts])
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        out = engine.generate([GenerateRequest(p, greedy, new, []) for p in prompts])
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+    bad = [r.error for r in first + out if r.finish == "error"]
+    if bad:
+        raise RuntimeError(bad[0])
+    if any(len(r.tokens) != new for r in out) or any(a.tokens[0] != b.tokens[0] for a, b in zip(first, out)):
+        raise RuntimeError("the workload's two runs disagree")
+    prefill_s = t1 - t0
+    decode_s = (t2 - t1) - prefill_s
+    step_ms = decode_s / (new - 1) * 1e3
+    pk = peaks()
+    step_bytes = nums["weight_bytes"] + (sum(lens) + batch * new // 2) * nums["kv_bytes_per_token"] + batch * nums["state_bytes"]
+    achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "workload": name, "metric": "decode tok/s through Engine.generate", "value": round(batch * (new - 1) / decode_s, 1),
+        "unit": "tok/s", "ms_per_step": round(step_ms, 4), "decode_steps": new, "dtype": "bf16",
+        "data": "synthetic token ids, random weights N(0, 0.02)",
+        "prefill": {"value": round(sum(lens) / prefill_s, 1), "tokens": sum(lens), "ms": round(prefill_s * 1e3, 1)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes), "peaks": pk["source"]},
+        "config": {"layers": cfg["num_hidden_layers"], "layers_of_shape": full_layers, "hidden": cfg["hidden_size"],
+                   "ffn": cfg["intermediate_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "vocab": V, "attn_layers": nums["n_attn"], "conv_layers": nums["n_conv"], "global_batch": batch,
+                   "prompt_min": min(lens), "prompt_max": max(lens), "context": cfg["max_position_embeddings"]},
+        "device_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1)}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=None, help="default: 256 decode steps, or the workload's own")
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=None, help="default: 8, or the workload's own")
     ap.add_argument("--layers", type=int, default=None, help="run only the first N layers (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="time one part only and print a short line (for profiler captures)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="instead of the default run: a batch of unequal prompts at another shape of the family")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -242,6 +321,10 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload is not None:
+        return run_workload(args.workload, args.layers, args.batch, args.steps)
+    args.batch = args.batch or 8
+    args.steps = args.steps or 256
 
     import torch
     from xpu_serve_b200 import load_model
@@ -289,7 +372,9 @@ def main() -> int:
         e2e_value, h2d, d2h = time_e2e(folder, args.batch, min(args.steps, 32), args.warmup, V)
 
     value = args.batch * 1000.0 / ms
-    step_bytes = nums["weight_bytes"] + args.batch * (PROMPT * nums["kv_bytes_per_token"] + nums["state_bytes"])
+    # the cache grows by one position a step: the timed steps read PROMPT + warmup + steps / 2 positions on average
+    kv_positions = PROMPT + args.warmup + args.steps // 2
+    step_bytes = nums["weight_bytes"] + args.batch * (kv_positions * nums["kv_bytes_per_token"] + nums["state_bytes"])
     achieved = step_bytes / (ms * 1e-3) / 1e9
     line = {
         "metric": "LFM3-1.2B-shape decode tok/s (batch 8, 2,048-token prompts)",
