@@ -64,8 +64,8 @@ def _signatures(lib) -> None:
     lib.xs_attention_mma_supports.argtypes = [c_int, c_int, c_int]
     lib.xs_attention_tc_supports.restype = c_int
     lib.xs_attention_tc_supports.argtypes = [c_int, c_int, c_int]
-    lib.xs_attention_mma_decode_ctas_per_sm.restype = c_int
-    lib.xs_attention_mma_decode_ctas_per_sm.argtypes = [c_int]
+    lib.xs_attention_mma_decode_slots.restype = c_int
+    lib.xs_attention_mma_decode_slots.argtypes = [c_int, c_int64]
     lib.xs_gemm_small_m_supports.restype = c_int
     lib.xs_gemm_small_m_supports.argtypes = [c_int, c_int, c_int64, c_int64]
     lib.xs_gemm_tc_supports.restype = c_int
@@ -262,14 +262,10 @@ def attention_mma_supports(head_dim: int, page_size: int, group: int) -> bool:
     return bool(load().xs_attention_mma_supports(head_dim, page_size, group))
 
 
-_decode_ctas = {}
-
-
-def attention_mma_decode_ctas_per_sm(head_dim: int) -> int:
-    """CTAs of the decode attention kernel that fit an SM at once (asked of the device once per head size)."""
-    if head_dim not in _decode_ctas:
-        _decode_ctas[head_dim] = int(load().xs_attention_mma_decode_ctas_per_sm(head_dim))
-    return _decode_ctas[head_dim]
+def attention_mma_decode_slots(head_dim: int, tiles: int) -> int:
+    """CTAs of the decode attention kernel that run at one time on the device when `tiles` = sequences x kv heads
+    (the kernel keeps fewer stages, and so more CTAs an SM, when the tiles alone overfill the device)."""
+    return int(load().xs_attention_mma_decode_slots(head_dim, tiles))
 
 
 def attention_mma_scratch_bytes(rows: int, head_dim: int, splits: int) -> int:

@@ -121,7 +121,7 @@ class AttentionMixer(Mixer):
             if s.window > 0:
                 blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
             if step.decode and s.heads // s.kv_heads <= 16 and rt.attn_split_factor == 0:
-                splits = decode_splits(tiles, blocks, rt.sm_count * max(1, ops.attention_mma_decode_ctas_per_sm(s.head_dim)))
+                splits = decode_splits(tiles, blocks, max(1, ops.attention_mma_decode_slots(s.head_dim, tiles)))
             else:
                 splits = max(1, min(blocks, 32, (max(rt.attn_split_factor, 1) * rt.sm_count) // max(tiles, 1)))
             # prompts: the tcgen05 kernel, unless few tiles face many keys (a short piece of a long sequence), where
