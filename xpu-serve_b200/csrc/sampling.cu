@@ -40,16 +40,47 @@ __device__ __forceinline__ uint64_t key_of(float logit, int token) {
     return ((uint64_t)ordered_bits(logit) << 32) | (uint64_t)(0xFFFFFFFFu - (uint32_t)token);
 }
 
-__device__ __forceinline__ double block_sum_f64(double v, double* scratch) {
+// Calls f(logit, token) for every token of the row, tokens dealt to the block's threads in turn, eight loads of a
+// thread in flight at a time (a row is read from L2: one load at a time would be one latency per token).
+template <typename F>
+__device__ __forceinline__ void for_row_strided(const float* __restrict__ row, int V, F&& f) {
+    const int step = (int)blockDim.x;
+    for (int t0 = threadIdx.x; t0 < V; t0 += step * 8) {
+        float l[8];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    double t = (threadIdx.x & 31) < (blockDim.x >> 5) ? scratch[threadIdx.x & 31] : 0.0;
+        for (int u = 0; u < 8; ++u) {
+            const int t = t0 + u * step;
+            l[u] = t < V ? __ldg(row + t) : 0.0f;
+        }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    return t;
+        for (int u = 0; u < 8; ++u) {
+            const int t = t0 + u * step;
+            if (t < V) f(l[u], t);
+        }
+    }
+}
+
+// The same for the tokens [begin, end) that one thread owns, in token order; 16-byte loads when `vec`.
+template <typename F>
+__device__ __forceinline__ void for_chunk(const float* __restrict__ row, int begin, int end, bool vec, F&& f) {
+    if (vec) {
+        for (int t0 = begin; t0 < end; t0 += 16) {
+            float4 l[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                l[u] = t0 + 4 * u < end ? __ldg(reinterpret_cast<const float4*>(row + t0 + 4 * u)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int t = t0 + 4 * u;
+                if (t < end) {
+                    if (!f(l[u].x, t) || !f(l[u].y, t + 1) || !f(l[u].z, t + 2) || !f(l[u].w, t + 3)) return;
+                }
+            }
+        }
+        return;
+    }
+    for (int t = begin; t < end; ++t)
+        if (!f(__ldg(row + t), t)) return;
 }
 
 struct ArgBest {
@@ -64,7 +95,7 @@ __device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
 // Largest value of a row and the lowest index that has it (NaN never wins). All threads get it.
 __device__ ArgBest block_argmax(const float* __restrict__ row, int V, ArgBest* scratch) {
     ArgBest best{-INFINITY, 0x7fffffff};
-    for (int t = threadIdx.x; t < V; t += blockDim.x) best = better(best, ArgBest{row[t], t});
+    for_row_strided(row, V, [&](float l, int t) { best = better(best, ArgBest{l, t}); });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -119,75 +150,244 @@ __global__ void argmax_finish_kernel(unsigned long long* __restrict__ packed, in
 }
 
 
+// Weights are added up as 64-bit fixed point (2^-40 of the largest weight, which is 1): integer sums do not
+// depend on the order in which threads add, so a row's kept set and draw are the same in every run.
+constexpr int kSub = 32;                          // histograms a block keeps, one per warp
+constexpr double kFixOne = 1099511627776.0;       // 2^40
+constexpr int kMaxVocab = 1 << 22;                // 2^22 weights of at most 2^40 stay below 2^63
+
+__device__ __forceinline__ unsigned long long fix_of(float w) { return __double2ull_rz((double)w * kFixOne); }
+
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    unsigned long long t = (threadIdx.x & 31) < (blockDim.x >> 5) ? scratch[threadIdx.x & 31] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+}
+
+// Exclusive prefix of v over the block's threads in thread order; *total gets the sum. scratch: 33 words.
+__device__ __forceinline__ unsigned long long block_exclusive_scan_u64(unsigned long long v, unsigned long long* scratch,
+                                                                       unsigned long long* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned long long inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += up;
+    }
+    __syncthreads();
+    if (lane == 31) scratch[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        const unsigned long long w = lane < (int)(blockDim.x >> 5) ? scratch[lane] : 0ull;
+        unsigned long long winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += up;
+        }
+        scratch[lane] = winc - w;                 // what the warps before this one hold
+        if (lane == 31) scratch[32] = winc;
+    }
+    __syncthreads();
+    *total = scratch[32];
+    return scratch[warp] + inc - v;
+}
+
+struct RadixScratch {
+    unsigned int* sub_count;            // [kSub][256]
+    unsigned int* sub_mass_lo;          // [kSub][256]: a warp's mass in a bucket is hi * 2^32 + lo
+    unsigned int* sub_mass_hi;          // [kSub][256]
+    unsigned int* count;                // [256]
+    unsigned long long* mass;           // [256]
+    uint64_t* key;
+    long long* above_count;
+    unsigned long long* above_mass;
+    unsigned int* left;                 // keys in the bucket the walk chose
+};
+
 // Radix descent, most significant byte first, over the keys >= `floor_key`.
 // by_count: the key of rank `target_count` (1-based) in descending order.
-// else:     the largest key K such that the weight of {keys >= K} reaches `target_mass`.
+// else:     the largest key K such that the weight of {keys >= K} reaches `target_mass` (in fixed point).
 // If the target is never reached the smallest eligible key is returned.
+// Every warp counts into a histogram of its own (all 65,536 logits of a row share a handful of leading bytes: one
+// histogram for the block would serialise a thousand threads on a few words), a thread per bucket adds the warps'
+// histograms, and one warp walks the 256 buckets, eight a lane.
 __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max_logit, float inv_temp,
                                  uint64_t floor_key, bool by_count, long long target_count, double target_mass,
-                                 unsigned int* hist_count, double* hist_mass, uint64_t* shared_key,
-                                 long long* shared_count, double* shared_mass) {
+                                 const RadixScratch& sc) {
     uint64_t prefix = 0;
     long long above_count = 0;
-    double above_mass = 0.0;
+    unsigned long long above_mass = 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned int* my_count = sc.sub_count + (warp % kSub) * 256;
+    unsigned int* my_lo = sc.sub_mass_lo + (warp % kSub) * 256;
+    unsigned int* my_hi = sc.sub_mass_hi + (warp % kSub) * 256;
     for (int pass = 7; pass >= 0; --pass) {
         const int shift = pass * 8;
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
-            hist_count[b] = 0;
-            hist_mass[b] = 0.0;
+        for (int b = threadIdx.x; b < kSub * 256; b += blockDim.x) {
+            sc.sub_count[b] = 0;
+            if (!by_count) {
+                sc.sub_mass_lo[b] = 0;
+                sc.sub_mass_hi[b] = 0;
+            }
         }
         __syncthreads();
         const uint64_t hi_mask = pass == 7 ? 0ull : (~0ull << (shift + 8));
-        for (int t = threadIdx.x; t < V; t += blockDim.x) {
-            const float l = row[t];
+        for_row_strided(row, V, [&](float l, int t) {
             const uint64_t key = key_of(l, t);
-            if (key < floor_key || (key & hi_mask) != prefix) continue;
+            if (key < floor_key || (key & hi_mask) != prefix) return;
             const int digit = (int)((key >> shift) & 0xFF);
-            atomicAdd(&hist_count[digit], 1u);
-            if (!by_count) atomicAdd(&hist_mass[digit], (double)expf((l - max_logit) * inv_temp));
+            atomicAdd(&my_count[digit], 1u);
+            if (!by_count) {
+                // a 64-bit sum out of 32-bit adds (the kind shared memory does by itself): the low word, one more
+                // in the high word whenever the low word wraps, and the weight's own high word (zero below 2^-8)
+                const unsigned long long f = fix_of(expf((l - max_logit) * inv_temp));
+                const unsigned int lo = (unsigned int)f, hi = (unsigned int)(f >> 32);
+                const unsigned int old = atomicAdd(&my_lo[digit], lo);
+                const unsigned int carry = old + lo < old ? 1u : 0u;
+                if (hi + carry != 0u) atomicAdd(&my_hi[digit], hi + carry);
+            }
+        });
+        __syncthreads();
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            unsigned int c = 0;
+            unsigned long long m = 0;
+#pragma unroll 8
+            for (int w = 0; w < kSub; ++w) {
+                c += sc.sub_count[w * 256 + b];
+                if (!by_count)
+                    m += ((unsigned long long)sc.sub_mass_hi[w * 256 + b] << 32) + sc.sub_mass_lo[w * 256 + b];
+            }
+            sc.count[b] = c;
+            sc.mass[b] = m;
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            long long c = above_count;
-            double m = above_mass;
-            int chosen = -1;
-            for (int b = 255; b >= 0; --b) {
-                if (hist_count[b] == 0) continue;
-                const long long c2 = c + hist_count[b];
-                const double m2 = m + hist_mass[b];
-                chosen = b;   // the lowest non-empty bucket so far: where an unreachable target lands
-                if (by_count ? (c2 >= target_count) : (m2 >= target_mass)) break;
+        if (warp == 0) {
+            // lane L owns buckets 255 - 8 L down to 248 - 8 L: lane 0 the largest digits
+            const int hi = 255 - 8 * lane;
+            long long c = 0;
+            unsigned long long m = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                c += sc.count[hi - j];
+                m += sc.mass[hi - j];
+            }
+            long long c_inc = c;
+            unsigned long long m_inc = m;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const long long cu = __shfl_up_sync(0xffffffffu, c_inc, o);
+                const unsigned long long mu = __shfl_up_sync(0xffffffffu, m_inc, o);
+                if (lane >= o) {
+                    c_inc += cu;
+                    m_inc += mu;
+                }
+            }
+            c = above_count + c_inc - c;          // what lies above this lane's buckets
+            m = above_mass + m_inc - m;
+            int found = -1, low = -1;
+            unsigned int found_n = 0, low_n = 0;
+            long long found_c = 0, low_c = 0;
+            unsigned long long found_m = 0, low_m = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int b = hi - j;
+                const unsigned int n = sc.count[b];
+                if (n == 0 || found >= 0) continue;
+                low = b;                           // the lowest non-empty bucket so far, and what lies above it
+                low_n = n;
+                low_c = c;
+                low_m = m;
+                const long long c2 = c + n;
+                const unsigned long long m2 = m + sc.mass[b];
+                if (by_count ? (c2 >= target_count) : ((double)m2 >= target_mass)) {
+                    found = b;
+                    found_n = n;
+                    found_c = c;
+                    found_m = m;
+                }
                 c = c2;
                 m = m2;
             }
-            if (chosen < 0) chosen = 0;
-            *shared_key = prefix | ((uint64_t)chosen << shift);
-            *shared_count = c;
-            *shared_mass = m;
+            const unsigned hit = __ballot_sync(0xffffffffu, found >= 0);
+            const unsigned any = __ballot_sync(0xffffffffu, low >= 0);
+            if (hit != 0u) {
+                if (lane == __ffs(hit) - 1) {
+                    *sc.key = prefix | ((uint64_t)found << shift);
+                    *sc.above_count = found_c;
+                    *sc.above_mass = found_m;
+                    *sc.left = found_n;
+                }
+            } else if (any != 0u) {               // an unreachable target lands on the lowest non-empty bucket
+                if (lane == 31 - __clz(any)) {
+                    *sc.key = prefix | ((uint64_t)low << shift);
+                    *sc.above_count = low_c;
+                    *sc.above_mass = low_m;
+                    *sc.left = low_n;
+                }
+            } else if (lane == 0) {
+                *sc.key = prefix;
+                *sc.above_count = above_count;
+                *sc.above_mass = above_mass;
+                *sc.left = 0;
+            }
         }
         __syncthreads();
-        prefix = *shared_key;
-        above_count = *shared_count;
-        above_mass = *shared_mass;
+        prefix = *sc.key;
+        above_count = *sc.above_count;
+        above_mass = *sc.above_mass;
+        const unsigned int left = *sc.left;
         __syncthreads();
+        if (left == 1 && pass > 0) {
+            // one key has this prefix: it is the answer, and whoever holds it says so (the remaining passes would
+            // each read the whole row to learn one more byte of it)
+            const uint64_t got_mask = ~0ull << shift;
+            for_row_strided(row, V, [&](float l, int t) {
+                const uint64_t key = key_of(l, t);
+                if (key >= floor_key && (key & got_mask) == prefix) *sc.key = key;
+            });
+            __syncthreads();
+            prefix = *sc.key;
+            __syncthreads();
+            return prefix;
+        }
     }
     return prefix;
 }
+
+constexpr size_t kSampleSmem = (size_t)kSub * 256 * 3 * sizeof(unsigned int);
 
 // One block per row.
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
               const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ counters, int32_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char sample_smem[];
     __shared__ ArgBest arg_scratch[32];
-    __shared__ double sum_scratch[32];
+    __shared__ unsigned long long sum_scratch[33];
     __shared__ unsigned int hist_count[256];
-    __shared__ double hist_mass[256];
+    __shared__ unsigned long long hist_mass[256];
     __shared__ uint64_t shared_key;
     __shared__ long long shared_count;
-    __shared__ double shared_mass;
-    __shared__ double chunk_sum[kThreads];
+    __shared__ unsigned long long shared_mass;
+    __shared__ unsigned int shared_left;
     __shared__ int result;
+    RadixScratch sc;
+    sc.sub_count = reinterpret_cast<unsigned int*>(sample_smem);
+    sc.sub_mass_lo = sc.sub_count + kSub * 256;
+    sc.sub_mass_hi = sc.sub_mass_lo + kSub * 256;
+    sc.count = hist_count;
+    sc.mass = hist_mass;
+    sc.key = &shared_key;
+    sc.above_count = &shared_count;
+    sc.above_mass = &shared_mass;
+    sc.left = &shared_left;
 
     const int rowi = blockIdx.x;
     const float* row = logits + (int64_t)rowi * ld;
@@ -203,65 +403,51 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
     const float w_cut = min_p[rowi];
 
     uint64_t floor_key = 0;   // keys below it are not candidates
-    if (k > 0 && k < V) {
-        floor_key = radix_select(row, V, top.v, inv_temp, 0, true, k, 0.0, hist_count, hist_mass, &shared_key,
-                                 &shared_count, &shared_mass);
-    }
+    if (k > 0 && k < V) floor_key = radix_select(row, V, top.v, inv_temp, 0, true, k, 0.0, sc);
     if (p_cut < 1.0f) {
-        double mass = 0.0;   // `total`: the weight of the top-k candidates
-        for (int t = threadIdx.x; t < V; t += blockDim.x) {
-            const float l = row[t];
-            if (key_of(l, t) >= floor_key) mass += (double)expf((l - top.v) * inv_temp);
-        }
-        mass = block_sum_f64(mass, sum_scratch);
-        const uint64_t p_key = radix_select(row, V, top.v, inv_temp, floor_key, false, 0, (double)p_cut * mass,
-                                            hist_count, hist_mass, &shared_key, &shared_count, &shared_mass);
+        unsigned long long mass = 0;   // `total`: the weight of the top-k candidates
+        for_row_strided(row, V, [&](float l, int t) {
+            if (key_of(l, t) >= floor_key) mass += fix_of(expf((l - top.v) * inv_temp));
+        });
+        mass = block_sum_u64(mass, sum_scratch);
+        const uint64_t p_key = radix_select(row, V, top.v, inv_temp, floor_key, false, 0, (double)p_cut * (double)mass, sc);
         floor_key = p_key > floor_key ? p_key : floor_key;
     }
 
     // Kept: key >= floor_key and weight >= min_p (the likeliest token always stays).
     const int per = (V + blockDim.x - 1) / blockDim.x;
     const int begin = min(V, (int)threadIdx.x * per), end = min(V, begin + per);
-    double mine = 0.0;
-    for (int t = begin; t < end; ++t) {
-        const float l = row[t];
+    const bool vec = per % 4 == 0 && V % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    unsigned long long mine = 0;
+    for_chunk(row, begin, end, vec, [&](float l, int t) {
         const float w = expf((l - top.v) * inv_temp);
-        if (key_of(l, t) >= floor_key && (w >= w_cut || t == top.i)) mine += (double)w;
-    }
-    chunk_sum[threadIdx.x] = mine;
+        if (key_of(l, t) >= floor_key && (w >= w_cut || t == top.i)) mine += fix_of(w);
+        return true;
+    });
     if (threadIdx.x == 0) result = -1;
-    __syncthreads();
-    if (threadIdx.x == 0) {   // exclusive prefix over the chunks, in place
-        double run = 0.0;
-        for (int i = 0; i < (int)blockDim.x; ++i) {
-            const double s = chunk_sum[i];
-            chunk_sum[i] = run;
-            run += s;
-        }
-        shared_mass = run;
-    }
-    __syncthreads();
-    const double total = shared_mass;
-    const double target = uniform_from(seeds[rowi], counters[rowi]) * total;
-    const double before = chunk_sum[threadIdx.x];
-    if (mine > 0.0 && target >= before && target < before + mine) {
-        double left = target - before;
+    unsigned long long total = 0;
+    const unsigned long long before = block_exclusive_scan_u64(mine, sum_scratch, &total);
+    unsigned long long target = __double2ull_rz(uniform_from(seeds[rowi], counters[rowi]) * (double)total);
+    if (total > 0 && target >= total) target = total - 1;
+    if (mine > 0 && target >= before && target < before + mine) {
+        unsigned long long left = target - before;
         int pick = -1, last = -1;
-        for (int t = begin; t < end; ++t) {
-            const float l = row[t];
+        for_chunk(row, begin, end, vec, [&](float l, int t) {
             const float w = expf((l - top.v) * inv_temp);
-            if (!(key_of(l, t) >= floor_key && (w >= w_cut || t == top.i))) continue;
+            if (!(key_of(l, t) >= floor_key && (w >= w_cut || t == top.i))) return true;
             last = t;
-            if (left < (double)w) {
+            const unsigned long long f = fix_of(w);
+            if (left < f) {
                 pick = t;
-                break;
+                return false;
             }
-            left -= (double)w;
-        }
+            left -= f;
+            return true;
+        });
         result = pick >= 0 ? pick : last;
     }
     __syncthreads();
-    if (threadIdx.x == 0) out[rowi] = result >= 0 ? result : top.i;   // rounding put the target past the end
+    if (threadIdx.x == 0) out[rowi] = result >= 0 ? result : top.i;   // every kept weight rounded to zero
 }
 
 // logits[r, t] for seen tokens: divided (positive) or multiplied (negative) by the repetition
@@ -320,8 +506,13 @@ XS_API int xs_sample(const float* logits, int64_t ld, int n, int V, const float*
                      const float* top_p, const float* min_p, const uint64_t* seeds, const uint64_t* counters,
                      int32_t* out, cudaStream_t stream) {
     if (n == 0) return 0;
-    XS_REQUIRE(n > 0 && V > 0 && ld >= V, "sample: %d rows of %d", n, V);
-    sample_kernel<<<n, kThreads, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, seeds, counters, out);
+    XS_REQUIRE(n > 0 && V > 0 && V <= kMaxVocab && ld >= V, "sample: %d rows of %d (at most %d)", n, V, kMaxVocab);
+    static bool opted = false;
+    if (!opted) {
+        cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleSmem);
+        opted = true;
+    }
+    sample_kernel<<<n, kThreads, kSampleSmem, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, seeds, counters, out);
     XS_LAUNCH_CHECK("sample");
     return 0;
 }
