@@ -174,14 +174,23 @@ def test_penalties_match_plain(folders):
             gen.append(t)
 
 
-def test_running_ahead_changes_no_token(folders, monkeypatch):
-    """Greedy batches decode with the next step already started on the device. Stop tokens that end one
-    sequence in the middle, unequal lengths, a page boundary (64) crossed while running ahead, a sequence
-    that reaches the context's end, a callback that cancels: the same tokens as without running ahead."""
+@pytest.mark.parametrize("kind", ["greedy", "sampled", "penalties", "mixed"])
+def test_running_ahead_changes_no_token(folders, monkeypatch, kind):
+    """Batches decode with the next step already started on the device, fed there with the tokens that the
+    graph's argmax or the sampling kernels chose. Stop tokens that end one sequence in the middle, unequal
+    lengths, a page boundary (64) crossed while running ahead, a sequence that reaches the context's end, a
+    callback that cancels: the same tokens as without running ahead, for greedy sequences, seeded draws,
+    penalties (whose token counts the step that runs ahead updates too) and a batch that mixes them."""
     from xpu_serve_b200 import GenerateRequest, SamplingParams
     from xpu_serve_b200.engine.engine import Engine
     folder = folders[("A", "float32")]
-    greedy = SamplingParams(temperature=0.0)
+    how = {
+        "greedy": lambda i: SamplingParams(temperature=0.0),
+        "sampled": lambda i: SamplingParams(temperature=0.9, top_p=0.95, top_k=60, seed=100 + i),
+        "penalties": lambda i: SamplingParams(temperature=0.0 if i % 2 else 0.8, repetition_penalty=1.3,
+                                              frequency_penalty=0.2, presence_penalty=0.1, seed=7 + i),
+        "mixed": lambda i: SamplingParams(temperature=0.0) if i % 2 else SamplingParams(temperature=1.1, min_p=0.02, seed=i),
+    }[kind]
     prompts = [tiny.prompt("A", n, salt=40 + i) for i, n in enumerate((60, 3, 17, 100))]
 
     def run(ahead, stops, cancel_at=None):
@@ -189,13 +198,23 @@ def test_running_ahead_changes_no_token(folders, monkeypatch):
         engine = Engine(folder, precision="f32", ctx=128, max_batch=8)
         assert engine.stepper.run_ahead == ahead
         seen = []
+        ran_ahead = [0]
+        take = engine.stepper._take_ahead
+
+        def counting_take(*a):
+            ran_ahead[0] += 1
+            return take(*a)
+
+        engine.stepper._take_ahead = counting_take
 
         def on_token(i, t):
             seen.append((i, t))
             return not (cancel_at is not None and i == 2 and sum(1 for j, _ in seen if j == 2) >= cancel_at)
 
-        reqs = [GenerateRequest(p, greedy, n, list(stops)) for p, n in zip(prompts, (40, 30, 25, 60))]
+        reqs = [GenerateRequest(p, how(i), n, list(stops)) for i, (p, n) in enumerate(zip(prompts, (40, 30, 25, 60)))]
         res = engine.generate(reqs, on_token)
+        if ahead:
+            assert ran_ahead[0] > 20, "the steps did not run ahead"
         engine.stepper.cache.check()
         assert engine.stepper.cache.slots.held_count == 0
         return [(r.finish, r.tokens) for r in res]

@@ -41,11 +41,35 @@ class _Handle:
 
 
 class _Ahead:
-    """A decode step that was started before the loop asked for it."""
-    __slots__ = ("row_of", "fed", "event", "host")
+    """A decode step that was started before the loop asked for it. `chosen`: its tokens on the device."""
+    __slots__ = ("row_of", "fed", "event", "host", "chosen")
 
-    def __init__(self, row_of, fed, event, host):
-        self.row_of, self.fed, self.event, self.host = row_of, fed, event, host
+    def __init__(self, row_of, fed, event, host, chosen):
+        self.row_of, self.fed, self.event, self.host, self.chosen = row_of, fed, event, host, chosen
+
+
+class _Choice:
+    """What the sampling kernels need for one set of sequences, on the device for as long as the same sequences
+    are chosen for step after step: the parameters do not change, and the draw counters advance by one a step,
+    on the device too. `counters_host` mirrors them so that a step that does not follow on is noticed."""
+
+    def __init__(self, chosen: Sequence[_Handle], device, with_penalties: bool, offset: int):
+        params = [h.request.sampling for h in chosen]
+        f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=device)          # noqa: E731
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)            # noqa: E731
+        self.key = tuple(chosen)
+        self.all_greedy = all(p.greedy() for p in params)
+        if not self.all_greedy:
+            self.temperature, self.top_k = f32([p.temperature for p in params]), i32([p.top_k for p in params])
+            self.top_p, self.min_p = f32([p.top_p for p in params]), f32([p.min_p for p in params])
+            self.seeds = torch.tensor([_i64(h.seed) for h in chosen], dtype=torch.int64, device=device)
+        self.counters_host = [h.counter + offset for h in chosen]
+        self.counters = torch.tensor(self.counters_host, dtype=torch.int64, device=device)
+        if with_penalties:
+            self.rows = i32([h.row for h in chosen])
+            self.repetition = f32([p.repetition_penalty for p in params])
+            self.presence = f32([p.presence_penalty for p in params])
+            self.frequency = f32([p.frequency_penalty for p in params])
 
 
 class DeviceStepper:
@@ -74,11 +98,13 @@ class DeviceStepper:
         self._turn = 0
         self.run_ahead = os.environ.get("XS_NO_RUN_AHEAD", "0") != "1"
         self._ahead: Optional[_Ahead] = None
+        self._choice: Optional[_Choice] = None
         self._live = set()          # handles that hold a slot
 
     # ---------------------------------------------------------------- slots
     def open(self, requests: Sequence[GenerateRequest]) -> List[_Handle]:
         self._ahead = None          # what ran ahead for an earlier batch is nobody's any more
+        self._choice = None
         slots = self.cache.open(len(requests))
         handles = []
         for row, (s, r) in enumerate(zip(slots, requests)):
@@ -130,25 +156,41 @@ class DeviceStepper:
             for h in chosen:
                 h.counter += 1
             return tokens
-        out = torch.empty(n, dtype=torch.int32, device=dev)
+        out = self._choose(logits, chosen, 0)
+        host, event = self._copy_out(out)
+        if n == len(handles):
+            self._start_ahead(handles, out)       # the next step, fed on the device, before waiting for this one
+        event.synchronize()
+        tokens = host[:n].tolist()
+        for h in chosen:
+            h.counter += 1
+        if self._ahead is not None:
+            self._ahead.fed = tokens
+        if n == len(want):
+            return tokens
+        it = iter(tokens)
+        return [next(it) if w else None for w in want]
+
+    def _choose(self, logits: torch.Tensor, chosen: Sequence[_Handle], offset: int) -> torch.Tensor:
+        """The sampling kernels over `logits` (one row per chosen sequence): penalties, then argmax or a seeded
+        draw with each sequence's draw counter (+ offset: 1 for a step that runs ahead of the loop's count), then
+        the note of the chosen tokens for the penalties. Returns the tokens, int32 on the device."""
+        c = self._choice
+        expected = [h.counter + offset for h in chosen]
+        if c is None or c.key != tuple(chosen) or c.counters_host != expected:
+            c = self._choice = _Choice(chosen, self.device, self._pen is not None, offset)
+        out = torch.empty(len(chosen), dtype=torch.int32, device=self.device)
         if self._pen is not None:
-            rows = torch.tensor([h.row for h in chosen], dtype=torch.int32, device=dev)
-            ops.apply_penalties(logits, self._pen[0], self._pen[1], rows,
-                                torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=dev),
-                                torch.tensor([p.presence_penalty for p in params], dtype=torch.float32, device=dev),
-                                torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32, device=dev))
-        if all(p.greedy() for p in params):
+            ops.apply_penalties(logits, self._pen[0], self._pen[1], c.rows, c.repetition, c.presence, c.frequency)
+        if c.all_greedy:
             ops.argmax(logits, out)
         else:
-            f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=dev)   # noqa: E731
-            ops.sample(logits, f32([p.temperature for p in params]),
-                       torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev),
-                       f32([p.top_p for p in params]), f32([p.min_p for p in params]),
-                       torch.tensor([_i64(h.seed) for h in chosen], dtype=torch.int64, device=dev),
-                       torch.tensor([h.counter for h in chosen], dtype=torch.int64, device=dev), out)
+            ops.sample(logits, c.temperature, c.top_k, c.top_p, c.min_p, c.seeds, c.counters, out)
+        c.counters.add_(1)
+        c.counters_host = [v + 1 for v in c.counters_host]
         if self._pen is not None:
-            ops.note_tokens(out, rows, self._pen[0], self._pen[1], generated=True)
-        return self._to_host(out, chosen, want)
+            ops.note_tokens(out, c.rows, self._pen[0], self._pen[1], generated=True)
+        return out
 
     def _copy_out(self, out: torch.Tensor):
         """Starts the step's only device-to-host copy (the chosen tokens, into pinned memory) and returns the
@@ -166,28 +208,26 @@ class DeviceStepper:
         event.record()
         return host, event
 
-    def _to_host(self, out: torch.Tensor, chosen, want) -> List[Optional[int]]:
-        host, event = self._copy_out(out)
-        event.synchronize()
-        tokens = host[:out.numel()].tolist()
-        for h in chosen:
-            h.counter += 1
-        if len(tokens) == len(want):
-            return tokens
-        it = iter(tokens)
-        return [next(it) if w else None for w in want]
-
     # ----------------------------------------------------------- running ahead
-    def _start_ahead(self, handles: Sequence[_Handle]) -> None:
+    def _start_ahead(self, handles: Sequence[_Handle], chosen_dev: Optional[torch.Tensor] = None) -> None:
         """Starts the decode step after the last one for the same sequences, fed on the device, if the last
-        step was a greedy graph step of exactly these sequences and the cache has room."""
-        if not self.run_ahead or self._pen is not None or not all(h.request.sampling.greedy() for h in handles):
+        step was a graph step of exactly these sequences and the cache has room. Greedy sequences without
+        penalties are fed the graph's own argmax; the others `chosen_dev`, what the sampling kernels chose from
+        the last step's logits, and their next tokens are chosen at once too."""
+        if not self.run_ahead:
             return
-        out = self.model.step_from_last_greedy(self.cache, [h.slot for h in handles])
+        slots = [h.slot for h in handles]
+        if self._pen is None and all(h.request.sampling.greedy() for h in handles):
+            out = self.model.step_from_last_greedy(self.cache, slots)
+        else:
+            if chosen_dev is None:
+                return
+            logits = self.model.step_fed(self.cache, slots, chosen_dev)
+            out = None if logits is None else self._choose(logits, handles, 1)
         if out is None:
             return
         host, event = self._copy_out(out)
-        self._ahead = _Ahead({h: i for i, h in enumerate(handles)}, None, event, host)
+        self._ahead = _Ahead({h: i for i, h in enumerate(handles)}, None, event, host, out)
 
     def _take_ahead(self, ahead: _Ahead, handles, token_lists, want) -> List[Optional[int]]:
         """The loop now asks for (a part of) the step that already runs."""
@@ -196,8 +236,8 @@ class DeviceStepper:
             if i is None or not w or len(toks) != 1 or int(toks[0]) != ahead.fed[i]:
                 raise RuntimeError("this stepper runs one decode step ahead: after decoding has begun, a sequence's "
                                    "next step must bring the token that the last step returned for it")
-        if len(handles) == len(ahead.row_of):
-            self._start_ahead(handles)          # the same sequences go on: keep the device busy
+        if len(handles) == len(ahead.row_of) and [ahead.row_of[h] for h in handles] == list(range(len(handles))):
+            self._start_ahead(handles, ahead.chosen)          # the same sequences go on: keep the device busy
         ahead.event.synchronize()
         tokens = ahead.host[:len(ahead.row_of)].tolist()
         got = [tokens[ahead.row_of[h]] for h in handles]

@@ -182,11 +182,12 @@ class Model:
             return g.logits[:0]
         return g.logits[torch.tensor(picked, dtype=torch.int64, device=self.rt.device)]
 
-    def step_from_last_greedy(self, cache: Cache, slots: Sequence[int]) -> Optional[torch.Tensor]:
-        """One more decode step of exactly the sequences of the last step, each fed the token that step's graph
-        chose, which never leaves the device. Returns the new choices (int32 [n] on the device, the graph's
-        own buffer), or None, with nothing changed, when the last step was no graph step of these sequences
-        with all rows wanted, or the cache cannot take another token for every one of them."""
+    def step_fed(self, cache: Cache, slots: Sequence[int], tokens_dev: torch.Tensor) -> Optional[torch.Tensor]:
+        """One more decode step of exactly the sequences of the last step, sequence i fed `tokens_dev[i]` (int32
+        on the device: what a sampling kernel chose from the last step's logits), so that the tokens never leave
+        the device. Returns the new logits ([n, vocab], the graph's own buffer, with `last_greedy` their argmax),
+        or None, with nothing changed, when the last step was no graph step of these sequences with all rows
+        wanted, or the cache cannot take another token for every one of them."""
         g = self._last_graph
         n = len(slots)
         if g is None or self.last_greedy is None or g.batch_key is None or g.batch_key[0] != tuple(slots):
@@ -196,14 +197,21 @@ class Model:
         except CacheError:
             return None
         batch_key = (tuple(slots), cache.tables_version())
-        if not (g.batch_key == batch_key and g.stager.restage_fed(g.greedy, n, starts)):
+        if not (g.batch_key == batch_key and g.stager.restage_fed(tokens_dev, n, starts)):
             g.stager.stage_decode_fixed(cache, slots, [0] * n, np.asarray(starts, dtype=np.int64), g.rows)
-            g.stager.feed_tokens(g.greedy, n)
+            g.stager.feed_tokens(tokens_dev, n)
             g.batch_key = batch_key
         self.last_h2d_bytes = g.stager.last_h2d_bytes
         g.graph.replay()
         ops.launches += g.kernels
         cache.end_step(slots, [1] * n)
+        return g.logits[:n]
+
+    def step_from_last_greedy(self, cache: Cache, slots: Sequence[int]) -> Optional[torch.Tensor]:
+        """`step_fed` with the tokens that the last step's graph chose itself (its argmax). Returns the new
+        choices (int32 [n] on the device, the graph's own buffer) or None."""
+        if self.last_greedy is None or self.step_fed(cache, slots, self.last_greedy) is None:
+            return None
         return self.last_greedy
 
     def forward(self, ctx: StepContext, cache: Cache) -> torch.Tensor:
