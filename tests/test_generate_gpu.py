@@ -117,32 +117,34 @@ def test_sampling_kernel_distribution_and_cuts():
     ties, a wide vocabulary that is no power of two, and every combination of cuts."""
     from xpu_serve_b200.ops import lib as ops
     rng = np.random.default_rng(0)
-    V = 5003
-    base = rng.normal(0, 2.5, size=V).astype(np.float32)
-    base[100:110] = base[100]                     # ties inside the likely region
-    base[7] = base.max() + 0.5
-    cases = [(1.0, 0, 1.0, 0.0), (0.7, 50, 1.0, 0.0), (1.0, 0, 0.9, 0.0), (1.5, 0, 1.0, 0.02),
-             (0.9, 200, 0.8, 0.01), (1.0, 3, 0.5, 0.0), (2.0, V, 0.999, 0.0), (1.0, 12, 1.0, 0.5)]
-    n = 256
-    for temp, k, p, mp in cases:
-        logits = torch.tensor(np.tile(base, (n, 1)), device="cuda")
-        seeds = torch.arange(n, dtype=torch.int64, device="cuda") * 7919 + 3
-        counters = torch.arange(n, dtype=torch.int64, device="cuda") % 5
-        out = torch.empty(n, dtype=torch.int32, device="cuda")
-        f = lambda v, dt=torch.float32: torch.full((n,), v, dtype=dt, device="cuda")   # noqa: E731
-        ops.sample(logits, f(temp), f(k, torch.int32), f(p), f(mp), seeds, counters, out)
-        got = out.cpu().numpy()
-        w = plain.kept_weights(base, temp, k, p, mp)
-        assert (w[got] > 0).all(), f"a dropped token was drawn with cuts {temp, k, p, mp}"
-        miss = 0
-        for i in range(n):
-            u = plain.uniform(int(seeds[i]), int(counters[i]))
-            assert ops.uniform(int(seeds[i]), int(counters[i])) == u
-            miss += int(plain.sample(base, temp, k, p, mp, u) != got[i])
-        assert miss <= 1, f"{miss} draws differ with cuts {temp, k, p, mp}"
-    # greedy rows: temperature 0 or top_k 1 pick the first largest
+    # 5,003: one CTA a row; 16,384 and 20,011: a row shared by a cluster of CTAs, with and without 16-byte loads
+    for V, n in ((5003, 256), (16384, 16), (20011, 9)):
+        base = rng.normal(0, 2.5, size=V).astype(np.float32)
+        base[100:110] = base[100]                     # ties inside the likely region
+        base[V - 3] = base[V // 2] = base[100]        # and across the parts of the row that different CTAs read
+        base[7] = base.max() + 0.5
+        cases = [(1.0, 0, 1.0, 0.0), (0.7, 50, 1.0, 0.0), (1.0, 0, 0.9, 0.0), (1.5, 0, 1.0, 0.02),
+                 (0.9, 200, 0.8, 0.01), (1.0, 3, 0.5, 0.0), (2.0, V, 0.999, 0.0), (1.0, 12, 1.0, 0.5)]
+        for temp, k, p, mp in cases:
+            logits = torch.tensor(np.tile(base, (n, 1)), device="cuda")
+            seeds = torch.arange(n, dtype=torch.int64, device="cuda") * 7919 + 3
+            counters = torch.arange(n, dtype=torch.int64, device="cuda") % 5
+            out = torch.empty(n, dtype=torch.int32, device="cuda")
+            f = lambda v, dt=torch.float32: torch.full((n,), v, dtype=dt, device="cuda")   # noqa: E731
+            ops.sample(logits, f(temp), f(k, torch.int32), f(p), f(mp), seeds, counters, out)
+            got = out.cpu().numpy()
+            w = plain.kept_weights(base, temp, k, p, mp)
+            assert (w[got] > 0).all(), f"a dropped token was drawn with cuts {temp, k, p, mp} of {V}"
+            miss = 0
+            for i in range(n):
+                u = plain.uniform(int(seeds[i]), int(counters[i]))
+                assert ops.uniform(int(seeds[i]), int(counters[i])) == u
+                miss += int(plain.sample(base, temp, k, p, mp, u) != got[i])
+            assert miss <= 1, f"{miss} draws differ with cuts {temp, k, p, mp} of {V}"
+    # greedy rows: temperature 0 or top_k 1 pick the first largest (the last, wide row: a cluster of CTAs)
     logits = torch.tensor(np.tile(base, (4, 1)), device="cuda")
     logits[1, 3] = logits[1, 7]                                  # a tie: the lower index wins
+    logits[2, V - 5] = logits[2, 7]                              # also when another CTA holds the other one
     out = torch.empty(4, dtype=torch.int32, device="cuda")
     ops.sample(logits, torch.tensor([0.0, 0.0, 1.0, 1.0], device="cuda"),
                torch.tensor([0, 0, 1, 1], dtype=torch.int32, device="cuda"), torch.ones(4, device="cuda"),

@@ -12,7 +12,11 @@
 // logit bits, then inverted token id), and the draw walks the kept tokens in vocabulary
 // order with the uniform u in [0, 1) that (seed, counter) gives (xs_uniform below), which
 // is the same distribution as walking them in sorted order.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -40,12 +44,12 @@ __device__ __forceinline__ uint64_t key_of(float logit, int token) {
     return ((uint64_t)ordered_bits(logit) << 32) | (uint64_t)(0xFFFFFFFFu - (uint32_t)token);
 }
 
-// Calls f(logit, token) for every token of the row, tokens dealt to the block's threads in turn, eight loads of a
+// Calls f(logit, token) for the tokens [from, V) of the row, tokens dealt to the block's threads in turn, eight loads of a
 // thread in flight at a time (a row is read from L2: one load at a time would be one latency per token).
 template <typename F>
-__device__ __forceinline__ void for_row_strided(const float* __restrict__ row, int V, F&& f) {
+__device__ __forceinline__ void for_row_strided(const float* __restrict__ row, int from, int V, F&& f) {
     const int step = (int)blockDim.x;
-    for (int t0 = threadIdx.x; t0 < V; t0 += step * 8) {
+    for (int t0 = from + threadIdx.x; t0 < V; t0 += step * 8) {
         float l[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -93,9 +97,9 @@ __device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
 }
 
 // Largest value of a row and the lowest index that has it (NaN never wins). All threads get it.
-__device__ ArgBest block_argmax(const float* __restrict__ row, int V, ArgBest* scratch) {
+__device__ ArgBest block_argmax(const float* __restrict__ row, int from, int V, ArgBest* scratch) {
     ArgBest best{-INFINITY, 0x7fffffff};
-    for_row_strided(row, V, [&](float l, int t) { best = better(best, ArgBest{l, t}); });
+    for_row_strided(row, from, V, [&](float l, int t) { best = better(best, ArgBest{l, t}); });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -110,13 +114,13 @@ __device__ ArgBest block_argmax(const float* __restrict__ row, int V, ArgBest* s
         ArgBest other{__shfl_xor_sync(0xffffffffu, r.v, o), __shfl_xor_sync(0xffffffffu, r.i, o)};
         r = better(r, other);
     }
-    if (r.i == 0x7fffffff) r.i = 0;   // a row of NaN or -inf
+    if (r.i == 0x7fffffff) r.i = from;   // a row of NaN or -inf
     return r;
 }
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int V, int32_t* __restrict__ out) {
     __shared__ ArgBest scratch[32];
-    const ArgBest r = block_argmax(logits + (int64_t)blockIdx.x * ld, V, scratch);
+    const ArgBest r = block_argmax(logits + (int64_t)blockIdx.x * ld, 0, V, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
 
@@ -132,7 +136,7 @@ __global__ void argmax_part_kernel(const float* __restrict__ logits, int64_t ld,
     const int per = (V + parts - 1) / parts;
     const int begin = min(V, part * per), count = min(V, begin + per) - begin;
     if (count <= 0) return;
-    ArgBest r = block_argmax(logits + (int64_t)row * ld + begin, count, scratch);
+    ArgBest r = block_argmax(logits + (int64_t)row * ld + begin, 0, count, scratch);
     if (threadIdx.x == 0) {
         const float v = r.v != r.v ? -INFINITY : r.v;
         const unsigned long long key = ((unsigned long long)ordered_bits(v) << 32) |
@@ -199,32 +203,68 @@ __device__ __forceinline__ unsigned long long block_exclusive_scan_u64(unsigned 
     return scratch[warp] + inc - v;
 }
 
+// A row is shared by the CTAs of a thread-block cluster: each reads its part of the vocabulary, and what the
+// parts have to know of one another (the largest logit, a pass's 256 bucket sums, the sums of the kept weights)
+// they read from one another's shared memory. With 8 or 64 rows and one CTA a row most of the device would idle
+// while each CTA reads its 65,536 logits a dozen times over.
+struct RowShare {
+    unsigned int count[256];            // this CTA's part of a pass's histogram
+    unsigned long long mass[256];
+    ArgBest best;
+    unsigned long long sum;
+    uint64_t key;
+    int key_set;
+};
+
 struct RadixScratch {
     unsigned int* sub_count;            // [kSub][256]
     unsigned int* sub_mass_lo;          // [kSub][256]: a warp's mass in a bucket is hi * 2^32 + lo
     unsigned int* sub_mass_hi;          // [kSub][256]
-    unsigned int* count;                // [256]
-    unsigned long long* mass;           // [256]
+    RowShare* share;                    // this CTA's
+    unsigned int* all_count;            // [256]: the whole row's
+    unsigned long long* all_mass;       // [256]
     uint64_t* key;
     long long* above_count;
     unsigned long long* above_mass;
     unsigned int* left;                 // keys in the bucket the walk chose
 };
 
-// Radix descent, most significant byte first, over the keys >= `floor_key`.
+__device__ __forceinline__ const RowShare* share_of(cg::cluster_group& cluster, RowShare* mine, unsigned int rank) {
+    return cluster.map_shared_rank(mine, rank);
+}
+
+// Sum of every CTA's v, in rank order, the same in all of them.
+__device__ __forceinline__ unsigned long long cluster_sum_u64(cg::cluster_group& cluster, RowShare* share,
+                                                              unsigned long long v, unsigned long long* before) {
+    if (threadIdx.x == 0) share->sum = v;
+    cluster.sync();
+    unsigned long long total = 0, lower = 0;
+    for (unsigned int r = 0; r < cluster.num_blocks(); ++r) {
+        const unsigned long long x = share_of(cluster, share, r)->sum;
+        if (r < cluster.block_rank()) lower += x;
+        total += x;
+    }
+    cluster.sync();                     // everybody has read before anybody writes the next
+    if (before != nullptr) *before = lower;
+    return total;
+}
+
+// Radix descent, most significant byte first, over the keys >= `floor_key` of the whole row; this CTA reads the
+// tokens [lo, hi) of it. Every CTA of the cluster returns the same key.
 // by_count: the key of rank `target_count` (1-based) in descending order.
 // else:     the largest key K such that the weight of {keys >= K} reaches `target_mass` (in fixed point).
 // If the target is never reached the smallest eligible key is returned.
 // Every warp counts into a histogram of its own (all 65,536 logits of a row share a handful of leading bytes: one
 // histogram for the block would serialise a thousand threads on a few words), a thread per bucket adds the warps'
-// histograms, and one warp walks the 256 buckets, eight a lane.
-__device__ uint64_t radix_select(const float* __restrict__ row, int V, float max_logit, float inv_temp,
-                                 uint64_t floor_key, bool by_count, long long target_count, double target_mass,
-                                 const RadixScratch& sc) {
+// histograms, and one warp of every CTA adds the CTAs' and walks the 256 buckets, eight a lane.
+__device__ uint64_t radix_select(cg::cluster_group& cluster, const float* __restrict__ row, int lo, int hi_tok,
+                                 float max_logit, float inv_temp, uint64_t floor_key, bool by_count,
+                                 long long target_count, double target_mass, const RadixScratch& sc) {
     uint64_t prefix = 0;
     long long above_count = 0;
     unsigned long long above_mass = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned int ranks = cluster.num_blocks();
     unsigned int* my_count = sc.sub_count + (warp % kSub) * 256;
     unsigned int* my_lo = sc.sub_mass_lo + (warp % kSub) * 256;
     unsigned int* my_hi = sc.sub_mass_hi + (warp % kSub) * 256;
@@ -239,7 +279,7 @@ __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max
         }
         __syncthreads();
         const uint64_t hi_mask = pass == 7 ? 0ull : (~0ull << (shift + 8));
-        for_row_strided(row, V, [&](float l, int t) {
+        for_row_strided(row, lo, hi_tok, [&](float l, int t) {
             const uint64_t key = key_of(l, t);
             if (key < floor_key || (key & hi_mask) != prefix) return;
             const int digit = (int)((key >> shift) & 0xFF);
@@ -248,10 +288,10 @@ __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max
                 // a 64-bit sum out of 32-bit adds (the kind shared memory does by itself): the low word, one more
                 // in the high word whenever the low word wraps, and the weight's own high word (zero below 2^-8)
                 const unsigned long long f = fix_of(expf((l - max_logit) * inv_temp));
-                const unsigned int lo = (unsigned int)f, hi = (unsigned int)(f >> 32);
-                const unsigned int old = atomicAdd(&my_lo[digit], lo);
-                const unsigned int carry = old + lo < old ? 1u : 0u;
-                if (hi + carry != 0u) atomicAdd(&my_hi[digit], hi + carry);
+                const unsigned int flo = (unsigned int)f, fhi = (unsigned int)(f >> 32);
+                const unsigned int old = atomicAdd(&my_lo[digit], flo);
+                const unsigned int carry = old + flo < old ? 1u : 0u;
+                if (fhi + carry != 0u) atomicAdd(&my_hi[digit], fhi + carry);
             }
         });
         __syncthreads();
@@ -264,19 +304,39 @@ __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max
                 if (!by_count)
                     m += ((unsigned long long)sc.sub_mass_hi[w * 256 + b] << 32) + sc.sub_mass_lo[w * 256 + b];
             }
-            sc.count[b] = c;
-            sc.mass[b] = m;
+            sc.share->count[b] = c;
+            sc.share->mass[b] = m;
+        }
+        cluster.sync();
+        // a thread per bucket adds the CTAs' sums (its loads from the other CTAs' shared memory all in flight at once)
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            unsigned int c = 0;
+            unsigned long long m = 0;
+            for (unsigned int r = 0; r < ranks; ++r) {
+                const RowShare* other = share_of(cluster, sc.share, r);
+                c += other->count[b];
+                if (!by_count) m += other->mass[b];
+            }
+            sc.all_count[b] = c;
+            sc.all_mass[b] = m;
         }
         __syncthreads();
         if (warp == 0) {
             // lane L owns buckets 255 - 8 L down to 248 - 8 L: lane 0 the largest digits
             const int hi = 255 - 8 * lane;
+            long long bc[8];
+            unsigned long long bm[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bc[j] = sc.all_count[hi - j];
+                bm[j] = sc.all_mass[hi - j];
+            }
             long long c = 0;
             unsigned long long m = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                c += sc.count[hi - j];
-                m += sc.mass[hi - j];
+                c += bc[j];
+                m += bm[j];
             }
             long long c_inc = c;
             unsigned long long m_inc = m;
@@ -292,22 +352,21 @@ __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max
             c = above_count + c_inc - c;          // what lies above this lane's buckets
             m = above_mass + m_inc - m;
             int found = -1, low = -1;
-            unsigned int found_n = 0, low_n = 0;
+            long long found_n = 0, low_n = 0;
             long long found_c = 0, low_c = 0;
             unsigned long long found_m = 0, low_m = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int b = hi - j;
-                const unsigned int n = sc.count[b];
+                const long long n = bc[j];
                 if (n == 0 || found >= 0) continue;
-                low = b;                           // the lowest non-empty bucket so far, and what lies above it
+                low = hi - j;                      // the lowest non-empty bucket so far, and what lies above it
                 low_n = n;
                 low_c = c;
                 low_m = m;
                 const long long c2 = c + n;
-                const unsigned long long m2 = m + sc.mass[b];
+                const unsigned long long m2 = m + bm[j];
                 if (by_count ? (c2 >= target_count) : ((double)m2 >= target_mass)) {
-                    found = b;
+                    found = hi - j;
                     found_n = n;
                     found_c = c;
                     found_m = m;
@@ -322,14 +381,14 @@ __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max
                     *sc.key = prefix | ((uint64_t)found << shift);
                     *sc.above_count = found_c;
                     *sc.above_mass = found_m;
-                    *sc.left = found_n;
+                    *sc.left = found_n == 1 ? 1u : 2u;
                 }
             } else if (any != 0u) {               // an unreachable target lands on the lowest non-empty bucket
                 if (lane == 31 - __clz(any)) {
                     *sc.key = prefix | ((uint64_t)low << shift);
                     *sc.above_count = low_c;
                     *sc.above_mass = low_m;
-                    *sc.left = low_n;
+                    *sc.left = low_n == 1 ? 1u : 2u;
                 }
             } else if (lane == 0) {
                 *sc.key = prefix;
@@ -337,33 +396,40 @@ __device__ uint64_t radix_select(const float* __restrict__ row, int V, float max
                 *sc.above_mass = above_mass;
                 *sc.left = 0;
             }
+            if (lane == 0) sc.share->key_set = 0;
         }
-        __syncthreads();
+        cluster.sync();                           // the histograms have been read: the next pass may clear them
         prefix = *sc.key;
         above_count = *sc.above_count;
         above_mass = *sc.above_mass;
         const unsigned int left = *sc.left;
-        __syncthreads();
         if (left == 1 && pass > 0) {
             // one key has this prefix: it is the answer, and whoever holds it says so (the remaining passes would
             // each read the whole row to learn one more byte of it)
             const uint64_t got_mask = ~0ull << shift;
-            for_row_strided(row, V, [&](float l, int t) {
+            for_row_strided(row, lo, hi_tok, [&](float l, int t) {
                 const uint64_t key = key_of(l, t);
-                if (key >= floor_key && (key & got_mask) == prefix) *sc.key = key;
+                if (key >= floor_key && (key & got_mask) == prefix) {
+                    sc.share->key = key;
+                    sc.share->key_set = 1;
+                }
             });
-            __syncthreads();
-            prefix = *sc.key;
-            __syncthreads();
+            cluster.sync();
+            for (unsigned int r = 0; r < ranks; ++r) {
+                const RowShare* other = share_of(cluster, sc.share, r);
+                if (other->key_set) prefix = other->key;
+            }
+            cluster.sync();
             return prefix;
         }
+        __syncthreads();
     }
     return prefix;
 }
 
 constexpr size_t kSampleSmem = (size_t)kSub * 256 * 3 * sizeof(unsigned int);
 
-// One block per row.
+// One cluster of CTAs per row (gridDim.x = rows x cluster size).
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
@@ -371,31 +437,44 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
     extern __shared__ __align__(16) unsigned char sample_smem[];
     __shared__ ArgBest arg_scratch[32];
     __shared__ unsigned long long sum_scratch[33];
-    __shared__ unsigned int hist_count[256];
-    __shared__ unsigned long long hist_mass[256];
+    __shared__ RowShare share;
+    __shared__ unsigned int all_count[256];
+    __shared__ unsigned long long all_mass[256];
     __shared__ uint64_t shared_key;
     __shared__ long long shared_count;
     __shared__ unsigned long long shared_mass;
     __shared__ unsigned int shared_left;
-    __shared__ int result;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned int ranks = cluster.num_blocks(), rank = cluster.block_rank();
     RadixScratch sc;
     sc.sub_count = reinterpret_cast<unsigned int*>(sample_smem);
     sc.sub_mass_lo = sc.sub_count + kSub * 256;
     sc.sub_mass_hi = sc.sub_mass_lo + kSub * 256;
-    sc.count = hist_count;
-    sc.mass = hist_mass;
+    sc.share = &share;
+    sc.all_count = all_count;
+    sc.all_mass = all_mass;
     sc.key = &shared_key;
     sc.above_count = &shared_count;
     sc.above_mass = &shared_mass;
     sc.left = &shared_left;
 
-    const int rowi = blockIdx.x;
+    const int rowi = blockIdx.x / ranks;
     const float* row = logits + (int64_t)rowi * ld;
-    const ArgBest top = block_argmax(row, V, arg_scratch);
+    // this CTA's part of the vocabulary, a multiple of 4 tokens long (16-byte loads below)
+    const int part = ((V + (int)ranks - 1) / (int)ranks + 3) & ~3;
+    const int lo = min(V, (int)rank * part), hi = min(V, lo + part);
+
+    const ArgBest mine_best = block_argmax(row, lo, hi, arg_scratch);
+    if (threadIdx.x == 0) share.best = lo < hi ? mine_best : ArgBest{-INFINITY, 0x7fffffff};
+    cluster.sync();
+    ArgBest top{-INFINITY, 0x7fffffff};
+    for (unsigned int r = 0; r < ranks; ++r) top = better(top, share_of(cluster, &share, r)->best);
+    if (top.i == 0x7fffffff) top.i = 0;   // a row of NaN or -inf
+    cluster.sync();
     const float temp = temperature[rowi];
     const int k = top_k[rowi];
     if (!(temp > 0.0f) || k == 1) {   // greedy (src/engine/sampler.h:36)
-        if (threadIdx.x == 0) out[rowi] = top.i;
+        if (threadIdx.x == 0 && rank == 0) out[rowi] = top.i;
         return;
     }
     const float inv_temp = 1.0f / temp;
@@ -403,30 +482,35 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
     const float w_cut = min_p[rowi];
 
     uint64_t floor_key = 0;   // keys below it are not candidates
-    if (k > 0 && k < V) floor_key = radix_select(row, V, top.v, inv_temp, 0, true, k, 0.0, sc);
+    if (k > 0 && k < V) floor_key = radix_select(cluster, row, lo, hi, top.v, inv_temp, 0, true, k, 0.0, sc);
     if (p_cut < 1.0f) {
         unsigned long long mass = 0;   // `total`: the weight of the top-k candidates
-        for_row_strided(row, V, [&](float l, int t) {
+        for_row_strided(row, lo, hi, [&](float l, int t) {
             if (key_of(l, t) >= floor_key) mass += fix_of(expf((l - top.v) * inv_temp));
         });
         mass = block_sum_u64(mass, sum_scratch);
-        const uint64_t p_key = radix_select(row, V, top.v, inv_temp, floor_key, false, 0, (double)p_cut * (double)mass, sc);
+        mass = cluster_sum_u64(cluster, &share, mass, nullptr);
+        const uint64_t p_key = radix_select(cluster, row, lo, hi, top.v, inv_temp, floor_key, false, 0,
+                                            (double)p_cut * (double)mass, sc);
         floor_key = p_key > floor_key ? p_key : floor_key;
     }
 
-    // Kept: key >= floor_key and weight >= min_p (the likeliest token always stays).
-    const int per = (V + blockDim.x - 1) / blockDim.x;
-    const int begin = min(V, (int)threadIdx.x * per), end = min(V, begin + per);
-    const bool vec = per % 4 == 0 && V % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    // Kept: key >= floor_key and weight >= min_p (the likeliest token always stays). The draw walks the kept
+    // tokens in vocabulary order: CTA after CTA, thread after thread, each thread a run of neighbouring tokens.
+    const int per = ((hi - lo + (int)blockDim.x - 1) / (int)blockDim.x + 3) & ~3;
+    const int begin = min(hi, lo + (int)threadIdx.x * per), end = min(hi, begin + per);
+    const bool vec = V % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
     unsigned long long mine = 0;
     for_chunk(row, begin, end, vec, [&](float l, int t) {
         const float w = expf((l - top.v) * inv_temp);
         if (key_of(l, t) >= floor_key && (w >= w_cut || t == top.i)) mine += fix_of(w);
         return true;
     });
-    if (threadIdx.x == 0) result = -1;
-    unsigned long long total = 0;
-    const unsigned long long before = block_exclusive_scan_u64(mine, sum_scratch, &total);
+    if (threadIdx.x == 0 && rank == 0) out[rowi] = top.i;     // stands only if every kept weight rounded to zero
+    unsigned long long cta_total = 0, lower = 0;
+    const unsigned long long before_in_cta = block_exclusive_scan_u64(mine, sum_scratch, &cta_total);
+    const unsigned long long total = cluster_sum_u64(cluster, &share, cta_total, &lower);   // also orders the write above
+    const unsigned long long before = lower + before_in_cta;
     unsigned long long target = __double2ull_rz(uniform_from(seeds[rowi], counters[rowi]) * (double)total);
     if (total > 0 && target >= total) target = total - 1;
     if (mine > 0 && target >= before && target < before + mine) {
@@ -444,10 +528,8 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
             left -= f;
             return true;
         });
-        result = pick >= 0 ? pick : last;
+        out[rowi] = pick >= 0 ? pick : last;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) out[rowi] = result >= 0 ? result : top.i;   // every kept weight rounded to zero
 }
 
 // logits[r, t] for seen tokens: divided (positive) or multiplied (negative) by the repetition
@@ -508,11 +590,35 @@ XS_API int xs_sample(const float* logits, int64_t ld, int n, int V, const float*
     if (n == 0) return 0;
     XS_REQUIRE(n > 0 && V > 0 && V <= kMaxVocab && ld >= V, "sample: %d rows of %d (at most %d)", n, V, kMaxVocab);
     static bool opted = false;
+    static int sms = 0;
     if (!opted) {
         cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleSmem);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         opted = true;
     }
-    sample_kernel<<<n, kThreads, kSampleSmem, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, seeds, counters, out);
+    // CTAs a row: 8, or fewer (4, 2) so that all rows' CTAs run at one time (a CTA of 1,024 threads has an SM to
+    // itself; measured on B200 at 64 rows of 65,536 with top-p: 2 a row 96 us, 4 a row 108 us, 1 a row 111 us); one
+    // when the rows alone fill the device or the vocabulary is small
+    int ranks = 1;
+    if (V >= 8192)
+        for (ranks = 8; ranks > 1 && (int64_t)n * ranks > (int64_t)sms; ranks >>= 1) {}
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n * ranks));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSampleSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, temperature, top_k, top_p, min_p, seeds,
+                                             counters, out);
+    XS_REQUIRE(e == cudaSuccess, "sample: launch failed: %s", cudaGetErrorString(e));
     XS_LAUNCH_CHECK("sample");
     return 0;
 }
