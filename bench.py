@@ -208,6 +208,34 @@ def time_prefill(model, V: int, warmup: int, runs: int):
     return statistics.median(times)
 
 
+def time_sampling(rows: int, V: int, runs: int):
+    """Device time of the sampling kernel alone on `rows` rows of V random logits, for the usual cuts."""
+    import torch
+    from xpu_serve_b200.ops import lib as ops
+    dev = "cuda:0"
+    logits = torch.randn(rows, V, device=dev) * 2.0
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    seeds = torch.arange(rows, dtype=torch.int64, device=dev) + 5
+    counters = torch.zeros(rows, dtype=torch.int64, device=dev)
+    full = lambda v, dt=torch.float32: torch.full((rows,), v, dtype=dt, device=dev)      # noqa: E731
+    cuts = {"temperature": (0.8, 0, 1.0, 0.0), "top_k": (1.0, 50, 1.0, 0.0), "top_p": (0.8, 0, 0.9, 0.0),
+            "top_k_top_p_min_p": (0.9, 200, 0.8, 0.01)}
+    result = {"only": "sample", "rows": rows, "vocab": V, "unit": "us"}
+    for name, (t, k, p, mp) in cuts.items():
+        a = (full(t), full(k, torch.int32), full(p), full(mp))
+        for _ in range(3):
+            ops.sample(logits, *a, seeds, counters, out)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(runs):
+            ops.sample(logits, *a, seeds, counters, out)
+        end.record()
+        torch.cuda.synchronize()
+        result[name] = round(start.elapsed_time(end) / runs * 1e3, 1)
+    return result
+
+
 def time_e2e(folder: str, batch: int, steps: int, warmup: int, V: int):
     """The same decode rate through Engine.generate: host token ids in, host token ids out, every
     step with its host-to-device copy of the step's description and its device-to-host copy of the
@@ -305,7 +333,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run only the first N layers (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
-    ap.add_argument("--only", default=None, choices=["decode", "prefill"],
+    ap.add_argument("--only", default=None, choices=["decode", "prefill", "sample"],
                     help="time one part only and print a short line (for profiler captures)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="instead of the default run: a batch of unequal prompts at another shape of the family")
@@ -330,6 +358,10 @@ def main() -> int:
     from xpu_serve_b200 import load_model
     from xpu_serve_b200.config import Lfm3Config
     from xpu_serve_b200.weights import write_random_model
+
+    if args.only == "sample":
+        print(json.dumps(time_sampling(args.batch, SHAPE_1_2B["vocab_size"], args.steps)))
+        return 0
 
     cfg = dict(SHAPE_1_2B)
     full_layers = cfg["num_hidden_layers"]
