@@ -30,12 +30,17 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Tuple, torch.Tensor] = {}      # (name, dtype, shape) -> the view handed out last time
         self.frozen = False
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(int(s) for s in shape)
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view
         n = 1
         for s in shape:
-            n *= int(s)
+            n *= s
         key = (name, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
@@ -43,7 +48,12 @@ class Workspace:
                 raise RuntimeError(f"scratch buffer '{name}' would have to grow after it was frozen")
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:n].view(*shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:     # views of the old buffer
+                del self._views[k]
+        view = buf[:n].view(*shape)
+        if len(self._views) < 4096:
+            self._views[(name, dtype, shape)] = view
+        return view
 
 
 class Runtime:
