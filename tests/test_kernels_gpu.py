@@ -168,8 +168,10 @@ def test_gemm_generic_rows_do_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
-# the two widest: more row tiles than CTAs fit on the device at once; (2048, 8192), (4096, 1024): no edge anywhere
-@pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (1000, 200), (2048, 8192), (333, 2056), (10007, 200), (20000, 1096), (4096, 1024)])
+# the two widest: more row tiles than CTAs fit on the device at once; (2048, 8192), (4096, 1024): no edge anywhere;
+# (2048, 8192), (3072, 2048), (512, 4096): few row tiles and K a multiple of 2,048, the variant of sixteen loads a round
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (1000, 200), (2048, 8192), (333, 2056), (10007, 200), (20000, 1096), (4096, 1024),
+                                 (3072, 2048), (512, 4096)])
 def test_gemm_small_m(M, N, K):
     lib = ops()
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -192,7 +194,8 @@ def test_gemm_small_m(M, N, K):
     assert torch.equal(one, out[M - 1:M]), "a row's result depends on the batch"
 
 
-@pytest.mark.parametrize("M,N,K,ksplit", [(8, 2048, 8192, 4), (3, 100, 4104, 3), (16, 256, 2048, 8), (1, 48, 512, 2), (5, 2048, 2048, 7)])
+@pytest.mark.parametrize("M,N,K,ksplit", [(8, 2048, 8192, 4), (3, 100, 4104, 3), (16, 256, 2048, 8), (1, 48, 512, 2), (5, 2048, 2048, 7),
+                                          (8, 2048, 8192, 2), (6, 1024, 6144, 3)])
 def test_gemm_small_m_k_slices(M, N, K, ksplit):
     """K cut into slices over several CTAs: the last CTA of a tile to arrive adds the slices in slice order, so
     the bits do not depend on which one that was; a second and third call find the counters reset."""
@@ -232,7 +235,8 @@ def test_gemm_small_m_with_fused_activation(M, F):
 
 
 @pytest.mark.parametrize("M,H,N2,K1,ks1,ks2", [(8, 2048, 512, 1024, 2, 1), (3, 200, 96, 64, 1, 1), (13, 2304, 256, 512, 4, 2),
-                                                (1, 64, 48, 4096, 4, 1), (8, 2048, 16384, 1024, 2, 1), (5, 96, 9616, 64, 1, 1)])
+                                                (1, 64, 48, 4096, 4, 1), (8, 2048, 16384, 1024, 2, 1), (5, 96, 9616, 64, 1, 1),
+                                                (8, 2048, 512, 4096, 2, 1)])
 def test_gemm_small_m_carries_the_norm(M, H, N2, K1, ks1, ks2):
     """Two products with an RMSNorm between them and no norm kernel: the first adds to the float32 stream and
     leaves stream * weight and per-tile sums of squares, the second scales its rows by 1 / rms. Widths that

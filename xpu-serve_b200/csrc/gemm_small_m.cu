@@ -32,10 +32,10 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int ROWS = 16;      // weight rows per CTA
-constexpr int UNROLL = 4;     // k blocks whose loads a warp issues together
+constexpr int UNROLL_DEFAULT = 4;     // k blocks whose loads a warp issues together
 constexpr bool kBlocked = true;   // measured on B200: 3 % faster than interleaved on the wide shapes
 constexpr int kSsqStaged = 128;  // producer tiles whose sums of squares are staged in shared memory
-constexpr int K_PER_CTA = WARPS * UNROLL * 32;   // a K slice this long is one round of loads per warp
+constexpr int K_PER_CTA = WARPS * UNROLL_DEFAULT * 32;   // a K slice this long is one round of loads per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                                unsigned b0, unsigned b1) {
@@ -116,8 +116,13 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
 
 // EXACT: N is a multiple of 16 and every K slice a multiple of 1,024 (8 warps x 4 blocks x 32), so no row is
 // clamped and no load is predicated: a third fewer instructions in the loop that feeds the memory system.
-template <int NT, typename TO, bool EXACT>
-__global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const SmallMParams p) {
+// UNROLL 8 (EXACT only, K slices that are multiples of 2,048): sixteen loads a lane in flight instead of eight, so a
+// slice of 2,048 is one round, all of it requested before the wait for the previous kernel; twice the registers
+// for weights, two CTAs an SM instead of four. For grids of at most one such wave (the narrow outputs, which are
+// bound by latency, not bandwidth): measured on the whole decode step, 1.2B shape, batch 8: 0.811 -> 0.773 ms with
+// it on the attention and convolution output projections and the q/k/v product; on grids of more CTAs it loses.
+template <int NT, typename TO, bool EXACT, int UNROLL = UNROLL_DEFAULT>
+__global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? 4 : 2) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
     __shared__ __align__(16) float ssq_in[kSsqStaged][16];
@@ -152,29 +157,37 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
     // that the weights are already on their way while the previous kernel of the step finishes.
     pdl_launch_dependents();
     uint4 wa[UNROLL], wb[UNROLL];
-    // k blocks of a round: warp w takes blocks w*ws + u*us. blocked (ws = UNROLL, us = 1): a warp's four loads
+    // k blocks of a round: warp w takes blocks w*ws + u*us. blocked (ws = 4, us = 1): a warp's four loads
     // cover 256 consecutive bytes of a row; interleaved (ws = 1, us = WARPS): the CTA's warps cover them together.
-    constexpr int ws = kBlocked ? UNROLL : 1, us = kBlocked ? 1 : WARPS;
+    // Sixteen loads a round are two rounds of eight in one (slots 4..7 are the warp's blocks of the next 32 of the
+    // CTA), so that a warp adds up the same blocks in the same order in both variants: a row's bits do not depend on
+    // which variant its batch or its shape chose.
+    constexpr int ws = kBlocked ? UNROLL_DEFAULT : 1, us = kBlocked ? 1 : WARPS;
+    auto slot = [](int u) { return (u / UNROLL_DEFAULT) * (WARPS * UNROLL_DEFAULT) + (u % UNROLL_DEFAULT) * us; };
     int kb = kb_begin + warp * ws;
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-        const int k0 = (kb + u * us) * 32;
+        const int k0 = (kb + slot(u)) * 32;
         // K is a multiple of 8: a lane's 8 elements are all inside or all outside
-        const bool in = EXACT || (kb + u * us < kb_end && k0 + q * 8 < p.K);
+        const bool in = EXACT || (kb + slot(u) < kb_end && k0 + q * 8 < p.K);
         wa[u] = in ? ld_stream(wa_p + k0) : zero;
         wb[u] = in ? ld_stream(wb_p + k0) : zero;
     }
     if (kBlocked) {
         // The rounds after the first are asked into L2 now (a hint, no registers held): when their loads are
         // issued after the first round's multiplies they find the lines on the chip. A warp's round is 256
-        // consecutive bytes of each of its 16 rows: lane -> (row, which 128-byte line).
+        // consecutive bytes (sixteen loads: two such pieces) of each of its 16 rows: lane -> (row, which 128-byte line).
         const int prow = min(n0 + (lane & 15), p.N - 1);
         const __nv_bfloat16* pbase = p.w + (int64_t)prow * p.ldw + (lane >> 4) * 64;
 #pragma unroll 1
         for (int r = 1; r <= 3; ++r) {
             const int pkb = kb + r * WARPS * UNROLL;
-            if (pkb < kb_end && pkb * 32 + (lane >> 4) * 64 < p.K)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(pbase + (int64_t)pkb * 32));
+#pragma unroll
+            for (int h = 0; h < UNROLL / UNROLL_DEFAULT; ++h) {
+                const int hkb = pkb + h * WARPS * UNROLL_DEFAULT;
+                if (hkb < kb_end && hkb * 32 + (lane >> 4) * 64 < p.K)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(pbase + (int64_t)hkb * 32));
+            }
         }
         // More row tiles than CTAs that fit on the chip at once: also ask for the first round of the tile
         // that will take this CTA's place (CTAs start in index order, `wave` of them at a time).
@@ -220,8 +233,8 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
         uint4 xv[UNROLL][NT];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int k0 = (kb + u * us) * 32;
-            const bool in = EXACT || (kb + u * us < kb_end && k0 + q * 8 < p.K);
+            const int k0 = (kb + slot(u)) * 32;
+            const bool in = EXACT || (kb + slot(u) < kb_end && k0 + q * 8 < p.K);
 #pragma unroll
             for (int t = 0; t < NT; ++t)
                 xv[u][t] = (in && x_ok[t]) ? *reinterpret_cast<const uint4*>(x_p[t] + k0) : zero;
@@ -239,15 +252,15 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemm_small_m_kernel(const Small
             if (nkb - warp * ws < kb_end) {       // the same for the whole CTA
 #pragma unroll
                 for (int u = 0; u < UNROLL; ++u) {
-                    wa[u] = ld_stream(wa_p + (nkb + u * us) * 32);
-                    wb[u] = ld_stream(wb_p + (nkb + u * us) * 32);
+                    wa[u] = ld_stream(wa_p + (nkb + slot(u)) * 32);
+                    wb[u] = ld_stream(wb_p + (nkb + slot(u)) * 32);
                 }
             }
         } else {
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int k0 = (nkb + u * us) * 32;
-                const bool in = nkb + u * us < kb_end && k0 + q * 8 < p.K;
+                const int k0 = (nkb + slot(u)) * 32;
+                const bool in = nkb + slot(u) < kb_end && k0 + q * 8 < p.K;
                 wa[u] = in ? ld_stream(wa_p + k0) : zero;
                 wb[u] = in ? ld_stream(wb_p + k0) : zero;
             }
@@ -318,6 +331,11 @@ XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
     return M >= 1 && M <= 16 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
 
+int g_small_m_ksplit_max = 4;
+XS_API void xs_gemm_small_m_set_ksplit_max(int n) { g_small_m_ksplit_max = n; }
+int g_small_m_one_round = 1;      // 0: off; 1: on, for grids of at most two CTAs an SM; n > 1: for grids of at most n CTAs
+XS_API void xs_gemm_small_m_set_one_round(int on) { g_small_m_one_round = on; }
+
 // How many K slices the kernel would like for this shape on a device with `sms` SMs, and the
 // scratch (bytes) that needs: partial sums, then one counter per row tile. 0 bytes when 1 slice.
 XS_API int xs_gemm_small_m_ksplit(int M, int N, int K, int sms) {
@@ -325,12 +343,18 @@ XS_API int xs_gemm_small_m_ksplit(int M, int N, int K, int sms) {
     // 11.4 in four; N 2048, K 2048 takes 7.4, 7.0, 6.1; N 16384, K 2048 gets slower with every slice.
     // In the whole decode step (1.2B shape, batch 8): slicing K 2048 products makes the step slower, the
     // K 8192 one is best in four slices.
-    (void)M;
+    // With sixteen loads a round (the variant for at most one wave of two CTAs an SM, see the kernel): the same
+    // product in two slices of two rounds each, 256 CTAs, makes the step 1.4 % faster than four slices of 512.
     const int tiles = ceil_div_i(N, ROWS);
     if (tiles >= 2 * sms) return 1;
     int ks = K / 2048;                // at least 2048 of K a slice
-    if (ks > 4) ks = 4;
-    return ks < 1 ? 1 : ks;
+    if (ks > g_small_m_ksplit_max) ks = g_small_m_ksplit_max;
+    if (ks < 1) ks = 1;
+    if (M <= 8 && N % ROWS == 0 && g_small_m_one_round == 1) {
+        for (int k2 = ks; k2 >= 1; --k2)
+            if (K % k2 == 0 && (K / k2) % (2 * K_PER_CTA) == 0 && (int64_t)tiles * k2 <= 2 * (int64_t)sms) return k2;
+    }
+    return ks;
 }
 
 // Scratch layout: partial sums from the front; the last kCounterBytes hold one counter per row tile.
@@ -404,8 +428,12 @@ XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bia
     const dim3 grid(tiles, ksplit);
     // (up to 8 rows: with 16 the unpredicated loop spills registers)
     const bool exact = M <= 8 && N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0;
+    // sixteen loads a round: slices that are multiples of 2,048 and at most one wave of two CTAs an SM
+    const bool one_round = exact && g_small_m_one_round && (K / ksplit) % (2 * K_PER_CTA) == 0 &&
+                           (int64_t)tiles * ksplit <= (g_small_m_one_round > 1 ? g_small_m_one_round : (int64_t)(g_small_m_wave / 4) * 2);
 #define XS_GO(NT, TO)                                                                                       \
-    ((exact && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true>, grid, dim3(WARPS * 32), 0, stream, p)  \
+    ((one_round && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, p) \
+     : (exact && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true>, grid, dim3(WARPS * 32), 0, stream, p)  \
                         : xs_launch(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, p))
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);

@@ -93,6 +93,8 @@ def load(verbose: bool = True):
         # tuning switches, read once (defaults are what measured best on B200)
         if "XS_ATTN_DECODE_STAGES" in os.environ:
             lib.xs_attention_mma_set_decode_stages(int(os.environ["XS_ATTN_DECODE_STAGES"]))
+        if os.environ.get("XS_NO_ONE_ROUND", "0") == "1":
+            lib.xs_gemm_small_m_set_one_round(0)
         if "XS_ATTN_PREFETCH_BLOCKS" in os.environ:
             lib.xs_attention_mma_set_prefetch_blocks(int(os.environ["XS_ATTN_PREFETCH_BLOCKS"]))
         if os.environ.get("XS_NO_PDL", "0") == "1":
