@@ -193,41 +193,54 @@ __global__ void __launch_bounds__(256) short_conv_bf16x8_run_kernel(
 }
 
 // Every sequence brings one token: the thread that owns (sequence, 8 channels) reads the state's
-// K-1 rows, computes the output and writes the shifted state, in one kernel.
+// K-1 rows, computes the output and writes the shifted state, in one kernel. The taps and the slot numbers are
+// written by no kernel of a step (weights; the step's description, copied before the step's first kernel), so
+// they are read before waiting for the kernel before this one, and the state's address is ready when the wait
+// ends. The state itself is read after the wait: the kernel that wrote it last is this layer's own in the step
+// before, and nothing but the chain of waits says that it is done.
+template <int KT>
 __global__ void short_conv_decode_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, int64_t ld,
                                                 const float* __restrict__ w_t, const float* __restrict__ bias,
                                                 __nv_bfloat16* __restrict__ state, const int32_t* __restrict__ slots,
-                                                __nv_bfloat16* __restrict__ out, int n_seqs, int H, int K) {
+                                                __nv_bfloat16* __restrict__ out, int n_seqs, int H) {
     pdl_launch_dependents();
-    pdl_wait();
     const int H8 = H >> 3;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (int64_t)n_seqs * H8) return;
-    const int seq = (int)(idx / H8), c8 = (int)(idx % H8) * 8;
-    __nv_bfloat16* st = state + (int64_t)slots[seq] * (K - 1) * H;
+    const bool live = idx < (int64_t)n_seqs * H8;
+    const int seq = live ? (int)(idx / H8) : 0, c8 = live ? (int)(idx % H8) * 8 : 0;
+    __nv_bfloat16* st = state + (int64_t)slots[seq] * (KT - 1) * H;
+    float4 w0[KT], w1[KT];
+#pragma unroll
+    for (int j = 0; j < KT; ++j) {
+        w0[j] = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8);
+        w1[j] = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8 + 4);
+    }
     float acc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = bias != nullptr ? bias[c8 + k] : 0.0f;
+    pdl_wait();
+    if (!live) return;
+    uint4 old[KT - 1];
+#pragma unroll
+    for (int j = 0; j < KT - 1; ++j) old[j] = *reinterpret_cast<const uint4*>(st + (int64_t)j * H + c8);
     float g[8];
     gated8(bcx + (int64_t)seq * ld, c8, H, g);
-    for (int j = 0; j < K; ++j) {
+#pragma unroll
+    for (int j = 0; j < KT; ++j) {
         float v[8];
-        if (j < K - 1) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(st + (int64_t)j * H + c8);
-            unpack8(raw, v);
-            if (j > 0) *reinterpret_cast<uint4*>(st + (int64_t)(j - 1) * H + c8) = raw;   // row j moves to j - 1
+        if (j < KT - 1) {
+            unpack8(old[j], v);
+            if (j > 0) *reinterpret_cast<uint4*>(st + (int64_t)(j - 1) * H + c8) = old[j];   // row j moves to j - 1
         } else {
 #pragma unroll
             for (int k = 0; k < 8; ++k) v[k] = g[k];
         }
-        const float4 w0 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8);
-        const float4 w1 = *reinterpret_cast<const float4*>(w_t + (int64_t)j * H + c8 + 4);
-        acc[0] = fmaf(w0.x, v[0], acc[0]); acc[1] = fmaf(w0.y, v[1], acc[1]);
-        acc[2] = fmaf(w0.z, v[2], acc[2]); acc[3] = fmaf(w0.w, v[3], acc[3]);
-        acc[4] = fmaf(w1.x, v[4], acc[4]); acc[5] = fmaf(w1.y, v[5], acc[5]);
-        acc[6] = fmaf(w1.z, v[6], acc[6]); acc[7] = fmaf(w1.w, v[7], acc[7]);
+        acc[0] = fmaf(w0[j].x, v[0], acc[0]); acc[1] = fmaf(w0[j].y, v[1], acc[1]);
+        acc[2] = fmaf(w0[j].z, v[2], acc[2]); acc[3] = fmaf(w0[j].w, v[3], acc[3]);
+        acc[4] = fmaf(w1[j].x, v[4], acc[4]); acc[5] = fmaf(w1[j].y, v[5], acc[5]);
+        acc[6] = fmaf(w1[j].z, v[6], acc[6]); acc[7] = fmaf(w1[j].w, v[7], acc[7]);
     }
-    *reinterpret_cast<uint4*>(st + (int64_t)(K - 2) * H + c8) = pack8(g);
+    *reinterpret_cast<uint4*>(st + (int64_t)(KT - 2) * H + c8) = pack8(g);
     float c[8];
     unpack8(*reinterpret_cast<const uint4*>(bcx + (int64_t)seq * ld + H + c8), c);
 #pragma unroll
@@ -246,9 +259,18 @@ XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const fl
     XS_REQUIRE(!all_single || T == n_seqs, "short_conv: %d tokens for %d sequences of one token each", T, n_seqs);
     const bool vec = dtype == XS_BF16 && H % 8 == 0 && ld % 8 == 0 && (uintptr_t)bcx % 16 == 0 &&
                      (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w_t % 16 == 0;
-    if (vec && all_single) {
-        xs_launch(short_conv_decode_bf16x8_kernel, dim3(ceil_div_i((int64_t)n_seqs * (H / 8), 128)), dim3(128), 0, stream,
-                  (const __nv_bfloat16*)bcx, ld, w_t, bias, (__nv_bfloat16*)state, slots, (__nv_bfloat16*)out, n_seqs, H, K);
+    if (vec && all_single && K >= 2 && K <= 5) {
+        const dim3 grid(ceil_div_i((int64_t)n_seqs * (H / 8), 128));
+#define XS_CONV_DECODE(KT)                                                                                           \
+    xs_launch(short_conv_decode_bf16x8_kernel<KT>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)bcx, ld, w_t, bias, \
+              (__nv_bfloat16*)state, slots, (__nv_bfloat16*)out, n_seqs, H)
+        switch (K) {
+            case 2: XS_CONV_DECODE(2); break;
+            case 3: XS_CONV_DECODE(3); break;
+            case 4: XS_CONV_DECODE(4); break;
+            default: XS_CONV_DECODE(5); break;
+        }
+#undef XS_CONV_DECODE
         XS_LAUNCH_CHECK("short_conv_decode");
         return 0;
     }
