@@ -153,9 +153,22 @@ def synthetic_prompt(V: int, n: int, salt: int):
 
 def time_decode(model, batch: int, steps: int, warmup: int, V: int):
     """Device time of `steps` decode steps (model step + argmax) of `batch` sequences after
-    2,048-token prompts. Returns (ms per step, kernel launches per step)."""
+    2,048-token prompts. Returns (ms per step, kernel launches per step). More steps than the context
+    has room for after the prompt are timed in several runs, each from fresh prompts after its own warm-up."""
     import torch
     from xpu_serve_b200.ops import lib as ops
+    room = CONTEXT - PROMPT - warmup - 2
+    total_ms, total_launches, left = 0.0, 0, steps
+    while left > 0:
+        part = min(left, room)
+        ms, launches = _time_decode_run(model, batch, part, warmup, V, torch, ops)
+        total_ms += ms * part
+        total_launches += launches * part
+        left -= part
+    return total_ms / steps, total_launches / steps
+
+
+def _time_decode_run(model, batch, steps, warmup, V, torch, ops):
     cache = model.new_cache(batch * CONTEXT, max_slots=batch, max_seq_tokens=CONTEXT)
     slots = cache.open(batch)
     chunk = max(1, 8192 // PROMPT)
@@ -401,11 +414,11 @@ def main() -> int:
         del model
         torch.cuda.empty_cache()
         copy_here = copy_bandwidth_here()
-        e2e_value, h2d, d2h = time_e2e(folder, args.batch, min(args.steps, 32), args.warmup, V)
+        e2e_value, h2d, d2h = time_e2e(folder, args.batch, min(args.steps, CONTEXT - PROMPT - args.warmup - 2), args.warmup, V)
 
     value = args.batch * 1000.0 / ms
     # the cache grows by one position a step: the timed steps read PROMPT + warmup + steps / 2 positions on average
-    kv_positions = PROMPT + args.warmup + args.steps // 2
+    kv_positions = PROMPT + args.warmup + min(args.steps, CONTEXT - PROMPT - args.warmup - 2) // 2
     step_bytes = nums["weight_bytes"] + args.batch * (kv_positions * nums["kv_bytes_per_token"] + nums["state_bytes"])
     achieved = step_bytes / (ms * 1e-3) / 1e9
     line = {

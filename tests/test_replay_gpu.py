@@ -204,3 +204,31 @@ def test_layers_of_the_1_2b_shape(tmp_path, dtype):
     gap, where, cos = tu.worst_gap(got, {k: ref[k] for k in got})
     bound = 1e-5 if dtype == "float32" else 4.0 * (10.0 * 3) ** 0.5 * U_BF16
     assert gap <= bound and cos >= COS[dtype], f"gap {gap:.3e} at {where}, cosine {cos}"
+
+
+def test_a_new_cache_gets_graphs_of_its_own(folders):
+    """Decode graphs hold the addresses of the cache they were captured on. A cache is dropped and another of the
+    same sizes made (Python may give it the first one's id()): its steps must not replay the first one's graphs.
+    The model keeps graphs per cache object, weakly, so the first cache's graphs are gone with it."""
+    import gc
+    from xpu_serve_b200.engine.model import load_model
+    model = load_model(folders[("A", "bfloat16")], dtype="bfloat16")
+    prompts = [tiny.prompt("A", n, salt=70 + i) for i, n in enumerate((9, 20, 5))]
+
+    def run():
+        cache = model.new_cache(512, max_slots=4, max_seq_tokens=128)
+        slots = cache.open(len(prompts))
+        logits = [model.step(cache, slots, prompts).clone()]
+        toks = [[3], [4], [5]]
+        for _ in range(6):
+            logits.append(model.step(cache, slots, toks).clone())
+        assert len(model._graphs) == 1 and cache in model._graphs
+        cache.close(slots)
+        return logits
+
+    first = run()
+    gc.collect()
+    assert len(model._graphs) == 0, "the dropped cache's graphs are still held"
+    second = run()
+    for a, b in zip(first, second):
+        assert torch.equal(a, b)

@@ -12,6 +12,7 @@ src/models/lfm3/lfm3_model.cpp:34-44); the layer order and formulas are the same
 from __future__ import annotations
 
 import os
+import weakref
 from contextlib import contextmanager
 from typing import Dict, List, Optional, Sequence
 
@@ -71,7 +72,9 @@ class Model:
         self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
         self.last_greedy: Optional[torch.Tensor] = None
         self._last_graph: Optional[_DecodeGraph] = None
-        self._graphs: Dict[tuple, _DecodeGraph] = {}
+        # decode graphs per cache (a graph holds the addresses of the cache's storage) and number of rows; weak keys:
+        # a cache that is gone takes its graphs with it, and a new cache never finds another's, whatever its id()
+        self._graphs: "weakref.WeakKeyDictionary[Cache, Dict[int, _DecodeGraph]]" = weakref.WeakKeyDictionary()
         self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
 
     # ----------------------------------------------------------------- cache
@@ -159,10 +162,12 @@ class Model:
     def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
         n = len(slots)
         rows = _bucket(n)
-        key = (id(cache), rows)
-        g = self._graphs.get(key)
+        per_cache = self._graphs.get(cache)
+        if per_cache is None:
+            per_cache = self._graphs[cache] = {}
+        g = per_cache.get(rows)
         if g is None:
-            g = self._graphs[key] = self._capture(cache, rows)
+            g = per_cache[rows] = self._capture(cache, rows)
             cache._graph_owner = self        # graphs die with the model; the cache only marks its use
         tokens = [t[0] for t in token_lists]
         batch_key = (tuple(slots), cache.tables_version())
