@@ -18,6 +18,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import itertools
+
 import numpy as np
 import torch
 
@@ -112,6 +114,9 @@ class CallView:
     owner: bool                # False when this call reads another call's cache
 
 
+_SERIALS = itertools.count(1)
+
+
 class Cache:
     """needs[i] is the need of call i of the running order (None: nothing kept), and
     shares[i] the call whose cache call i reads (None: its own)."""
@@ -121,6 +126,7 @@ class Cache:
                  max_seq_tokens: Optional[int] = None, dtype: torch.dtype = torch.bfloat16, device="cuda"):
         if max_tokens <= 0:
             raise ValueError("max_tokens must be positive")
+        self.serial = next(_SERIALS)       # unlike id(), never given to another cache
         self.page_size = page_size
         self.max_tokens = _ceil_div(max_tokens, page_size) * page_size
         n_pages = self.max_tokens // page_size

@@ -11,6 +11,7 @@ src/models/lfm3/lfm3_model.cpp:34-44); the layer order and formulas are the same
 """
 from __future__ import annotations
 
+import gc
 import os
 import weakref
 from contextlib import contextmanager
@@ -72,9 +73,13 @@ class Model:
         self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
         self.last_greedy: Optional[torch.Tensor] = None
         self._last_graph: Optional[_DecodeGraph] = None
-        # decode graphs per cache (a graph holds the addresses of the cache's storage) and number of rows; weak keys:
-        # a cache that is gone takes its graphs with it, and a new cache never finds another's, whatever its id()
-        self._graphs: "weakref.WeakKeyDictionary[Cache, Dict[int, _DecodeGraph]]" = weakref.WeakKeyDictionary()
+        # Decode graphs per cache (a graph holds the addresses of the cache's storage; by the cache's serial number,
+        # which unlike its id() no later cache gets) and number of rows. When a cache is gone its graphs are set
+        # aside and destroyed at the next decode step: the garbage collector may notice the cache in the middle
+        # of a graph capture, where destroying a graph is not allowed.
+        self._graphs: Dict[int, Dict[int, _DecodeGraph]] = {}
+        self._cache_refs: Dict[int, weakref.ref] = {}
+        self._retired: List[Dict[int, _DecodeGraph]] = []
         self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
 
     # ----------------------------------------------------------------- cache
@@ -138,6 +143,24 @@ class Model:
         finally:
             self.rt.ws = old
 
+    def _graphs_of(self, cache: Cache) -> Dict[int, _DecodeGraph]:
+        self._retired.clear()            # no capture is under way here
+        per_cache = self._graphs.get(cache.serial)
+        if per_cache is None:
+            per_cache = self._graphs[cache.serial] = {}
+            serial, me = cache.serial, weakref.ref(self)
+
+            def gone(_ref):
+                model = me()
+                if model is not None:
+                    model._cache_refs.pop(serial, None)
+                    dead = model._graphs.pop(serial, None)
+                    if dead:
+                        model._retired.append(dead)
+
+            self._cache_refs[serial] = weakref.ref(cache, gone)
+        return per_cache
+
     def _capture(self, cache: Cache, rows: int) -> _DecodeGraph:
         """Captures the decode step for `rows` sequences. Warm-up and capture run on padding rows only
         (the cache's spare slot and page), so no sequence's state is touched before the first replay."""
@@ -152,9 +175,15 @@ class Model:
             torch.cuda.synchronize(rt.device)
             before = ops.launches
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.forward(ctx, cache)
-                ops.argmax(logits, greedy)               # greedy decoding needs no launch after the graph
+            collecting = gc.isenabled()
+            gc.disable()          # a collection inside the capture could destroy another model's graphs there
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.forward(ctx, cache)
+                    ops.argmax(logits, greedy)               # greedy decoding needs no launch after the graph
+            finally:
+                if collecting:
+                    gc.enable()
             kernels = ops.launches - before
         ws.frozen = True
         return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels)
@@ -162,9 +191,7 @@ class Model:
     def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
         n = len(slots)
         rows = _bucket(n)
-        per_cache = self._graphs.get(cache)
-        if per_cache is None:
-            per_cache = self._graphs[cache] = {}
+        per_cache = self._graphs_of(cache)
         g = per_cache.get(rows)
         if g is None:
             g = per_cache[rows] = self._capture(cache, rows)
