@@ -77,9 +77,10 @@ class DeviceStepper:
     the next token by the sampling kernels; only token ids cross to the host.
 
     Running ahead. A generation loop feeds every live sequence the token the last step chose for it, so
-    while greedy sequences decode, the step after the one being asked for is started at once, fed on the
-    device from the graph's own choice; by the time the loop has looked at a step's tokens the next step is
-    already running. A sequence that the loop ends (a stop token, its length, a callback) has then run one
+    while sequences decode, the step after the one being asked for is started at once, fed on the device
+    from the graph's own argmax (greedy sequences) or from what the sampling kernels chose (seeded draws,
+    penalties; the draw for the step that runs ahead uses the sequence's next counter); by the time the loop
+    has looked at a step's tokens the next step is already running. A sequence that the loop ends (a stop token, its length, a callback) has then run one
     step too many: a row of work that nobody reads, in a slot that the loop closes. The promise the loop
     makes in return (`generate` keeps it): after decoding has begun, a sequence's next call brings the token
     the last call returned for it. A call that breaks it is refused."""
