@@ -104,7 +104,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     constexpr int G = D / 8;        // threads of a head
     constexpr int half = D / 2;
     pdl_launch_dependents();
-    pdl_wait();
+    // Positions, page numbers, norm weights and the rotation table are not written by the kernel before this one
+    // (the q/k/v product): they are read before waiting for it, and only the product's output after.
     const int heads_total = Hq + (write_kv ? 2 * Hkv : 0);
     const int64_t thread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t item = thread / G;
@@ -114,8 +115,6 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     const int hh = live ? (int)(item % heads_total) : 0;
     const int pos = positions[t];
     const int c0 = part * 8;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = *reinterpret_cast<const uint4*>(qkv + (int64_t)t * ld + (int64_t)hh * D + c0);
 
     __nv_bfloat16* dst;
     const float* w;
@@ -133,6 +132,22 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
         w = which == 0 ? k_w : nullptr;
         rotate = which == 0;
     }
+    float wv[8];
+    if (rotate && w != nullptr) {
+        const float4 w0 = *reinterpret_cast<const float4*>(w + c0), w1 = *reinterpret_cast<const float4*>(w + c0 + 4);
+        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w;
+        wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+    }
+    const bool low = c0 < half;
+    float2 cs[8];
+    if (rotate && rope != nullptr) {
+        const float2* at = rope + (int64_t)pos * half + (low ? c0 : c0 - half);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cs[j] = at[j];
+    }
+    pdl_wait();
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(qkv + (int64_t)t * ld + (int64_t)hh * D + c0);
     float x[8];
     {
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -150,8 +165,6 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (rotate && w != nullptr) {
         const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-        const float4 w0 = *reinterpret_cast<const float4*>(w + c0), w1 = *reinterpret_cast<const float4*>(w + c0 + 4);
-        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * wv[j];
     }
@@ -160,8 +173,6 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
 #pragma unroll
     for (int j = 0; j < 8; ++j) y[j] = G > 1 ? __shfl_xor_sync(0xffffffffu, x[j], G / 2) : 0.0f;
     if (rotate && rope != nullptr) {
-        const bool low = c0 < half;
-        const float2* cs = rope + (int64_t)pos * half + (low ? c0 : c0 - half);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float2 a = cs[j];

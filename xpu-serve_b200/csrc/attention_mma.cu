@@ -563,7 +563,10 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 #pragma unroll 16
         for (int s = 0; s < splits; ++s) {
             const float w = __shfl_sync(0xffffffffu, s < 32 ? wgt0 : wgt1, s & 31);
-            const float2 v = (w == 0.0f || d >= D) ? make_float2(0.0f, 0.0f) : *reinterpret_cast<const float2*>(po + s * D + d);
+            // (read whatever the weight: the loads then wait for nothing but the row's address; an empty part's
+            // slot may hold anything, so its value is dropped, not multiplied by zero)
+            const float2 raw = d < D ? *reinterpret_cast<const float2*>(po + s * D + d) : make_float2(0.0f, 0.0f);
+            const float2 v = w == 0.0f ? make_float2(0.0f, 0.0f) : raw;
             a0 = fmaf(w, v.x, a0);
             a1 = fmaf(w, v.y, a1);
         }
