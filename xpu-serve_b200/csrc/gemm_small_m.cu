@@ -71,8 +71,11 @@ struct SmallMParams {
     float* out_ssq;           // [tiles, 16]
 };
 
+// `staged` (8 batch rows only): this tile's old stream values [m][16] and the next norm's weights [16], fetched into
+// shared memory while the weights streamed, so that the CTA's tail does not begin with a trip to L2.
 template <int NT, typename TO>
-__device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0) {
+__device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0,
+                                         const float* staged = nullptr) {
     TO* out = reinterpret_cast<TO*>(p.out);
     if (p.swiglu) {
         // rows 0..7 of the tile are gate rows, rows 8..15 the up rows of the same outputs
@@ -98,9 +101,13 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
         float sq = 0.0f;
         if (live) {
             if (p.residual != nullptr) {
-                const float h = p.residual[(int64_t)m * p.ldo + n] + v;
+                const float old = staged != nullptr ? staged[m * ROWS + r] : p.residual[(int64_t)m * p.ldo + n];
+                const float h = old + v;
                 p.residual[(int64_t)m * p.ldo + n] = h;
-                if (p.next_x != nullptr) p.next_x[(int64_t)m * p.ld_next + n] = __float2bfloat16_rn(h * p.next_w[n]);
+                if (p.next_x != nullptr) {
+                    const float nw = staged != nullptr ? staged[8 * ROWS + r] : p.next_w[n];
+                    p.next_x[(int64_t)m * p.ld_next + n] = __float2bfloat16_rn(h * nw);
+                }
                 sq = h * h;
             } else {
                 out[(int64_t)m * p.ldo + n] = from_f32<TO>(v);
@@ -128,6 +135,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? 4 : 2) gemm_small_m_
     __shared__ __align__(16) float ssq_in[kSsqStaged][16];
     __shared__ float ssq_red[16][17];
     __shared__ float inv[16];
+    __shared__ __align__(16) float staged[9 * ROWS];      // old stream values [8][16], then the next norm's weights [16]
     __shared__ bool last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -199,6 +207,22 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? 4 : 2) gemm_small_m_
         }
     }
     pdl_wait();
+    // the stream values this tile will be added to, and the next norm's weights, travel to shared memory beside the
+    // main loop too (whole tiles of up to 8 batch rows only)
+    const bool stage_tail = NT == 1 && EXACT && p.residual != nullptr && !p.swiglu;
+    if (stage_tail) {
+        const int i = threadIdx.x;
+        if (i < 8 * ROWS) {
+            const int m = i / ROWS, r = i % ROWS;
+            if (m < p.M)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(&staged[i])),
+                             "l"(p.residual + (int64_t)m * p.ldo + n0 + r) : "memory");
+        } else if (i < 9 * ROWS && p.next_w != nullptr) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(&staged[i])),
+                         "l"(p.next_w + n0 + (i - 8 * ROWS)) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     // the producer's per-tile sums of squares travel to shared memory beside the main loop (no registers held,
     // nothing waits for them until the loop is done)
     if (p.in_ssq != nullptr) {
@@ -298,8 +322,12 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? 4 : 2) gemm_small_m_
         inv[m] = v;
     }
     __syncthreads();
+    if (stage_tail) {       // (long landed; a barrier follows on both paths below or has just passed)
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+    }
     if (p.ksplit == 1) {
-        epilogue<NT, TO>(p, sum, inv, n0);
+        epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
         return;
     }
     // ---- several K slices: leave this slice's partial, and let the last CTA to arrive add them all
@@ -319,7 +347,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? 4 : 2) gemm_small_m_
     }
     if (threadIdx.x == 0) p.counters[tile] = 0;    // ready for the next call
     __syncthreads();
-    epilogue<NT, TO>(p, sum, inv, n0);
+    epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
 }
 
 }  // namespace
