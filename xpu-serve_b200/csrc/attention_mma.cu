@@ -351,9 +351,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
             }
         }
     }
-    pdl_wait();
-
-    // this CTA's page numbers in one coalesced read (in pieces of 64 blocks)
+    // this CTA's page numbers in one coalesced read (in pieces of 64 blocks); the first piece before the wait: the
+    // page table is part of the step's description
     auto load_pages = [&](int from) {
         __syncthreads();
         if (threadIdx.x < 64 && from + (int)threadIdx.x < be) pages_sm[threadIdx.x] = table[from + threadIdx.x];
@@ -361,6 +360,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
     };
     int pages_from = bs;
     load_pages(pages_from);
+    pdl_wait();
 
     for (int c = threadIdx.x; c < QROWS * CHUNKS; c += NTHREADS) {
         const int r = c / CHUNKS, ch = c % CHUNKS;
