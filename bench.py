@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the 1.2B family shape
+# The 1.2B family shape: the headline workload
 SHAPE_1_2B = {
     "model_type": "lfm3", "vocab_size": 65536, "hidden_size": 2048, "intermediate_size": 8192,
     "num_hidden_layers": 16,
@@ -47,7 +47,7 @@ def family_shape(layers, hidden, heads, ffn, context, attn_at):
     return cfg
 
 
-# BASELINE.json configs[3] and configs[4]: (shape, batch, prompt lengths uniform in [lo, hi], decode steps)
+# The 2.6B shape with ragged prompts and the 350M shape at long context: (shape, batch, prompt lengths uniform in [lo, hi], decode steps)
 WORKLOADS = {
     "ragged_2.6b": (family_shape(30, 2048, 32, 10752, 8192, range(2, 30, 3)), 16, (256, 4096), 512),
     "long_350m": (family_shape(16, 1024, 16, 6656, 32768, (2, 5, 8, 10, 12, 14)), 64, (1024, 24576), 256),

@@ -12,7 +12,7 @@ import json
 import math
 import os
 import struct
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 
@@ -173,8 +173,8 @@ def _rope_of(cfg: dict, kind: str, D: int) -> np.ndarray:
     return rope_inv_freq(float(r["rope_theta"]), D, pairs)
 
 
-def forward(cfg: dict, W: Dict[str, np.ndarray], ids: List[int]) -> np.ndarray:
-    """Logits [T, vocab] of one whole sequence from position 0
+def forward(cfg: dict, W: Dict[str, np.ndarray], ids: List[int], rows: Optional[Sequence[int]] = None) -> np.ndarray:
+    """Logits [T, vocab] of one whole sequence from position 0, or of its positions `rows` only
     (layer frame: src/models/lfm3/lfm3_decoder.cpp:49-90; head: src/models/lfm3/lfm3_model.cpp:37-38)."""
     H = cfg["hidden_size"]
     Hq, Hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -200,6 +200,8 @@ def forward(cfg: dict, W: Dict[str, np.ndarray], ids: List[int]) -> np.ndarray:
         y = rms_norm(h, W[L + "ffn_norm.weight"], eps)
         f = swiglu(y, W, L)
         h = h + (rms_norm(f, W[L + "post_ffn_norm.weight"], eps) if sandwich else f)
+    if rows is not None:
+        h = h[np.asarray(rows, dtype=np.int64)]
     last = rms_norm(h, W[P + "embedding_norm.weight"], eps)
     head = W[P + "embed_tokens.weight"] if tied else W["lm_head.weight"]
     return last @ head.T

@@ -212,3 +212,38 @@ def test_decoding_the_same_batch_step_after_step(window):
     c.begin_step(slots[:2], [1, 1])
     c.end_step(slots[:2], [1, 1])
     c.check()
+
+
+@pytest.mark.parametrize("window", [0, 70])
+def test_a_failed_step_gives_its_pages_back(window):
+    """`begin_step` reserved, then a kernel failed: `abort_step` puts the books back (pages, tables, lengths),
+    also for a window group that has given pages back before, and the slots can step again or be closed."""
+    c = make(max_tokens=2048, window=window)
+    a, b = c.open(2)
+    c.begin_step([a, b], [200, 10])
+    c.end_step([a, b], [200, 10])
+
+    def books():
+        return ([int(c.groups[g].pages.held_count) for g in c.kv_groups], [c.groups[g].table.copy() for g in c.kv_groups],
+                c.lens.copy(), c.tokens_held())
+
+    before = books()
+    versions = c.tables_version()
+    c.begin_step([a, b], [130, 60])                 # both cross page boundaries
+    assert books()[0] != before[0]
+    c.abort_step([a, b])
+    after = books()
+    assert after[0] == before[0] and all((x == y).all() for x, y in zip(after[1], before[1]))
+    assert (after[2] == before[2]).all() and after[3] == before[3]
+    assert c.tables_version() != versions            # a staged copy of the tables is stale
+    c.check()
+    c.begin_step([a], [1])                           # a step inside the pages already held: nothing to undo
+    c.abort_step([a])
+    assert books()[0] == before[0]
+    starts = c.begin_step([a, b], [130, 60])
+    assert list(starts) == [200, 10]
+    c.end_step([a, b], [130, 60])
+    c.check()
+    c.close([a, b])
+    c.check()
+    assert c.tokens_held() == 0

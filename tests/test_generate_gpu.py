@@ -64,6 +64,42 @@ def test_greedy_bfloat16_follows_plain_until_a_near_tie(folders):
             seq.append(t)
 
 
+@pytest.mark.parametrize("name,precision", [("W", "f32"), ("B", "f32"), ("W", "bf16")])
+def test_prompts_in_pieces_of_16_tokens(folders, name, precision):
+    """`prefill_chunk=16`: a batch's prompts go through the step function 16 tokens a step (a piece may end
+    in the middle of one prompt and the next step go on from there; src/engine/engine.cpp:296-313 cuts a
+    single prompt the same way). The tokens are the plain greedy run's."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    dtype = {"f32": "float32", "bf16": "bfloat16"}[precision]
+    folder = folders[(name, dtype)]
+    cfg, W = plain.load_folder(folder)
+    engine = Engine(folder, precision=precision, ctx=256, max_batch=8, prefill_chunk=16)
+    steps = []
+    real = engine.stepper.step
+    engine.stepper.step = lambda h, t, w: (steps.append([len(x) for x in t]), real(h, t, w))[1]
+    prompts = [tiny.prompt(name, n, salt=60 + i) for i, n in enumerate((5, 50, 41, 23))]
+    res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), 6, []) for p in prompts])
+    prompt_steps = [s for s in steps if max(s) > 1]
+    assert len(prompt_steps) == 8 and all(sum(s) <= 16 for s in prompt_steps)        # 119 tokens, 16 a step
+    assert [5, 11] in prompt_steps                # a step that ends one prompt and starts the next one
+    for p, r in zip(prompts, res):
+        assert r.finish == "length"
+        if precision == "f32":
+            want, margins = plain_greedy(cfg, W, p, 6)
+            assert min(margins) > 1e-4, "the test's own tokens are near ties; pick another prompt"
+            assert r.tokens == want
+        else:
+            seq = list(p)
+            for t in r.tokens:
+                logits = plain.forward(cfg, W, seq)[-1]
+                best = int(np.argmax(logits))
+                assert t == best or (logits[best] - logits[t]) / np.abs(logits).max() < min(2e-2, 2 * tiny.bound(name, dtype))
+                seq.append(t)
+    engine.stepper.cache.check()
+    assert engine.stepper.cache.slots.held_count == 0
+
+
 def test_stop_tokens_and_early_enders(folders):
     from xpu_serve_b200 import GenerateRequest, SamplingParams
     from xpu_serve_b200.engine.engine import Engine
@@ -244,3 +280,39 @@ def test_running_ahead_refuses_another_token(folders):
     with pytest.raises(RuntimeError, match="one decode step ahead"):
         st.step(hs, [[(t1 + 1) % 512]], [True])
     st.close(hs)
+
+
+def test_a_tcgen05_wait_that_gave_up_fails_the_step(folders, tmp_path):
+    """The tcgen05 kernels bound their waits and set a status word when one runs out; what they computed is
+    then partial. No wait is made to run out here: the word is set by hand, as a kernel would have left it.
+    The generation loop reads it with the tokens it waits for anyway and fails the batch; replay reads it
+    with the logits; the word is cleared, and the next call works."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.ops import lib as ops
+    folder = folders[("A", "bfloat16")]
+    engine = Engine(folder, precision="bf16", ctx=128, max_batch=4)
+    dev = engine.model.rt.device
+    reqs = [GenerateRequest(tiny.prompt("A", n, salt=80 + i), SamplingParams(temperature=0.0), 5, []) for i, n in enumerate((9, 4))]
+    good = engine.generate(reqs)
+    assert all(r.finish == "length" for r in good)
+
+    def as_a_kernel_would():
+        ops.gemm_tc_status(dev).fill_(3)
+        ops._tc_unread.add(ops.gemm_tc_status(dev).device)
+
+    as_a_kernel_would()
+    bad = engine.generate(reqs)
+    assert all(r.finish == "error" and "tcgen05" in r.error and r.tokens == [] for r in bad)
+    assert ops.gemm_tc_status(dev).item() == 0 and not ops.tc_status_unread(dev)
+    engine.stepper.cache.check()
+    assert engine.stepper.cache.slots.held_count == 0
+    assert [r.tokens for r in engine.generate(reqs)] == [r.tokens for r in good]
+    rp = Replayer(engine.model, 256, None)
+    as_a_kernel_would()
+    step = {"step": 0, "entries": [{"id": "a", "tokens": reqs[0].prompt, "want": [0]}], "end": []}
+    with pytest.raises(ops.KernelError, match="tcgen05"):
+        rp.run_step(step)
+    assert rp.cache.slots.held_count == 0 and ops.gemm_tc_status(dev).item() == 0
+    assert rp.run_step(dict(step, end=["a"])) is not None

@@ -374,6 +374,18 @@ class Paged:
                 self.pool[pg, 0, :, r] = self.k[s][j].to(self.pool.dtype)
                 self.pool[pg, 1, :, r] = self.v[s][j].to(self.pool.dtype)
 
+    def drop_pages_behind(self, window):
+        """What the cache does behind a window: pages that no query of this step can see are given back and the
+        table says -1 there (their storage now belongs to somebody else: it is made loud)."""
+        dropped = 0
+        for s, start in enumerate(self.starts):
+            first = max(0, start - window + 1) // self.page
+            for lp in range(first):
+                self.pool[int(self.table[s, lp])] = 1e4
+                self.table[s, lp] = -1
+                dropped += 1
+        return dropped
+
     def dev(self):
         i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)   # noqa: E731
         return dict(pool=self.pool.to(DEV), table=self.table.to(DEV), cu=i32(self.cu), seq_of=i32(self.seq_of),
@@ -409,6 +421,8 @@ ATTN_CASES = [
     ([500, 37, 1999], [1, 1, 1], 16, 2, 128, 0),
     ([0], [90], 5, 5, 80, 17),                       # a head size only the generic kernel takes
     ([4100, 30], [1, 1], 8, 2, 64, 0),               # more than 32 blocks of keys: 40 splits all hold some
+    ([500], [200], 16, 1, 64, 100),                  # a piece of a prompt behind a window that has left pages behind
+    ([700, 130, 260], [1, 1, 1], 8, 2, 64, 50),      # decoding behind such a window
 ]
 
 
@@ -433,11 +447,14 @@ def test_attention(case, kernel, dtype):
     pg.fill_pool()
     scale = 1.0 / math.sqrt(D)
     gate = torch.randn(sum(q_lens), Hq + 3).to(DT[dtype])
-    for gt in (None, gate):
-        ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
-        for splits in ([1] if kernel == "generic" else [1, 2, 5, 40]):
-            out = run_attention(lib, pg, kernel, scale, window, gt, splits)
-            close(out, ref, dtype, factor=3 if dtype == "bfloat16" else 20)
+    for trimmed in ((False, True) if window > 0 else (False,)):
+        if trimmed and pg.drop_pages_behind(window) == 0:
+            continue
+        for gt in (None, gate):
+            ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
+            for splits in ([1] if kernel == "generic" else [1, 2, 5, 40]):
+                out = run_attention(lib, pg, kernel, scale, window, gt, splits)
+                close(out, ref, dtype, factor=3 if dtype == "bfloat16" else 20)
 
 
 def test_attention_refuses_more_splits_than_it_combines():
@@ -454,6 +471,7 @@ ATTN_TC_CASES = [
     ([10, 100, 700], [60, 3, 130], 4, 4, 0),         # continuing sequences, one head a group
     ([0, 130], [150, 1], 4, 1, 37),                  # a window with its edge inside and across pages
     ([500], [200], 16, 1, 100),                      # 16 heads a group, a window that has left whole blocks behind
+    ([300, 0, 129], [40, 7, 2], 4, 2, 50),           # short pieces behind a window, pages given back
     ([0], [129], 2, 2, 0),                           # one row into the second tile, one key into the second block
 ]
 
@@ -479,12 +497,16 @@ def test_attention_tc(case):
     pg.fill_pool()
     scale = 1.0 / math.sqrt(D)
     gate = torch.randn(sum(q_lens), Hq + 3).to(torch.bfloat16)
-    for gt in (None, gate):
-        ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
-        out = run_attention(lib, pg, "tc", scale, window, gt, 1)
-        close(out, ref, "bfloat16", factor=3)
-        same = run_attention(lib, pg, "mma", scale, window, gt, 1)
-        close(out, same.double(), "bfloat16", factor=3)
+    for trimmed in ((False, True) if window > 0 else (False,)):
+        # the second time with the pages behind the window given back: -1 in the table, loud values in their storage
+        if trimmed and pg.drop_pages_behind(window) == 0:
+            continue
+        for gt in (None, gate):
+            ref = pg.reference(scale, window, None if gt is None else gt[:, :Hq])
+            out = run_attention(lib, pg, "tc", scale, window, gt, 1)
+            close(out, ref, "bfloat16", factor=3)
+            same = run_attention(lib, pg, "mma", scale, window, gt, 1)
+            close(out, same.double(), "bfloat16", factor=3)
 
 
 def run_attention(lib, pg, kernel, scale, window, gate, splits):

@@ -326,6 +326,7 @@ def test_toy_mixer_order_and_shared_cache(dtype):
         live = [i for i in live if i not in done]
     tol = 1e-5 if dtype == "float32" else 5e-2
     for g, r in zip(got, refs):
+        print(f"GAP toy-mixer {dtype} gap={gap_of(np.concatenate(g, 0), r):.3e}")
         assert gap_of(np.concatenate(g, 0), r) <= tol
     cache.check()
     # slots are used again, and the toy's state starts from zero again
@@ -440,7 +441,7 @@ def plain_routed_forward(spec, tensors, ids):
     H, Hq, Hkv, D, K, eps = 64, 4, 2, 16, 3, cfg["norm_eps"]
     inv = plain.rope_inv_freq(cfg["rope_theta"], D, D // 2)
     h = W["model.embed_tokens.weight"][np.asarray(ids)]
-    margins = []
+    margins = []          # per routed layer and position: (2nd - 3rd router logit) / largest |router logit|
     for call in spec.order:
         layer = spec.layers[call.layer]
         L = f"model.layers.{call.layer}."
@@ -460,7 +461,7 @@ def plain_routed_forward(spec, tensors, ids):
             f = np.zeros_like(y)
             for t in range(len(ids)):
                 order = np.argsort(-logits[t])
-                margins.append(logits[t, order[1]] - logits[t, order[2]])
+                margins.append((logits[t, order[1]] - logits[t, order[2]]) / np.abs(logits[t]).max())
                 best = order[:2]
                 pe = np.exp(logits[t, best] - logits[t, best].max())
                 pe /= pe.sum()
@@ -479,19 +480,27 @@ def test_toy_routed_ffn_and_toy_position_encoding(dtype):
     graphs, where the toy feed-forward takes the plain norm between the fused products around it)."""
     spec, tensors, model = routed_model(dtype)
     cache = model.new_cache(1024)
-    prompts = [tiny.prompt("A", n, salt=20 + i) for i, n in enumerate((12, 40, 5))]
-    refs = []
-    for p in prompts:
-        ref, margin = plain_routed_forward(spec, tensors, p)
-        assert margin > 1e-4, "the test's own routing is near a tie for float32; pick another prompt"
-        refs.append(ref)
+    # Sequences whose every routing decision is clear of a tie in float64 (the third-best expert's logit lies
+    # at least 4 % of the largest below the second's): bfloat16 noise cannot flip them, so every position can be
+    # held to the ordinary bound. A flipped decision would change the position's feed-forward output altogether.
+    prompts, refs = [], []
+    for n in (12, 25, 5):
+        for salt in range(20, 400):
+            p = tiny.prompt("A", n, salt=salt)
+            ref, margin = plain_routed_forward(spec, tensors, p)
+            if margin > 0.04 and p not in prompts:
+                prompts.append(p)
+                refs.append(ref)
+                break
+        else:
+            raise AssertionError("no prompt with clear routing found; loosen the search")
     # the stretch matters: without it the logits are others
     flat, _ = plain_routed_forward(replace(spec, layers=(replace(spec.layers[0], mixer=replace(
         spec.layers[0].mixer, position=replace(spec.layers[0].mixer.position, stretch=1.0))),) + spec.layers[1:]),
         tensors, prompts[1])
     assert gap_of(flat, refs[1]) > 1e-3
     slots = cache.open(3)
-    heads = [7, 25, 1]
+    heads = [7, 15, 1]
     got = [[] for _ in prompts]
     lg = model.step(cache, slots, [p[:h] for p, h in zip(prompts, heads)], [list(range(h)) for h in heads]).cpu().numpy()
     o = 0
@@ -509,11 +518,10 @@ def test_toy_routed_ffn_and_toy_position_encoding(dtype):
         cache.close([slots[i] for i in done])
         live = [i for i in live if i not in done]
     gaps = [np.abs(np.concatenate(g, 0) - r).max(1) / np.abs(r).max() for g, r in zip(got, refs)]
-    if dtype == "float32":
-        assert max(g.max() for g in gaps) <= 1e-5
-    else:
-        # bfloat16 noise can turn a routing decision that float64 makes by a hair; most positions must agree
-        assert np.median(np.concatenate(gaps)) <= 5e-2 and np.isfinite(np.concatenate(gaps)).all()
+    bound = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * 3) * 2 ** -9
+    worst = max(g.max() for g in gaps)
+    print(f"GAP toy-routed {dtype} gap={worst:.3e}")
+    assert worst <= bound
     cache.check()
 
 
@@ -536,9 +544,9 @@ def test_long_decoding(tmp_path, name, dtype):
     (s,) = cache.open(1)
     assert s == warm
     rows = [model.step(cache, [s], [[t]]).cpu().numpy()[0] for t in toks]
-    layers = cfg["num_hidden_layers"]
-    tol = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * layers) * 2 ** -9
-    assert gap_of(np.stack(rows), ref) <= tol
+    gap = gap_of(np.stack(rows), ref)
+    print(f"GAP long-decoding {name} {dtype} gap={gap:.3e}")
+    assert gap <= tiny.bound(name, dtype)
     cache.close([s])
     cache.check()
 
@@ -552,7 +560,7 @@ def test_first_tokens(tmp_path, name, dtype):
     cfg, W = plain.load_folder(folder)
     model = load_model(folder, dtype=dtype)
     cache = model.new_cache(512)
-    tol = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * cfg["num_hidden_layers"]) * 2 ** -9
+    tol = tiny.bound(name, dtype)
     toks = tiny.prompt(name, 3, salt=1)
     ref = plain.forward(cfg, W, toks)
     (s,) = cache.open(1)

@@ -119,3 +119,26 @@ def test_vl_prefix_is_probed(tmp_path):
     write_safetensors(str(tmp_path / "model.safetensors"), renamed)
     w = load_weights(spec, str(tmp_path))
     assert "embed_tokens.weight" in w and "layers.3.conv.out_proj.weight" in w
+
+
+def test_a_wrapped_checkpoint_may_hold_other_towers(tmp_path):
+    """An lfm3_vl checkpoint keeps the text decoder under model.language_model. beside vision tensors
+    (src/models/lfm3/lfm3_decoder.cpp:14-19). Those are not this model's: it loads. A stray tensor under the
+    decoder's own prefix is still named, and so is any stray tensor of a plain checkpoint."""
+    import torch
+    cfg = Lfm3Config.from_json(tiny.CONFIG_A)
+    spec = cfg.model_spec()
+    renamed = [(n.replace("model.", "model.language_model.", 1), t) for n, t in random_tensors(spec, 0, "float32")]
+    extra = [("model.vision_tower.patch_embed.weight", torch.zeros(4, 4)), ("model.multi_modal_projector.w", torch.zeros(2))]
+    for d in ("vl", "vl2", "plain"):
+        os.makedirs(tmp_path / d)
+    write_safetensors(str(tmp_path / "vl" / "model.safetensors"), renamed + extra)
+    w = load_weights(spec, str(tmp_path / "vl"))
+    assert "embed_tokens.weight" in w and not any("vision" in k for k in w)
+    write_safetensors(str(tmp_path / "vl2" / "model.safetensors"),
+                      renamed + extra + [("model.language_model.layers.0.stray.weight", torch.zeros(3))])
+    with pytest.raises(WeightError, match=r"unexpected \(1\): model.language_model.layers.0.stray.weight"):
+        load_weights(spec, str(tmp_path / "vl2"))
+    write_safetensors(str(tmp_path / "plain" / "model.safetensors"), list(random_tensors(spec, 0, "float32")) + extra[:1])
+    with pytest.raises(WeightError, match=r"unexpected \(1\): model.vision_tower.patch_embed.weight"):
+        load_weights(spec, str(tmp_path / "plain"))

@@ -1,8 +1,8 @@
 """The tiny LFM3 configurations the tests use, and helpers to write them as model folders.
 
-A and B are the two small shapes the build's baseline names; they differ in every size and
+A and B are the two small shapes of the 1.2B family's test plan; they differ in every size and
 option (layers, widths that are no power of two, heads and groups, head size, taps, bias,
-theta, eps, tied or untied head). R is the layout the reference's own loader reads:
+theta, eps, tied or untied head); C is B without its biases. R is the layout the reference's own loader reads:
 sandwich norms, a gate per head, partly rotated heads, a sliding layer whose window is
 shorter than the test prompts, 7 taps (tests/parity/model/make_tiny.py:113-140 of the
 reference). W adds to B's options a sliding layer with an odd window and two rope bases. X has
@@ -31,6 +31,10 @@ CONFIG_B = {
     "max_position_embeddings": 2048, "tie_word_embeddings": False,
     "use_sandwich_norm": False, "attn_head_gate": False, "initializer_range": 0.05,
 }
+
+# B without the biases: `conv_bias` is the one option whose formula the reference cannot pin (it refuses the
+# key, src/models/lfm3/lfm3_config.cpp:44), so B's other sizes and options are also run without it
+CONFIG_C = dict(CONFIG_B, conv_bias=False)
 
 CONFIG_R = {
     "model_type": "lfm3", "vocab_size": 300, "hidden_size": 64, "intermediate_size": 96,
@@ -76,8 +80,8 @@ CONFIG_H = {
                         "sliding_attention": {"rope_theta": 300.0, "partial_rotary_factor": 0.5}},
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "R": CONFIG_R, "W": CONFIG_W, "X": CONFIG_X, "H": CONFIG_H}
-SEEDS = {"A": 0, "B": 1, "R": 2, "W": 3, "X": 4, "H": 5}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "R": CONFIG_R, "W": CONFIG_W, "X": CONFIG_X, "H": CONFIG_H}
+SEEDS = {"A": 0, "B": 1, "C": 1, "R": 2, "W": 3, "X": 4, "H": 5}
 # Plain N(0, sigma) weights give near-uniform attention and near-linear layers. These factors make the
 # parts matter: q and k large enough for peaked scores, taps and gates of order one.
 LIVELY = {"q_proj.weight": 6.0, "k_proj.weight": 6.0, "conv.conv.weight": 12.0, "gate_proj.weight": 8.0,
@@ -98,3 +102,28 @@ def make_folder(root, name: str, dtype: str = "float32", lively: bool = True) ->
 def prompt(name: str, length: int, salt: int = 0):
     V = CONFIGS[name]["vocab_size"]
     return [(i * 37 + 5 + 11 * salt + (i * i) % 7) % V for i in range(length)]
+
+
+# ---------------------------------------------------------------------------------------------- bounds
+# Largest |difference| over largest |reference logit|, engine against the plain float64 implementation.
+# Upper limits. float32: 1e-5, the target of the 32-bit path. bfloat16: a value is rounded to 8 significant bits
+# (relative error up to u = 2^-9) about ten times a layer (normed input, projections, mixer state and output,
+# gate/up, activation, branch output); independent roundings add like a random walk, so a logit's typical error
+# is about sqrt(10 * layers) * u of the logits' scale, and the largest of some 10^5 logits lies a few times
+# higher: 4 * sqrt(10 * layers) * u.
+# Measured on a B200, the worst of the replay schedules (whole, last 32 one by one, batches of 3 / 5 / 11,
+# prompts in pieces) per configuration; a test's bound is three times that, capped by the upper limit, so that
+# a fault that costs a configuration a few times its usual error fails the test.
+U_BF16 = 2.0 ** -9
+MEASURED_GAP = {
+    "float32": {"A": 2.0e-7, "B": 3.2e-7, "C": 2.9e-7, "R": 1.9e-6, "W": 1.2e-6, "X": 2.2e-7, "H": 1.9e-7},
+    "bfloat16": {"A": 1.1e-3, "B": 4.4e-3, "C": 4.1e-3, "R": 2.9e-2, "W": 1.9e-2, "X": 8.7e-4, "H": 7.5e-4},
+}
+
+
+def upper_limit(layers: int, dtype: str) -> float:
+    return 1e-5 if dtype == "float32" else 4.0 * (10.0 * layers) ** 0.5 * U_BF16
+
+
+def bound(name: str, dtype: str) -> float:
+    return min(upper_limit(CONFIGS[name]["num_hidden_layers"], dtype), 3.0 * MEASURED_GAP[dtype][name])

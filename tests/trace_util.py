@@ -59,6 +59,42 @@ def batch_trace(requests: Dict[str, List[int]], batch: int, prompt_frac: float =
     return steps
 
 
+PIECES = (7, 64, 65, 129, 3, 16, 40)
+
+
+def pieces_trace(requests: Dict[str, List[int]], batch: int, prompt_frac: float = 0.8,
+                 pieces: Sequence[int] = PIECES) -> List[dict]:
+    """Prompts in pieces, and steps that mix pieces with single tokens. A batch's requests start together with
+    the first piece of each; from then on every live request brings, while its prompt (the first
+    `prompt_frac` of its tokens) lasts, the next piece of it (sizes cycle through `pieces`, each request
+    starting at another place of the cycle), and after that one token a step. So a later piece of a long
+    request stands in the same step as single tokens of shorter ones, and shorter requests end earlier."""
+    steps, n = [], 0
+    rids = list(requests)
+    for b0 in range(0, len(rids), batch):
+        group = rids[b0:b0 + batch]
+        prompt_len = {r: max(1, int(len(requests[r]) * prompt_frac)) for r in group}
+        at = {r: 0 for r in group}
+        turn = {r: 0 for r in group}
+        live = list(group)
+        while live:
+            entries = []
+            for k, r in enumerate(live):
+                if at[r] < prompt_len[r]:
+                    size = pieces[(turn[r] + (k if turn[r] else 0)) % len(pieces)]
+                    take = min(size, prompt_len[r] - at[r])
+                    turn[r] += 1
+                else:
+                    take = 1
+                entries.append({"id": r, "tokens": requests[r][at[r]:at[r] + take], "want": list(range(take))})
+                at[r] += take
+            ends = [r for r in live if at[r] == len(requests[r])]
+            steps.append({"step": n, "entries": entries, "end": ends})
+            n += 1
+            live = [r for r in live if r not in ends]
+    return steps
+
+
 def collect(steps: List[dict], outputs: Dict[int, np.ndarray], vocab: int) -> Dict[Tuple[str, int], np.ndarray]:
     """{(request, position): logits} from the per-step outputs of a trace."""
     pos: Dict[str, int] = {}

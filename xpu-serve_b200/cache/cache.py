@@ -81,6 +81,17 @@ class KVGroup:
             self.first_held[slot] = first
             self.version += 1
 
+    def unreserve(self, slot: int, length: int) -> None:
+        """Gives back the pages held beyond those that `length` positions need (a step that reserved and then
+        failed)."""
+        keep = max(_ceil_div(length, self.page_size), int(self.first_held[slot]))
+        end = int(self.end_held[slot])
+        if end > keep:
+            self.pages.give_back(int(p) for p in self.table[slot, keep:end])
+            self.table[slot, keep:end] = -1
+            self.end_held[slot] = keep
+            self.version += 1
+
     def release(self, slot: int) -> None:
         lo, hi = int(self.first_held[slot]), int(self.end_held[slot])
         self.pages.give_back(int(p) for p in self.table[slot, lo:hi])
@@ -239,6 +250,16 @@ class Cache:
         if int(lens.max()) + 1 > self.max_seq_tokens or (lens % self.page_size == 0).any():
             return False
         return all(self.slots.is_held(s) for s in slots)
+
+    def abort_step(self, slots: Sequence[int]) -> None:
+        """Undoes `begin_step` for a step that failed before `end_step`: pages reserved for the step's tokens
+        go back, lengths stay. The books are then as before the step. What the step's kernels had already
+        written (fixed-size state, keys and values at the step's positions) is not undone: a sequence of a
+        failed step cannot go on and has to be closed."""
+        self._last_slots = None
+        for s in slots:
+            for gi in self.kv_groups:
+                self.groups[gi].unreserve(s, int(self.lens[s]))
 
     def end_step(self, slots: Sequence[int], q_lens: Sequence[int]) -> None:
         key = tuple(slots)

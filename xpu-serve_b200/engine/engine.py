@@ -20,7 +20,8 @@ import numpy as np
 import torch
 
 from ..ops import lib as ops
-from ..sampling.params import GenerateRequest, GenerateResult, SamplingParams, TokenCallback, read_generation_defaults
+from ..sampling.params import (GenerateRequest, GenerateResult, SamplingParams, TokenCallback, merged_stop_ids,
+                               read_generation_defaults)
 from .generate import generate as _generate
 from .model import Model, load_model
 
@@ -148,9 +149,9 @@ class DeviceStepper:
         params = [h.request.sampling for h in chosen]
         if self._pen is None and n == len(handles) and self.model.last_greedy is not None and all(p.greedy() for p in params):
             # the decode graph has chosen already; start the next step before waiting for this one's tokens
-            host, event = self._copy_out(self.model.last_greedy)
+            host, event, status_at = self._copy_out(self.model.last_greedy)
             self._start_ahead(handles)
-            event.synchronize()
+            self._landed(host, event, status_at)
             tokens = host[:n].tolist()
             if self._ahead is not None:
                 self._ahead.fed = tokens
@@ -158,10 +159,10 @@ class DeviceStepper:
                 h.counter += 1
             return tokens
         out = self._choose(logits, chosen, 0)
-        host, event = self._copy_out(out)
+        host, event, status_at = self._copy_out(out)
         if n == len(handles):
             self._start_ahead(handles, out)       # the next step, fed on the device, before waiting for this one
-        event.synchronize()
+        self._landed(host, event, status_at)
         tokens = host[:n].tolist()
         for h in chosen:
             h.counter += 1
@@ -195,19 +196,31 @@ class DeviceStepper:
 
     def _copy_out(self, out: torch.Tensor):
         """Starts the step's only device-to-host copy (the chosen tokens, into pinned memory) and returns the
-        host buffer and the event that says it has landed. Two buffers take turns: a step that runs ahead
-        copies out while the one before it is still being read."""
+        host buffer, the event that says it has landed and where in the buffer a status word lies (None: nowhere). Two buffers take turns: a step that runs ahead
+        copies out while the one before it is still being read. When a tcgen05 kernel ran since its status
+        word was last read (prompt steps; decode steps launch none), the word travels behind the tokens and
+        `_landed` looks at it."""
         n = out.numel()
         self._turn ^= 1
         while len(self._host_bufs) < 2:
             self._host_bufs.append(torch.empty(64, dtype=torch.int32, pin_memory=True))
-        if self._host_bufs[self._turn].numel() < n:
-            self._host_bufs[self._turn] = torch.empty(2 * n, dtype=torch.int32, pin_memory=True)
+        if self._host_bufs[self._turn].numel() < n + 1:
+            self._host_bufs[self._turn] = torch.empty(2 * n + 1, dtype=torch.int32, pin_memory=True)
         host = self._host_bufs[self._turn]
         host[:n].copy_(out, non_blocking=True)
+        status_at = None
+        if ops.tc_status_unread(self.device):
+            host[n:n + 1].copy_(ops.gemm_tc_status(self.device), non_blocking=True)
+            status_at = n
         event = torch.cuda.Event()
         event.record()
-        return host, event
+        return host, event, status_at
+
+    def _landed(self, host: torch.Tensor, event, status_at: Optional[int]) -> None:
+        """Waits for a `_copy_out`, and fails the step if the status word that came with it is set."""
+        event.synchronize()
+        if status_at is not None:
+            ops.tc_status_read(int(host[status_at]), self.device)
 
     # ----------------------------------------------------------- running ahead
     def _start_ahead(self, handles: Sequence[_Handle], chosen_dev: Optional[torch.Tensor] = None) -> None:
@@ -227,7 +240,7 @@ class DeviceStepper:
             out = None if logits is None else self._choose(logits, handles, 1)
         if out is None:
             return
-        host, event = self._copy_out(out)
+        host, event, _ = self._copy_out(out)        # decode steps launch no tcgen05 kernel: no status to read
         self._ahead = _Ahead({h: i for i, h in enumerate(handles)}, None, event, host, out)
 
     def _take_ahead(self, ahead: _Ahead, handles, token_lists, want) -> List[Optional[int]]:
@@ -255,9 +268,8 @@ class Engine:
         if precision not in PRECISIONS:
             raise ValueError(f"precision '{precision}' is not supported (bf16, f32 are)")
         self.model: Model = load_model(model_dir, dtype=PRECISIONS[precision], device=device)
-        self.default_sampling, gen_stops = read_generation_defaults(model_dir)
-        cfg_stops = list(getattr(self.model.config, "eos_token_id", ()) or ())
-        self.stop_token_ids: List[int] = sorted(set(gen_stops) | set(cfg_stops))
+        self.default_sampling, _ = read_generation_defaults(model_dir)
+        self.stop_token_ids: List[int] = merged_stop_ids(model_dir, self.model.config)
         ctx = min(ctx, self.model.spec.max_position)
         self.max_batch = max_batch
         self.prefill_chunk = prefill_chunk

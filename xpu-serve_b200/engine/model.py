@@ -110,8 +110,10 @@ class Model:
              want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
         """Runs each sequence's next tokens. `want[i]` lists the places among sequence i's tokens of
         this step whose logits are returned (default: the last). Returns [wanted, vocab] float32 on
-        the device, in the order of the sequences and of `want`. On an error nothing of the cache's
-        accounting has changed."""
+        the device, in the order of the sequences and of `want`. On an error the cache's books (lengths,
+        pages held) are as before the step; a kernel that failed in the middle may already have written
+        state, keys and values for the step's positions, so its sequences cannot go on and must be closed
+        (the generation loop and trace replay do that)."""
         if want is None:
             want = [[len(t) - 1] for t in token_lists]
         if len(slots) != len(token_lists) or len(want) != len(slots):
@@ -125,12 +127,16 @@ class Model:
         self.last_greedy = None      # set by a decode graph: argmax of the returned rows, already on the device
         self._last_graph = None
         starts = cache.begin_step(slots, q_lens)
-        if self.use_graphs and max(q_lens) == 1:
-            logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
-        else:
-            ctx = self.stager.stage(cache, slots, token_lists, want, starts)
-            self.last_h2d_bytes = self.stager.last_h2d_bytes
-            logits = self.forward(ctx, cache)
+        try:
+            if self.use_graphs and max(q_lens) == 1:
+                logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
+            else:
+                ctx = self.stager.stage(cache, slots, token_lists, want, starts)
+                self.last_h2d_bytes = self.stager.last_h2d_bytes
+                logits = self.forward(ctx, cache)
+        except Exception:
+            cache.abort_step(slots)
+            raise
         cache.end_step(slots, q_lens)
         return logits
 

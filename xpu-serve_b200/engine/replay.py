@@ -22,6 +22,7 @@ from typing import Dict, IO, Optional
 
 import numpy as np
 
+from ..ops import lib as ops
 from .model import Model, load_model
 
 
@@ -53,6 +54,9 @@ class Replayer:
                 out = self.model.step(self.cache, slots, tokens, want)
                 if out.shape[0] > 0:
                     logits = out.detach().to("cpu").numpy().astype("<f4", copy=False)
+                    dev = self.model.rt.device
+                    if ops.tc_status_unread(dev):        # the copy above has waited for the step's kernels
+                        ops.tc_status_read(int(ops.gemm_tc_status(dev).item()), dev)
                     if self.out_dir:
                         logits.tofile(os.path.join(self.out_dir, f"{step}.f32"))
         except Exception:

@@ -323,6 +323,7 @@ def attention_tc(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, 
         if gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < heads:
             raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {heads} heads")
         ld_gate = gate.stride(0)
+    _tc_unread.add(gemm_tc_status(q.device).device)
     _check(load().xs_attention_tc(
         q.data_ptr(), pool.data_ptr(), pool.shape[0], page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
         kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), T, n_seqs, max_q_len, heads, kv_heads, D, page_size,
@@ -408,9 +409,34 @@ def gemm_tc_scratch_bytes(T: int, N: int, ksplit: int) -> int:
 def gemm_tc_status(device) -> torch.Tensor:
     """The device word that the tcgen05 kernels set non-zero when one of their waits gave up."""
     device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     if device not in _tc_status:
         _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
     return _tc_status[device]
+
+
+# Devices on which a tcgen05 kernel was launched since the status word was last looked at. Whoever next
+# waits for the device anyway (the generation loop for its tokens, trace replay for its logits) reads the
+# word with what it waits for and hands it to `tc_status_read`; decode steps launch no such kernel and
+# pay nothing.
+_tc_unread = set()
+
+
+def tc_status_unread(device) -> bool:
+    return gemm_tc_status(device).device in _tc_unread
+
+
+def tc_status_read(value: int, device) -> None:
+    """`value`: the status word as copied from the device after every tcgen05 kernel launched so far has run.
+    Non-zero: a bounded wait inside such a kernel gave up, so what the step wrote (activations, keys and
+    values in the cache) is partly computed: the word is cleared and the step fails."""
+    word = gemm_tc_status(device)
+    _tc_unread.discard(word.device)
+    if int(value) != 0:
+        word.zero_()
+        raise KernelError(f"a tcgen05 kernel gave up waiting (status {int(value)}): this step's results and what it "
+                          f"wrote to the cache are not valid")
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -428,6 +454,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         raise KernelError(f"gemm (tcgen05): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if bias is not None:
         _need(bias, "bias", torch.float32)
+    _tc_unread.add(gemm_tc_status(x.device).device)
     _check(load().xs_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), _code(out), int(epilogue), T, N, K,
                              x.stride(0), w.stride(0), out.stride(0), int(ksplit), _ptr(scratch),
                              0 if scratch is None else scratch.numel() * scratch.element_size(),

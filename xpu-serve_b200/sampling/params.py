@@ -106,3 +106,13 @@ def read_generation_defaults(folder: str):
         if isinstance(v, (int, float)) and not isinstance(v, bool):
             p = replace(p, **{key: float(v)})
     return p, get_int_list(j, "eos_token_id", where)
+
+
+def merged_stop_ids(folder: str, config=None) -> List[int]:
+    """The ids that end a sequence: generation_config.json's `eos_token_id` and config.json's, merged, sorted,
+    each once (src/models/lfm3/lfm3_model.cpp:69-77; the reference adds the tokenizer's end-of-turn id, and
+    refuses a model without any: a folder of random weights may have none here). `config`: the typed
+    configuration, whose `eos_token_id` holds config.json's."""
+    _, gen_stops = read_generation_defaults(folder)
+    cfg_stops = list(getattr(config, "eos_token_id", ()) or ())
+    return sorted(set(gen_stops) | set(cfg_stops))

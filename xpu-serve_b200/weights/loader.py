@@ -34,7 +34,12 @@ def check_store(spec: ModelSpec, store: WeightStore) -> str:
     prefix = probe_prefix(spec, store.names())
     expected = expected_tensors(spec, prefix)
     missing = [n for n in expected if n not in store]
-    unexpected = [n for n in store.names() if n not in expected]
+    # Under a wrapper's prefix (a checkpoint that holds other towers beside the text decoder) only names under
+    # that prefix, and the head's, are this model's to judge: the rest is read by name and left alone, as the
+    # reference does (src/io/safetensors.cpp:14-18). Under the plain prefix every stray tensor is named.
+    wrapped = prefix != spec.prefixes[-1]
+    unexpected = [n for n in store.names() if n not in expected
+                  and (not wrapped or n.startswith(prefix) or n == spec.names["head"])]
     wrong = [f"{n} is {list(store.shape(n))}, expected {list(ts.shape)}"
              for n, ts in expected.items() if n in store and tuple(store.shape(n)) != tuple(ts.shape)]
     bad_dtype = [f"{n} is {store.dtype(n)}" for n in expected
