@@ -141,7 +141,7 @@ def test_shared_cache_view():
     c = Cache(needs, [None, 0, None], 256, dtype=torch.float32, device="cpu")
     assert c.views[1].storage.data_ptr() == c.views[0].storage.data_ptr()
     assert c.views[0].owner and not c.views[1].owner and len(c.groups) == 2
-    assert c.groups[c.views[0].group].calls == [0]
+    assert c.groups[c.views[0].group].calls == [(0, 0)]
 
 
 def test_random_traffic_keeps_the_books():
@@ -247,3 +247,37 @@ def test_a_failed_step_gives_its_pages_back(window):
     c.close([a, b])
     c.check()
     assert c.tokens_held() == 0
+
+
+def test_a_call_with_several_needs():
+    """A mixer may keep several things per sequence (say a window of inputs, a running state and keys/values).
+    Each need lies in the group of its kind and geometry, beside other calls' equal needs, and the call's view
+    hands them out in declaration order; a reader of that call's cache sees the same storage."""
+    both = (StateNeed((2, 8)), StateNeed((8,), "float32"), KVNeed(2, 16, 0))
+    needs = [both, StateNeed((2, 8)), KVNeed(2, 16, 0), both, None]
+    c = Cache(needs, [None, None, None, None, 0], 512, dtype=torch.bfloat16, device="cpu")
+    assert len(c.groups) == 3 and len(c.kv_groups) == 1
+    v = c.views[0]
+    assert len(v) == 3 and v.storage is v[0].storage and v.owner
+    assert tuple(v[0].storage.shape[1:]) == (2, 8) and v[0].storage.dtype == torch.bfloat16
+    assert tuple(v[1].storage.shape[1:]) == (8,) and v[1].storage.dtype == torch.float32
+    assert tuple(v[2].storage.shape[1:]) == (2, 2, 64, 16) and v[2].group == c.kv_groups[0]
+    assert v[0].group == c.views[1].group and v[0].storage.data_ptr() != c.views[1].storage.data_ptr()
+    assert v[2].group == c.views[2].group and len(c.views[1]) == 1 and c.views[1][0] is c.views[1]
+    ptrs = {c.views[i][k].storage.data_ptr() for i in (0, 3) for k in range(3)}
+    assert len(ptrs) == 6                                            # two calls of the same kind: storage of their own
+    assert len(c.views[4]) == 0 and c.views[4].storage is None       # declares nothing: reads nothing
+    shared = Cache([both, both], [None, 0], 512, dtype=torch.bfloat16, device="cpu")
+    r = shared.views[1]
+    assert not r.owner and [r[k].storage.data_ptr() for k in range(3)] == [shared.views[0][k].storage.data_ptr() for k in range(3)]
+    # every state is zeroed when a slot is opened, pages are counted once per group
+    (s,) = c.open(1)
+    c.begin_step([s], [70])
+    c.end_step([s], [70])
+    assert c.groups[c.kv_groups[0]].pages.held_count == 2
+    for k in (0, 1):
+        v[k].storage[s] = 7
+    c.close([s])
+    (s2,) = c.open(1)
+    assert s2 == s and all(float(v[k].storage[s].abs().sum()) == 0 for k in (0, 1))
+    c.check()

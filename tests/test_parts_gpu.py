@@ -525,6 +525,254 @@ def test_toy_routed_ffn_and_toy_position_encoding(dtype):
     cache.check()
 
 
+# ---------------------- a mixer with two states, a norm with mean and bias, a parallel layer, the model's two hooks
+@dataclass(frozen=True)
+class ToyWindowEmaSpec:
+    """c_t = sum_j tap_j z_{t-K+1+j} over a window of K inputs z = x W^T (zeros before the sequence), then
+    s_t = d s_{t-1} + (1 - d) c_t, out_t = s_t: a window of inputs AND a running state per sequence."""
+    hidden: int
+    taps: int
+    names: Dict[str, str] = field(default_factory=lambda: {"w": "toy2.proj.weight", "taps": "toy2.taps", "decay": "toy2.decay"})
+    kind: str = "toy_window_ema"
+
+
+def make_two_state_class():
+    from xpu_serve_b200.parts.base import Mixer, StateNeed, TensorSpec
+
+    class ToyWindowEma(Mixer):
+        kind = "toy_window_ema"
+
+        @classmethod
+        def tensors(cls, spec):
+            n = spec.names
+            return {n["w"]: TensorSpec((spec.hidden, spec.hidden)), n["taps"]: TensorSpec((spec.taps,), role="vector"),
+                    n["decay"]: TensorSpec((spec.hidden,), init="ones", role="vector")}
+
+        @classmethod
+        def cache_need(cls, spec):          # two needs: the cache hands back a view with two parts
+            return (StateNeed((spec.taps - 1, spec.hidden), "float32"), StateNeed((spec.hidden,), "float32"))
+
+        def __init__(self, spec, weights, rt):
+            self.spec, self.rt = spec, rt
+            n = spec.names
+            self.w = rt.matrix(weights[n["w"]])
+            self.taps = rt.vector(weights[n["taps"]])
+            self.decay = torch.sigmoid(rt.vector(weights[n["decay"]]))
+
+        def forward(self, x, step, cache):
+            assert len(cache) == 2
+            window, ema = cache[0].storage, cache[1].storage
+            z = x.float() @ self.w.float().t()
+            slots = step.slots.long()
+            d = self.decay
+            if step.decode:                       # one token a sequence: no host-side loop, graph-safe
+                full = torch.cat([window[slots], z[:, None, :]], 1)
+                c = (full * self.taps[None, :, None]).sum(1)
+                s = d * ema[slots] + (1 - d) * c
+                window.index_copy_(0, slots, full[:, 1:])
+                ema.index_copy_(0, slots, s)
+                return s.to(self.rt.act_dtype)
+            out = torch.empty_like(z)
+            cu = np.concatenate([[0], np.cumsum(step.q_lens_host)])
+            for i in range(step.n_seqs):
+                full = torch.cat([window[slots[i]], z[int(cu[i]):int(cu[i + 1])]], 0)
+                s = ema[slots[i]]
+                K = self.spec.taps
+                for t in range(int(cu[i + 1] - cu[i])):
+                    c = (full[t:t + K] * self.taps[:, None]).sum(0)
+                    s = d * s + (1 - d) * c
+                    out[int(cu[i]) + t] = s
+                window[slots[i]] = full[-(K - 1):]
+                ema[slots[i]] = s
+            return out.to(self.rt.act_dtype)
+
+    return ToyWindowEma
+
+
+def make_toy_norm_class():
+    from xpu_serve_b200.parts.base import Norm, TensorSpec
+
+    class ToyLayerNorm(Norm):
+        """(x - mean) / sqrt(var + eps) * w + b: a mean and a bias, which RMSNorm has not."""
+        kind = "toy_layernorm"
+
+        @classmethod
+        def tensors(cls, spec, weight_name):
+            return {weight_name: TensorSpec((spec.width,), init="ones", role="vector"),
+                    weight_name.replace("weight", "bias"): TensorSpec((spec.width,), role="vector")}
+
+        def __init__(self, spec, weights, weight_name, rt):
+            super().__init__(spec, weights, weight_name, rt)
+            self.w = rt.vector(weights[weight_name])
+            self.b = rt.vector(weights[weight_name.replace("weight", "bias")])
+
+        def normed(self, x):
+            x = x.float()
+            x = x - x.mean(-1, keepdim=True)
+            return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + self.spec.eps) * self.w + self.b).to(self.rt.act_dtype)
+
+    return ToyLayerNorm
+
+
+def make_toy_parallel_class():
+    from xpu_serve_b200 import registry
+
+    class ToyParallel:
+        """h = h + mixer(norm(h)) + ffn(norm(h)): one norm feeds both parts, which join the stream together."""
+        kind = "toy_parallel"
+
+        @classmethod
+        def tensors(cls, layer):
+            out = dict(registry.norm_class(layer.norm.kind).tensors(layer.norm, layer.names["pre_mixer"]))
+            out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
+            out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
+            return out
+
+        @classmethod
+        def cache_need(cls, layer):
+            return registry.mixer_class(layer.mixer.kind).cache_need(layer.mixer)
+
+        def __init__(self, layer, weights, rt):
+            self.norm = registry.norm_class(layer.norm.kind)(layer.norm, weights, layer.names["pre_mixer"], rt)
+            self.mixer = registry.mixer_class(layer.mixer.kind)(layer.mixer, weights, rt)
+            self.ffn = registry.ffn_class(layer.ffn.kind)(layer.ffn, weights, rt)
+            self.first_norm = self.norm
+
+        def forward(self, stream, step, cache, next_norm=None):
+            x = stream.norm(self.norm)
+            stream.add(self.mixer.forward(x, step, cache))
+            stream.add(self.ffn.forward(x, step))
+
+    return ToyParallel
+
+
+EXTENDED = {"embed_scale": 3.0, "logit_cap": 2.0, "taps": 4}
+
+
+def extended_model(dtype):
+    """Layer 0: the two-state toy mixer between toy layer norms; layer 1: attention and SwiGLU side by side (the
+    toy parallel arrangement, RMSNorm); layer 2: the library's conv layer as it is. A toy layer norm at the end,
+    an embedding multiplier and a logit cap."""
+    from xpu_serve_b200 import registry
+    from xpu_serve_b200.config import Lfm3Config
+    from xpu_serve_b200.config.spec import LayerCall, NormSpec
+    from xpu_serve_b200.engine.model import Model
+    from xpu_serve_b200.weights import random_tensors
+    for table, kind, make in ((registry.mixer_class, "toy_window_ema", make_two_state_class),
+                              (registry.norm_class, "toy_layernorm", make_toy_norm_class),
+                              (registry.arrangement_class, "toy_parallel", make_toy_parallel_class)):
+        try:
+            table(kind)
+        except KeyError:
+            {"toy_window_ema": registry.register_mixer, "toy_layernorm": registry.register_norm,
+             "toy_parallel": registry.register_arrangement}[kind](kind, make())
+    base = Lfm3Config.from_json(tiny.CONFIG_A).model_spec()
+    attn = next(l for l in base.layers if l.mixer.kind == "attention")
+    conv = next(l for l in base.layers if l.mixer.kind == "short_conv")
+    ln = NormSpec(base.hidden, 1e-5, kind="toy_layernorm")
+    layers = (replace(conv, prefix="layers.0.", mixer=ToyWindowEmaSpec(base.hidden, EXTENDED["taps"]), norm=ln),
+              replace(attn, prefix="layers.1.", kind="toy_parallel"),
+              replace(conv, prefix="layers.2."))
+    spec = replace(base, layers=layers, order=(LayerCall(0), LayerCall(1), LayerCall(2)), final_norm=ln,
+                   embed_scale=EXTENDED["embed_scale"], logit_cap=EXTENDED["logit_cap"])
+    scale = dict(tiny.LIVELY, **{"norm.bias": 20.0, "toy2.taps": 25.0})
+    scale["embed_tokens.weight"] = 2.0
+    tensors = dict(random_tensors(spec, 13, "float32", norm_range=(0.5, 1.5), scale=scale))
+    weights = {k[len("model."):]: v for k, v in tensors.items()}
+    return spec, tensors, Model(spec, weights, dtype=dtype)
+
+
+def plain_extended_forward(tensors, ids, embed_scale=EXTENDED["embed_scale"], logit_cap=EXTENDED["logit_cap"]):
+    W = {k: v.double().numpy() for k, v in tensors.items()}
+    cfg = tiny.CONFIG_A
+    H, Hq, Hkv, D, K, eps = 64, 4, 2, 16, 3, cfg["norm_eps"]
+    inv = plain.rope_inv_freq(cfg["rope_theta"], D, D // 2)
+
+    def layer_norm(x, name):
+        x = x - x.mean(-1, keepdims=True)
+        return x / np.sqrt((x * x).mean(-1, keepdims=True) + 1e-5) * W[name + "weight"] + W[name + "bias"]
+
+    h = W["model.embed_tokens.weight"][np.asarray(ids)] * embed_scale
+    T = len(ids)
+    # layer 0: two-state mixer between layer norms
+    L = "model.layers.0."
+    z = layer_norm(h, L + "operator_norm.") @ W[L + "toy2.proj.weight"].T
+    taps, Kt = W[L + "toy2.taps"], EXTENDED["taps"]
+    d = 1 / (1 + np.exp(-W[L + "toy2.decay"]))
+    full = np.concatenate([np.zeros((Kt - 1, H)), z], 0)
+    s, m = np.zeros(H), np.zeros_like(z)
+    for t in range(T):
+        s = d * s + (1 - d) * (full[t:t + Kt] * taps[:, None]).sum(0)
+        m[t] = s
+    h = h + m
+    h = h + plain.swiglu(layer_norm(h, L + "ffn_norm."), W, L)
+    # layer 1: attention and feed-forward from the same normed input
+    L = "model.layers.1."
+    x = plain.rms_norm(h, W[L + "operator_norm.weight"], eps)
+    h = h + plain.self_attention(x, W, L, Hq, Hkv, D, eps, inv, 0, False) + plain.swiglu(x, W, L)
+    # layer 2: the library's conv layer
+    L = "model.layers.2."
+    h = h + plain.short_conv(plain.rms_norm(h, W[L + "operator_norm.weight"], eps), W, L, H, K, False)
+    h = h + plain.swiglu(plain.rms_norm(h, W[L + "ffn_norm.weight"], eps), W, L)
+    logits = layer_norm(h, "model.embedding_norm.") @ W["model.embed_tokens.weight"].T
+    return logit_cap * np.tanh(logits / logit_cap) if logit_cap > 0 else logits
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_states_a_toy_norm_a_parallel_layer_and_the_model_hooks(dtype):
+    """Registered from here, none of them in the package: a mixer that declares two states (a window and a running
+    mean), a norm with mean and bias, a layer arrangement that runs mixer and feed-forward side by side; and the
+    model's own optional hooks (embedding multiplier, logit cap). Whole, one by one and in an unequal batch
+    through the decode graphs, against a plain restatement; slots used again start from zero."""
+    spec, tensors, model = extended_model(dtype)
+    needs, _ = model.cache_needs()
+    assert isinstance(needs[0], tuple) and len(needs[0]) == 2
+    cache = model.new_cache(1024)
+    assert len(cache.views[0]) == 2 and cache.views[0][0].storage.shape[1:] == (EXTENDED["taps"] - 1, 64)
+    prompts = [tiny.prompt("A", n, salt=50 + i) for i, n in enumerate((11, 34, 4))]
+    refs = [plain_extended_forward(tensors, p) for p in prompts]
+    # the hooks matter: without the cap, or without the multiplier, the logits are others
+    assert gap_of(plain_extended_forward(tensors, prompts[0], logit_cap=0.0), refs[0]) > 5e-2
+    assert gap_of(plain_extended_forward(tensors, prompts[0], embed_scale=1.0), refs[0]) > 5e-2
+    tol = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * 3) * 2 ** -9
+    worst = 0.0
+    # whole
+    for p, r in zip(prompts, refs):
+        (s,) = cache.open(1)
+        lg = model.step(cache, [s], [p], [list(range(len(p)))]).cpu().numpy()
+        cache.close([s])
+        worst = max(worst, gap_of(lg, r))
+    # one by one (decode graphs from the first token on), then an unequal batch whose shorter sequences end earlier
+    (s,) = cache.open(1)
+    rows = [model.step(cache, [s], [[t]]).cpu().numpy()[0] for t in prompts[0]]
+    cache.close([s])
+    worst = max(worst, gap_of(np.stack(rows), refs[0]))
+    slots = cache.open(3)
+    heads = [5, 20, 1]
+    got = [[] for _ in prompts]
+    lg = model.step(cache, slots, [p[:h] for p, h in zip(prompts, heads)], [list(range(h)) for h in heads]).cpu().numpy()
+    o = 0
+    for i, h in enumerate(heads):
+        got[i].append(lg[o:o + h])
+        o += h
+    at, live = list(heads), [0, 1, 2]
+    while live:
+        lg = model.step(cache, [slots[i] for i in live], [[prompts[i][at[i]]] for i in live]).cpu().numpy()
+        for r, i in enumerate(live):
+            got[i].append(lg[r:r + 1])
+            at[i] += 1
+        done = [i for i in live if at[i] == len(prompts[i])]
+        cache.close([slots[i] for i in done])
+        live = [i for i in live if i not in done]
+    for g, r in zip(got, refs):
+        worst = max(worst, gap_of(np.concatenate(g, 0), r))
+    print(f"GAP toy-extended {dtype} gap={worst:.3e}")
+    assert worst <= tol
+    assert len(model._graphs) == 1, "the single tokens did not go through decode graphs"
+    cache.check()
+    assert cache.slots.held_count == 0
+
+
 # ------------------------------------------------------------------------------ long runs, first tokens
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["R", "W"])

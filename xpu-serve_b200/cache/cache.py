@@ -34,8 +34,9 @@ def _ceil_div(a: int, b: int) -> int:
 
 
 class KVGroup:
-    def __init__(self, need: KVNeed, calls: List[int], n_pages: int, page_size: int, max_slots: int,
+    def __init__(self, need: KVNeed, calls: List[Tuple[int, int]], n_pages: int, page_size: int, max_slots: int,
                  max_seq_pages: int, dtype: torch.dtype, device):
+        """`calls`: the (layer call, index of the need in that call's declaration) pairs this group serves."""
         self.need = need
         self.calls = list(calls)
         self.page_size = page_size
@@ -48,7 +49,7 @@ class KVGroup:
         self.version = 0      # grows whenever a row of `table` changes (a staged copy of the table is then stale)
         # one page more than the pool hands out: padding rows of a fixed-size batch write there
         self.dummy_page = n_pages
-        self.storage: Dict[int, torch.Tensor] = {
+        self.storage: Dict[Tuple[int, int], torch.Tensor] = {
             c: torch.zeros((n_pages + 1, 2, need.kv_heads, page_size, need.head_dim),
                            dtype=dtype, device=device) for c in calls}
 
@@ -102,12 +103,12 @@ class KVGroup:
 
 
 class StateGroup:
-    def __init__(self, need: StateNeed, calls: List[int], max_slots: int, compute_dtype: torch.dtype, device):
+    def __init__(self, need: StateNeed, calls: List[Tuple[int, int]], max_slots: int, compute_dtype: torch.dtype, device):
         self.need = need
         self.calls = list(calls)
         dtype = torch.float32 if need.dtype == "float32" else compute_dtype
         # one row more than there are slots: the state of padding rows
-        self.storage: Dict[int, torch.Tensor] = {
+        self.storage: Dict[Tuple[int, int], torch.Tensor] = {
             c: torch.zeros((max_slots + 1, *need.shape), dtype=dtype, device=device) for c in calls}
 
     def zero(self, slots: torch.Tensor) -> None:
@@ -117,20 +118,37 @@ class StateGroup:
 
 @dataclass
 class CallView:
-    """What a mixer is handed for one layer call."""
+    """What a mixer is handed for one layer call: the storage of its need. A mixer that declared several
+    needs finds them in declaration order as `view[0]`, `view[1]`, ... (`view.storage` is then the first's)."""
     call: int
     group: int                 # index into Cache.groups; -1 for none
     storage: Optional[torch.Tensor]
     need: object
     owner: bool                # False when this call reads another call's cache
+    parts: Tuple["CallView", ...] = ()
+
+    def __getitem__(self, k: int) -> "CallView":
+        return self.parts[k] if self.parts else (self,)[k]
+
+    def __len__(self) -> int:
+        return len(self.parts) if self.parts else (0 if self.storage is None else 1)
+
+
+def _as_needs(need) -> Tuple[object, ...]:
+    """A call's declaration as a tuple of needs: none, one, or several."""
+    if need is None:
+        return ()
+    if isinstance(need, (tuple, list)):
+        return tuple(need)
+    return (need,)
 
 
 _SERIALS = itertools.count(1)
 
 
 class Cache:
-    """needs[i] is the need of call i of the running order (None: nothing kept), and
-    shares[i] the call whose cache call i reads (None: its own)."""
+    """needs[i] is what call i of the running order keeps per sequence (None: nothing; a KVNeed or a
+    StateNeed; or a tuple of them), and shares[i] the call whose cache call i reads (None: its own)."""
 
     def __init__(self, needs: Sequence[object], shares: Sequence[Optional[int]], max_tokens: int, *,
                  page_size: int = PAGE_SIZE, max_slots: Optional[int] = None,
@@ -150,29 +168,39 @@ class Cache:
         self.dummy_slot = self.max_slots      # never handed out; padding rows of a fixed-size batch use it
         self.lens = np.zeros(self.max_slots, dtype=np.int64)
         self.groups: List[object] = []
-        by_need: Dict[object, List[int]] = {}
-        for call, (need, share) in enumerate(zip(needs, shares)):
-            if need is not None and share is None:
-                by_need.setdefault(need, []).append(call)
-        self._group_of_call: Dict[int, int] = {}
-        for need, calls in by_need.items():
+        needs = [_as_needs(n) for n in needs]
+        # storage is keyed by (call, index of the need within the call's declaration)
+        by_need: Dict[object, List[Tuple[int, int]]] = {}
+        for call, (declared, share) in enumerate(zip(needs, shares)):
+            if share is None:
+                for k, need in enumerate(declared):
+                    by_need.setdefault(need, []).append((call, k))
+        self._group_of: Dict[Tuple[int, int], int] = {}
+        for need, keys in by_need.items():
             if isinstance(need, KVNeed):
-                g: object = KVGroup(need, calls, n_pages, page_size, self.max_slots, max_seq_pages, dtype, self.device)
+                g: object = KVGroup(need, keys, n_pages, page_size, self.max_slots, max_seq_pages, dtype, self.device)
             elif isinstance(need, StateNeed):
-                g = StateGroup(need, calls, self.max_slots, dtype, self.device)
+                g = StateGroup(need, keys, self.max_slots, dtype, self.device)
             else:
-                raise TypeError(f"call {calls[0]} declares an unknown cache need {need!r}")
-            for c in calls:
-                self._group_of_call[c] = len(self.groups)
+                raise TypeError(f"call {keys[0][0]} declares an unknown cache need {need!r}")
+            for key in keys:
+                self._group_of[key] = len(self.groups)
             self.groups.append(g)
         self.views: List[CallView] = []
-        for call, (need, share) in enumerate(zip(needs, shares)):
+        for call, (declared, share) in enumerate(zip(needs, shares)):
             src = call if share is None else share
-            if src in self._group_of_call and (share is None or needs[call] is not None):
-                gi = self._group_of_call[src]
-                self.views.append(CallView(call, gi, self.groups[gi].storage[src], self.groups[gi].need, share is None))
-            else:
+            parts = []
+            # a reader of another call's cache that declares no need of its own reads nothing
+            for k in range(len(needs[src]) if (share is None or declared) else 0):
+                gi = self._group_of[(src, k)]
+                parts.append(CallView(call, gi, self.groups[gi].storage[(src, k)], self.groups[gi].need, share is None))
+            if not parts:
                 self.views.append(CallView(call, -1, None, None, True))
+            elif len(parts) == 1:
+                self.views.append(parts[0])
+            else:
+                first = parts[0]
+                self.views.append(CallView(call, first.group, first.storage, first.need, first.owner, tuple(parts)))
         self.kv_groups = [i for i, g in enumerate(self.groups) if isinstance(g, KVGroup)]
         self._any_window = any(self.groups[i].need.window > 0 for i in self.kv_groups)
         self._last_slots: Optional[tuple] = None       # the batch of the last finished step (decode fast path)

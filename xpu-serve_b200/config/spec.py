@@ -98,6 +98,7 @@ class LayerSpec:
     names: Dict[str, str] = field(default_factory=lambda: {
         "pre_mixer": "operator_norm.weight", "post_mixer": "post_operator_norm.weight",
         "pre_ffn": "ffn_norm.weight", "post_ffn": "post_ffn_norm.weight"})
+    kind: str = "pre_norm"   # the arrangement (registry.register_arrangement); the formula above is "pre_norm"
 
 
 @dataclass(frozen=True)
@@ -121,6 +122,8 @@ class ModelSpec:
     final_norm: NormSpec
     tied_head: bool
     init_std: float = 0.02   # random-weights mode: matrices and tables ~ N(0, init_std)
+    embed_scale: float = 1.0  # the embedding rows are multiplied by it (1: as stored, LFM3's)
+    logit_cap: float = 0.0    # > 0: logits = cap * tanh(logits / cap) (0: none, LFM3's)
     prefixes: Tuple[str, ...] = ("model.",)   # tried in turn for "<prefix>embed_tokens.weight"
     names: Dict[str, str] = field(default_factory=lambda: {
         "embed": "embed_tokens.weight", "final_norm": "embedding_norm.weight",

@@ -20,7 +20,7 @@ void xs_set_error(const char* fmt, ...) {
 
 XS_API const char* xs_last_error() { return g_error; }
 
-XS_API int xs_abi_version() { return 4; }
+XS_API int xs_abi_version() { return 5; }
 
 int g_xs_pdl = 1;
 // 1: kernels of a step may overlap their start with the previous kernel's end (programmatic
@@ -32,25 +32,42 @@ XS_API int xs_set_pdl(int on) {
 }
 
 // ------------------------------------------------------------------ embedding
-// h[t, :] = table[ids[t], :] as float32 (no scaling: src/models/lfm3/lfm3_decoder.cpp:50).
+// h[t, :] = table[ids[t], :] * scale as float32 (LFM3: scale 1, src/models/lfm3/lfm3_decoder.cpp:50).
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int32_t* __restrict__ ids,
-                             float* __restrict__ h, int T, int H) {
+                             float* __restrict__ h, int T, int H, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const TW* row = table + (int64_t)ids[t] * H;
     float* out = h + (int64_t)t * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = to_f32(row[c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = to_f32(row[c]) * scale;
 }
 
-XS_API int xs_embed(const void* table, int table_dtype, const int32_t* ids, float* h, int T, int H,
+// logits = cap * tanh(logits / cap), in place: a soft limit that some architectures put on their logits.
+__global__ void logit_cap_kernel(float* __restrict__ logits, int64_t n, float cap, float inv_cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        logits[i] = cap * tanhf(logits[i] * inv_cap);
+}
+
+XS_API int xs_embed(const void* table, int table_dtype, const int32_t* ids, float* h, int T, int H, float scale,
                     cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && H > 0, "embed: %d tokens of width %d", T, H);
     XS_DISPATCH_DTYPE(table_dtype, TW,
-                      xs_launch(embed_kernel<TW>, dim3(T), dim3(256), 0, stream, (const TW*)table, ids, h, T, H));
+                      xs_launch(embed_kernel<TW>, dim3(T), dim3(256), 0, stream, (const TW*)table, ids, h, T, H, scale));
     XS_LAUNCH_CHECK("embed");
+    return 0;
+}
+
+XS_API int xs_logit_cap(float* logits, int64_t n, float cap, cudaStream_t stream) {
+    if (n == 0) return 0;
+    XS_REQUIRE(n > 0 && cap > 0.0f, "logit cap: %lld values, cap %g", (long long)n, (double)cap);
+    const int blocks = (int)(n / 1024 < 1 ? 1 : (n / 1024 > 1184 ? 1184 : n / 1024));
+    xs_launch(logit_cap_kernel, dim3(blocks), dim3(256), 0, stream, logits, n, cap, 1.0f / cap);
+    XS_LAUNCH_CHECK("logit_cap");
     return 0;
 }
 

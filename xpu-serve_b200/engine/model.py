@@ -25,7 +25,7 @@ from ..cache import Cache, CacheError
 from ..config.json_util import ConfigError, read_json
 from ..config.spec import ModelSpec
 from ..ops import lib as ops
-from ..parts.block import Block, ResidualStream
+from ..parts.block import ResidualStream
 from ..weights.loader import load_weights
 from .runtime import Runtime, Workspace
 from .step import StepContext, StepStager
@@ -62,11 +62,11 @@ class Model:
         rt = self.rt
         self.embed = rt.matrix(weights[spec.names["embed"]])
         self.head = self.embed if spec.tied_head else rt.matrix(weights[spec.names["head"]])
-        self.final_norm = rt.vector(weights[spec.names["final_norm"]])
-        self.blocks: List[Block] = []
+        self.final_norm = registry.norm_class(spec.final_norm.kind)(spec.final_norm, weights, spec.names["final_norm"], rt)
+        self.blocks: List[object] = []
         for layer in spec.layers:
             own = {k[len(layer.prefix):]: v for k, v in weights.items() if k.startswith(layer.prefix)}
-            self.blocks.append(Block(layer, own, rt))
+            self.blocks.append(registry.arrangement_class(layer.kind)(layer, own, rt))
         self.stager = StepStager(rt.device)
         # Decode steps are launch-bound (some 150 small kernels): they are captured once per batch
         # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
@@ -86,8 +86,8 @@ class Model:
     def cache_needs(self):
         needs, shares = [], []
         for call in self.spec.order:
-            mixer = self.spec.layers[call.layer].mixer
-            needs.append(registry.mixer_class(mixer.kind).cache_need(mixer))
+            layer = self.spec.layers[call.layer]
+            needs.append(registry.arrangement_class(layer.kind).cache_need(layer))
             shares.append(call.cache_of)
         return needs, shares
 
@@ -255,21 +255,24 @@ class Model:
     def forward(self, ctx: StepContext, cache: Cache) -> torch.Tensor:
         rt, spec = self.rt, self.spec
         h = rt.ws.get("stream", (ctx.n_tokens, spec.hidden), torch.float32)
-        ops.embed(self.embed, ctx.tokens, h)
+        ops.embed(self.embed, ctx.tokens, h, spec.embed_scale)
         stream = ResidualStream(h, rt)
         last = len(spec.order) - 1
         for i, call in enumerate(spec.order):
             # the norm that reads the stream after this block, for products that carry the norm with them
-            next_w = self.blocks[spec.order[i + 1].layer].w_pre_mixer if i < last else self.final_norm
-            self.blocks[call.layer].forward(stream, ctx, cache.views[i], next_w)
+            next_norm = self.blocks[spec.order[i + 1].layer].first_norm if i < last else self.final_norm
+            self.blocks[call.layer].forward(stream, ctx, cache.views[i], next_norm)
         if ctx.want_rows.numel() == 0:
-            stream.flush()
+            stream.flush(self.final_norm)
             return torch.empty((0, spec.vocab), dtype=torch.float32, device=rt.device)
         if ctx.want_all and stream.fuses():
-            y = stream.norm_input(self.final_norm, spec.final_norm.eps, lazy=True)
+            y = stream.norm_input(self.final_norm, lazy=True)
         else:
-            y = stream.norm(self.final_norm, spec.final_norm.eps, ctx.want_rows)
-        return rt.linear(y, self.head, "logits", out_dtype=torch.float32)
+            y = stream.norm(self.final_norm, ctx.want_rows)
+        logits = rt.linear(y, self.head, "logits", out_dtype=torch.float32)
+        if spec.logit_cap > 0.0:
+            ops.logit_cap(logits, spec.logit_cap)
+        return logits
 
 
 def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> Model:

@@ -31,7 +31,8 @@ launches = 0      # kernels launched through this module since import (a graph r
 def _signatures(lib) -> None:
     P, I, L, F = c_void_p, c_int, c_int64, c_float
     sig = {
-        "xs_embed": [P, I, P, P, I, I, P],
+        "xs_embed": [P, I, P, P, I, I, F, P],
+        "xs_logit_cap": [P, L, F, P],
         "xs_add_rmsnorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
         "xs_silu_mul": [P, P, I, I, I, L, I, P],
         "xs_zero_rows": [P, P, I, L, P],
@@ -153,10 +154,17 @@ def uniform(seed: int, counter: int) -> float:
 
 
 # ------------------------------------------------------------------ wrappers
-def embed(table: torch.Tensor, ids: torch.Tensor, h: torch.Tensor) -> None:
+def embed(table: torch.Tensor, ids: torch.Tensor, h: torch.Tensor, scale: float = 1.0) -> None:
+    """h[t] = table[ids[t]] * scale, float32."""
     _need(table, "embedding table"); _need(ids, "ids", torch.int32); _need(h, "h", torch.float32)
     T, H = h.shape
-    _check(load().xs_embed(table.data_ptr(), _code(table), ids.data_ptr(), h.data_ptr(), T, H, _stream()))
+    _check(load().xs_embed(table.data_ptr(), _code(table), ids.data_ptr(), h.data_ptr(), T, H, float(scale), _stream()))
+
+
+def logit_cap(logits: torch.Tensor, cap: float) -> None:
+    """logits = cap * tanh(logits / cap), in place."""
+    _need(logits, "logits", torch.float32)
+    _check(load().xs_logit_cap(logits.data_ptr(), logits.numel(), float(cap), _stream()))
 
 
 def add_rmsnorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[torch.Tensor],

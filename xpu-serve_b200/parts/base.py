@@ -7,12 +7,24 @@ a model folder can be checked, or written with random weights, on any machine.
 Interfaces
 ----------
 Mixer:        tensors(spec) -> {relative name: TensorSpec}
-              cache_need(spec) -> KVNeed | StateNeed | None
+              cache_need(spec) -> None | KVNeed | StateNeed | a tuple of those (a mixer that keeps
+                                  several things per sequence: a window of inputs and a running
+                                  state, keys/values and a state, ...)
               __init__(spec, weights, rt)          weights: {relative name: device tensor}
-              forward(x, step, cache) -> [tokens, hidden]   x is the normed stream
+              forward(x, step, cache) -> [tokens, hidden]   x is the normed stream; `cache` is the
+                                  view of this call's storage (cache.CallView): `cache.storage`
+                                  for one need, `cache[k].storage` for the k-th of several
 FeedForward:  tensors(spec); __init__(spec, weights, rt); forward(y, step) -> [tokens, hidden]
-Position:     __init__(spec, rt, max_position); table() -> device tensors the mixer passes
-              to its kernels
+Position:     __init__(spec, rt); table(n_positions) -> device tensor the mixer passes to its
+              kernels
+Norm:         tensors(spec, weight_name) -> {relative name: TensorSpec}
+              __init__(spec, weights, weight_name, rt)
+              normed(x) -> the normed rows of x, float32 or the activation type
+              (optional) add_norm(h, branch, post, y, rows): h += post(branch); y = self(h[rows])
+              in one pass; the base class does it in steps through `normed`
+Arrangement   (of one layer: which norm feeds which part and how branches join the stream):
+              tensors(layer) ; cache_need(layer) ; __init__(layer, weights, rt) ;
+              forward(stream, step, cache, next_norm=None) ; `first_norm`
 Optional, for decode steps (few rows): a part whose class sets `fuses_norm = True` takes
 `forward(x, step, cache, into=None)` (feed-forward: `forward(y, step, into=None)`). Its x may then be
 a parts.block.Prenormed (the stream times the norm's weight, with the row scale still to apply),
@@ -71,3 +83,28 @@ class Mixer(Part):
 class FeedForward(Part):
     def forward(self, y, step):
         raise NotImplementedError
+
+
+class Norm(Part):
+    """A normalisation over the last dimension. A new kind implements `tensors` and `normed`; `add_norm`
+    (what the residual stream calls) then works through them. `carried` says whether the few-row products
+    can carry this norm across themselves (RMSNorm only: see parts/block.py)."""
+    carried: bool = False
+
+    @classmethod
+    def tensors(cls, spec, weight_name: str) -> Dict[str, TensorSpec]:
+        return {weight_name: TensorSpec((spec.width,), init="ones", role="vector")}
+
+    def __init__(self, spec, weights, weight_name: str, rt):
+        self.spec, self.rt = spec, rt
+
+    def normed(self, x):
+        raise NotImplementedError
+
+    def add_norm(self, h, branch, post: Optional["Norm"], y, rows) -> None:
+        """h (the float32 stream) += post(branch) (branch alone without `post`); then y = self(h), of the
+        rows `rows` only when given. `branch` or `y` may be None (no branch pending; only the sum wanted)."""
+        if branch is not None:
+            h.add_(post.normed(branch).float() if post is not None else branch.float())
+        if y is not None:
+            y.copy_(self.normed(h if rows is None else h.index_select(0, rows.long())))

@@ -12,16 +12,23 @@ Decode steps (few rows, bfloat16, no sandwich norms) go without that kernel: the
 ends a branch adds its result to the stream in its epilogue and leaves, beside it, the stream
 times the next norm's weight and per-tile sums of squares; the product that starts the next
 branch reads those and scales its result by each row's 1 / rms (`Prenormed`, `StreamSink`;
-the kernel side is csrc/gemm_small_m.cu). Parts opt in with `fuses_norm`.
+the kernel side is csrc/gemm_small_m.cu). Parts opt in with `fuses_norm`; it applies to norms that
+say `carried` (RMSNorm).
+
+The norms are parts too (parts/norm.py, registry.register_norm): the stream only calls their
+`add_norm`. The arrangement itself is registered (`registry.register_arrangement`): `Block` is
+"pre_norm"; another wiring of the same parts (post-norm, mixer and feed-forward side by side) is
+another class with the same five members: tensors(layer), cache_need(layer), __init__(layer,
+weights, rt), forward(stream, step, cache, next_norm), first_norm.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
 from .. import registry
-from ..ops import lib as ops
+from .base import Norm, TensorSpec
 
 
 class Prenormed:
@@ -40,8 +47,10 @@ class Prenormed:
 class StreamSink:
     """Where a part's last product goes when it fuses: into the stream, inside the product's kernel."""
 
-    def __init__(self, stream: "ResidualStream", next_w: Optional[torch.Tensor]):
-        self.stream, self.next_w = stream, next_w
+    def __init__(self, stream: "ResidualStream", next_norm: Optional[Norm]):
+        """`next_norm`: the norm that reads the stream next, if the products can carry it (an RMSNorm)."""
+        self.stream = stream
+        self.next_w = next_norm.w if next_norm is not None and next_norm.carried else None
 
     def product(self, act: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
         st = self.stream
@@ -49,7 +58,7 @@ class StreamSink:
         st.flush()
         if not rt.few_rows(act, w):
             st._pre = None
-            st.add(rt.linear(act, w, "branch_out", bias), None, 0.0)
+            st.add(rt.linear(act, w, "branch_out", bias))
             return
         M, N = st.h.shape
         if self.next_w is None:
@@ -66,19 +75,25 @@ class StreamSink:
 class ResidualStream:
     def __init__(self, h: torch.Tensor, rt):
         self.h, self.rt = h, rt
-        self._pending = None      # (branch, post_w, eps_post)
+        self._pending = None      # (branch, the norm it passes through before it joins the stream, or None)
         self._pre = None          # (norm weight, stream * weight, sums of squares) left by the last fused product
         self._flip = 0
+        self._plain_add: Optional[Norm] = None
 
-    def add(self, branch: torch.Tensor, post_w: Optional[torch.Tensor], eps_post: float) -> None:
+    def add(self, branch: torch.Tensor, post: Optional[Norm] = None) -> None:
         if self._pending is not None:
             self.flush()
-        self._pending = (branch, post_w, eps_post)
+        self._pending = (branch, post)
 
-    def flush(self) -> None:
+    def flush(self, norm: Optional[Norm] = None) -> None:
+        """Joins the pending branch to the stream now. `norm`: any norm of the model (its `add_norm` does the
+        sum); without one the last norm that read the stream is used."""
         if self._pending is not None:
-            m, post_w, eps_post = self._pending
-            ops.add_rmsnorm(self.h, m, post_w, None, None, None, eps_post, eps_post)
+            m, post = self._pending
+            norm = norm or post or self._plain_add
+            if norm is None:
+                raise RuntimeError("a branch is pending but no norm has read the stream yet")
+            norm.add_norm(self.h, m, post, None, None)
             self._pending = None
             self._pre = None
 
@@ -87,56 +102,81 @@ class ResidualStream:
         rt = self.rt
         return (rt.mode == "bfloat16" and rt.fuse_norms and self.h.shape[0] <= rt.small_m and self.h.shape[1] % 8 == 0)
 
-    def sink(self, next_w: Optional[torch.Tensor]) -> StreamSink:
-        return StreamSink(self, next_w)
+    def sink(self, next_norm: Optional[Norm]) -> StreamSink:
+        return StreamSink(self, next_norm)
 
-    def norm_input(self, w: torch.Tensor, eps: float, lazy: bool):
+    def norm_input(self, norm: Norm, lazy: bool):
         """What a part reads: the normed stream, or (lazy, and the last fused product prepared for this very
-        weight) the stream times the weight with its row scale pending."""
-        if lazy and self._pending is None and self._pre is not None and self._pre[0] is w:
-            return Prenormed(self._pre[1], self._pre[2], self.h.shape[1], eps)
-        return self.norm(w, eps)
+        norm) the stream times the norm's weight with its row scale pending."""
+        if (lazy and norm.carried and self._pending is None and self._pre is not None and self._pre[0] is norm.w):
+            return Prenormed(self._pre[1], self._pre[2], self.h.shape[1], norm.eps)
+        return self.norm(norm)
 
-    def norm(self, w: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """RMSNorm of the stream (after any pending branch joined it), in the activation type.
+    def norm(self, norm: Norm, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`norm` of the stream (after any pending branch joined it), in the activation type.
         With `rows`, only those rows, packed."""
         n = self.h.shape[0] if rows is None else rows.numel()
         self._flip ^= 1
         y = self.rt.ws.get(f"normed{self._flip}", (n, self.h.shape[1]), self.rt.act_dtype)
-        m, post_w, eps_post = self._pending if self._pending is not None else (None, None, eps)
-        ops.add_rmsnorm(self.h, m, post_w, w, y, rows, eps, eps_post)
+        m, post = self._pending if self._pending is not None else (None, None)
+        norm.add_norm(self.h, m, post, y, rows)
         if self._pending is not None:
             self._pre = None
         self._pending = None
+        self._plain_add = norm
         return y
 
 
 class Block:
+    """The pre-norm arrangement (with optional sandwich norms)."""
+    kind = "pre_norm"
+
+    @classmethod
+    def tensors(cls, layer) -> Dict[str, TensorSpec]:
+        """Relative names (under the layer's prefix) of the layer's tensors: its norms', its mixer's, its
+        feed-forward's."""
+        out: Dict[str, TensorSpec] = {}
+        norm_cls = registry.norm_class(layer.norm.kind)
+        keys = ["pre_mixer", "pre_ffn"] + (["post_mixer", "post_ffn"] if layer.sandwich else [])
+        for key in keys:
+            out.update(norm_cls.tensors(layer.norm, layer.names[key]))
+        out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
+        out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
+        return out
+
+    @classmethod
+    def cache_need(cls, layer):
+        return registry.mixer_class(layer.mixer.kind).cache_need(layer.mixer)
+
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
         """`weights`: this layer's tensors by their names under the layer's prefix."""
         self.spec, self.rt = spec, rt
         self.mixer = registry.mixer_class(spec.mixer.kind)(spec.mixer, weights, rt)
         self.ffn = registry.ffn_class(spec.ffn.kind)(spec.ffn, weights, rt)
         n = spec.names
-        self.w_pre_mixer = rt.vector(weights[n["pre_mixer"]])
-        self.w_pre_ffn = rt.vector(weights[n["pre_ffn"]])
-        self.w_post_mixer = rt.vector(weights[n["post_mixer"]]) if spec.sandwich else None
-        self.w_post_ffn = rt.vector(weights[n["post_ffn"]]) if spec.sandwich else None
-        self.eps = spec.norm.eps
+        norm_cls = registry.norm_class(spec.norm.kind)
+        self.pre_mixer = norm_cls(spec.norm, weights, n["pre_mixer"], rt)
+        self.pre_ffn = norm_cls(spec.norm, weights, n["pre_ffn"], rt)
+        self.post_mixer = norm_cls(spec.norm, weights, n["post_mixer"], rt) if spec.sandwich else None
+        self.post_ffn = norm_cls(spec.norm, weights, n["post_ffn"], rt) if spec.sandwich else None
+        self.first_norm = self.pre_mixer      # the norm that reads the stream first: what the block before may prepare
 
-    def forward(self, stream: ResidualStream, step, cache, next_w: Optional[torch.Tensor] = None) -> None:
-        """`next_w`: the weight of the norm that reads the stream after this block (the next block's, or the
-        final norm's), for the fused path; None is always right."""
-        fuse = stream.fuses() and not self.spec.sandwich
+    def forward(self, stream: ResidualStream, step, cache, next_norm: Optional[Norm] = None) -> None:
+        """`next_norm`: the norm that reads the stream after this block (the next block's first, or the
+        final norm), for the fused path; None is always right."""
+        fuse = stream.fuses() and not self.spec.sandwich and self.pre_mixer.carried
         if fuse and self.mixer.fuses_norm:
-            x = stream.norm_input(self.w_pre_mixer, self.eps, lazy=True)
-            self.mixer.forward(x, step, cache, into=stream.sink(self.w_pre_ffn))
+            x = stream.norm_input(self.pre_mixer, lazy=True)
+            self.mixer.forward(x, step, cache, into=stream.sink(self.pre_ffn))
         else:
-            x = stream.norm(self.w_pre_mixer, self.eps)
-            stream.add(self.mixer.forward(x, step, cache), self.w_post_mixer, self.eps)
+            x = stream.norm(self.pre_mixer)
+            stream.add(self.mixer.forward(x, step, cache), self.post_mixer)
         if fuse and self.ffn.fuses_norm:
-            y = stream.norm_input(self.w_pre_ffn, self.eps, lazy=True)
-            self.ffn.forward(y, step, into=stream.sink(next_w))
+            y = stream.norm_input(self.pre_ffn, lazy=True)
+            self.ffn.forward(y, step, into=stream.sink(next_norm))
         else:
-            y = stream.norm(self.w_pre_ffn, self.eps)
-            stream.add(self.ffn.forward(y, step), self.w_post_ffn, self.eps)
+            y = stream.norm(self.pre_ffn)
+            stream.add(self.ffn.forward(y, step), self.post_ffn)
+
+
+registry.register_arrangement(Block.kind, Block)

@@ -2,8 +2,8 @@
 
 `architecture_for(config_json)` dispatches on config.json's `model_type` as the
 reference's loader does (src/models/registry.cpp:70-104) and lists what is supported
-when nothing matches. Parts (mixers, feed-forwards, position encodings) register under
-the `kind` string their spec carries, so a new part is one class plus one
+when nothing matches. Parts (mixers, feed-forwards, position encodings, norms, layer
+arrangements) register under the `kind` string their spec carries, so a new part is one class plus one
 `register_*` call, in the framework or outside it.
 """
 from __future__ import annotations
@@ -24,6 +24,8 @@ _ARCHITECTURES: Dict[str, Architecture] = {}
 _MIXERS: Dict[str, type] = {}
 _FFNS: Dict[str, type] = {}
 _POSITIONS: Dict[str, type] = {}
+_NORMS: Dict[str, type] = {}
+_ARRANGEMENTS: Dict[str, type] = {}
 
 
 def register_architecture(name: str, config_class: type, aliases=()) -> None:
@@ -74,6 +76,15 @@ def register_position(kind: str, cls: type) -> None:
     _register(_POSITIONS, "position encoding", kind, cls)
 
 
+def register_norm(kind: str, cls: type) -> None:
+    _register(_NORMS, "norm", kind, cls)
+
+
+def register_arrangement(kind: str, cls: type) -> None:
+    """How one layer's norms, mixer and feed-forward are wired (parts/block.py registers "pre_norm")."""
+    _register(_ARRANGEMENTS, "layer arrangement", kind, cls)
+
+
 def mixer_class(kind: str) -> type:
     return _lookup(_MIXERS, "mixer", kind)
 
@@ -84,3 +95,11 @@ def ffn_class(kind: str) -> type:
 
 def position_class(kind: str) -> type:
     return _lookup(_POSITIONS, "position encoding", kind)
+
+
+def norm_class(kind: str) -> type:
+    return _lookup(_NORMS, "norm", kind)
+
+
+def arrangement_class(kind: str) -> type:
+    return _lookup(_ARRANGEMENTS, "layer arrangement", kind)

@@ -9,15 +9,8 @@ from .. import registry
 
 
 def layer_tensors(layer) -> Dict[str, TensorSpec]:
-    """Relative names (under the layer's prefix) of one layer's tensors."""
-    out: Dict[str, TensorSpec] = {}
-    width = layer.norm.width
-    keys = ["pre_mixer", "pre_ffn"] + (["post_mixer", "post_ffn"] if layer.sandwich else [])
-    for key in keys:
-        out[layer.names[key]] = TensorSpec((width,), init="ones", role="vector")
-    out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
-    out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
-    return out
+    """Relative names (under the layer's prefix) of one layer's tensors, as its arrangement declares them."""
+    return registry.arrangement_class(layer.kind).tensors(layer)
 
 
 def expected_tensors(spec: ModelSpec, prefix: Optional[str] = None) -> Dict[str, TensorSpec]:
@@ -27,7 +20,8 @@ def expected_tensors(spec: ModelSpec, prefix: Optional[str] = None) -> Dict[str,
     p = spec.prefixes[-1] if prefix is None else prefix
     out: Dict[str, TensorSpec] = {}
     out[p + spec.names["embed"]] = TensorSpec((spec.vocab, spec.hidden))
-    out[p + spec.names["final_norm"]] = TensorSpec((spec.final_norm.width,), init="ones", role="vector")
+    for rel, ts in registry.norm_class(spec.final_norm.kind).tensors(spec.final_norm, spec.names["final_norm"]).items():
+        out[p + rel] = ts
     if not spec.tied_head:
         out[spec.names["head"]] = TensorSpec((spec.vocab, spec.hidden))
     for layer in spec.layers:
