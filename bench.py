@@ -77,6 +77,7 @@ class ClockSampler:
     def __init__(self):
         self.rows = []
         self._proc = None
+        self._paused = False
 
     def start(self):
         try:
@@ -89,7 +90,14 @@ class ClockSampler:
 
     def _read(self):
         for line in self._proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            if not self._paused:
+                self.rows.append([c.strip() for c in line.split(",")])
+
+    def pause(self):
+        self._paused = True
+
+    def resume(self):
+        self._paused = False
 
     def stop(self):
         if self._proc is not None:
@@ -202,13 +210,14 @@ def _time_decode_run(model, batch, steps, warmup, V, torch, ops):
     return ms, launches
 
 
-def time_prefill(model, V: int, warmup: int, runs: int):
+def time_prefill(model, V: int, warmup: int, runs: int, tokens: int = PROMPT):
+    """Median device time (ms) of one prompt of `tokens` tokens in one step."""
     import torch
     cache = model.new_cache(CONTEXT, max_slots=1, max_seq_tokens=CONTEXT)
     times = []
     for r in range(warmup + runs):
         (slot,) = cache.open(1)
-        prompt = synthetic_prompt(V, PROMPT, 100 + r)
+        prompt = synthetic_prompt(V, tokens, 100 + r)
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -275,9 +284,9 @@ def time_e2e(folder: str, batch: int, steps: int, warmup: int, V: int):
     return batch * steps / span, h2d, 4 * batch
 
 
-def run_workload(name: str, layers=None, batch=None, new=None) -> int:
+def measure_workload(name: str, layers=None, batch=None, new=None, repeats: int = 2) -> dict:
     """A batch of unequal prompts through Engine.generate (host token ids in and out): the prompts with one new
-    token first (prefill), then the whole workload; decode time is the difference. Second of two runs."""
+    token first (prefill), then the whole workload; decode time is the difference. The last of `repeats` runs."""
     import random
     import torch
     from xpu_serve_b200 import Engine, GenerateRequest, SamplingParams
@@ -301,7 +310,7 @@ def run_workload(name: str, layers=None, batch=None, new=None) -> int:
                         max_batch=batch)
     prompts = [synthetic_prompt(V, n, i) for i, n in enumerate(lens)]
     greedy = SamplingParams(temperature=0.0)
-    for _ in range(2):
+    for _ in range(max(1, repeats)):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         first = engine.generate([GenerateRequest(p, greedy, 1, []) for p in prompts])
@@ -321,7 +330,10 @@ def run_workload(name: str, layers=None, batch=None, new=None) -> int:
     pk = peaks()
     step_bytes = nums["weight_bytes"] + (sum(lens) + batch * new // 2) * nums["kv_bytes_per_token"] + batch * nums["state_bytes"]
     achieved = step_bytes / (step_ms * 1e-3) / 1e9
-    print(json.dumps({
+    device_gb = round(torch.cuda.max_memory_allocated() / 1e9, 1)
+    del engine
+    torch.cuda.empty_cache()
+    return {
         "workload": name, "metric": "decode tok/s through Engine.generate", "value": round(batch * (new - 1) / decode_s, 1),
         "unit": "tok/s", "ms_per_step": round(step_ms, 4), "decode_steps": new, "dtype": "bf16",
         "data": "synthetic token ids, random weights N(0, 0.02)",
@@ -333,7 +345,11 @@ def run_workload(name: str, layers=None, batch=None, new=None) -> int:
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "vocab": V, "attn_layers": nums["n_attn"], "conv_layers": nums["n_conv"], "global_batch": batch,
                    "prompt_min": min(lens), "prompt_max": max(lens), "context": cfg["max_position_embeddings"]},
-        "device_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1)}))
+        "device_gb": device_gb}
+
+
+def run_workload(name: str, layers=None, batch=None, new=None) -> int:
+    print(json.dumps(measure_workload(name, layers, batch, new)))
     return 0
 
 
@@ -346,6 +362,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run only the first N layers (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    ap.add_argument("--skip-family", action="store_true",
+                    help="leave out the two other workloads of the family (2.6B shape with unequal prompts, 350M shape "
+                         "at long context), which the default run adds to `points`")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sample"],
                     help="time one part only and print a short line (for profiler captures)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
@@ -398,7 +417,11 @@ def main() -> int:
             ms = time_prefill(model, V, warmup=args.warmup, runs=args.steps)
             print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": PROMPT, "ms": round(ms, 4)}))
             return 0
-        prefill_ms = time_prefill(model, V, warmup=2, runs=3)
+        around = ClockSampler()          # clocks during the prefill and the batch 1 / 64 points (`clocks_points`)
+        around.start()
+        prefill_ms = time_prefill(model, V, warmup=3, runs=5)
+        short_ms = time_prefill(model, V, warmup=3, runs=5, tokens=128)
+        around.pause()
         pf = prefill_flops(cfg, nums, PROMPT)
 
         sampler = ClockSampler()
@@ -406,15 +429,26 @@ def main() -> int:
         ms, launches = time_decode(model, args.batch, args.steps, args.warmup, V)
         clocks = sampler.stop()
 
-        points = {}
+        points = {"prefill_128_ms": round(short_ms, 3)}
         if not args.skip_points:
+            around.resume()
             for b in (1, 64):
-                pms, _ = time_decode(model, b, max(8, args.steps // 4), 3, V)
+                pms, _ = time_decode(model, b, max(64, args.steps // 4), 3, V)
                 points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+                points[f"decode_b{b}_ms"] = round(pms, 4)
+        clocks_points = around.stop()
         del model
         torch.cuda.empty_cache()
         copy_here = copy_bandwidth_here()
         e2e_value, h2d, d2h = time_e2e(folder, args.batch, min(args.steps, CONTEXT - PROMPT - args.warmup - 2), args.warmup, V)
+    if not args.skip_family and args.layers is None:
+        # the family's two other workloads, through Engine.generate: decode ms a step and fraction of the HBM peak
+        for name, key in (("ragged_2.6b", "ragged_2_6b"), ("long_350m", "long_350m")):
+            w = measure_workload(name)
+            points[f"{key}_tok_s"] = w["value"]
+            points[f"{key}_ms"] = w["ms_per_step"]
+            points[f"{key}_frac"] = w["roofline"]["frac"]
+            points[f"{key}_prefill_tok_s"] = w["prefill"]["value"]
 
     value = args.batch * 1000.0 / ms
     # the cache grows by one position a step: the timed steps read PROMPT + warmup + steps / 2 positions on average
@@ -442,6 +476,7 @@ def main() -> int:
                      "peaks": pk["source"], "copy_gbs_here": round(copy_here, 1)},
         "points": points,
         "clocks": clocks,
+        "clocks_points": clocks_points,
         "gpu_launches": int(round(launches * args.steps)),
     }
     print(json.dumps(line))

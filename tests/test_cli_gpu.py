@@ -18,8 +18,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CLI = [sys.executable, os.path.join(ROOT, "bin", "xpu-serve")]
 
 
-def run_cli(*args):
-    p = subprocess.run(CLI + [str(a) for a in args], capture_output=True, text=True, timeout=300)
+def run_cli(*args, env=None):
+    p = subprocess.run(CLI + [str(a) for a in args], capture_output=True, text=True, timeout=300,
+                       env=None if env is None else dict(os.environ, **env))
     return p.returncode, p.stdout, p.stderr
 
 
@@ -104,3 +105,25 @@ def test_bench_prints_a_line_a_run(model):
         m = re.match(rf"run {i}: batch 1, prompt 24 tok, prefill [\d.]+ ms \([\d.]+ tok/s\) \| generated 8 tok, "
                      r"decode ([\d.]+) tok/s \| wall [\d.]+ s", l)
         assert m and float(m.group(1)) > 0, l
+
+
+def test_profile_and_sync_switches(model):
+    """XS_PROFILE=1 times every launch with CUDA events and prints the sums by kernel and sizes at exit; XS_SYNC=1
+    waits for the device after every launch (an error would carry the launch's name). Neither changes a token."""
+    args = ("run", model["folder"], "--prompt", " ".join(map(str, model["prompt"])), "--max-tokens", 16, "--precision", "bf16",
+            "--ctx", 128, "--log-level", "error")
+    rc, out, err = run_cli(*args)
+    assert rc == 0, err
+    plain_run = json.loads(out.strip().splitlines()[-1])
+    rc, out, err = run_cli(*args, env={"XS_PROFILE": "1"})
+    assert rc == 0, err
+    assert json.loads(out.strip().splitlines()[-1]) == plain_run
+    head = re.search(r"\[xpu_serve_b200 profile\] (\d+) launches, (\d+) us on the device", err)
+    assert head and int(head.group(1)) > 50 and int(head.group(2)) > 0, err[-2000:]
+    rows = re.findall(r"^\s+([\d.]+) us\s+([\d.]+) %\s+x(\d+)\s+(xs_\w+) \(([\d, -]*)\)", err, flags=re.M)
+    names = {r[3] for r in rows}
+    assert {"xs_gemm_small_m_ex", "xs_embed", "xs_qk_norm_rope_store"} <= names, names
+    assert abs(sum(float(r[1]) for r in rows) - 100.0) < 1.0
+    rc, out, err = run_cli(*args, env={"XS_SYNC": "1"})
+    assert rc == 0, err
+    assert json.loads(out.strip().splitlines()[-1]) == plain_run

@@ -219,6 +219,83 @@ def test_gemm_small_m_k_slices(M, N, K, ksplit):
     close(res, want, "float32", factor=4)
 
 
+@pytest.mark.parametrize("M,H,K,taps,bias", [(8, 2048, 2048, 3, False), (1, 64, 64, 7, True), (5, 96, 200, 2, False), (13, 160, 72, 8, True),
+                                             (8, 1024, 512, 4, False)])
+def test_gemm_small_m_with_the_convolution_behind_it(M, H, K, taps, bias):
+    """in_proj and, in the tail of the same kernel, the gated convolution of one token a sequence with its state's
+    update: against a float64 restatement, bit for bit against the convolution kernel of its own, three steps in
+    a row (the counters must come back to zero), shuffled slots, neighbouring slots untouched."""
+    lib = ops()
+    g = torch.Generator(device="cpu").manual_seed(M * H + taps)
+    w = (torch.randn(3 * H, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    b_in = torch.randn(3 * H, generator=g).to(DEV) if bias else None
+    w_t = torch.randn(taps, H, generator=g).to(DEV)
+    b_conv = torch.randn(H, generator=g).to(DEV) if bias else None
+    n_slots = M + 3
+    slots = torch.randperm(n_slots, generator=g)[:M].to(torch.int32).to(DEV)
+    state0 = torch.randn(n_slots, taps - 1, H, generator=g).to(torch.bfloat16).to(DEV)
+    fused_state, split_state = state0.clone(), state0.clone()
+    ref_state = state0.double().cpu()
+    counters = torch.zeros(max(H // 16, 1), dtype=torch.int32, device=DEV)
+    seq_of = torch.arange(M, dtype=torch.int32, device=DEV)
+    cu = torch.arange(M + 1, dtype=torch.int32, device=DEV)
+    for step in range(3):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+        bcx = torch.full((M, 3 * H), float("nan"), device=DEV, dtype=torch.bfloat16)
+        y = torch.full((M, H), float("nan"), device=DEV, dtype=torch.bfloat16)
+        lib.gemm_small_m(x, w, bcx, b_in, conv=dict(taps=w_t, bias=b_conv, state=fused_state, slots=slots, out=y, counters=counters))
+        assert int(counters.abs().sum()) == 0, "the counters were not left at zero"
+        # the same in two kernels
+        bcx2 = torch.empty_like(bcx)
+        lib.gemm_small_m(x, w, bcx2, b_in)
+        assert torch.equal(bcx, bcx2)
+        y2 = torch.empty_like(y)
+        lib.short_conv(bcx2, w_t, b_conv, split_state, seq_of, cu, slots, y2, all_single=True)
+        assert torch.equal(y, y2) and torch.equal(fused_state, split_state), "the fused tail and the kernel of its own differ"
+        # float64, from the bfloat16 values of B, C, X that both read
+        b, c, xx = bcx.double().cpu()[:, :H], bcx.double().cpu()[:, H:2 * H], bcx.double().cpu()[:, 2 * H:]
+        gg = (b * xx).to(torch.bfloat16).double()
+        sl = slots.cpu().long()
+        acc = (b_conv.double().cpu() if bias else 0) + (w_t.double().cpu()[:-1, None, :] * ref_state[sl].transpose(0, 1)).sum(0) \
+            + w_t.double().cpu()[-1] * gg
+        close(y, acc * c, "bfloat16", factor=2)
+        ref_state[sl] = torch.cat([ref_state[sl][:, 1:], gg[:, None, :]], 1)
+        assert torch.equal(fused_state.double().cpu(), ref_state), "the state holds other values than the inputs that went by"
+
+
+@pytest.mark.parametrize("M,N,K,ksplit", [(8, 65536, 256, 1), (1, 1000, 96, 1), (5, 20011, 64, 1), (16, 512, 4096, 2), (3, 48, 32, 1)])
+def test_gemm_small_m_with_the_argmax_behind_it(M, N, K, ksplit):
+    """The head product leaves every row's most likely column beside the logits: the lowest column among equal
+    values (planted: equal rows of the weight far apart, in other CTAs' tiles), rows of negative values only, three
+    calls in a row (keys and counter must come back to zero)."""
+    lib = ops()
+    g = torch.Generator(device="cpu").manual_seed(N + M)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    w[N - 2] = w[7]                                        # equal logits in tiles far apart: the lower column wins
+    w[N // 2] = w[7]
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    x[0] = (w[7].float() * 4).to(torch.bfloat16)           # row 0 points at column 7 (and its copies)
+    w, x = w.to(DEV), x.to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV) * 0.01
+    bias[N - 2] = bias[N // 2] = bias[7]
+    keys = torch.zeros(16, dtype=torch.int64, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(lib.gemm_small_m_scratch_bytes(M, N, ksplit), dtype=torch.uint8, device=DEV) if ksplit > 1 else None
+    for call in range(3):
+        shift = 0.0 if call < 2 else -50.0                 # the last call: every logit negative
+        out = torch.empty(M, N, device=DEV)
+        best = torch.full((M,), -7, dtype=torch.int32, device=DEV)
+        lib.gemm_small_m(x, w, out, bias + shift, ksplit=ksplit, scratch=scratch, argmax=(best, keys, counter))
+        assert int(keys.abs().sum()) == 0 and int(counter.item()) == 0
+        want = torch.empty(M, dtype=torch.int32, device=DEV)
+        lib.argmax(out, want)
+        assert torch.equal(best, want), (best.tolist(), want.tolist())
+        assert (out.argmax(1) == best).all() or out[0, 7] == out[0, N // 2]
+        assert best[0].item() == 7
+        if call == 2:
+            assert (out.max(1).values < 0).all()
+
+
 @pytest.mark.parametrize("F", [344, 10400])
 @pytest.mark.parametrize("M", [1, 7, 8, 13])
 def test_gemm_small_m_with_fused_activation(M, F):
@@ -455,6 +532,13 @@ def test_attention(case, kernel, dtype):
             for splits in ([1] if kernel == "generic" else [1, 2, 5, 40]):
                 out = run_attention(lib, pg, kernel, scale, window, gt, splits)
                 close(out, ref, dtype, factor=3 if dtype == "bfloat16" else 20)
+                if kernel == "mma" and splits > 1 and max(q_lens) == 1:
+                    # one token a sequence: the key splits merged by the last CTA to finish, bit for bit the combine
+                    # kernel's result, the counters back at zero, twice in a row
+                    counters = torch.zeros(len(starts) * Hkv, dtype=torch.int32, device=DEV)
+                    for _ in range(2):
+                        merged = run_attention(lib, pg, kernel, scale, window, gt, splits, counters=counters)
+                        assert torch.equal(merged, out) and int(counters.abs().sum()) == 0
 
 
 def test_attention_refuses_more_splits_than_it_combines():
@@ -509,7 +593,7 @@ def test_attention_tc(case):
             close(out, same.double(), "bfloat16", factor=3)
 
 
-def run_attention(lib, pg, kernel, scale, window, gate, splits):
+def run_attention(lib, pg, kernel, scale, window, gate, splits, counters=None):
     d = pg.dev()
     T = d["q"].shape[0]
     out = torch.full((T, pg.Hq, pg.D), float("nan"), device=DEV, dtype=d["q"].dtype)
@@ -524,7 +608,7 @@ def run_attention(lib, pg, kernel, scale, window, gate, splits):
         need = lib.attention_mma_scratch_bytes(T * pg.Hq, pg.D, splits)
         scratch = torch.full((max(need, 1),), 255, dtype=torch.uint8, device=DEV) if splits > 1 else None
         lib.attention_mma(d["q"], d["pool"], d["table"], d["cu"], d["kv_lens"], gt, out, scratch, len(pg.starts),
-                          max(pg.q_lens), pg.Hkv, 64, scale, window, splits)
+                          max(pg.q_lens), pg.Hkv, 64, scale, window, splits, counters=counters)
     return out
 
 
@@ -578,7 +662,7 @@ def test_qk_norm_rope_store(dtype, D, pairs, Hq, Hkv):
 
 # ------------------------------------------------------------------------------ short convolution
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,K", [(96, 3), (200, 4), (64, 7), (40, 2)])
+@pytest.mark.parametrize("H,K", [(96, 3), (200, 4), (64, 7), (40, 2), (72, 8), (48, 6)])
 def test_short_conv_in_steps_equals_one_pass(dtype, H, K):
     """Three sequences fed in pieces of different sizes (one of them 5, 1, 1, 3, 2 as in the reference's
     tests/unit/backend/recurrent_ops_cases.h:89-118) give what one pass over each whole sequence gives,

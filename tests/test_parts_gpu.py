@@ -324,7 +324,7 @@ def test_toy_mixer_order_and_shared_cache(dtype):
         done = [i for i in live if at[i] == len(prompts[i])]
         cache.close([slots[i] for i in done])
         live = [i for i in live if i not in done]
-    tol = 1e-5 if dtype == "float32" else 5e-2
+    tol = 6e-7 if dtype == "float32" else 8e-3          # measured on a B200: 1.8e-7 and 2.6e-3
     for g, r in zip(got, refs):
         print(f"GAP toy-mixer {dtype} gap={gap_of(np.concatenate(g, 0), r):.3e}")
         assert gap_of(np.concatenate(g, 0), r) <= tol
@@ -518,7 +518,7 @@ def test_toy_routed_ffn_and_toy_position_encoding(dtype):
         cache.close([slots[i] for i in done])
         live = [i for i in live if i not in done]
     gaps = [np.abs(np.concatenate(g, 0) - r).max(1) / np.abs(r).max() for g, r in zip(got, refs)]
-    bound = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * 3) * 2 ** -9
+    bound = 5e-7 if dtype == "float32" else 5e-3        # measured on a B200: 1.5e-7 and 1.5e-3
     worst = max(g.max() for g in gaps)
     print(f"GAP toy-routed {dtype} gap={worst:.3e}")
     assert worst <= bound
@@ -734,7 +734,7 @@ def test_two_states_a_toy_norm_a_parallel_layer_and_the_model_hooks(dtype):
     # the hooks matter: without the cap, or without the multiplier, the logits are others
     assert gap_of(plain_extended_forward(tensors, prompts[0], logit_cap=0.0), refs[0]) > 5e-2
     assert gap_of(plain_extended_forward(tensors, prompts[0], embed_scale=1.0), refs[0]) > 5e-2
-    tol = 1e-5 if dtype == "float32" else 4 * math.sqrt(10 * 3) * 2 ** -9
+    tol = 6e-7 if dtype == "float32" else 1.2e-2        # measured on a B200: 2.0e-7 and 3.9e-3
     worst = 0.0
     # whole
     for p, r in zip(prompts, refs):

@@ -43,6 +43,7 @@ struct AttnParams {
     int prefetch_blocks;             // decode: how many of a CTA's first key blocks are hinted into L2 before the wait
     int decode_rows;                 // every tile has at most 16 rows: the warps split the keys instead
     float scale_log2;
+    unsigned int* counters;          // decode with key splits: one zeroed word per (sequence, kv head), left zeroed; or null
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -530,6 +531,55 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
             }
         }
     }
+    if (p.splits == 1 || p.counters == nullptr) return;
+    // ---- key splits without a kernel of their own to merge them: the CTA of a (sequence, kv head) that stores its part
+    // last merges all of them (the same sums in the same order as attention_combine_kernel). Nobody waits for anybody.
+    __shared__ bool is_last;
+    __threadfence();
+    __syncthreads();
+    unsigned int* counter = p.counters + (int64_t)seq * p.Hkv + kvh;
+    if (threadIdx.x == 0) is_last = atomicAdd(counter, 1u) == (unsigned)p.splits - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float* w_sm = reinterpret_cast<float*>(v_sm);            // [rows][splits] weights, then [rows] 1 / sum (times the gate)
+    float* f_sm = w_sm + QROWS * 64;
+    for (int r = warp; r < rows_valid; r += NTHREADS / 32) {           // a warp a row; lane s holds splits s and s + 32
+        const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+        const float* ml = p.part_ml + ((int64_t)t * p.Hq + h) * p.splits * 2;
+        const float ms0 = lane < p.splits ? __ldcg(ml + 2 * lane) : -INFINITY;
+        const float ms1 = lane + 32 < p.splits ? __ldcg(ml + 2 * (lane + 32)) : -INFINITY;
+        const float ls0 = lane < p.splits ? __ldcg(ml + 2 * lane + 1) : 0.0f;
+        const float ls1 = lane + 32 < p.splits ? __ldcg(ml + 2 * (lane + 32) + 1) : 0.0f;
+        const float m = warp_max(fmaxf(ms0, ms1));
+        const float wgt0 = ms0 == -INFINITY ? 0.0f : fast_exp2(ms0 - m);
+        const float wgt1 = ms1 == -INFINITY ? 0.0f : fast_exp2(ms1 - m);
+        const float l = warp_sum(ls0 * wgt0 + ls1 * wgt1);
+        float f = l > 0.0f ? 1.0f / l : 0.0f;
+        if (p.gate != nullptr) f *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(int64_t)t * p.ld_gate + h])));
+        w_sm[r * 64 + lane] = wgt0;
+        w_sm[r * 64 + 32 + lane] = wgt1;
+        if (lane == 0) f_sm[r] = f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows_valid * (D / 2); idx += NTHREADS) {
+        const int r = idx / (D / 2), d = (idx % (D / 2)) * 2;
+        const int t = tok_begin + t0 + r / G, h = kvh * G + r % G;
+        const int64_t row = (int64_t)t * p.Hq + h;
+        const float* po = p.part_o + row * p.splits * D + d;
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 8
+        for (int s = 0; s < p.splits; ++s) {
+            const float w = w_sm[r * 64 + s];
+            const float2 raw = __ldcg(reinterpret_cast<const float2*>(po + (int64_t)s * D));
+            const float2 v = w == 0.0f ? make_float2(0.0f, 0.0f) : raw;      // an empty part's slot may hold anything
+            a0 = fmaf(w, v.x, a0);
+            a1 = fmaf(w, v.y, a1);
+        }
+        const float f = f_sm[r];
+        *reinterpret_cast<__nv_bfloat162*>(p.out + row * D + d) = __floats2bfloat162_rn(a0 * f, a1 * f);
+    }
+    if (threadIdx.x == 0) *counter = 0;          // ready for the next call
 }
 
 // out[row, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), times the head's gate. One warp per row; lane s holds
@@ -703,10 +753,13 @@ XS_API int xs_attention_mma_supports(int D, int page_size, int G) {
     return d_ok && page_size == BN && G >= 1 && G <= BM;
 }
 
-XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page_table, int P,
-                            const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate, int64_t ld_gate,
-                            void* out, void* scratch, int64_t scratch_bytes, int T, int n_seqs, int max_q_len, int Hq,
-                            int Hkv, int D, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+// `counters` (or null): n_seqs * Hkv zeroed words, left zeroed. With them, when every sequence brings one token and its
+// keys are split, the CTA of a (sequence, kv head) that finishes last merges the parts, and no second kernel is launched.
+XS_API int xs_attention_mma_merged(const void* q, const void* pool, const int32_t* page_table, int P,
+                                   const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate, int64_t ld_gate,
+                                   void* out, void* scratch, int64_t scratch_bytes, void* counters, int T, int n_seqs,
+                                   int max_q_len, int Hq, int Hkv, int D, int page_size, float scale, int window,
+                                   int splits, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d heads over %d kv heads", Hq, Hkv);
     const int G = Hq / Hkv;
@@ -741,6 +794,7 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
     p.splits = splits;
     p.prefetch_blocks = g_attn_prefetch_blocks;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.counters = (p.decode_rows && splits > 1) ? (unsigned int*)counters : nullptr;
     const int max_tiles = ceil_div_i(max_q_len, p.tokens_per_tile);
     switch (D) {
         case 16: launch<16>(p, max_tiles, n_seqs, stream); break;
@@ -752,13 +806,21 @@ XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page
         default: XS_REQUIRE(false, "attention (tensor cores): head size %d", D);
     }
     XS_LAUNCH_CHECK("attention_mma");
-    if (splits > 1) {
+    if (splits > 1 && p.counters == nullptr) {
         const int64_t rows = (int64_t)T * Hq;
         xs_launch(attention_combine_kernel, dim3(ceil_div_i(rows, 4)), dim3(128), 0, stream, (const float*)p.part_o,
                   (const float*)p.part_ml, p.gate, ld_gate, p.out, rows, Hq, D, splits);
         XS_LAUNCH_CHECK("attention_combine");
     }
     return 0;
+}
+
+XS_API int xs_attention_mma(const void* q, const void* pool, const int32_t* page_table, int P,
+                            const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate, int64_t ld_gate,
+                            void* out, void* scratch, int64_t scratch_bytes, int T, int n_seqs, int max_q_len, int Hq,
+                            int Hkv, int D, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    return xs_attention_mma_merged(q, pool, page_table, P, cu_seqlens, kv_lens, gate, ld_gate, out, scratch, scratch_bytes,
+                                   nullptr, T, n_seqs, max_q_len, Hq, Hkv, D, page_size, scale, window, splits, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -69,7 +69,103 @@ struct SmallMParams {
     __nv_bfloat16* next_x;    // [M, N]: bfloat16(stream * next_w)
     int64_t ld_next;
     float* out_ssq;           // [tiles, 16]
+    // Gated short convolution behind the product (decode; null / 0 when unused): out is [M, 3 * conv_h] = [B | C | X]
+    const float* conv_taps;   // [conv_k, conv_h]
+    const float* conv_bias;   // [conv_h] or null
+    __nv_bfloat16* conv_state;   // [slots, conv_k - 1, conv_h]
+    const int32_t* conv_slots;   // [M]: batch row m's slot
+    __nv_bfloat16* conv_out;     // [M, conv_h]
+    unsigned int* conv_counters; // [conv_h / 16], zero between calls
+    int conv_k, conv_h;
+    // Argmax of every batch row behind the product (the head; null when unused)
+    unsigned long long* amax_keys;   // [16], zero between calls
+    unsigned int* amax_counter;      // [1], zero between calls
+    int32_t* amax_out;               // [M]
 };
+
+__device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* p) {
+    const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(p));
+    return __bfloat162float(__ushort_as_bfloat16(raw));
+}
+
+// The convolution that follows in_proj, by whichever of the three CTAs that own a group of 16 channels (its B, its
+// C and its X rows: tiles g, g + H / 16, g + 2 H / 16) stores its part last; nobody waits for anybody. Every sequence
+// brings one token (batch row m is sequence m): g = bfloat16(B * X); out = C * (bias + sum_j tap_j * state_j + tap_last * g);
+// the state moves up by one row and takes g. The same arithmetic, in the same order, as the kernel of its own
+// (short_conv.cu), so a sequence's values do not depend on which of them ran.
+template <int NT>
+__device__ __forceinline__ void conv_tail(const SmallMParams& p) {
+    __shared__ bool is_last;
+    __threadfence();
+    __syncthreads();
+    const int groups = p.conv_h / ROWS;
+    const int group = (int)(blockIdx.x % (unsigned)groups);
+    if (threadIdx.x == 0) is_last = atomicAdd(&p.conv_counters[group], 1u) == 2u;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const int H = p.conv_h, K = p.conv_k;
+    const __nv_bfloat16* bcx = reinterpret_cast<const __nv_bfloat16*>(p.out);
+    for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
+        const int r = i % ROWS, m = i / ROWS;
+        if (m >= p.M) continue;
+        const int c = group * ROWS + r;
+        const __nv_bfloat16* row = bcx + (int64_t)m * p.ldo;
+        const float b = ldcg_bf16(row + c), gate = ldcg_bf16(row + H + c), x = ldcg_bf16(row + 2 * H + c);
+        const __nv_bfloat16 g16 = __float2bfloat16_rn(b * x);
+        const float g = __bfloat162float(g16);
+        __nv_bfloat16* st = p.conv_state + (int64_t)p.conv_slots[m] * (K - 1) * H + c;
+        float acc = p.conv_bias != nullptr ? p.conv_bias[c] : 0.0f;
+        for (int j = 0; j < K - 1; ++j) {
+            const __nv_bfloat16 old = st[(int64_t)j * H];
+            acc = fmaf(p.conv_taps[(int64_t)j * H + c], __bfloat162float(old), acc);
+            if (j > 0) st[(int64_t)(j - 1) * H] = old;        // row j moves to j - 1
+        }
+        acc = fmaf(p.conv_taps[(int64_t)(K - 1) * H + c], g, acc);
+        st[(int64_t)(K - 2) * H] = g16;
+        p.conv_out[(int64_t)m * H + c] = __float2bfloat16_rn(acc * gate);
+    }
+    if (threadIdx.x == 0) p.conv_counters[group] = 0;        // ready for the next call
+}
+
+// Each batch row's largest output and its column, the lowest column among equals: every CTA folds its 16 columns into one
+// 64-bit key per batch row (the value's bits made monotone, then the column counted down), the keys meet by atomicMax,
+// and the CTA that stores last unpacks them and clears them for the next call.
+template <int NT>
+__device__ __forceinline__ void argmax_tail(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0) {
+    __shared__ bool is_last;
+    if (threadIdx.x < 8 * NT && (int)threadIdx.x < p.M) {
+        const int m = threadIdx.x;
+        float best = -INFINITY;
+        int at = -1;
+        for (int r = 0; r < ROWS; ++r) {
+            const int n = n0 + r;
+            if (n >= p.N) break;
+            float v = sum[r][m] * inv[m];               // the value as it was stored
+            if (p.bias != nullptr) v += p.bias[n];
+            if (v > best || at < 0) {
+                best = v;
+                at = n;
+            }
+        }
+        if (at >= 0) {
+            unsigned int u = __float_as_uint(best);
+            u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+            atomicMax(&p.amax_keys[m], ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)at));
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(p.amax_counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if ((int)threadIdx.x < p.M) {
+        const unsigned long long key = atomicExch(&p.amax_keys[threadIdx.x], 0ull);
+        p.amax_out[threadIdx.x] = (int32_t)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
+    }
+    if (threadIdx.x == 0) *p.amax_counter = 0;
+}
 
 // `staged` (8 batch rows only): this tile's old stream values [m][16] and the next norm's weights [16], fetched into
 // shared memory while the weights streamed, so that the CTA's tail does not begin with a trip to L2.
@@ -119,6 +215,8 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
             if (r == 0) p.out_ssq[(int64_t)blockIdx.x * 16 + m] = sq;
         }
     }
+    if (p.conv_out != nullptr) conv_tail<NT>(p);
+    if (p.amax_out != nullptr) argmax_tail<NT>(p, sum, inv, n0);
 }
 
 // EXACT: N is a multiple of 16 and every K slice a multiple of 1,024 (8 warps x 4 blocks x 32), so no row is
@@ -406,12 +504,29 @@ XS_API int64_t xs_gemm_small_m_scratch_bytes(int M, int N, int ksplit) {
 //     tile; the result is scaled by 1 / sqrt(sum / in_width + in_eps) per batch row (before the bias).
 //   next_w [N], next_x [M, N] bfloat16 (stride ld_next), out_ssq [ceil(N / 16), 16]: with `residual`, also leave
 //     bfloat16(stream * next_w) and this product's per-tile sums of squares of the new stream values.
-XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bias, void* out, float* residual,
-                                  int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
-                                  int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
-                                  int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
-                                  float* out_ssq, cudaStream_t stream) {
+//
+// Work that follows the product in the same kernel, by the CTA that finishes last (nobody waits), all optional:
+//   conv_*: the product is a short-convolution layer's in_proj for one token a sequence (out bfloat16 [M, 3 H] = [B | C | X],
+//     one K slice, H a multiple of 16): the gated convolution over each sequence's state (conv_state [slots, taps - 1, H],
+//     conv_slots [M]) goes to conv_out [M, H] and the state moves on. conv_counters: H / 16 zeroed words, left zeroed.
+//   amax_*: amax_out [M] takes each batch row's column of the largest output (the lowest among equals); amax_keys:
+//     16 zeroed 64-bit words and amax_counter one zeroed word, left zeroed.
+XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, void* out, float* residual,
+                              int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
+                              int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
+                              int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
+                              float* out_ssq, const float* conv_taps, const float* conv_bias, void* conv_state,
+                              const int32_t* conv_slots, void* conv_out, void* conv_counters, int conv_k, int conv_h,
+                              void* amax_keys, void* amax_counter, int32_t* amax_out, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    XS_REQUIRE(conv_out == nullptr ||
+                   (conv_taps != nullptr && conv_state != nullptr && conv_slots != nullptr && conv_counters != nullptr &&
+                    conv_k >= 2 && conv_h > 0 && conv_h % ROWS == 0 && N == 3 * conv_h && ksplit == 1 && !swiglu &&
+                    residual == nullptr && out != nullptr && out_dtype == XS_BF16),
+               "gemm (few rows): the convolution behind the product needs a bfloat16 output of 3 x %d columns (a multiple "
+               "of 16 channels), one K slice, %d taps", conv_h, conv_k);
+    XS_REQUIRE(amax_out == nullptr || (amax_keys != nullptr && amax_counter != nullptr && !swiglu && (uintptr_t)amax_keys % 8 == 0),
+               "gemm (few rows): the argmax behind the product needs its keys and its counter");
     XS_REQUIRE(in_ssq == nullptr || (in_tiles > 0 && in_width > 0 && (uintptr_t)in_ssq % 16 == 0),
                "gemm (few rows): %d tiles of sums over a width of %d", in_tiles, in_width);
     XS_REQUIRE((next_x == nullptr) == (next_w == nullptr) && (next_x == nullptr || (out_ssq != nullptr && ld_next >= N)),
@@ -444,6 +559,9 @@ XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bia
     p.ldx = ldx; p.ldw = ldw; p.ldo = ldo;
     p.in_ssq = in_ssq; p.in_tiles = in_tiles; p.in_width = in_width; p.in_eps = in_eps;
     p.next_w = next_w; p.next_x = (__nv_bfloat16*)next_x; p.ld_next = ld_next; p.out_ssq = out_ssq;
+    p.conv_taps = conv_taps; p.conv_bias = conv_bias; p.conv_state = (__nv_bfloat16*)conv_state; p.conv_slots = conv_slots;
+    p.conv_out = (__nv_bfloat16*)conv_out; p.conv_counters = (unsigned int*)conv_counters; p.conv_k = conv_k; p.conv_h = conv_h;
+    p.amax_keys = (unsigned long long*)amax_keys; p.amax_counter = (unsigned int*)amax_counter; p.amax_out = amax_out;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_small_m_scratch_bytes(M, N, ksplit);
         XS_REQUIRE(scratch != nullptr && scratch_bytes >= need && (uintptr_t)scratch % 16 == 0 && scratch_bytes % 16 == 0,
@@ -473,6 +591,16 @@ XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bia
 #undef XS_GO
     XS_LAUNCH_CHECK("gemm_small_m");
     return 0;
+}
+
+XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bias, void* out, float* residual,
+                                  int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
+                                  int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
+                                  int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
+                                  float* out_ssq, cudaStream_t stream) {
+    return xs_gemm_small_m_ex(x, w, bias, out, residual, out_dtype, M, N, K, ldx, ldw, ldo, swiglu, ksplit, scratch,
+                              scratch_bytes, in_ssq, in_tiles, in_width, in_eps, next_w, next_x, ld_next, out_ssq, nullptr,
+                              nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, nullptr, nullptr, stream);
 }
 
 XS_API int xs_gemm_small_m(const void* x, const void* w, const float* bias, void* out, float* residual, int out_dtype,

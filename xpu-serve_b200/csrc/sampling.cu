@@ -433,7 +433,7 @@ constexpr size_t kSampleSmem = (size_t)kSub * 256 * 3 * sizeof(unsigned int);
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
-              const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ counters, int32_t* __restrict__ out) {
+              const uint64_t* __restrict__ seeds, uint64_t* __restrict__ counters, int advance, int32_t* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char sample_smem[];
     __shared__ ArgBest arg_scratch[32];
     __shared__ unsigned long long sum_scratch[33];
@@ -460,6 +460,7 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
 
     const int rowi = blockIdx.x / ranks;
     const float* row = logits + (int64_t)rowi * ld;
+    const uint64_t draw = counters[rowi];       // every CTA of the row reads it before the first cluster-wide barrier
     // this CTA's part of the vocabulary, a multiple of 4 tokens long (16-byte loads below)
     const int part = ((V + (int)ranks - 1) / (int)ranks + 3) & ~3;
     const int lo = min(V, (int)rank * part), hi = min(V, lo + part);
@@ -471,6 +472,8 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
     for (unsigned int r = 0; r < ranks; ++r) top = better(top, share_of(cluster, &share, r)->best);
     if (top.i == 0x7fffffff) top.i = 0;   // a row of NaN or -inf
     cluster.sync();
+    // the row's draw counter moves on here, on the device (greedy rows too: a counter counts steps), once all have read it
+    if (advance && threadIdx.x == 0 && rank == 0) counters[rowi] = draw + 1;
     const float temp = temperature[rowi];
     const int k = top_k[rowi];
     if (!(temp > 0.0f) || k == 1) {   // greedy (src/engine/sampler.h:36)
@@ -511,7 +514,7 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V, const float* 
     const unsigned long long before_in_cta = block_exclusive_scan_u64(mine, sum_scratch, &cta_total);
     const unsigned long long total = cluster_sum_u64(cluster, &share, cta_total, &lower);   // also orders the write above
     const unsigned long long before = lower + before_in_cta;
-    unsigned long long target = __double2ull_rz(uniform_from(seeds[rowi], counters[rowi]) * (double)total);
+    unsigned long long target = __double2ull_rz(uniform_from(seeds[rowi], draw) * (double)total);
     if (total > 0 && target >= total) target = total - 1;
     if (mine > 0 && target >= before && target < before + mine) {
         unsigned long long left = target - before;
@@ -585,7 +588,7 @@ XS_API int xs_argmax(const float* logits, int64_t ld, int n, int V, int32_t* out
 }
 
 XS_API int xs_sample(const float* logits, int64_t ld, int n, int V, const float* temperature, const int32_t* top_k,
-                     const float* top_p, const float* min_p, const uint64_t* seeds, const uint64_t* counters,
+                     const float* top_p, const float* min_p, const uint64_t* seeds, uint64_t* counters, int advance,
                      int32_t* out, cudaStream_t stream) {
     if (n == 0) return 0;
     XS_REQUIRE(n > 0 && V > 0 && V <= kMaxVocab && ld >= V, "sample: %d rows of %d (at most %d)", n, V, kMaxVocab);
@@ -617,7 +620,7 @@ XS_API int xs_sample(const float* logits, int64_t ld, int n, int V, const float*
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, temperature, top_k, top_p, min_p, seeds,
-                                             counters, out);
+                                             counters, advance, out);
     XS_REQUIRE(e == cudaSuccess, "sample: launch failed: %s", cudaGetErrorString(e));
     XS_LAUNCH_CHECK("sample");
     return 0;

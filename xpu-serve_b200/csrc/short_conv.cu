@@ -259,7 +259,7 @@ XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const fl
     XS_REQUIRE(!all_single || T == n_seqs, "short_conv: %d tokens for %d sequences of one token each", T, n_seqs);
     const bool vec = dtype == XS_BF16 && H % 8 == 0 && ld % 8 == 0 && (uintptr_t)bcx % 16 == 0 &&
                      (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w_t % 16 == 0;
-    if (vec && all_single && K >= 2 && K <= 5) {
+    if (vec && all_single && K >= 2 && K <= 8) {
         const dim3 grid(ceil_div_i((int64_t)n_seqs * (H / 8), 128));
 #define XS_CONV_DECODE(KT)                                                                                           \
     xs_launch(short_conv_decode_bf16x8_kernel<KT>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)bcx, ld, w_t, bias, \
@@ -268,7 +268,10 @@ XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const fl
             case 2: XS_CONV_DECODE(2); break;
             case 3: XS_CONV_DECODE(3); break;
             case 4: XS_CONV_DECODE(4); break;
-            default: XS_CONV_DECODE(5); break;
+            case 5: XS_CONV_DECODE(5); break;
+            case 6: XS_CONV_DECODE(6); break;
+            case 7: XS_CONV_DECODE(7); break;       // the reference's default number of taps
+            default: XS_CONV_DECODE(8); break;
         }
 #undef XS_CONV_DECODE
         XS_LAUNCH_CHECK("short_conv_decode");

@@ -65,7 +65,8 @@ class _Choice:
             self.top_p, self.min_p = f32([p.top_p for p in params]), f32([p.min_p for p in params])
             self.seeds = torch.tensor([_i64(h.seed) for h in chosen], dtype=torch.int64, device=device)
         self.counters_host = [h.counter + offset for h in chosen]
-        self.counters = torch.tensor(self.counters_host, dtype=torch.int64, device=device)
+        if not self.all_greedy:
+            self.counters = torch.tensor(self.counters_host, dtype=torch.int64, device=device)
         if with_penalties:
             self.rows = i32([h.row for h in chosen])
             self.repetition = f32([p.repetition_penalty for p in params])
@@ -102,6 +103,8 @@ class DeviceStepper:
         self._ahead: Optional[_Ahead] = None
         self._choice: Optional[_Choice] = None
         self._live = set()          # handles that hold a slot
+        self._out_bufs: List[Optional[torch.Tensor]] = [None, None]      # where the sampling kernels leave their choice
+        self._out_turn = 0
 
     # ---------------------------------------------------------------- slots
     def open(self, requests: Sequence[GenerateRequest]) -> List[_Handle]:
@@ -181,14 +184,17 @@ class DeviceStepper:
         expected = [h.counter + offset for h in chosen]
         if c is None or c.key != tuple(chosen) or c.counters_host != expected:
             c = self._choice = _Choice(chosen, self.device, self._pen is not None, offset)
-        out = torch.empty(len(chosen), dtype=torch.int32, device=self.device)
+        self._out_turn ^= 1                    # two buffers in turns: a step that runs ahead chooses while the last
+        out = self._out_bufs[self._out_turn]   # step's choice is still on its way to the host
+        if out is None or out.numel() < len(chosen):
+            out = self._out_bufs[self._out_turn] = torch.empty(max(64, 2 * len(chosen)), dtype=torch.int32, device=self.device)
+        out = out[:len(chosen)]
         if self._pen is not None:
             ops.apply_penalties(logits, self._pen[0], self._pen[1], c.rows, c.repetition, c.presence, c.frequency)
         if c.all_greedy:
-            ops.argmax(logits, out)
+            ops.argmax(logits, out)           # (no draw: the device's counters are not used, the host's mirror goes on)
         else:
-            ops.sample(logits, c.temperature, c.top_k, c.top_p, c.min_p, c.seeds, c.counters, out)
-        c.counters.add_(1)
+            ops.sample(logits, c.temperature, c.top_k, c.top_p, c.min_p, c.seeds, c.counters, out, advance=True)
         c.counters_host = [v + 1 for v in c.counters_host]
         if self._pen is not None:
             ops.note_tokens(out, c.rows, self._pen[0], self._pen[1], generated=True)

@@ -70,7 +70,8 @@ class Model:
         self.stager = StepStager(rt.device)
         # Decode steps are launch-bound (some 150 small kernels): they are captured once per batch
         # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
-        self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1"
+        # (XS_PROFILE=1 and XS_SYNC=1, the per-launch timing and error-naming switches of ops/lib.py, do the same.)
+        self.use_graphs = os.environ.get("XS_NO_GRAPHS", "0") != "1" and not ops.watched()
         self.last_greedy: Optional[torch.Tensor] = None
         self._last_graph: Optional[_DecodeGraph] = None
         # Decode graphs per cache (a graph holds the addresses of the cache's storage; by the cache's serial number,
@@ -177,7 +178,7 @@ class Model:
         ctx = stager.stage_decode_fixed(cache, [], [], np.zeros(0, dtype=np.int64), rows)
         greedy = torch.empty(rows, dtype=torch.int32, device=rt.device)
         with self._workspace(ws):
-            ops.argmax(self.forward(ctx, cache), greedy)     # allocates the scratch buffers, loads the kernels
+            self.forward(ctx, cache, greedy)                 # allocates the scratch buffers, loads the kernels
             torch.cuda.synchronize(rt.device)
             before = ops.launches
             graph = torch.cuda.CUDAGraph()
@@ -185,8 +186,7 @@ class Model:
             gc.disable()          # a collection inside the capture could destroy another model's graphs there
             try:
                 with torch.cuda.graph(graph):
-                    logits = self.forward(ctx, cache)
-                    ops.argmax(logits, greedy)               # greedy decoding needs no launch after the graph
+                    logits = self.forward(ctx, cache, greedy)    # greedy decoding needs no launch after the graph
             finally:
                 if collecting:
                     gc.enable()
@@ -252,7 +252,9 @@ class Model:
             return None
         return self.last_greedy
 
-    def forward(self, ctx: StepContext, cache: Cache) -> torch.Tensor:
+    def forward(self, ctx: StepContext, cache: Cache, greedy: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The step's kernels. `greedy` (int32, one word per wanted row) also takes each returned row's most likely
+        token (a soft cap on the logits keeps their order, so it does not matter that it comes after)."""
         rt, spec = self.rt, self.spec
         h = rt.ws.get("stream", (ctx.n_tokens, spec.hidden), torch.float32)
         ops.embed(self.embed, ctx.tokens, h, spec.embed_scale)
@@ -269,7 +271,7 @@ class Model:
             y = stream.norm_input(self.final_norm, lazy=True)
         else:
             y = stream.norm(self.final_norm, ctx.want_rows)
-        logits = rt.linear(y, self.head, "logits", out_dtype=torch.float32)
+        logits = rt.linear(y, self.head, "logits", out_dtype=torch.float32, argmax_into=greedy)
         if spec.logit_cap > 0.0:
             ops.logit_cap(logits, spec.logit_cap)
         return logits

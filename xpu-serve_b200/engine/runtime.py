@@ -100,6 +100,16 @@ class Runtime:
         ops.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
+        # Zeroed words that kernels with a "whoever finishes last" tail count in and leave zeroed: the convolution
+        # behind in_proj (a word per 16 channels), the merge of decode attention's key splits (a word per sequence
+        # and kv head), the argmax behind the head product (16 keys and a word). XS_NO_TAILS=1: kernels of their own.
+        self.fuse_tails = os.environ.get("XS_NO_TAILS", "0") != "1"
+        tails = os.environ.get("XS_TAILS", "conv,attn,argmax").split(",")
+        self.tail_conv, self.tail_attn, self.tail_argmax = ["conv" in tails, "attn" in tails, "argmax" in tails]
+        self.conv_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
+        self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=self.device)
+        self.amax_keys = torch.zeros(16, dtype=torch.int64, device=self.device)
+        self.amax_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     # -------------------------------------------------------------- weights
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
@@ -127,7 +137,7 @@ class Runtime:
         return ops.gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))
 
     def few_rows_product(self, x, w, out, bias=None, swiglu: bool = False, residual=None, next_w=None, next_x=None,
-                         out_ssq=None) -> None:
+                         out_ssq=None, conv=None, argmax_into=None) -> None:
         """The library's weight-streaming product, with K cut over several CTAs where the output is
         narrow; the partial sums meet in one zero-initialised scratch buffer that lives as long as
         the runtime (its tail holds the kernel's counters). `x` may be a Prenormed input; `residual`
@@ -140,14 +150,33 @@ class Runtime:
         ksplit = ops.gemm_small_m_ksplit(x.shape[0], w.shape[0], x.shape[1], self.sm_count)
         if ksplit > 1 and ops.gemm_small_m_scratch_bytes(x.shape[0], w.shape[0], ksplit) > self.gemm_scratch.numel():
             ksplit = 1
+        if conv is not None:
+            ksplit = 1          # the convolution behind the product counts whole tiles
+            conv = dict(conv, counters=self.conv_counters)
         ops.gemm_small_m(x, w, out, bias, residual=residual, swiglu=swiglu, ksplit=ksplit,
                          scratch=self.gemm_scratch if ksplit > 1 else None, next_w=next_w, next_x=next_x, out_ssq=out_ssq,
+                         conv=conv, argmax=None if argmax_into is None else (argmax_into, self.amax_keys, self.amax_counter),
                          **norm)
 
+    def conv_behind_product(self, x, w, channels: int) -> bool:
+        """Whether a short convolution of one token a sequence can run in the tail of its in_proj product."""
+        return (self.fuse_tails and self.tail_conv and self.few_rows(x, w) and channels % 16 == 0 and channels // 16 <= self.conv_counters.numel()
+                and w.shape[0] == 3 * channels)
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
-               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`. x may be a Prenormed input."""
+               out_dtype: Optional[torch.dtype] = None, argmax_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x[M, K] . w[N, K]^T (+ bias) into the scratch buffer `name`. x may be a Prenormed input. `argmax_into`
+        (int32 [M]) also takes each row's column of the largest output, behind the product where the few-row kernel
+        runs it, by the argmax kernel otherwise."""
         M, N = x.shape[0], w.shape[0]
+        if argmax_into is not None:
+            if self.mode == "bfloat16" and self.fuse_tails and self.tail_argmax and M <= 16 and self.few_rows(x, w):
+                out = self.ws.get(name, (M, N), out_dtype or self.act_dtype)
+                self.few_rows_product(x, w, out, bias, argmax_into=argmax_into)
+                return out
+            out = self.linear(x, w, name, bias, out_dtype)
+            ops.argmax(out, argmax_into)
+            return out
         if hasattr(x, "ssq") and not self.few_rows(x, w):
             raise RuntimeError("a Prenormed input needs the few-row product")
         out_dtype = out_dtype or self.act_dtype

@@ -44,9 +44,12 @@ def _signatures(lib) -> None:
         "xs_attention_tc": [P, P, L, P, I, P, P, P, L, P, I, I, I, I, I, I, I, F, I, P, P],
         "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P],
         "xs_gemm_small_m_normed": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P, P],
+        "xs_gemm_small_m_ex": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P,
+                               P, P, P, P, P, P, I, I, P, P, P, P],
+        "xs_attention_mma_merged": [P, P, P, I, P, P, P, L, P, P, L, P, I, I, I, I, I, I, I, F, I, I, P],
         "xs_gemm_tc": [P, P, P, P, I, I, I, I, I, L, L, L, I, P, L, P, P],
         "xs_argmax": [P, L, I, I, P, P, P],
-        "xs_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
+        "xs_sample": [P, L, I, I, P, P, P, P, P, P, I, P, P],
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
         "xs_note_tokens": [P, P, I, I, P, P, I, P],
     }
@@ -81,6 +84,73 @@ def _signatures(lib) -> None:
     lib.xs_gemm_small_m_scratch_bytes.argtypes = [c_int, c_int, c_int]
 
 
+class _Watched:
+    """The library behind two debugging switches (the reference has the same pair for its own backend,
+    XS_SYCL_PROFILE and XS_SYCL_SYNC, src/backend/sycl/sycl_backend.cpp:351-353, 2520-2570):
+
+    XS_PROFILE=1  CUDA events around every launch; `profile_report()` (also printed at exit) sums the device time by
+                  kernel function and by its sizes (the call's integer arguments).
+    XS_SYNC=1     the device is waited for after every launch, and an error that shows up there is raised with the
+                  name and the sizes of the launch it belongs to, instead of surfacing at some later call.
+
+    Both run every step kernel by kernel (no CUDA graphs: engine/model.py) and cost time; neither is on by default."""
+
+    def __init__(self, lib, profile: bool, sync: bool):
+        self._lib, self._profile, self._sync = lib, profile, sync
+        self.spans = []         # (name, sizes, start event, end event)
+        self._name = lib._name
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        argtypes = getattr(fn, "argtypes", None)
+        if not name.startswith("xs_") or not argtypes or argtypes[-1] is not c_void_p or fn.restype is not c_int:
+            return fn           # not a launch (a query, a switch)
+
+        def call(*args):
+            sizes = tuple(a for a, t in zip(args, argtypes) if t in (c_int, c_int64) and isinstance(a, int) and abs(a) < (1 << 40))
+            capturing = torch.cuda.is_current_stream_capturing()
+            if self._profile and not capturing:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                rc = fn(*args)
+                end.record()
+                self.spans.append((name, sizes, start, end))
+            else:
+                rc = fn(*args)
+            if self._sync and not capturing and rc == 0:
+                try:
+                    torch.cuda.synchronize()
+                except RuntimeError as e:
+                    raise KernelError(f"{name}{sizes}: the device reported an error after this launch: {e}") from None
+            return rc
+
+        call.__name__ = name
+        setattr(self, name, call)
+        return call
+
+
+def profile_report(reset: bool = True, file=None) -> dict:
+    """{(kernel function, sizes): (launches, total microseconds)} of the launches made under XS_PROFILE=1 since
+    the last report, printed as a table (largest first) to `file` (standard error)."""
+    import sys
+    lib = _lib
+    if not isinstance(lib, _Watched) or not lib.spans:
+        return {}
+    torch.cuda.synchronize()
+    table = {}
+    for name, sizes, start, end in lib.spans:
+        n, us = table.get((name, sizes), (0, 0.0))
+        table[(name, sizes)] = (n + 1, us + start.elapsed_time(end) * 1e3)
+    if reset:
+        lib.spans = []
+    out = file or sys.stderr
+    total = sum(us for _, us in table.values())
+    print(f"[xpu_serve_b200 profile] {sum(n for n, _ in table.values())} launches, {total:.0f} us on the device", file=out)
+    for (name, sizes), (n, us) in sorted(table.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {us:10.1f} us {100 * us / max(total, 1e-9):5.1f} %  x{n:<5d} {name} {sizes}", file=out)
+    return table
+
+
 def load(verbose: bool = True):
     """The library handle, built first if its file is missing."""
     global _lib
@@ -102,8 +172,19 @@ def load(verbose: bool = True):
             lib.xs_set_pdl(0)
         if os.environ.get("XS_TC_NO_PAIR", "0") == "1":
             lib.xs_gemm_tc_set_pair(0)
+        profile, sync = os.environ.get("XS_PROFILE", "0") == "1", os.environ.get("XS_SYNC", "0") == "1"
+        if profile or sync:
+            lib = _Watched(lib, profile, sync)
+            if profile:
+                import atexit
+                atexit.register(profile_report)
         _lib = lib
     return _lib
+
+
+def watched() -> bool:
+    """Whether XS_PROFILE or XS_SYNC is on (steps then run kernel by kernel, without CUDA graphs)."""
+    return os.environ.get("XS_PROFILE", "0") == "1" or os.environ.get("XS_SYNC", "0") == "1"
 
 
 def loaded_path() -> Optional[str]:
@@ -292,9 +373,11 @@ def attention_mma_scratch_bytes(rows: int, head_dim: int, splits: int) -> int:
 def attention_mma(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor,
                   kv_lens: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
                   scratch: Optional[torch.Tensor], n_seqs: int, max_q_len: int, kv_heads: int, page_size: int,
-                  scale: float, window: int, splits: int) -> None:
+                  scale: float, window: int, splits: int, counters: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention over the paged bfloat16 cache. `scratch`: a byte buffer of at least
-    attention_mma_scratch_bytes(tokens * heads, head_dim, splits) when splits > 1."""
+    attention_mma_scratch_bytes(tokens * heads, head_dim, splits) when splits > 1. `counters`: at least
+    n_seqs * kv_heads zeroed int32 words that the kernel leaves zeroed; with them a decode step (one token a
+    sequence) merges its key splits inside the attention kernel instead of in a second one."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "cache", torch.bfloat16)
     _need(page_table, "page table", torch.int32)
     T, heads, D = q.shape
@@ -306,10 +389,16 @@ def attention_mma(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
             raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {heads} heads")
         ld_gate = gate.stride(0)
     sbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
-    _check(load().xs_attention_mma(
+    merged = counters is not None and splits > 1 and max_q_len == 1 and heads // kv_heads <= 16
+    if merged:
+        _need(counters, "counters", torch.int32)
+        if counters.numel() < n_seqs * kv_heads:
+            raise KernelError(f"attention: {counters.numel()} counters for {n_seqs} sequences of {kv_heads} kv heads")
+    _check(load().xs_attention_mma_merged(
         q.data_ptr(), pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
-        kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), _ptr(scratch), sbytes, T, n_seqs, max_q_len, heads,
-        kv_heads, D, page_size, float(scale), int(window), int(splits), _stream()), kernels=2 if splits > 1 else 1)
+        kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), _ptr(scratch), sbytes, _ptr(counters) if merged else None,
+        T, n_seqs, max_q_len, heads, kv_heads, D, page_size, float(scale), int(window), int(splits), _stream()),
+        kernels=2 if splits > 1 and not merged else 1)
 
 
 def attention_tc_supports(head_dim: int, page_size: int, group: int) -> bool:
@@ -355,7 +444,8 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
                  residual: Optional[torch.Tensor] = None, swiglu: bool = False, ksplit: int = 1,
                  scratch: Optional[torch.Tensor] = None, in_ssq: Optional[torch.Tensor] = None, in_width: int = 0,
                  in_eps: float = 0.0, next_w: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None,
-                 out_ssq: Optional[torch.Tensor] = None) -> None:
+                 out_ssq: Optional[torch.Tensor] = None, conv: Optional[dict] = None,
+                 argmax: Optional[tuple] = None) -> None:
     """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product;
     or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows.
     ksplit > 1 cuts K over several CTAs; `scratch` is then a zero-initialised byte buffer of at least
@@ -365,7 +455,13 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
     leaves next_x = bfloat16(residual * next_w) and, in `out_ssq` [ceil(N / 16), 16] float32, each tile's
     sums of squares of the new residual values per row. A product given that `out_ssq` as `in_ssq` (with the
     residual's width and the norm's eps) and that `next_x` as x scales its result by each row's
-    1 / sqrt(mean square + eps): together they are norm(residual) . w^T without a norm kernel between."""
+    1 / sqrt(mean square + eps): together they are norm(residual) . w^T without a norm kernel between.
+
+    Work behind the product, in the same kernel: `conv` = dict(taps [k, H] float32, bias [H] or None, state
+    [slots, k - 1, H] bfloat16, slots [M] int32, out [M, H] bfloat16, counters: H / 16 zeroed int32 words, left
+    zeroed): the product is a short-convolution layer's in_proj for one token a sequence, out = [B | C | X], and the
+    gated convolution with its state update follows. `argmax` = (out [M] int32, keys: 16 zeroed int64 words,
+    counter: one zeroed int32 word; both left zeroed): each row's column of the largest output."""
     for t, name in ((x, "x"), (w, "w")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
             raise KernelError(f"gemm (few rows): {name} must be a bfloat16 CUDA matrix with contiguous rows")
@@ -395,11 +491,32 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         _need(out_ssq, "out_ssq", torch.float32)
         if tuple(out_ssq.shape) != ((N + 15) // 16, 16) or not out_ssq.is_contiguous():
             raise KernelError(f"gemm (few rows): out_ssq is {tuple(out_ssq.shape)}, expected [{(N + 15) // 16}, 16]")
-    _check(load().xs_gemm_small_m_normed(
+    cv = [None] * 6 + [0, 0]
+    if conv is not None:
+        taps, state, slots, cout, counters = conv["taps"], conv["state"], conv["slots"], conv["out"], conv["counters"]
+        k, H = taps.shape
+        _need(taps, "taps", torch.float32); _need(state, "state", torch.bfloat16); _need(slots, "slots", torch.int32)
+        _need(cout, "conv out", torch.bfloat16); _need(counters, "conv counters", torch.int32)
+        if conv.get("bias") is not None:
+            _need(conv["bias"], "conv bias", torch.float32)
+        if (N != 3 * H or tuple(state.shape[1:]) != (k - 1, H) or slots.numel() < M or tuple(cout.shape) != (M, H)
+                or counters.numel() < H // 16 or out is None or out.dtype != torch.bfloat16):
+            raise KernelError(f"gemm (few rows): convolution of {k} taps over {H} channels behind a product of {N} columns, "
+                              f"state {tuple(state.shape)}, out {tuple(cout.shape)}")
+        cv = [taps.data_ptr(), _ptr(conv.get("bias")), state.data_ptr(), slots.data_ptr(), cout.data_ptr(),
+              counters.data_ptr(), int(k), int(H)]
+    am = [None, None, None]
+    if argmax is not None:
+        a_out, keys, counter = argmax
+        _need(a_out, "argmax out", torch.int32); _need(keys, "argmax keys", torch.int64); _need(counter, "argmax counter", torch.int32)
+        if a_out.numel() < M or keys.numel() < 16 or M > 16:
+            raise KernelError(f"gemm (few rows): argmax of {M} rows into {a_out.numel()} words")
+        am = [keys.data_ptr(), counter.data_ptr(), a_out.data_ptr()]
+    _check(load().xs_gemm_small_m_ex(
         x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual), F32 if out is None else _code(out), M, N, K,
         x.stride(0), w.stride(0), target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
         0 if scratch is None else scratch.numel() * scratch.element_size(), _ptr(in_ssq), in_tiles, int(in_width),
-        float(in_eps), _ptr(next_w), _ptr(next_x), ld_next, _ptr(out_ssq), _stream()))
+        float(in_eps), _ptr(next_w), _ptr(next_x), ld_next, _ptr(out_ssq), *cv, *am, _stream()))
 
 
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
@@ -485,7 +602,7 @@ def short_conv(bcx: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor
     _check(load().xs_short_conv(bcx.data_ptr(), bcx.stride(0), w_t.data_ptr(), _ptr(bias), state.data_ptr(),
                                 seq_of_token.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(),
                                 T, slots.numel(), H, K, _code(bcx), 1 if all_single else 0, _stream()),
-           kernels=1 if all_single and bcx.dtype == torch.bfloat16 and H % 8 == 0 else 2)
+           kernels=1 if all_single and bcx.dtype == torch.bfloat16 and H % 8 == 0 and K <= 8 else 2)
 
 
 _argmax_scratch = {}
@@ -503,7 +620,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           min_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor) -> None:
+           min_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor,
+           advance: bool = False) -> None:
+    """A seeded draw per row from (seed, counter). `advance`: every row's counter goes up by one inside the kernel
+    (greedy rows' too), so that a generation loop needs no launch of its own for that."""
     _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
     n, V = logits.shape
     for t, name, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
@@ -514,7 +634,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
             raise KernelError(f"{name} has {t.numel()} entries for {n} rows")
     _check(load().xs_sample(logits.data_ptr(), logits.stride(0), n, V, temperature.data_ptr(), top_k.data_ptr(),
                             top_p.data_ptr(), min_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(),
-                            out.data_ptr(), _stream()))
+                            1 if advance else 0, out.data_ptr(), _stream()))
 
 
 def apply_penalties(logits: torch.Tensor, seen: torch.Tensor, gen_count: torch.Tensor, state_rows: torch.Tensor,

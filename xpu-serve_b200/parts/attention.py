@@ -135,8 +135,9 @@ class AttentionMixer(Mixer):
             if splits > 1:
                 need = ops.attention_mma_scratch_bytes(q.shape[0] * s.heads, s.head_dim, splits)
                 scratch = rt.ws.get("attn_scratch", (need,), torch.uint8)
+            counters = rt.attn_counters if (rt.fuse_tails and rt.tail_attn and step.n_seqs * s.kv_heads <= rt.attn_counters.numel()) else None
             ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, scratch, step.n_seqs,
-                              step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, splits)
+                              step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, splits, counters=counters)
             return
         ops.attention_generic(q, cache.storage, table, step.seq_of_token, step.positions, gate, o, s.kv_heads,
                               step.page_size, s.scale, s.window)

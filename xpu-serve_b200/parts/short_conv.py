@@ -49,8 +49,16 @@ class ShortConvMixer(Mixer):
         rt, H = self.rt, self.spec.hidden
         if cache is None or cache.storage is None or not cache.owner:
             raise RuntimeError("short_conv keeps its own state and cannot read another call's")
-        bcx = rt.linear(x, self.w_in, "conv_bcx", self.b_in)
         y = rt.ws.get("conv_y", (x.shape[0], H), rt.act_dtype)
+        if step.decode and rt.conv_behind_product(x, self.w_in, H):
+            # one token a sequence: the convolution and the state's update run in the tail of the in_proj product
+            bcx = rt.ws.get("conv_bcx", (x.shape[0], 3 * H), rt.act_dtype)
+            rt.few_rows_product(x, self.w_in, bcx, self.b_in,
+                                conv=dict(taps=self.taps, bias=self.b_conv, state=cache.storage, slots=step.slots, out=y))
+            if into is not None:
+                return into.product(y, self.w_out, self.b_out)
+            return rt.linear(y, self.w_out, "mixer_out", self.b_out)
+        bcx = rt.linear(x, self.w_in, "conv_bcx", self.b_in)
         ops.short_conv(bcx, self.taps, self.b_conv, cache.storage, step.seq_of_token, step.cu_seqlens, step.slots, y,
                        all_single=step.decode)
         if into is not None:
