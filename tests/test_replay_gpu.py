@@ -410,3 +410,34 @@ def test_a_wrong_norm_in_one_layer_is_caught_in_bfloat16(name, fault, folders, r
     gap, where, _ = tu.worst_gap(got, references(name, "bfloat16"))
     print(f"GAP planted {name} {fault} gap={gap:.3e} tol={tolerance(name, 'bfloat16'):.1e}")
     assert gap > 1.5 * tolerance(name, "bfloat16"), f"{name}: a wrong norm moved the logits by {gap:.3e} only"
+
+
+@pytest.mark.parametrize("name", ["A", "R", "H"])
+def test_every_tail_on_the_model_path(name, folders, references, monkeypatch):
+    """XS_TAILS=conv,attn,argmax: the convolution in the tail of its in_proj product, decode attention's key splits
+    merged by the CTA that finishes last, the argmax behind the head product (by default only the second runs:
+    the other two measured slower than kernels of their own). The same batches, the same bounds; the tokens that
+    the decode graph chooses are the logits' largest."""
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    monkeypatch.setenv("XS_TAILS", "conv,attn,argmax")
+    model = load_model(folders[(name, "bfloat16")], dtype="bfloat16")
+    rt = model.rt
+    assert rt.tail_conv and rt.tail_attn and rt.tail_argmax
+    rp = Replayer(model, 1024, None)
+    reqs = requests_for(name)
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    for steps in (tu.tail_trace(reqs, 32), tu.batch_trace(reqs, 5)):
+        got = tu.collect(steps, tu.run_in_process(rp, steps), vocab)
+        gap, where, cos = tu.worst_gap(got, references(name, "bfloat16"))
+        assert gap <= tolerance(name, "bfloat16") and cos >= COS["bfloat16"], f"gap {gap:.3e} at {where}"
+    cache = model.new_cache(512)
+    slots = cache.open(3)
+    model.step(cache, slots, [tiny.prompt(name, n, salt=i) for i, n in enumerate((70, 9, 130))])
+    for _ in range(3):
+        logits = model.step(cache, slots, [[5], [6], [7]])
+        assert model.last_greedy is not None
+        assert torch.equal(model.last_greedy.long(), logits.argmax(-1))
+    cache.close(slots)
+    assert int(rt.conv_counters.abs().sum()) == 0 and int(rt.attn_counters.abs().sum()) == 0
+    assert int(rt.amax_keys.abs().sum()) == 0 and int(rt.amax_counter.item()) == 0

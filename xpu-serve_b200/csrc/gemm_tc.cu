@@ -151,7 +151,7 @@ __device__ __forceinline__ void emit16(const GemmTcParams& p, const uint32_t* r,
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, (STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 <= 110 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemmTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -277,11 +277,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             if (warp >= 2) {
                 const int quarter = warp & 3;
                 const int row = tile_m * BM + quarter * 32 + lane;
-                const float* all = p.partials + tile * p.ksplit * (int64_t)(BM * BN);
-                for (int c = 0; c < BN; ++c) {
-                    float v = 0.0f;
-                    for (int s = 0; s < p.ksplit; ++s) v += __ldcg(all + (int64_t)s * (BM * BN) + c * BM + quarter * 32 + lane);
-                    emit<BN>(p, v, row, tile_n * BN + c, lane);
+                const float* all = p.partials + tile * p.ksplit * (int64_t)(BM * BN) + quarter * 32 + lane;
+                // sixteen tokens at a time: a slice's sixteen loads are in flight together (one after the other, each
+                // would wait for L2 on its own), the slices are added in slice order
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    for (int s = 0; s < p.ksplit; ++s) {
+                        float t[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) t[j] = __ldcg(all + (int64_t)s * (BM * BN) + (c + j) * BM);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] += t[j];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) emit<BN>(p, v[j], row, tile_n * BN + c + j, lane);
                 }
             }
             if (threadIdx.x == 0) p.counters[tile] = 0;
@@ -640,6 +652,7 @@ int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTc
 }
 
 int g_pair = 1;   // CTA pairs for more than 128 tokens (xs_gemm_tc_set_pair)
+int g_few_deep = 0;   // few tokens: 1 = a deep ring and one CTA an SM; 0 = four stages and two CTAs an SM
 
 template <int STAGES>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTcParams& p, cudaStream_t stream) {
@@ -688,6 +701,7 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTcParams
 }  // namespace
 
 XS_API void xs_gemm_tc_set_pair(int on) { g_pair = on ? 1 : 0; }
+XS_API void xs_gemm_tc_set_few_deep(int on) { g_few_deep = on ? 1 : 0; }
 
 XS_API int xs_gemm_tc_supports(int T, int N, int K, int64_t ldx, int64_t ldw) {
     return T >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && encode_fn() != nullptr;
@@ -742,10 +756,18 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
         // few tokens: the weight's rows on the M side, the tokens a narrow N
         XS_REQUIRE(make_map(&mw, w, N, K, ldw, BM), "gemm (tcgen05): the weight's tensor map could not be made");
         XS_REQUIRE(make_map(&mx, x, T, K, ldx, bn), "gemm (tcgen05): the input's tensor map could not be made");
-        switch (bn) {
-            case 16: rc = launch<16, 8>(mw, mx, p, stream); break;
-            case 32: rc = launch<32, 8>(mw, mx, p, stream); break;
-            default: rc = launch<64, 6>(mw, mx, p, stream); break;
+        if (g_few_deep) {
+            switch (bn) {
+                case 16: rc = launch<16, 8>(mw, mx, p, stream); break;
+                case 32: rc = launch<32, 8>(mw, mx, p, stream); break;
+                default: rc = launch<64, 6>(mw, mx, p, stream); break;
+            }
+        } else {
+            switch (bn) {
+                case 16: rc = launch<16, 5>(mw, mx, p, stream); break;
+                case 32: rc = launch<32, 5>(mw, mx, p, stream); break;
+                default: rc = launch<64, 4>(mw, mx, p, stream); break;
+            }
         }
     } else {
         // many tokens: the tokens on the M side, 128 or 256 weight rows on the N side; pairs of CTAs beyond 128 tokens
