@@ -539,6 +539,16 @@ def test_attention(case, kernel, dtype):
                     for _ in range(2):
                         merged = run_attention(lib, pg, kernel, scale, window, gt, splits, counters=counters)
                         assert torch.equal(merged, out) and int(counters.abs().sum()) == 0
+                if kernel == "mma" and max(q_lens) == 1 and D == 64:
+                    # head size 64, one token a sequence: the kernel that the TMA unit feeds (pages as whole boxes, swizzled
+                    # shared memory, stale rows past a sequence's end and pages given back left as they are and masked)
+                    counters = torch.zeros(len(starts) * Hkv, dtype=torch.int32, device=DEV)
+                    for with_counters in (False, True):
+                        fed = run_attention(lib, pg, kernel, scale, window, gt, splits, tma=True,
+                                            counters=counters if with_counters else None)
+                        close(fed, ref, dtype, factor=3)
+                        assert lib.gemm_tc_status(DEV).item() == 0, "a wait inside the kernel gave up"
+                        assert int(counters.abs().sum()) == 0
 
 
 def test_attention_refuses_more_splits_than_it_combines():
@@ -593,7 +603,7 @@ def test_attention_tc(case):
             close(out, same.double(), "bfloat16", factor=3)
 
 
-def run_attention(lib, pg, kernel, scale, window, gate, splits, counters=None):
+def run_attention(lib, pg, kernel, scale, window, gate, splits, counters=None, tma=False):
     d = pg.dev()
     T = d["q"].shape[0]
     out = torch.full((T, pg.Hq, pg.D), float("nan"), device=DEV, dtype=d["q"].dtype)
@@ -608,7 +618,7 @@ def run_attention(lib, pg, kernel, scale, window, gate, splits, counters=None):
         need = lib.attention_mma_scratch_bytes(T * pg.Hq, pg.D, splits)
         scratch = torch.full((max(need, 1),), 255, dtype=torch.uint8, device=DEV) if splits > 1 else None
         lib.attention_mma(d["q"], d["pool"], d["table"], d["cu"], d["kv_lens"], gt, out, scratch, len(pg.starts),
-                          max(pg.q_lens), pg.Hkv, 64, scale, window, splits, counters=counters)
+                          max(pg.q_lens), pg.Hkv, 64, scale, window, splits, counters=counters, bounded_waits=tma)
     return out
 
 

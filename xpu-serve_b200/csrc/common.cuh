@@ -97,18 +97,36 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 extern int g_xs_pdl;   // 1: launches carry the attribute (xs_set_pdl)
 
+// `carveout` >= 0: this launch prefers that much of an SM's memory as shared memory (per cent of the most), the rest as L1
+// cache; -1 leaves the choice to the driver. It matters beyond the kernel itself: a neighbour of the step that overlaps this
+// kernel on an SM (programmatic dependent launch) runs under the same split, and the few-row products want their L1.
 template <typename... KArgs, typename... Args>
-inline cudaError_t xs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args... args) {
+inline cudaError_t xs_launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int carveout,
+                                Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (g_xs_pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (carveout >= 0) {
+        attr[n].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+        attr[n].val.sharedMemCarveout = (unsigned int)carveout;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = g_xs_pdl ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t xs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    return xs_launch_ex(kernel, grid, block, smem, stream, -1, args...);
 }

@@ -43,10 +43,11 @@ class _Handle:
 
 class _Ahead:
     """A decode step that was started before the loop asked for it. `chosen`: its tokens on the device."""
-    __slots__ = ("row_of", "fed", "event", "host", "chosen")
+    __slots__ = ("row_of", "fed", "event", "host", "chosen", "status_at")
 
-    def __init__(self, row_of, fed, event, host, chosen):
+    def __init__(self, row_of, fed, event, host, chosen, status_at=None):
         self.row_of, self.fed, self.event, self.host, self.chosen = row_of, fed, event, host, chosen
+        self.status_at = status_at       # where in `host` the status word of kernels with bounded waits lies, if it travels
 
 
 class _Choice:
@@ -203,9 +204,9 @@ class DeviceStepper:
     def _copy_out(self, out: torch.Tensor):
         """Starts the step's only device-to-host copy (the chosen tokens, into pinned memory) and returns the
         host buffer, the event that says it has landed and where in the buffer a status word lies (None: nowhere). Two buffers take turns: a step that runs ahead
-        copies out while the one before it is still being read. When a tcgen05 kernel ran since its status
-        word was last read (prompt steps; decode steps launch none), the word travels behind the tokens and
-        `_landed` looks at it."""
+        copies out while the one before it is still being read. When a kernel with bounded waits ran since the
+        status word was last read (the tcgen05 kernels of prompt steps; decode attention at head size 64), the
+        word travels behind the tokens and `_landed` looks at it."""
         n = out.numel()
         self._turn ^= 1
         while len(self._host_bufs) < 2:
@@ -246,8 +247,8 @@ class DeviceStepper:
             out = None if logits is None else self._choose(logits, handles, 1)
         if out is None:
             return
-        host, event, _ = self._copy_out(out)        # decode steps launch no tcgen05 kernel: no status to read
-        self._ahead = _Ahead({h: i for i, h in enumerate(handles)}, None, event, host, out)
+        host, event, status_at = self._copy_out(out)
+        self._ahead = _Ahead({h: i for i, h in enumerate(handles)}, None, event, host, out, status_at)
 
     def _take_ahead(self, ahead: _Ahead, handles, token_lists, want) -> List[Optional[int]]:
         """The loop now asks for (a part of) the step that already runs."""
@@ -258,7 +259,7 @@ class DeviceStepper:
                                    "next step must bring the token that the last step returned for it")
         if len(handles) == len(ahead.row_of) and [ahead.row_of[h] for h in handles] == list(range(len(handles))):
             self._start_ahead(handles, ahead.chosen)          # the same sequences go on: keep the device busy
-        ahead.event.synchronize()
+        self._landed(ahead.host, ahead.event, ahead.status_at)
         tokens = ahead.host[:len(ahead.row_of)].tolist()
         got = [tokens[ahead.row_of[h]] for h in handles]
         if self._ahead is not None:

@@ -46,8 +46,9 @@ class _DecodeGraph:
     description buffer, whose addresses the graph holds."""
 
     def __init__(self, rows: int, graph, stager: StepStager, ws: Workspace, logits: torch.Tensor, greedy: torch.Tensor,
-                 kernels: int):
+                 kernels: int, bounded: bool):
         self.rows, self.graph, self.stager, self.ws, self.logits, self.kernels = rows, graph, stager, ws, logits, kernels
+        self.bounded = bounded     # the graph holds a kernel with bounded waits: its status word wants a look after a replay
         self.greedy = greedy       # int32 [rows]: each row's most likely token, found inside the graph
         self.batch_key = None      # (slots, version of the cache's page tables) of the step staged last
 
@@ -180,7 +181,7 @@ class Model:
         with self._workspace(ws):
             self.forward(ctx, cache, greedy)                 # allocates the scratch buffers, loads the kernels
             torch.cuda.synchronize(rt.device)
-            before = ops.launches
+            before, bounded_before = ops.launches, ops.bounded_launches
             graph = torch.cuda.CUDAGraph()
             collecting = gc.isenabled()
             gc.disable()          # a collection inside the capture could destroy another model's graphs there
@@ -192,7 +193,7 @@ class Model:
                     gc.enable()
             kernels = ops.launches - before
         ws.frozen = True
-        return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels)
+        return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels, ops.bounded_launches > bounded_before)
 
     def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
         n = len(slots)
@@ -211,6 +212,8 @@ class Model:
         self.last_h2d_bytes = g.stager.last_h2d_bytes
         g.graph.replay()
         ops.launches += g.kernels
+        if g.bounded:
+            ops.mark_bounded(self.rt.device)
         picked = [i for i, places in enumerate(want) for _ in places]
         if picked == list(range(n)):
             self.last_greedy = g.greedy[:n]
@@ -242,6 +245,8 @@ class Model:
         self.last_h2d_bytes = g.stager.last_h2d_bytes
         g.graph.replay()
         ops.launches += g.kernels
+        if g.bounded:
+            ops.mark_bounded(self.rt.device)
         cache.end_step(slots, [1] * n)
         return g.logits[:n]
 

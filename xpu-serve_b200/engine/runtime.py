@@ -72,6 +72,7 @@ class Runtime:
         # decode attention cuts each sequence's keys over enough CTAs to fill this many CTA slots an SM
         # (0: sized by rounds of CTAs, parts/attention.py decode_splits; n > 0: n CTAs an SM, the earlier rule)
         self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "0"))
+        self.attn_fixed_cost = float(os.environ.get("XS_ATTN_FIXED_COST", "2"))
         # attention of prompts: "tcgen05" (head size 64 and groups that divide 128; everything else takes the
         # mma.sync kernel anyway) or "mma". Measured on B200, 32 heads over 8: 2,048 tokens 67 against 97 us,
         # 2,048 tokens after 30,000: 1.01 against 1.87 ms.

@@ -46,7 +46,7 @@ def _signatures(lib) -> None:
         "xs_gemm_small_m_normed": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P, P],
         "xs_gemm_small_m_ex": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P,
                                P, P, P, P, P, P, I, I, P, P, P, P],
-        "xs_attention_mma_merged": [P, P, P, I, P, P, P, L, P, P, L, P, I, I, I, I, I, I, I, F, I, I, P],
+        "xs_attention_mma_merged": [P, P, P, I, P, P, P, L, P, P, L, P, L, P, I, I, I, I, I, I, I, F, I, I, P],
         "xs_gemm_tc": [P, P, P, P, I, I, I, I, I, L, L, L, I, P, L, P, P],
         "xs_argmax": [P, L, I, I, P, P, P],
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, I, P, P],
@@ -172,6 +172,11 @@ def load(verbose: bool = True):
             lib.xs_set_pdl(0)
         if os.environ.get("XS_TC_NO_PAIR", "0") == "1":
             lib.xs_gemm_tc_set_pair(0)
+        if "XS_ATTN_TMA_CARVEOUT" in os.environ:
+            lib.xs_attention_mma_set_tma_carveout(int(os.environ["XS_ATTN_TMA_CARVEOUT"]))
+        if "XS_ATTN_DECODE_TMA" in os.environ:        # "0": cp.async kernel for every head size; "n" (2..6): that many stages
+            n = int(os.environ["XS_ATTN_DECODE_TMA"])
+            lib.xs_attention_mma_set_decode_tma(1 if n > 0 else 0, n)
         profile, sync = os.environ.get("XS_PROFILE", "0") == "1", os.environ.get("XS_SYNC", "0") == "1"
         if profile or sync:
             lib = _Watched(lib, profile, sync)
@@ -373,11 +378,14 @@ def attention_mma_scratch_bytes(rows: int, head_dim: int, splits: int) -> int:
 def attention_mma(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor,
                   kv_lens: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
                   scratch: Optional[torch.Tensor], n_seqs: int, max_q_len: int, kv_heads: int, page_size: int,
-                  scale: float, window: int, splits: int, counters: Optional[torch.Tensor] = None) -> None:
+                  scale: float, window: int, splits: int, counters: Optional[torch.Tensor] = None,
+                  bounded_waits: bool = False) -> None:
     """Tensor-core attention over the paged bfloat16 cache. `scratch`: a byte buffer of at least
     attention_mma_scratch_bytes(tokens * heads, head_dim, splits) when splits > 1. `counters`: at least
     n_seqs * kv_heads zeroed int32 words that the kernel leaves zeroed; with them a decode step (one token a
-    sequence) merges its key splits inside the attention kernel instead of in a second one."""
+    sequence) merges its key splits inside the attention kernel instead of in a second one. `bounded_waits`: a decode
+    step at head size 64 may take the kernel that the TMA unit feeds; its waits are bounded, and one that gives up sets
+    gemm_tc_status(device), which the caller then has to look at (tc_status_unread)."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "cache", torch.bfloat16)
     _need(page_table, "page table", torch.int32)
     T, heads, D = q.shape
@@ -394,9 +402,13 @@ def attention_mma(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
         _need(counters, "counters", torch.int32)
         if counters.numel() < n_seqs * kv_heads:
             raise KernelError(f"attention: {counters.numel()} counters for {n_seqs} sequences of {kv_heads} kv heads")
+    tma = bounded_waits and max_q_len == 1 and D == 64 and heads // kv_heads <= 16
+    if tma:
+        mark_bounded(q.device)
     _check(load().xs_attention_mma_merged(
         q.data_ptr(), pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
         kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), _ptr(scratch), sbytes, _ptr(counters) if merged else None,
+        pool.shape[0] if tma else 0, gemm_tc_status(q.device).data_ptr() if tma else None,
         T, n_seqs, max_q_len, heads, kv_heads, D, page_size, float(scale), int(window), int(splits), _stream()),
         kernels=2 if splits > 1 and not merged else 1)
 
@@ -420,7 +432,7 @@ def attention_tc(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, 
         if gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < heads:
             raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {heads} heads")
         ld_gate = gate.stride(0)
-    _tc_unread.add(gemm_tc_status(q.device).device)
+    mark_bounded(q.device)
     _check(load().xs_attention_tc(
         q.data_ptr(), pool.data_ptr(), pool.shape[0], page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
         kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), T, n_seqs, max_q_len, heads, kv_heads, D, page_size,
@@ -541,11 +553,20 @@ def gemm_tc_status(device) -> torch.Tensor:
     return _tc_status[device]
 
 
-# Devices on which a tcgen05 kernel was launched since the status word was last looked at. Whoever next
-# waits for the device anyway (the generation loop for its tokens, trace replay for its logits) reads the
-# word with what it waits for and hands it to `tc_status_read`; decode steps launch no such kernel and
-# pay nothing.
+# Devices on which a kernel with bounded waits (the tcgen05 kernels, decode attention fed by the TMA unit) was launched
+# since the status word was last looked at. Whoever next waits for the device anyway (the generation loop for its
+# tokens, trace replay for its logits) reads the word with what it waits for and hands it to `tc_status_read`.
 _tc_unread = set()
+
+
+bounded_launches = 0      # launches of kernels with bounded waits since import (a graph's capture counts its own)
+
+
+def mark_bounded(device) -> None:
+    """A kernel with bounded waits was launched (or a graph that holds one replayed) on `device`."""
+    global bounded_launches
+    bounded_launches += 1
+    _tc_unread.add(gemm_tc_status(device).device)
 
 
 def tc_status_unread(device) -> bool:
@@ -579,7 +600,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         raise KernelError(f"gemm (tcgen05): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if bias is not None:
         _need(bias, "bias", torch.float32)
-    _tc_unread.add(gemm_tc_status(x.device).device)
+    mark_bounded(x.device)
     _check(load().xs_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), _code(out), int(epilogue), T, N, K,
                              x.stride(0), w.stride(0), out.stride(0), int(ksplit), _ptr(scratch),
                              0 if scratch is None else scratch.numel() * scratch.element_size(),

@@ -18,7 +18,7 @@ from ..ops import lib as ops
 from .base import KVNeed, Mixer, TensorSpec
 
 
-def decode_splits(tiles: int, blocks: int, slots: int) -> int:
+def decode_splits(tiles: int, blocks: int, slots: int, fixed: float = 2.0) -> int:
     """Into how many parts to cut each sequence's keys when every sequence brings one token: `tiles` CTAs
     (sequences x kv heads) would each walk `blocks` 64-key blocks; `slots` CTAs run at one time. The cost of a
     choice is its number of rounds of CTAs times a CTA's length (its blocks and a fixed cost worth about two),
@@ -28,7 +28,7 @@ def decode_splits(tiles: int, blocks: int, slots: int) -> int:
     best, best_cost = 1, None
     for parts in range(1, max(1, min(blocks, 64)) + 1):
         rounds = -(-tiles * parts // slots)
-        cost = rounds * (-(-blocks // parts) + 2) + (1.5 + parts / 3.0 if parts > 1 else 0.0)
+        cost = rounds * (-(-blocks // parts) + fixed) + (1.5 + parts / 3.0 if parts > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = parts, cost
     return best
@@ -121,7 +121,8 @@ class AttentionMixer(Mixer):
             if s.window > 0:
                 blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
             if step.decode and s.heads // s.kv_heads <= 16 and rt.attn_split_factor == 0:
-                splits = decode_splits(tiles, blocks, max(1, ops.attention_mma_decode_slots(s.head_dim, tiles)))
+                splits = decode_splits(tiles, blocks, max(1, ops.attention_mma_decode_slots(s.head_dim, tiles)),
+                                       rt.attn_fixed_cost)
             else:
                 splits = max(1, min(blocks, 32, (max(rt.attn_split_factor, 1) * rt.sm_count) // max(tiles, 1)))
             # prompts: the tcgen05 kernel, unless few tiles face many keys (a short piece of a long sequence), where
@@ -137,7 +138,8 @@ class AttentionMixer(Mixer):
                 scratch = rt.ws.get("attn_scratch", (need,), torch.uint8)
             counters = rt.attn_counters if (rt.fuse_tails and rt.tail_attn and step.n_seqs * s.kv_heads <= rt.attn_counters.numel()) else None
             ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, scratch, step.n_seqs,
-                              step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, splits, counters=counters)
+                              step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, splits, counters=counters,
+                              bounded_waits=step.decode)
             return
         ops.attention_generic(q, cache.storage, table, step.seq_of_token, step.positions, gate, o, s.kv_heads,
                               step.page_size, s.scale, s.window)
