@@ -441,3 +441,51 @@ def test_every_tail_on_the_model_path(name, folders, references, monkeypatch):
     cache.close(slots)
     assert int(rt.conv_counters.abs().sum()) == 0 and int(rt.attn_counters.abs().sum()) == 0
     assert int(rt.amax_keys.abs().sum()) == 0 and int(rt.amax_counter.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "R", "H", "X"])
+def test_prompt_steps_of_one_sequence_through_graphs(name, dtype, folders, monkeypatch):
+    """One sequence's prompt (or a later piece of it) whose last row is wanted runs as a CUDA graph captured per number
+    of rows (32 to 512), padded with a sequence in the cache's spare slot. The same logits as kernel by kernel (in
+    float32 bit for bit); pieces at every start, a piece that ends a page, the smallest and the
+    largest piece of a bucket, decoding after it (the cache and the conv state were written where they belong), a
+    second sequence in another slot, and the spare slot's rubbish never read."""
+    from xpu_serve_b200.engine.model import load_model
+    folder = folders[(name, dtype)]
+    toks = tiny.prompt(name, 400, salt=21)
+    other = tiny.prompt(name, 90, salt=22)
+    cuts = [(0, 32), (32, 64), (64, 191), (191, 193), (193, 400)]          # rows 32 (filled: no padding), 32, 128, 32, 256
+
+    def run(graphs):
+        monkeypatch.setenv("XS_NO_PROMPT_GRAPHS", "0" if graphs else "1")
+        model = load_model(folder, dtype=dtype)
+        assert model.use_prompt_graphs == graphs
+        cache = model.new_cache(1024)
+        a, b = cache.open(2)
+        out = []
+        for lo, hi in cuts:
+            out.append(model.step(cache, [a], [toks[lo:hi]]).clone())
+            if lo == 32:
+                out.append(model.step(cache, [b], [other]).clone())       # another sequence in between (128 rows)
+        for t in (5, 6, 7):
+            out.append(model.step(cache, [a, b], [[t], [t + 1]]).clone())
+        if graphs:
+            assert sorted(model._prompt_graphs[cache.serial]) == [32, 128, 256]
+        cache.close([a, b])
+        cache.check()
+        return out
+
+    plain_run, graph_run = run(False), run(True)
+    for x, y in zip(plain_run, graph_run):
+        if dtype == "float32":
+            assert torch.equal(x, y)        # the same kernels on the same rows: the same bits
+        else:                               # (the library product and the key splits may differ with the number of rows)
+            assert (x - y).abs().max().item() <= tolerance(name, dtype) * x.abs().max().item()
+    ref = tu.plain_logits(folder, {"a": toks, "b": other})
+    last = torch.stack([graph_run[i][0] for i in (0, 1, 3, 4, 5)]).double().cpu().numpy()
+    want = np.stack([ref[("a", hi - 1)] for _, hi in cuts])
+    gap = np.abs(last - want).max() / np.abs(want).max()
+    assert gap <= tolerance(name, dtype), f"gap {gap:.3e}"
+    gap_b = np.abs(graph_run[2][0].double().cpu().numpy() - ref[("b", 89)]).max() / np.abs(want).max()
+    assert gap_b <= tolerance(name, dtype)

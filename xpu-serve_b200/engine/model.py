@@ -31,6 +31,17 @@ from .runtime import Runtime, Workspace
 from .step import StepContext, StepStager
 
 
+PROMPT_BUCKETS = (32, 64, 128, 256, 512)
+
+
+def _prompt_bucket(n: int) -> Optional[int]:
+    """Rows of the graph that serves one sequence's piece of n tokens (the piece and its padding rows, if any), or None."""
+    for b in PROMPT_BUCKETS:
+        if n <= b:
+            return b
+    return None
+
+
 def _bucket(n: int) -> int:
     """Batch sizes that decode graphs are captured for: exact up to 8, then multiples of 8 up to 64,
     then multiples of 32."""
@@ -82,6 +93,16 @@ class Model:
         self._graphs: Dict[int, Dict[int, _DecodeGraph]] = {}
         self._cache_refs: Dict[int, weakref.ref] = {}
         self._retired: List[Dict[int, _DecodeGraph]] = []
+        # Prompt steps of one sequence are bound by the host (some 130 launches at 10 to 15 us each, against half a
+        # millisecond of device time for 128 tokens), so they are captured too: per cache and per number of rows (32 to
+        # 512; the piece is padded with a sequence in the cache's spare slot). XS_NO_PROMPT_GRAPHS=1: kernel by kernel.
+        # Only when every part of the model says that its prompt code can be captured for any lengths (parts/base.py).
+        parts_ok = all(getattr(c, "fixed_shape_ok", False) for layer in spec.layers for c in (
+            registry.arrangement_class(layer.kind), registry.mixer_class(layer.mixer.kind),
+            registry.ffn_class(layer.ffn.kind), registry.norm_class(layer.norm.kind)))
+        parts_ok = parts_ok and getattr(registry.norm_class(spec.final_norm.kind), "fixed_shape_ok", False)
+        self.use_prompt_graphs = self.use_graphs and parts_ok and os.environ.get("XS_NO_PROMPT_GRAPHS", "0") != "1"
+        self._prompt_graphs: Dict[int, Dict[int, _DecodeGraph]] = {}
         self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
 
     # ----------------------------------------------------------------- cache
@@ -132,6 +153,9 @@ class Model:
         try:
             if self.use_graphs and max(q_lens) == 1:
                 logits = self._decode_with_graph(cache, slots, token_lists, want, starts)
+            elif (self.use_prompt_graphs and len(slots) == 1 and _prompt_bucket(q_lens[0]) is not None
+                  and list(want[0]) == [q_lens[0] - 1]):
+                logits = self._prompt_with_graph(cache, slots[0], token_lists[0], int(starts[0]))
             else:
                 ctx = self.stager.stage(cache, slots, token_lists, want, starts)
                 self.last_h2d_bytes = self.stager.last_h2d_bytes
@@ -162,9 +186,10 @@ class Model:
                 model = me()
                 if model is not None:
                     model._cache_refs.pop(serial, None)
-                    dead = model._graphs.pop(serial, None)
-                    if dead:
-                        model._retired.append(dead)
+                    for table in (model._graphs, model._prompt_graphs):
+                        dead = table.pop(serial, None)
+                        if dead:
+                            model._retired.append(dead)
 
             self._cache_refs[serial] = weakref.ref(cache, gone)
         return per_cache
@@ -194,6 +219,49 @@ class Model:
             kernels = ops.launches - before
         ws.frozen = True
         return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels, ops.bounded_launches > bounded_before)
+
+    def _capture_prompt(self, cache: Cache, rows: int) -> _DecodeGraph:
+        """Captures a prompt step of `rows` rows (one sequence's piece and its padding sequence). Warm-up and capture
+        run in the cache's spare slot and page only."""
+        rt = self.rt
+        ws = Workspace(rt.device)
+        width = sum(cache.groups[gi].max_seq_pages for gi in cache.kv_groups)
+        stager = StepStager(rt.device, capacity=3 * rows + 2 * width + 64, fixed=True)
+        ctx = stager.stage_prompt_fixed(cache, cache.dummy_slot, [0], 0, rows)
+        greedy = torch.empty(1, dtype=torch.int32, device=rt.device)
+        with self._workspace(ws):
+            self.forward(ctx, cache, greedy)
+            torch.cuda.synchronize(rt.device)
+            before, bounded_before = ops.launches, ops.bounded_launches
+            graph = torch.cuda.CUDAGraph()
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.forward(ctx, cache, greedy)
+            finally:
+                if collecting:
+                    gc.enable()
+            kernels = ops.launches - before
+        ws.frozen = True
+        return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels, ops.bounded_launches > bounded_before)
+
+    def _prompt_with_graph(self, cache: Cache, slot: int, tokens: Sequence[int], start: int) -> torch.Tensor:
+        rows = _prompt_bucket(len(tokens))
+        self._graphs_of(cache)                    # (registers the cache's end of life, clears retired graphs)
+        per_cache = self._prompt_graphs.setdefault(cache.serial, {})
+        g = per_cache.get(rows)
+        if g is None:
+            g = per_cache[rows] = self._capture_prompt(cache, rows)
+            cache._graph_owner = self
+        g.stager.stage_prompt_fixed(cache, slot, tokens, start, rows)
+        self.last_h2d_bytes = g.stager.last_h2d_bytes
+        g.graph.replay()
+        ops.launches += g.kernels
+        if g.bounded:
+            ops.mark_bounded(self.rt.device)
+        self.last_greedy = g.greedy          # the row's most likely token, chosen inside the graph
+        return g.logits                      # [1, vocab]: the graph's own output buffer, valid until the next step of this size
 
     def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
         n = len(slots)

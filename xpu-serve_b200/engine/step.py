@@ -45,6 +45,8 @@ class StepContext:
     page_tables: Dict[int, torch.Tensor] = field(default_factory=dict)
     q_lens_host: Optional[np.ndarray] = None
     starts_host: Optional[np.ndarray] = None
+    fixed_shape: bool = False    # the step is (being captured as) a graph for any lengths up to max_q_len / max_kv_len:
+                                 # parts choose their kernels and grids from those bounds, not from q_lens_host
 
 
 class StepStager:
@@ -102,6 +104,29 @@ class StepStager:
         r4 = _round4(rows)
         # (sequences, offsets of tokens, positions and lengths, words up to the end of the lengths)
         self._fixed_layout = (n, 0, r4, 3 * r4 + _round4(rows + 1) + r4, 3 * r4 + _round4(rows + 1) + 2 * r4)
+        return ctx
+
+    def stage_prompt_fixed(self, cache, slot: int, tokens: Sequence[int], start: int, rows: int) -> StepContext:
+        """One sequence's next `len(tokens)` tokens (at most `rows`), laid out as a step of exactly `rows` tokens in
+        two sequences: the real one, then a padding sequence of the remaining rows (none when the piece fills the step)
+        in the cache's spare slot and page (nothing it computes is ever read). The layout, every address and every size that a kernel launch gets from the
+        host depend on `rows` and the cache alone, so a graph captured for `rows` serves any shorter prompt piece at any
+        position. The logits wanted are the real sequence's last row's."""
+        T = len(tokens)
+        if not 0 < T <= rows:
+            raise ValueError(f"{T} tokens do not fit a fixed step of {rows} rows")
+        tok = np.zeros(rows, dtype=np.int64)
+        tok[:T] = np.asarray(tokens, dtype=np.int64)
+        pos = np.concatenate([np.arange(start, start + T, dtype=np.int64), np.arange(rows - T, dtype=np.int64)])
+        seq_of = np.concatenate([np.zeros(T, dtype=np.int64), np.ones(rows - T, dtype=np.int64)])
+        cu = np.asarray([0, T, rows], dtype=np.int64)
+        sl = np.asarray([slot, cache.dummy_slot], dtype=np.int64)
+        kv = np.asarray([start + T, rows - T], dtype=np.int64)
+        real = [] if slot == cache.dummy_slot else [slot]        # (a capture runs in the spare slot: spare pages for both rows)
+        tables = {gi: cache.page_table_fixed(gi, real, 2) for gi in cache.kv_groups}
+        ctx = self._emit(cache, tok, pos, seq_of, cu, sl, kv, np.asarray([T - 1], dtype=np.int64), tables,
+                         np.asarray([rows, rows], dtype=np.int64), np.asarray([start, 0], dtype=np.int64), cache.max_seq_tokens)
+        ctx.decode, ctx.max_q_len, ctx.fixed_shape, ctx.want_all = False, rows, True, False
         return ctx
 
     def restage_next_token(self, tokens: Sequence[int], starts: np.ndarray) -> bool:

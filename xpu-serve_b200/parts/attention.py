@@ -37,6 +37,7 @@ def decode_splits(tiles: int, blocks: int, slots: int, fixed: float = 2.0) -> in
 class AttentionMixer(Mixer):
     kind = "attention"
     fuses_norm = True
+    fixed_shape_ok = True
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
@@ -112,6 +113,15 @@ class AttentionMixer(Mixer):
 
     def attend(self, q, cache, table, step, gate, o) -> None:
         s, rt = self.spec, self.rt
+        if step.fixed_shape and rt.mode == "bfloat16" and ops.attention_mma_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
+            # a step captured for any lengths up to its bounds: one key split, grids from the bounds
+            if rt.prompt_attention == "tcgen05" and ops.attention_tc_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
+                ops.attention_tc(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, step.n_seqs,
+                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window)
+            else:
+                ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, None, step.n_seqs,
+                                  step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, 1)
+            return
         if rt.mode == "bfloat16" and ops.attention_mma_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
             # Few tiles and long key ranges (decoding): split each range over several CTAs so that
             # every SM streams a part of the cache; the partial results meet in scratch memory.

@@ -65,6 +65,11 @@ class StateNeed:
 class Part:
     kind: str = ""
     fuses_norm: bool = False    # see the module text: takes a Prenormed input and an `into` sink
+    # Whether the part's code for prompt steps can be captured in a CUDA graph that serves any lengths up to the step's
+    # bounds (`step.fixed_shape`): no host-side loop over `step.q_lens_host`, no host sync, sizes from the tensors'
+    # shapes and `step.max_q_len` only. The library's parts say yes; the model captures single-sequence prompt steps
+    # only when every part of it does. (Decode steps must be capturable in any case.)
+    fixed_shape_ok: bool = False
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
@@ -90,6 +95,7 @@ class Norm(Part):
     (what the residual stream calls) then works through them. `carried` says whether the few-row products
     can carry this norm across themselves (RMSNorm only: see parts/block.py)."""
     carried: bool = False
+    fixed_shape_ok = True       # `normed` works on tensors alone
 
     @classmethod
     def tensors(cls, spec, weight_name: str) -> Dict[str, TensorSpec]:

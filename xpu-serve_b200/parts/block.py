@@ -130,6 +130,7 @@ class ResidualStream:
 class Block:
     """The pre-norm arrangement (with optional sandwich norms)."""
     kind = "pre_norm"
+    fixed_shape_ok = True
 
     @classmethod
     def tensors(cls, layer) -> Dict[str, TensorSpec]:

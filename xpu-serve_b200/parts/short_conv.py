@@ -16,6 +16,7 @@ from .base import Mixer, StateNeed, TensorSpec
 class ShortConvMixer(Mixer):
     kind = "short_conv"
     fuses_norm = True
+    fixed_shape_ok = True
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:

@@ -17,6 +17,7 @@ from .base import FeedForward, TensorSpec
 class SwiGLU(FeedForward):
     kind = "swiglu"
     fuses_norm = True
+    fixed_shape_ok = True
 
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
