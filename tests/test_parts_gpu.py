@@ -800,6 +800,64 @@ def test_long_decoding(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_a_key_length_bound_of_the_graphs(tmp_path, dtype):
+    """Decode graphs are captured per number of rows and per bound on the keys of a sequence (1,024, 1,536, ...): two
+    sequences decode from 1,010 and 1,017 keys to beyond 1,024, through `Model.step` and, fed from the device, through
+    `step_from_last_greedy`; the logits on both sides of the bound match the plain implementation, and the model holds
+    a graph for each bound."""
+    from xpu_serve_b200.engine.model import load_model
+    name = "A"
+    folder = tiny.make_folder(tmp_path, name, dtype)
+    cfg, W = plain.load_folder(folder)
+    model = load_model(folder, dtype=dtype)
+    cache = model.new_cache(4096, max_slots=2, max_seq_tokens=2048)
+    tol = tiny.bound(name, dtype)
+    seqs = [tiny.prompt(name, 1010, salt=5), tiny.prompt(name, 1017, salt=6)]
+    slots = cache.open(2)
+    model.step(cache, slots, seqs, [[], []])
+    # (a) tokens given by the host
+    rows = [[], []]
+    for k in range(12):
+        nxt = [[(31 * k + 7 * i + 3) % cfg["vocab_size"]] for i in range(2)]
+        lg = model.step(cache, slots, nxt).float().cpu().numpy()
+        for i in range(2):
+            seqs[i] = seqs[i] + nxt[i]
+            rows[i].append(lg[i])
+    for i in range(2):
+        ref = plain.forward(cfg, W, seqs[i], rows=list(range(len(seqs[i]) - 12, len(seqs[i]))))
+        gap = gap_of(np.stack(rows[i]), ref)
+        print(f"GAP across-bound {dtype} seq {i} gap={gap:.3e}")
+        assert gap <= tol
+    bounds = sorted(k[1] for k in model._graphs[cache.serial])
+    assert bounds == [1024, 1536], bounds
+    cache.close(slots)
+    # (b) tokens chosen on the device, from 1,019 and 1,022 keys on (the graph changes under the run-ahead path)
+    seqs = [tiny.prompt(name, 1019, salt=8), tiny.prompt(name, 1022, salt=9)]
+    slots = cache.open(2)
+    first = model.step(cache, slots, seqs).float().cpu().numpy()
+    chosen = [[int(np.argmax(first[i]))] for i in range(2)]
+    model.step(cache, slots, chosen)                 # a graph step: from here on the device feeds itself
+    assert model.last_greedy is not None
+    fed = [model.last_greedy.cpu().tolist()]
+    for _ in range(8):
+        got = model.step_from_last_greedy(cache, slots)
+        assert got is not None
+        fed.append(got.cpu().tolist())
+    for i in range(2):
+        seq = seqs[i] + chosen[i]
+        for k, step_tokens in enumerate(fed):
+            logits = plain.forward(cfg, W, seq, rows=[len(seq) - 1])[0]
+            order = np.argsort(-logits)
+            margin = float(logits[order[0]] - logits[order[1]]) / float(np.abs(logits).max())
+            if margin > 2 * tol:
+                assert step_tokens[i] == int(order[0]), (i, k, margin)
+            seq = seq + [step_tokens[i]]
+    assert len(seq) > 1024 + 4
+    cache.close(slots)
+    cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(tiny.CONFIGS))
 def test_first_tokens(tmp_path, name, dtype):
     """Positions 0, 1, 2: a one-token prompt, then single tokens; and prompts of 1, 2 and 3 tokens in one batch."""

@@ -15,7 +15,7 @@ import gc
 import os
 import weakref
 from contextlib import contextmanager
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -52,13 +52,25 @@ def _bucket(n: int) -> int:
     return -(-n // 32) * 32
 
 
+def _kv_bucket(n: int, limit: int) -> int:
+    """Key lengths that decode graphs are captured for: 1,024, 1,536, 2,048, 3,072, ... up to the cache's limit
+    for one sequence. The split of a sequence's keys over CTAs is fixed when a graph is captured, so it should fit
+    the lengths that the graph then sees: measured on B200 (1.2B shape, 2,048 cached tokens), a graph sized for
+    131,072 keys takes 0.86 instead of 0.75 ms a step at batch 8 and 1.32 instead of 1.16 at batch 64."""
+    b = 1024
+    while b < n:
+        b = b * 3 // 2 if (b & (b - 1)) == 0 else (b // 3) * 4
+    return min(b, limit)
+
+
 class _DecodeGraph:
     """A captured decode step for a fixed number of rows: its own scratch buffers and its own
     description buffer, whose addresses the graph holds."""
 
     def __init__(self, rows: int, graph, stager: StepStager, ws: Workspace, logits: torch.Tensor, greedy: torch.Tensor,
-                 kernels: int, bounded: bool):
+                 kernels: int, bounded: bool, kv_limit: Optional[int] = None):
         self.rows, self.graph, self.stager, self.ws, self.logits, self.kernels = rows, graph, stager, ws, logits, kernels
+        self.kv_limit = kv_limit   # decode graphs: the most keys a sequence may have when this graph is replayed
         self.bounded = bounded     # the graph holds a kernel with bounded waits: its status word wants a look after a replay
         self.greedy = greedy       # int32 [rows]: each row's most likely token, found inside the graph
         self.batch_key = None      # (slots, version of the cache's page tables) of the step staged last
@@ -90,7 +102,7 @@ class Model:
         # which unlike its id() no later cache gets) and number of rows. When a cache is gone its graphs are set
         # aside and destroyed at the next decode step: the garbage collector may notice the cache in the middle
         # of a graph capture, where destroying a graph is not allowed.
-        self._graphs: Dict[int, Dict[int, _DecodeGraph]] = {}
+        self._graphs: Dict[int, Dict[Tuple[int, int], _DecodeGraph]] = {}
         self._cache_refs: Dict[int, weakref.ref] = {}
         self._retired: List[Dict[int, _DecodeGraph]] = []
         # Prompt steps of one sequence are bound by the host (some 130 launches at 10 to 15 us each, against half a
@@ -175,7 +187,7 @@ class Model:
         finally:
             self.rt.ws = old
 
-    def _graphs_of(self, cache: Cache) -> Dict[int, _DecodeGraph]:
+    def _graphs_of(self, cache: Cache) -> Dict[Tuple[int, int], _DecodeGraph]:
         self._retired.clear()            # no capture is under way here
         per_cache = self._graphs.get(cache.serial)
         if per_cache is None:
@@ -194,14 +206,24 @@ class Model:
             self._cache_refs[serial] = weakref.ref(cache, gone)
         return per_cache
 
-    def _capture(self, cache: Cache, rows: int) -> _DecodeGraph:
-        """Captures the decode step for `rows` sequences. Warm-up and capture run on padding rows only
-        (the cache's spare slot and page), so no sequence's state is touched before the first replay."""
+    def _decode_graph(self, cache: Cache, rows: int, keys: int) -> _DecodeGraph:
+        """The graph for `rows` sequences of at most `keys` keys each, captured at its first use."""
+        per_cache = self._graphs_of(cache)
+        key = (rows, _kv_bucket(keys, cache.max_seq_tokens))
+        g = per_cache.get(key)
+        if g is None:
+            g = per_cache[key] = self._capture(cache, rows, key[1])
+            cache._graph_owner = self        # graphs die with the model; the cache only marks its use
+        return g
+
+    def _capture(self, cache: Cache, rows: int, kv_limit: int) -> _DecodeGraph:
+        """Captures the decode step for `rows` sequences of at most `kv_limit` keys. Warm-up and capture run on
+        padding rows only (the cache's spare slot and page), so no sequence's state is touched before the first replay."""
         rt = self.rt
         ws = Workspace(rt.device)
         width = sum(cache.groups[gi].max_seq_pages for gi in cache.kv_groups)
         stager = StepStager(rt.device, capacity=8 * rows + rows * width + 64, fixed=True)
-        ctx = stager.stage_decode_fixed(cache, [], [], np.zeros(0, dtype=np.int64), rows)
+        ctx = stager.stage_decode_fixed(cache, [], [], np.zeros(0, dtype=np.int64), rows, kv_limit)
         greedy = torch.empty(rows, dtype=torch.int32, device=rt.device)
         with self._workspace(ws):
             self.forward(ctx, cache, greedy)                 # allocates the scratch buffers, loads the kernels
@@ -218,7 +240,7 @@ class Model:
                     gc.enable()
             kernels = ops.launches - before
         ws.frozen = True
-        return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels, ops.bounded_launches > bounded_before)
+        return _DecodeGraph(rows, graph, stager, ws, logits, greedy, kernels, ops.bounded_launches > bounded_before, kv_limit)
 
     def _capture_prompt(self, cache: Cache, rows: int) -> _DecodeGraph:
         """Captures a prompt step of `rows` rows (one sequence's piece and its padding sequence). Warm-up and capture
@@ -265,17 +287,13 @@ class Model:
 
     def _decode_with_graph(self, cache: Cache, slots, token_lists, want, starts) -> torch.Tensor:
         n = len(slots)
-        rows = _bucket(n)
-        per_cache = self._graphs_of(cache)
-        g = per_cache.get(rows)
-        if g is None:
-            g = per_cache[rows] = self._capture(cache, rows)
-            cache._graph_owner = self        # graphs die with the model; the cache only marks its use
+        g = self._decode_graph(cache, _bucket(n), int(np.max(starts)) + 1)
+        rows = g.rows
         tokens = [t[0] for t in token_lists]
         batch_key = (tuple(slots), cache.tables_version())
         # the same sequences as in this graph's last step and no page table changed: rewrite tokens and positions only
         if not (g.batch_key == batch_key and g.stager.restage_next_token(tokens, starts)):
-            g.stager.stage_decode_fixed(cache, slots, tokens, np.asarray(starts, dtype=np.int64), rows)
+            g.stager.stage_decode_fixed(cache, slots, tokens, np.asarray(starts, dtype=np.int64), rows, g.kv_limit)
             g.batch_key = batch_key
         self.last_h2d_bytes = g.stager.last_h2d_bytes
         g.graph.replay()
@@ -305,9 +323,13 @@ class Model:
             starts = cache.begin_step(slots, [1] * n)
         except CacheError:
             return None
+        if int(np.max(starts)) + 1 > g.kv_limit:
+            # the sequences have outgrown the key lengths this graph was sized for: the next graph (tokens_dev, the
+            # old graph's buffer, is copied into the new graph's description before `last_greedy` moves on)
+            g = self._decode_graph(cache, g.rows, int(np.max(starts)) + 1)
         batch_key = (tuple(slots), cache.tables_version())
         if not (g.batch_key == batch_key and g.stager.restage_fed(tokens_dev, n, starts)):
-            g.stager.stage_decode_fixed(cache, slots, [0] * n, np.asarray(starts, dtype=np.int64), g.rows)
+            g.stager.stage_decode_fixed(cache, slots, [0] * n, np.asarray(starts, dtype=np.int64), g.rows, g.kv_limit)
             g.stager.feed_tokens(tokens_dev, n)
             g.batch_key = batch_key
         self.last_h2d_bytes = g.stager.last_h2d_bytes
@@ -316,6 +338,7 @@ class Model:
         if g.bounded:
             ops.mark_bounded(self.rt.device)
         cache.end_step(slots, [1] * n)
+        self._last_graph, self.last_greedy = g, g.greedy[:n]
         return g.logits[:n]
 
     def step_from_last_greedy(self, cache: Cache, slots: Sequence[int]) -> Optional[torch.Tensor]:

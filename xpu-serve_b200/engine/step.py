@@ -84,11 +84,13 @@ class StepStager:
                           tables, q_lens, np.asarray(starts, dtype=np.int64), int((starts + q_lens).max()))
 
     def stage_decode_fixed(self, cache, slots: Sequence[int], tokens: Sequence[int], starts: np.ndarray,
-                           rows: int) -> StepContext:
+                           rows: int, kv_limit: Optional[int] = None) -> StepContext:
         """One token for each of `slots`, laid out as a batch of exactly `rows` sequences with page
         tables of the cache's full width, so that the layout (and every address a captured graph
         reads) is the same from step to step. Rows past len(slots) are padding: they use the cache's
-        spare slot and page, stand at position 0 and are never read by the real rows."""
+        spare slot and page, stand at position 0 and are never read by the real rows. `kv_limit`: the most keys
+        a sequence of this step will have (what the launches that are captured size their key splits by);
+        the cache's own limit when not given."""
         n = len(slots)
         tok = np.zeros(rows, dtype=np.int64)
         tok[:n] = np.asarray(tokens, dtype=np.int64)
@@ -100,7 +102,7 @@ class StepStager:
         tables = {gi: cache.page_table_fixed(gi, slots, rows) for gi in cache.kv_groups}
         q_lens = np.ones(rows, dtype=np.int64)
         ctx = self._emit(cache, tok, pos, idx, np.arange(rows + 1, dtype=np.int64), sl, pos + 1, idx, tables, q_lens,
-                         pos, cache.max_seq_tokens)
+                         pos, cache.max_seq_tokens if kv_limit is None else min(kv_limit, cache.max_seq_tokens))
         r4 = _round4(rows)
         # (sequences, offsets of tokens, positions and lengths, words up to the end of the lengths)
         self._fixed_layout = (n, 0, r4, 3 * r4 + _round4(rows + 1) + r4, 3 * r4 + _round4(rows + 1) + 2 * r4)
