@@ -227,7 +227,7 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
 // bound by latency, not bandwidth): measured on the whole decode step, 1.2B shape, batch 8: 0.811 -> 0.773 ms with
 // it on the attention and convolution output projections and the q/k/v product; on grids of more CTAs it loses.
 template <int NT, typename TO, bool EXACT, int UNROLL = UNROLL_DEFAULT>
-__global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? 4 : 2) gemm_small_m_kernel(const SmallMParams p) {
+__global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) ? 3 : 4) : 2) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
     __shared__ __align__(16) float ssq_in[kSsqStaged][16];
@@ -572,15 +572,18 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
         p.counters = (unsigned int*)((char*)scratch + scratch_bytes - kCounterBytes);
     }
     const dim3 grid(tiles, ksplit);
-    // (up to 8 rows: with 16 the unpredicated loop spills registers)
-    const bool exact = M <= 8 && N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0;
+    // (9 to 16 rows: the unpredicated loop needs 78 registers, three CTAs an SM; with sixteen loads a round, 128 and two.
+    // Measured on the whole decode step, 1.2B shape, batch 16: 1.05 ms predicated, 1.03 unpredicated, 0.99 with sixteen
+    // loads, against 0.93 with the library product, which is why the default keeps this kernel to 8 rows.)
+    const bool exact = N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0;
     // sixteen loads a round: slices that are multiples of 2,048 and at most one wave of two CTAs an SM
     const bool one_round = exact && g_small_m_one_round && (K / ksplit) % (2 * K_PER_CTA) == 0 &&
                            (int64_t)tiles * ksplit <= (g_small_m_one_round > 1 ? g_small_m_one_round : (int64_t)(g_small_m_wave / 4) * 2);
 #define XS_GO(NT, TO)                                                                                       \
     ((one_round && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, p) \
-     : (exact && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true>, grid, dim3(WARPS * 32), 0, stream, p)  \
-                        : xs_launch(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, p))
+     : (exact && NT == 2 && (K / ksplit) % (2 * K_PER_CTA) == 0) ? xs_launch(gemm_small_m_kernel<2, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, p) \
+     : exact ? xs_launch(gemm_small_m_kernel<NT, TO, true>, grid, dim3(WARPS * 32), 0, stream, p)  \
+             : xs_launch(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, p))
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
     } else if (out_dtype == XS_BF16) {
