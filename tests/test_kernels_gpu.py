@@ -725,13 +725,13 @@ def test_short_conv_in_steps_equals_one_pass(dtype, H, K):
     assert (got[2].double().cpu() - flipped).abs().max() > 0.5
 
 
-@pytest.mark.parametrize("K", [2, 3, 4, 5])
-def test_short_conv_long_prompts(K):
+@pytest.mark.parametrize("H,steps", [(1024, [[900, 3, 1, 1499], [1201, 2, 6, 1000]]),          # runs of 4 tokens
+                                     (2048, [[2101, 5, 1, 299], [17, 2, 2300, 101]])])           # runs of 8 tokens
+@pytest.mark.parametrize("K", [2, 3, 4, 5, 7, 8])
+def test_short_conv_long_prompts(K, H, steps):
     """Long ragged prompts take the kernel in which a thread walks several tokens: sequences that start inside
     a thread's run, a run that ends past the last token, and a second step that continues from the state."""
     lib = ops()
-    H = 1024
-    steps = [[900, 3, 1, 1499], [1201, 2, 6, 1000]]
     totals = [sum(st[s] for st in steps) for s in range(4)]
     bcx_all = [(torch.randn(n, 3 * H) * 2).to(torch.bfloat16) for n in totals]
     taps, bias = torch.randn(H, K), torch.randn(H)

@@ -130,10 +130,13 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
 
 // Long prompts: a thread walks RUN neighbouring tokens of its 8 channels with the last KT-1 gated inputs in
 // registers, so that B, C and X of a token are read once (not once per tap) and the taps once per thread.
-// At the run's first token, and wherever a sequence starts inside the run, the history is fetched as the
-// plain kernel does (state rows, or earlier tokens of the same sequence).
+// A run that lies inside one sequence (nearly all of them) asks for nothing by index but its first token's sequence:
+// its loads do not wait for one another, four tokens' worth are in flight at a time. A run that crosses from one
+// sequence into the next, or ends the step, goes token by token: at its first token, and wherever a sequence starts,
+// the history is fetched as the plain kernel does (state rows, or earlier tokens of the same sequence). Both add up
+// a token's taps in the plain kernel's order.
 template <int KT, int RUN>
-__global__ void __launch_bounds__(256) short_conv_bf16x8_run_kernel(
+__global__ void __launch_bounds__(128) short_conv_bf16x8_run_kernel(
     const __nv_bfloat16* __restrict__ bcx, int64_t ld, const float* __restrict__ w_t, const float* __restrict__ bias,
     const __nv_bfloat16* __restrict__ state, const int32_t* __restrict__ seq_of_token,
     const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots, __nv_bfloat16* __restrict__ out, int Tn,
@@ -145,6 +148,8 @@ __global__ void __launch_bounds__(256) short_conv_bf16x8_run_kernel(
     const int run = (int)(idx / H8), c8 = (int)(idx % H8) * 8;
     const int t0 = run * RUN;
     if (t0 >= Tn) return;
+    const int t_last = min(t0 + RUN, Tn) - 1;
+    const int seq0 = seq_of_token[t0], seq1 = seq_of_token[t_last];
     float w[KT][8], b0[8];
 #pragma unroll
     for (int j = 0; j < KT; ++j) {
@@ -156,25 +161,8 @@ __global__ void __launch_bounds__(256) short_conv_bf16x8_run_kernel(
 #pragma unroll
     for (int k = 0; k < 8; ++k) b0[k] = bias != nullptr ? bias[c8 + k] : 0.0f;
     float hist[KT - 1][8];
-#pragma unroll
-    for (int i = 0; i < RUN; ++i) {
-        const int t = t0 + i;
-        if (t >= Tn) break;
-        const int seq = seq_of_token[t];
-        const int first = cu_seqlens[seq];
-        const int t_local = t - first;
-        if (i == 0 || t_local == 0) {
-            const __nv_bfloat16* st = state + (int64_t)slots[seq] * (KT - 1) * H;
-#pragma unroll
-            for (int j = 0; j < KT - 1; ++j) {
-                const int r = t_local + j;
-                if (r < KT - 1) unpack8(*reinterpret_cast<const uint4*>(st + (int64_t)r * H + c8), hist[j]);
-                else gated8(bcx + ((int64_t)first + r - (KT - 1)) * ld, c8, H, hist[j]);
-            }
-        }
-        float g[8], acc[8], c[8];
-        gated8(bcx + (int64_t)t * ld, c8, H, g);
-        unpack8(*reinterpret_cast<const uint4*>(bcx + (int64_t)t * ld + H + c8), c);
+    auto one_token = [&](const float (&g)[8], const float (&c)[8], int t) {
+        float acc[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             float a = b0[k];
@@ -189,6 +177,62 @@ __global__ void __launch_bounds__(256) short_conv_bf16x8_run_kernel(
             for (int k = 0; k < 8; ++k) hist[j][k] = hist[j + 1][k];
 #pragma unroll
         for (int k = 0; k < 8; ++k) hist[KT - 2][k] = g[k];
+    };
+    if (seq0 == seq1 && t_last == t0 + RUN - 1) {
+        const int t_local = t0 - cu_seqlens[seq0];
+        if (t_local >= KT - 1) {            // (the same for all threads of a run)
+#pragma unroll
+            for (int j = 0; j < KT - 1; ++j) gated8(bcx + (int64_t)(t0 + j - (KT - 1)) * ld, c8, H, hist[j]);
+        } else {
+            const __nv_bfloat16* st = state + (int64_t)slots[seq0] * (KT - 1) * H;
+#pragma unroll
+            for (int j = 0; j < KT - 1; ++j) {
+                const int r = t_local + j;
+                if (r < KT - 1) unpack8(*reinterpret_cast<const uint4*>(st + (int64_t)r * H + c8), hist[j]);
+                else gated8(bcx + (int64_t)(t0 + j - (KT - 1)) * ld, c8, H, hist[j]);
+            }
+        }
+#pragma unroll
+        for (int i0 = 0; i0 < RUN; i0 += 4) {
+            uint4 rb[4], rx[4], rc[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat16* row = bcx + (int64_t)(t0 + i0 + i) * ld + c8;
+                rb[i] = *reinterpret_cast<const uint4*>(row);
+                rc[i] = *reinterpret_cast<const uint4*>(row + H);
+                rx[i] = *reinterpret_cast<const uint4*>(row + 2 * H);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float b[8], x[8], g[8], c[8];
+                unpack8(rb[i], b);
+                unpack8(rx[i], x);
+                unpack8(rc[i], c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) g[k] = __bfloat162float(__float2bfloat16_rn(b[k] * x[k]));
+                one_token(g, c, t0 + i0 + i);
+            }
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int t = t0; t <= t_last; ++t) {
+        const int seq = seq_of_token[t];
+        const int first = cu_seqlens[seq];
+        const int t_local = t - first;
+        if (t == t0 || t_local == 0) {
+            const __nv_bfloat16* st = state + (int64_t)slots[seq] * (KT - 1) * H;
+#pragma unroll
+            for (int j = 0; j < KT - 1; ++j) {
+                const int r = t_local + j;
+                if (r < KT - 1) unpack8(*reinterpret_cast<const uint4*>(st + (int64_t)r * H + c8), hist[j]);
+                else gated8(bcx + ((int64_t)first + r - (KT - 1)) * ld, c8, H, hist[j]);
+            }
+        }
+        float g[8], c[8];
+        gated8(bcx + (int64_t)t * ld, c8, H, g);
+        unpack8(*reinterpret_cast<const uint4*>(bcx + (int64_t)t * ld + H + c8), c);
+        one_token(g, c, t);
     }
 }
 
@@ -278,19 +322,31 @@ XS_API int xs_short_conv(const void* bcx, int64_t ld, const float* w_t, const fl
         return 0;
     }
     if (vec) {
-        constexpr int RUN = 4;
-        const int64_t run_threads = (int64_t)ceil_div_i(T, RUN) * (H / 8);
-        if (K >= 2 && K <= 5 && run_threads >= 64 * 1024) {    // enough runs to fill the device
-            const dim3 grid(ceil_div_i(run_threads, 256));
+        // runs of 8 tokens when that still makes 64 k threads (2,048 tokens of 2,048 channels), else runs of 4, else
+        // (short steps) one thread a token
+        const int64_t threads8 = (int64_t)ceil_div_i(T, 8) * (H / 8), threads4 = (int64_t)ceil_div_i(T, 4) * (H / 8);
+        if (K >= 2 && K <= 8 && threads4 >= 64 * 1024) {
+            const bool long_runs = threads8 >= 64 * 1024;
+            const dim3 grid(ceil_div_i(long_runs ? threads8 : threads4, 128));
 #define XS_CONV_RUN(KT)                                                                                              \
-    short_conv_bf16x8_run_kernel<KT, RUN><<<grid, 256, 0, stream>>>(                                                  \
-        (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots,       \
-        (__nv_bfloat16*)out, T, H)
+    do {                                                                                                             \
+        if (long_runs)                                                                                               \
+            short_conv_bf16x8_run_kernel<KT, 8><<<grid, 128, 0, stream>>>(                                            \
+                (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots, \
+                (__nv_bfloat16*)out, T, H);                                                                          \
+        else                                                                                                         \
+            short_conv_bf16x8_run_kernel<KT, 4><<<grid, 128, 0, stream>>>(                                            \
+                (const __nv_bfloat16*)bcx, ld, w_t, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots, \
+                (__nv_bfloat16*)out, T, H);                                                                          \
+    } while (0)
             switch (K) {
                 case 2: XS_CONV_RUN(2); break;
                 case 3: XS_CONV_RUN(3); break;
                 case 4: XS_CONV_RUN(4); break;
-                default: XS_CONV_RUN(5); break;
+                case 5: XS_CONV_RUN(5); break;
+                case 6: XS_CONV_RUN(6); break;
+                case 7: XS_CONV_RUN(7); break;       // the reference's default number of taps
+                default: XS_CONV_RUN(8); break;
             }
 #undef XS_CONV_RUN
         } else {
