@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from xpu_serve_b200.cache import Cache
-from xpu_serve_b200.engine.model import _bucket
+from xpu_serve_b200.engine.model import _bucket, _kv_bucket
 from xpu_serve_b200.engine.runtime import Workspace
 from xpu_serve_b200.parts.attention import decode_splits
 from xpu_serve_b200.parts.base import KVNeed, StateNeed
@@ -50,6 +50,13 @@ def test_decode_splits_rule():
 def test_decode_batch_buckets():
     assert [_bucket(n) for n in (1, 5, 8, 9, 16, 17, 63, 64, 65, 96, 97)] == [1, 5, 8, 16, 16, 24, 64, 64, 96, 96, 128]
     assert all(_bucket(n) >= n for n in range(1, 300))
+
+
+def test_key_length_bounds_of_decode_graphs():
+    assert [_kv_bucket(n, 1 << 20) for n in (1, 1024, 1025, 1536, 1537, 2048, 2049, 3073, 100000)] == \
+        [1024, 1024, 1536, 1536, 2048, 2048, 3072, 4096, 131072]
+    assert all(n <= _kv_bucket(n, 1 << 20) < 2 * max(n, 1024) for n in range(1, 5000, 7))
+    assert _kv_bucket(5, 300) == 300 and _kv_bucket(3100, 3500) == 3500       # never beyond the cache's limit
 
 
 def test_every_cache_has_a_serial_number_of_its_own():

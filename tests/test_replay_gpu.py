@@ -363,6 +363,34 @@ def test_a_new_cache_gets_graphs_of_its_own(folders):
         assert torch.equal(a, b)
 
 
+def test_decode_graphs_beyond_the_cap_are_let_go_and_captured_again(folders, monkeypatch):
+    """A cache keeps a bounded number of decode graphs: with the cap at 2, batches of 1, 2 and 3 sequences make the
+    model let the first graph go; a batch of 1 again captures it anew, and every step's logits match the plain
+    implementation."""
+    from xpu_serve_b200.engine import model as model_mod
+    monkeypatch.setattr(model_mod, "MAX_DECODE_GRAPHS", 2)
+    folder = folders[("A", "bfloat16")]
+    cfg, W = plain.load_folder(folder)
+    model = model_mod.load_model(folder, dtype="bfloat16")
+    cache = model.new_cache(512, max_slots=4, max_seq_tokens=128)
+    tol = tolerance("A", "bfloat16")
+    for round_, n in enumerate((1, 2, 3, 1, 3)):
+        seqs = [tiny.prompt("A", 6 + 5 * i + round_, salt=40 + i + 10 * round_) for i in range(n)]
+        slots = cache.open(n)
+        model.step(cache, slots, seqs, [[] for _ in seqs])
+        for k in range(3):
+            nxt = [[(13 * k + 5 * i + round_) % cfg["vocab_size"]] for i in range(n)]
+            lg = model.step(cache, slots, nxt).float().cpu().numpy()
+            seqs = [s + t for s, t in zip(seqs, nxt)]
+            for i in range(n):
+                ref = plain.forward(cfg, W, seqs[i], rows=[len(seqs[i]) - 1])[0]
+                assert np.abs(lg[i] - ref).max() / np.abs(ref).max() <= tol, (round_, k, i)
+        assert len(model._graphs[cache.serial]) <= 2
+        cache.close(slots)
+    assert sorted(k[0] for k in model._graphs[cache.serial]) == [1, 3]
+    cache.check()
+
+
 def test_a_kernel_that_refuses_in_mid_step_leaves_the_books_as_they_were(folders, monkeypatch):
     """A layer in the middle of a step raises (as a kernel that refuses its arguments does): the pages the
     step had reserved go back, lengths stay, and the generation loop's answer, closing the sequences, works."""

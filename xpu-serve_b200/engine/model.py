@@ -32,6 +32,7 @@ from .step import StepContext, StepStager
 
 
 PROMPT_BUCKETS = (32, 64, 128, 256, 512)
+MAX_DECODE_GRAPHS = 24      # per cache: (rows, bound on keys) pairs kept at one time
 
 
 def _prompt_bucket(n: int) -> Optional[int]:
@@ -71,6 +72,7 @@ class _DecodeGraph:
                  kernels: int, bounded: bool, kv_limit: Optional[int] = None):
         self.rows, self.graph, self.stager, self.ws, self.logits, self.kernels = rows, graph, stager, ws, logits, kernels
         self.kv_limit = kv_limit   # decode graphs: the most keys a sequence may have when this graph is replayed
+        self.last_use = 0
         self.bounded = bounded     # the graph holds a kernel with bounded waits: its status word wants a look after a replay
         self.greedy = greedy       # int32 [rows]: each row's most likely token, found inside the graph
         self.batch_key = None      # (slots, version of the cache's page tables) of the step staged last
@@ -104,7 +106,8 @@ class Model:
         # of a graph capture, where destroying a graph is not allowed.
         self._graphs: Dict[int, Dict[Tuple[int, int], _DecodeGraph]] = {}
         self._cache_refs: Dict[int, weakref.ref] = {}
-        self._retired: List[Dict[int, _DecodeGraph]] = []
+        self._retired: List[Dict] = []
+        self._uses = 0
         # Prompt steps of one sequence are bound by the host (some 130 launches at 10 to 15 us each, against half a
         # millisecond of device time for 128 tokens), so they are captured too: per cache and per number of rows (32 to
         # 512; the piece is padded with a sequence in the cache's spare slot). XS_NO_PROMPT_GRAPHS=1: kernel by kernel.
@@ -214,6 +217,11 @@ class Model:
         if g is None:
             g = per_cache[key] = self._capture(cache, rows, key[1])
             cache._graph_owner = self        # graphs die with the model; the cache only marks its use
+            if len(per_cache) > MAX_DECODE_GRAPHS:       # each holds its scratch buffers and its logits: let the one unused longest go
+                oldest = min((k for k in per_cache if k != key), key=lambda k: per_cache[k].last_use)
+                self._retired.append({oldest: per_cache.pop(oldest)})    # destroyed at the next step, outside any capture
+        self._uses += 1
+        g.last_use = self._uses
         return g
 
     def _capture(self, cache: Cache, rows: int, kv_limit: int) -> _DecodeGraph:
