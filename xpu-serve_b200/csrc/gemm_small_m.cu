@@ -1,13 +1,19 @@
 // out[M, N] = x[M, K] . w[N, K]^T for few rows (M <= 16): the decode-time matrix product.
 //
-// The weight is read exactly once, straight from HBM into registers with 16-byte loads, and
-// never staged: with M this small the product is bound by weight bandwidth. A CTA of 8 warps
+// The weight is read exactly once, straight from HBM into registers (32-byte loads where nothing needs a predicate,
+// 16-byte loads otherwise), and never staged: with M this small the product is bound by weight bandwidth. A CTA of 8 warps
 // owns 16 weight rows and a slice of K; its warps take the slice's 32-wide k blocks in turn
 // (warp w: blocks w, w+8, ...), four blocks' loads issued together. They multiply on tensor
 // cores (mma.sync m16n8k16: weight rows on the M side, the batch on the N side) and add their
 // partial sums in shared memory in warp order. A lane's 16 bytes are 8 consecutive k of one
 // row; the same assignment of k to fragment slots is used for the weight and for x, which is
 // all a contraction needs.
+//
+// What the activations cost (measured on B200, N 16384, K 2048, 8 rows, weights from memory, us): 14.3 with x read
+// 16 bytes a lane; 12.0 with no x at all (the multiplies on zeros); 13.5 with 32 bytes a lane (a warp's load then
+// covers whole lines of its 8 rows: half the trips through the load path, for x and for the weight). Every CTA reads
+// all of x for its 16 weight rows, 32 KB for 64 KB of weight; the multiplies themselves and the epilogue cost nothing
+// measurable (mma.sync replaced by integer adds: the same time).
 //
 // Narrow outputs with a long K (the feed-forward's down projection) would leave most SMs
 // idle, so K is cut into `ksplit` slices over blockIdx.y. Each slice's CTA writes its 16 x M
@@ -49,6 +55,17 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {   // weights are use
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
+}
+
+// 32 bytes a lane: a warp's load covers whole 128-byte lines of 8 rows, half the trips through the load path of
+// two 16-byte loads (sm_100 has 256-bit global loads).
+__device__ __forceinline__ void ld_stream32(const void* p, uint4& lo, uint4& hi) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(p));
+}
+__device__ __forceinline__ void ld_act32(const void* p, uint4& lo, uint4& hi) {      // activations: kept in L1 for the SM's other CTAs
+    asm volatile("ld.global.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(p));
 }
 
 struct SmallMParams {
@@ -241,14 +258,18 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     const int n0 = tile * ROWS;
     // clamped: out-of-range rows are not stored
     const int ra = EXACT ? n0 + g : min(n0 + g, p.N - 1), rb = EXACT ? n0 + g + 8 : min(n0 + g + 8, p.N - 1);
-    const __nv_bfloat16* wa_p = p.w + (int64_t)ra * p.ldw + q * 8;
-    const __nv_bfloat16* wb_p = p.w + (int64_t)rb * p.ldw + q * 8;
+    // EXACT: a lane takes 16 consecutive k (32 bytes) of a row at a time, which fill the fragment slots of two
+    // neighbouring 32-wide k blocks; otherwise 8 (16 bytes) of one block. Weights and x use the same assignment.
+    static_assert(kBlocked, "pairs of neighbouring k blocks");
+    constexpr int kLane = EXACT ? 16 : 8;
+    const __nv_bfloat16* wa_p = p.w + (int64_t)ra * p.ldw + q * kLane;
+    const __nv_bfloat16* wb_p = p.w + (int64_t)rb * p.ldw + q * kLane;
     const __nv_bfloat16* x_p[NT];
     bool x_ok[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         x_ok[t] = t * 8 + g < p.M;
-        x_p[t] = p.x + (int64_t)(x_ok[t] ? t * 8 + g : 0) * p.ldx + q * 8;
+        x_p[t] = p.x + (int64_t)(x_ok[t] ? t * 8 + g : 0) * p.ldx + q * kLane;
     }
     float acc[NT][4];
 #pragma unroll
@@ -271,13 +292,21 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     constexpr int ws = kBlocked ? UNROLL_DEFAULT : 1, us = kBlocked ? 1 : WARPS;
     auto slot = [](int u) { return (u / UNROLL_DEFAULT) * (WARPS * UNROLL_DEFAULT) + (u % UNROLL_DEFAULT) * us; };
     int kb = kb_begin + warp * ws;
+    if (EXACT) {
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-        const int k0 = (kb + slot(u)) * 32;
-        // K is a multiple of 8: a lane's 8 elements are all inside or all outside
-        const bool in = EXACT || (kb + slot(u) < kb_end && k0 + q * 8 < p.K);
-        wa[u] = in ? ld_stream(wa_p + k0) : zero;
-        wb[u] = in ? ld_stream(wb_p + k0) : zero;
+        for (int u = 0; u < UNROLL; u += 2) {
+            ld_stream32(wa_p + (kb + slot(u)) * 32, wa[u], wa[u + 1]);
+            ld_stream32(wb_p + (kb + slot(u)) * 32, wb[u], wb[u + 1]);
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k0 = (kb + slot(u)) * 32;
+            // K is a multiple of 8: a lane's 8 elements are all inside or all outside
+            const bool in = kb + slot(u) < kb_end && k0 + q * 8 < p.K;
+            wa[u] = in ? ld_stream(wa_p + k0) : zero;
+            wb[u] = in ? ld_stream(wb_p + k0) : zero;
+        }
     }
     if (kBlocked) {
         // The rounds after the first are asked into L2 now (a hint, no registers held): when their loads are
@@ -353,13 +382,24 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     };
     for (; kb - warp * ws < kb_end; kb += WARPS * UNROLL) {
         uint4 xv[UNROLL][NT];
+        if (EXACT) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k0 = (kb + slot(u)) * 32;
-            const bool in = EXACT || (kb + slot(u) < kb_end && k0 + q * 8 < p.K);
+            for (int u = 0; u < UNROLL; u += 2) {
 #pragma unroll
-            for (int t = 0; t < NT; ++t)
-                xv[u][t] = (in && x_ok[t]) ? *reinterpret_cast<const uint4*>(x_p[t] + k0) : zero;
+                for (int t = 0; t < NT; ++t) {
+                    if (x_ok[t]) ld_act32(x_p[t] + (kb + slot(u)) * 32, xv[u][t], xv[u + 1][t]);
+                    else xv[u][t] = xv[u + 1][t] = zero;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int k0 = (kb + slot(u)) * 32;
+                const bool in = kb + slot(u) < kb_end && k0 + q * 8 < p.K;
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    xv[u][t] = (in && x_ok[t]) ? *reinterpret_cast<const uint4*>(x_p[t] + k0) : zero;
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -373,9 +413,9 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         if (EXACT) {
             if (nkb - warp * ws < kb_end) {       // the same for the whole CTA
 #pragma unroll
-                for (int u = 0; u < UNROLL; ++u) {
-                    wa[u] = ld_stream(wa_p + (nkb + slot(u)) * 32);
-                    wb[u] = ld_stream(wb_p + (nkb + slot(u)) * 32);
+                for (int u = 0; u < UNROLL; u += 2) {
+                    ld_stream32(wa_p + (nkb + slot(u)) * 32, wa[u], wa[u + 1]);
+                    ld_stream32(wb_p + (nkb + slot(u)) * 32, wb[u], wb[u + 1]);
                 }
             }
         } else {
@@ -575,7 +615,9 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
     // (9 to 16 rows: the unpredicated loop needs 78 registers, three CTAs an SM; with sixteen loads a round, 128 and two.
     // Measured on the whole decode step, 1.2B shape, batch 16: 1.05 ms predicated, 1.03 unpredicated, 0.99 with sixteen
     // loads, against 0.93 with the library product, which is why the default keeps this kernel to 8 rows.)
-    const bool exact = N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0;
+    // (the unpredicated instances load 32 bytes a lane: operands and rows on 32-byte boundaries)
+    const bool exact = N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0 && (uintptr_t)x % 32 == 0 &&
+                       (uintptr_t)w % 32 == 0 && ldx % 16 == 0 && ldw % 16 == 0;
     // sixteen loads a round: slices that are multiples of 2,048 and at most one wave of two CTAs an SM
     const bool one_round = exact && g_small_m_one_round && (K / ksplit) % (2 * K_PER_CTA) == 0 &&
                            (int64_t)tiles * ksplit <= (g_small_m_one_round > 1 ? g_small_m_one_round : (int64_t)(g_small_m_wave / 4) * 2);
