@@ -1,19 +1,13 @@
 // out[M, N] = x[M, K] . w[N, K]^T for few rows (M <= 16): the decode-time matrix product.
 //
-// The weight is read exactly once, straight from HBM into registers (32-byte loads where nothing needs a predicate,
-// 16-byte loads otherwise), and never staged: with M this small the product is bound by weight bandwidth. A CTA of 8 warps
+// The weight is read exactly once, straight from HBM into registers with 16-byte loads, and
+// never staged: with M this small the product is bound by weight bandwidth. A CTA of 8 warps
 // owns 16 weight rows and a slice of K; its warps take the slice's 32-wide k blocks in turn
 // (warp w: blocks w, w+8, ...), four blocks' loads issued together. They multiply on tensor
 // cores (mma.sync m16n8k16: weight rows on the M side, the batch on the N side) and add their
 // partial sums in shared memory in warp order. A lane's 16 bytes are 8 consecutive k of one
 // row; the same assignment of k to fragment slots is used for the weight and for x, which is
 // all a contraction needs.
-//
-// What the activations cost (measured on B200, N 16384, K 2048, 8 rows, weights from memory, us): 14.3 with x read
-// 16 bytes a lane; 12.0 with no x at all (the multiplies on zeros); 13.5 with 32 bytes a lane (a warp's load then
-// covers whole lines of its 8 rows: half the trips through the load path, for x and for the weight). Every CTA reads
-// all of x for its 16 weight rows, 32 KB for 64 KB of weight; the multiplies themselves and the epilogue cost nothing
-// measurable (mma.sync replaced by integer adds: the same time).
 //
 // Narrow outputs with a long K (the feed-forward's down projection) would leave most SMs
 // idle, so K is cut into `ksplit` slices over blockIdx.y. Each slice's CTA writes its 16 x M
@@ -248,7 +242,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
     __shared__ __align__(16) float ssq_in[kSsqStaged][16];
-    __shared__ float ssq_red[16][17];
+    __shared__ float ssq_red[WARPS][17];
     __shared__ float inv[16];
     __shared__ __align__(16) float staged[9 * ROWS];      // old stream values [8][16], then the next norm's weights [16]
     __shared__ bool last;
@@ -351,8 +345,11 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     // the producer's per-tile sums of squares travel to shared memory beside the main loop (no registers held,
-    // nothing waits for them until the loop is done)
-    if (p.in_ssq != nullptr) {
+    // nothing waits for them until the first round's multiplies are done): a thread asks for the 16-byte chunks
+    // (a tile's sums of 4 batch rows) that it will add up itself, and only those of rows the batch has
+    const int ssq_rows = (threadIdx.x & 3) * 4;          // this thread's batch rows: ssq_rows .. ssq_rows + 3
+    const bool ssq_mine = p.in_ssq != nullptr && ssq_rows < p.M;
+    if (ssq_mine) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int c = threadIdx.x + WARPS * 32 * u;          // 16-byte chunk: tile c / 4, batch rows (c % 4) * 4 ...
@@ -362,23 +359,42 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    // The sums of squares are added up (first level: thread (j, m) takes tiles j * 8 .. j * 8 + 7 of batch row m,
-    // then every 16th tile beyond the staged ones) after the first round's multiplies, while the second round's
-    // weights are on their way, not in the CTA's tail, where its place on the SM streams nothing.
-    bool ssq_done = p.in_ssq == nullptr;
+    // The sums of squares are added up behind the main loop without a barrier of their own: a thread adds the chunks
+    // it asked for itself (tiles t and t + 64, then every 64th beyond the staged ones), the lanes of a warp that hold
+    // the same batch rows meet by shuffles, and the warps' sums wait in shared memory for the barrier that the
+    // reduction of the products needs anyway. Fixed order: no sum depends on timing. (Measured on B200, N 16384,
+    // K 2048, 8 rows: the carried norm costs its consumer 1.0 of 14.6 us: 0.5 the loads, 0.7 these sums, 0.4 the
+    // rows' 1 / rms, not additive; done after the first round's multiplies instead: the same or slightly slower.)
     auto ssq_first_level = [&]() {
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        __syncthreads();
-        const int sm_ = threadIdx.x & 15, sj_ = threadIdx.x >> 4;
-        float v = 0.0f;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (ssq_mine) {
+            asm volatile("cp.async.wait_all;" ::: "memory");
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int t = sj_ * 8 + u;
-            v += t < p.in_tiles ? ssq_in[t][sm_] : 0.0f;
+            for (int u = 0; u < 2; ++u) {
+                const int c = threadIdx.x + WARPS * 32 * u;
+                if ((c >> 2) < p.in_tiles) {
+                    const float4 a = *reinterpret_cast<const float4*>(&ssq_in[c >> 2][ssq_rows]);
+                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                }
+            }
+            for (int t = kSsqStaged + (threadIdx.x >> 2); t < p.in_tiles; t += WARPS * 8) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.in_ssq + (int64_t)t * 16 + ssq_rows));
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
         }
-        for (int t = kSsqStaged + sj_; t < p.in_tiles; t += 16) v += __ldcg(p.in_ssq + (int64_t)t * 16 + sm_);
-        ssq_red[sj_][sm_] = v;
-        ssq_done = true;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            v.x += __shfl_xor_sync(0xffffffffu, v.x, o);
+            v.y += __shfl_xor_sync(0xffffffffu, v.y, o);
+            v.z += __shfl_xor_sync(0xffffffffu, v.z, o);
+            v.w += __shfl_xor_sync(0xffffffffu, v.w, o);
+        }
+        if (lane < 4) {
+            ssq_red[warp][lane * 4 + 0] = v.x;
+            ssq_red[warp][lane * 4 + 1] = v.y;
+            ssq_red[warp][lane * 4 + 2] = v.z;
+            ssq_red[warp][lane * 4 + 3] = v.w;
+        }
     };
     for (; kb - warp * ws < kb_end; kb += WARPS * UNROLL) {
         uint4 xv[UNROLL][NT];
@@ -427,11 +443,8 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
                 wb[u] = in ? ld_stream(wb_p + k0) : zero;
             }
         }
-        // (every warp runs the same number of rounds: the barrier inside is safe; with 16 batch rows the registers
-        // do not allow it, and it happens after the loop)
-        if (NT == 1 && !ssq_done) ssq_first_level();
     }
-    if (!ssq_done) ssq_first_level();
+    if (p.in_ssq != nullptr) ssq_first_level();
     // c0, c1: (weight row g, batch q * 2 + {0, 1}); c2, c3: weight row g + 8
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -454,7 +467,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         if (p.in_ssq != nullptr) {
             float ss = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ss += ssq_red[j][m];
+            for (int j = 0; j < WARPS; ++j) ss += ssq_red[j][m];
             v = 1.0f / sqrtf(ss / (float)p.in_width + p.in_eps);
         }
         inv[m] = v;
