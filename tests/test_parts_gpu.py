@@ -82,14 +82,48 @@ def as_plain(weights, prefix):
 CUTS = [[5, 70, 0], [1, 1, 9], [1, 0, 1], [3, 2, 1]]      # prompts of unequal lengths, a late joiner, decoding
 
 
+def plain_attention_with_options(x, W, L, Hq, Hkv, D, eps, inv, window, gate, pairing, bias):
+    """plain.self_attention with the two options LFM3 does not use: a bias on q, k and v, and a rotation that couples
+    channels 2i and 2i + 1 (angle pos * inv[i], as for the pair (i, i + D/2) of the other order)."""
+    T = x.shape[0]
+    A = L + "self_attn."
+
+    def proj(name, heads):
+        y = x @ W[A + name + "_proj.weight"].T
+        if bias:
+            y = y + W[A + name + "_proj.bias"]
+        return y.reshape(T, heads, D)
+
+    def rotate(t):
+        if pairing == "half":
+            return plain.rope(t, np.arange(T), inv)
+        ang = np.arange(T)[:, None].astype(np.float64) * inv[None, :]
+        c, s_ = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        a, b = t[..., 0::2], t[..., 1::2]
+        out = np.empty_like(t)
+        out[..., 0::2], out[..., 1::2] = a * c - b * s_, b * c + a * s_
+        return out
+
+    q = rotate(plain.rms_norm(proj("q", Hq), W[A + "q_norm.weight"], eps))
+    k = rotate(plain.rms_norm(proj("k", Hkv), W[A + "k_norm.weight"], eps))
+    v = proj("v", Hkv)
+    o = plain.attention(q, k, v, 1.0 / math.sqrt(D), window)
+    if gate:
+        o = o * (1.0 / (1.0 + np.exp(-(x @ W[A + "gate_proj.weight"].T))))[:, :, None]
+    return o.reshape(T, Hq * D) @ W[A + "o_proj.weight"].T
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("Hq,Hkv,D,window,gate,pairs", [(4, 2, 16, 0, False, 8), (6, 3, 48, 11, True, 10), (8, 2, 64, 0, True, 32)])
-def test_attention_mixer_alone(dtype, Hq, Hkv, D, window, gate, pairs):
+@pytest.mark.parametrize("Hq,Hkv,D,window,gate,pairs,pairing,bias", [
+    (4, 2, 16, 0, False, 8, "half", False), (6, 3, 48, 11, True, 10, "half", False), (8, 2, 64, 0, True, 32, "half", False),
+    (6, 3, 48, 11, True, 10, "interleaved", True), (8, 2, 64, 0, False, 20, "interleaved", False), (4, 2, 16, 5, True, 8, "half", True)])
+def test_attention_mixer_alone(dtype, Hq, Hkv, D, window, gate, pairs, pairing, bias):
     from xpu_serve_b200.config.spec import AttentionSpec, RopeSpec
     from xpu_serve_b200.parts import AttentionMixer
     H = 72
     spec = AttentionSpec(hidden=H, heads=Hq, kv_heads=Hkv, head_dim=D, qk_norm=True, qk_norm_eps=1e-6,
-                         position=RopeSpec(D, 300.0, pairs), window=window, head_gate=gate, scale=1.0 / math.sqrt(D))
+                         position=RopeSpec(D, 300.0, pairs, pairing=pairing), window=window, head_gate=gate,
+                         scale=1.0 / math.sqrt(D), qkv_bias=bias)
     w = weights_for(AttentionMixer, spec, 1, dtype, scale={"q_proj": 4.0, "k_proj": 4.0})
     hs = Harness(dtype, AttentionMixer.cache_need(spec))
     mixer = AttentionMixer(spec, w, hs.rt)
@@ -100,7 +134,10 @@ def test_attention_mixer_alone(dtype, Hq, Hkv, D, window, gate, pairs):
     W = as_plain(w, "L.")
     inv = plain.rope_inv_freq(300.0, D, pairs)
     for x, y in zip(xs, got):
-        ref = plain.self_attention(x, W, "L.", Hq, Hkv, D, 1e-6, inv, window, gate)
+        if pairing == "half" and not bias:
+            ref = plain.self_attention(x, W, "L.", Hq, Hkv, D, 1e-6, inv, window, gate)
+        else:
+            ref = plain_attention_with_options(x, W, "L.", Hq, Hkv, D, 1e-6, inv, window, gate, pairing, bias)
         assert gap_of(y, ref) <= TOL[dtype]
 
 

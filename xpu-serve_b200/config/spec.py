@@ -23,12 +23,15 @@ class RopeSpec:
     """Rotate-half rotary position encoding (src/models/common/blocks.cpp:131-141).
 
     Pair i couples channels i and i + head_dim/2; pairs i < `pairs` turn by
-    pos * theta^(-2i/head_dim), the others by 0 (identity).
+    pos * theta^(-2i/head_dim), the others by 0 (identity). `pairing` "interleaved": pair i couples
+    channels 2i and 2i + 1 instead (LFM3 has "half"; the mixer that reads this brings such a checkpoint
+    into the rotate-half order when it loads its weights, so the kernels know one order only).
     """
     head_dim: int
     theta: float
     pairs: int
     kind: str = "rope"
+    pairing: str = "half"
 
 
 @dataclass(frozen=True)
@@ -48,8 +51,10 @@ class AttentionSpec:
         "q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight",
         "v": "self_attn.v_proj.weight", "o": "self_attn.o_proj.weight",
         "gate": "self_attn.gate_proj.weight",
-        "q_norm": "self_attn.q_norm.weight", "k_norm": "self_attn.k_norm.weight"})
+        "q_norm": "self_attn.q_norm.weight", "k_norm": "self_attn.k_norm.weight",
+        "q_bias": "self_attn.q_proj.bias", "k_bias": "self_attn.k_proj.bias", "v_bias": "self_attn.v_proj.bias"})
     kind: str = "attention"
+    qkv_bias: bool = False   # q, k and v projections with a bias each (LFM3 has none)
 
 
 @dataclass(frozen=True)

@@ -204,7 +204,12 @@ class Runtime:
         elif self.tensor_core_product(x, w):
             ops.gemm_tc(x, w, out, bias)
         elif bias is not None:
-            ops.gemm_generic(x, w, out, bias)
+            # (the library product has no float32 bias: this library's tensor-core kernel adds it in its epilogue)
+            if (self.many_rows != "library" and not hasattr(x, "ssq")
+                    and ops.gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))):
+                ops.gemm_tc(x, w, out, bias)
+            else:
+                ops.gemm_generic(x, w, out, bias)
         elif out_dtype == torch.float32:
             out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
         else:

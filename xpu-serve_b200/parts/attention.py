@@ -52,6 +52,10 @@ class AttentionMixer(Mixer):
         if spec.qk_norm:
             out[n["q_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
             out[n["k_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
+        if spec.qkv_bias:
+            out[n["q_bias"]] = TensorSpec((qd,), init="zeros", role="vector")
+            out[n["k_bias"]] = TensorSpec((kd,), init="zeros", role="vector")
+            out[n["v_bias"]] = TensorSpec((kd,), init="zeros", role="vector")
         return out
 
     @classmethod
@@ -67,8 +71,26 @@ class AttentionMixer(Mixer):
         n = spec.names
         self.q_dim = spec.heads * spec.head_dim
         self.kv_dim = spec.kv_heads * spec.head_dim
-        rows = [weights[n["q"]], weights[n["k"]], weights[n["v"]]]
-        q_rows = [weights[n["q"]]]
+        # A checkpoint whose rotation couples channels 2i and 2i + 1 is brought into the rotate-half order here: within
+        # every head the even channels first, then the odd ones, for q and k alike (their products do not change), and
+        # the per-head norm weights with them.
+        D = spec.head_dim
+        interleaved = spec.position is not None and getattr(spec.position, "pairing", "half") == "interleaved"
+        order = torch.cat([torch.arange(0, D, 2), torch.arange(1, D, 2)]) if interleaved else None
+
+        def per_head(t: torch.Tensor, heads: int) -> torch.Tensor:     # rows (or elements) of q or k, head by head
+            if order is None:
+                return t
+            return t.reshape(heads, D, *t.shape[1:])[:, order].reshape(t.shape)
+
+        wq, wk = per_head(weights[n["q"]], spec.heads), per_head(weights[n["k"]], spec.kv_heads)
+        rows = [wq, wk, weights[n["v"]]]
+        q_rows = [wq]
+        biases = q_biases = None
+        if spec.qkv_bias:
+            bq = per_head(weights[n["q_bias"]], spec.heads)
+            biases = [bq, per_head(weights[n["k_bias"]], spec.kv_heads), weights[n["v_bias"]]]
+            q_biases = [bq]
         if spec.head_gate:
             g = weights[n["gate"]]
             pad = (-g.shape[0]) % 8
@@ -76,12 +98,16 @@ class AttentionMixer(Mixer):
                 g = torch.cat([g, torch.zeros(pad, g.shape[1], dtype=g.dtype)], 0)
             rows.append(g)
             q_rows.append(g)
+            if biases is not None:
+                biases.append(torch.zeros(g.shape[0]))
+                q_biases.append(torch.zeros(g.shape[0]))
         self.w_qkvg = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
-        self._q_rows = q_rows          # stacked on the device on the first use as a reader of another cache
-        self.w_qg = None
+        self.b_qkvg = rt.vector(torch.cat([b.to(torch.float32) for b in biases])) if biases is not None else None
+        self._q_rows, self._q_biases = q_rows, q_biases          # stacked on the device on the first use as a reader of another cache
+        self.w_qg = self.b_qg = None
         self.w_o = rt.matrix(weights[n["o"]])
-        self.q_norm = rt.vector(weights[n["q_norm"]]) if spec.qk_norm else None
-        self.k_norm = rt.vector(weights[n["k_norm"]]) if spec.qk_norm else None
+        self.q_norm = rt.vector(per_head(weights[n["q_norm"]], 1)) if spec.qk_norm else None
+        self.k_norm = rt.vector(per_head(weights[n["k_norm"]], 1)) if spec.qk_norm else None
         self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
                          if spec.position is not None else None)
 
@@ -91,12 +117,14 @@ class AttentionMixer(Mixer):
         if cache is None or cache.storage is None:
             raise RuntimeError("attention needs a key/value cache")
         if cache.owner:
-            proj = rt.linear(x, self.w_qkvg, "attn_qkv")
+            proj = rt.linear(x, self.w_qkvg, "attn_qkv", self.b_qkvg)
             gate_at = self.q_dim + 2 * self.kv_dim
         else:
             if self.w_qg is None:
                 self.w_qg = rt.matrix(torch.cat([r.to(torch.float32) for r in self._q_rows], 0))
-            proj = rt.linear(x, self.w_qg, "attn_qkv")
+                if self._q_biases is not None:
+                    self.b_qg = rt.vector(torch.cat([b.to(torch.float32) for b in self._q_biases]))
+            proj = rt.linear(x, self.w_qg, "attn_qkv", self.b_qg)
             gate_at = self.q_dim
         table = step.page_tables[cache.group]
         rope = self.position.table(step.max_positions) if self.position is not None else None
