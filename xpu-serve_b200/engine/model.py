@@ -372,7 +372,7 @@ class Model:
             stream.flush(self.final_norm)
             return torch.empty((0, spec.vocab), dtype=torch.float32, device=rt.device)
         if ctx.want_all and stream.fuses():
-            y = stream.norm_input(self.final_norm, lazy=True)
+            y = stream.norm_input(self.final_norm, lazy=rt.few_rows_shape(ctx.n_tokens, self.head))
         else:
             y = stream.norm(self.final_norm, ctx.want_rows)
         logits = rt.linear(y, self.head, "logits", out_dtype=torch.float32, argmax_into=greedy)

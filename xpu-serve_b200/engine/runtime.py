@@ -89,7 +89,7 @@ class Runtime:
         self.narrow_m = int(os.environ.get("XS_NARROW_M", "16"))
         if not 0 <= self.narrow_m <= 16:
             raise ValueError("XS_NARROW_M must be 0 to 16")
-        self.narrow_n = 4096
+        self.narrow_n = 8192
         # decode: RMSNorm carried by the products on either side of it instead of a kernel of its own
         self.fuse_norms = os.environ.get("XS_NO_NORM_FUSION", "0") != "1"
         # Products with more rows. "auto": this library's tcgen05 kernel where it fuses an epilogue that the
@@ -131,17 +131,20 @@ class Runtime:
         return t.to(device=self.device, dtype=torch.float32).contiguous()
 
     # ------------------------------------------------------ matrix products
+    def few_rows_shape(self, rows: int, w: torch.Tensor) -> bool:
+        """Whether a product of `rows` rows with the weight w goes to the library's own weight-streaming kernel."""
+        # up to `small_m` rows: every product. Up to `narrow_m` rows: the products with narrow outputs, where the
+        # library's kernels leave most SMs idle (measured on B200 at 9 to 16 rows, us, this kernel against the
+        # library: N 2048 K 2048 2.9 to 3.0 against 5.1; N 3072 K 2048 3.5 to 3.6 against 5.4; N 2048 K 8192
+        # 10.9 to 11.2 against 12.7; N 6144 K 2048 6.8 to 7.0 against 7.2; but N 16384 K 2048 15.3 to 16.2 against
+        # 13.0 and N 65536 46 to 50 against 42)
+        return self.mode == "bfloat16" and (rows <= self.small_m or (rows <= self.narrow_m and w.shape[0] <= self.narrow_n))
+
     def few_rows(self, x, w: torch.Tensor) -> bool:
         """Whether this product goes to the library's own weight-streaming kernel."""
         x = getattr(x, "x", x)      # a Prenormed input counts as its tensor
-        rows = x.shape[0]
-        # up to `small_m` rows: every product. Up to `narrow_m` rows: the products with narrow outputs, where the
-        # library's kernels leave most SMs idle (measured on B200 at 9 to 16 rows, us, this kernel against the
-        # library: N 2048 K 2048 3.4 to 3.6 against 5.1; N 3072 K 2048 3.9 to 4.1 against 5.4; N 2048 K 8192
-        # 11.6 to 12.3 against 12.7; but N 6144 K 2048 8.0 to 8.3 against 7.2 and N 16384 K 2048 17 to 18 against 12.8)
-        few = rows <= self.small_m or (rows <= self.narrow_m and w.shape[0] <= self.narrow_n)
-        return (self.mode == "bfloat16" and few
-                and ops.gemm_small_m_supports(rows, x.shape[1], x.stride(0), w.stride(0)))
+        return (self.few_rows_shape(x.shape[0], w)
+                and ops.gemm_small_m_supports(x.shape[0], x.shape[1], x.stride(0), w.stride(0)))
 
     def tensor_core_product(self, x: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
         """Whether this product goes to the library's tcgen05 kernel. `fused`: the caller would use an

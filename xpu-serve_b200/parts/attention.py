@@ -111,6 +111,9 @@ class AttentionMixer(Mixer):
         self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
                          if spec.position is not None else None)
 
+    def takes_prenormed(self, rows: int) -> bool:
+        return self.rt.few_rows_shape(rows, self.w_qkvg) and self.w_qkvg.shape[1] % 8 == 0
+
     def forward(self, x, step, cache, into=None) -> torch.Tensor:
         s, rt = self.spec, self.rt
         T = x.shape[0]

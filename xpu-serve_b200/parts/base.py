@@ -31,6 +31,8 @@ a parts.block.Prenormed (the stream times the norm's weight, with the row scale 
 which it may hand to `rt.linear` / `rt.few_rows_product` only; and when `into` is given it sends its
 last product through `into.product(act, w, bias)` (which adds it to the stream inside the product's
 kernel) and returns None. Parts without the flag get the normed tensor and return their branch.
+Such a part also says, per number of rows, whether the product that reads its input runs on the few-row kernel
+(`takes_prenormed(rows)`): only then is it handed a Prenormed; otherwise it gets the normed tensor, and still `into`.
 `step` is engine.step.StepContext (which tokens belong to which sequence, where each
 sequence stands), `cache` the view of this call's storage (cache/views.py).
 """
@@ -74,6 +76,11 @@ class Part:
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
         return {}
+
+    def takes_prenormed(self, rows: int) -> bool:
+        """Parts with `fuses_norm`: whether, for a step of `rows` rows, the product that reads the part's input runs on
+        the few-row kernel, which alone can apply a norm's row scale (engine/runtime.py: Runtime.few_rows_shape)."""
+        return False
 
 
 class Mixer(Part):

@@ -98,9 +98,11 @@ class ResidualStream:
             self._pre = None
 
     def fuses(self) -> bool:
-        """Whether this step's products between norms can carry the norm (few rows, bfloat16)."""
+        """Whether products of this step can add their result to the stream themselves and carry a norm across (few
+        rows, bfloat16); which of them do is then asked part by part (`takes_prenormed`, `StreamSink.product`)."""
         rt = self.rt
-        return (rt.mode == "bfloat16" and rt.fuse_norms and self.h.shape[0] <= rt.small_m and self.h.shape[1] % 8 == 0)
+        return (rt.mode == "bfloat16" and rt.fuse_norms and self.h.shape[0] <= max(rt.small_m, rt.narrow_m)
+                and self.h.shape[1] % 8 == 0)
 
     def sink(self, next_norm: Optional[Norm]) -> StreamSink:
         return StreamSink(self, next_norm)
@@ -166,14 +168,18 @@ class Block:
         """`next_norm`: the norm that reads the stream after this block (the next block's first, or the
         final norm), for the fused path; None is always right."""
         fuse = stream.fuses() and not self.spec.sandwich and self.pre_mixer.carried
+        rows = stream.h.shape[0]
+        # (a part whose first product runs elsewhere at this number of rows gets the normed tensor, and the product
+        # before it does not prepare the norm's input for it; its last product may still add to the stream itself)
+        ffn_lazy = fuse and self.ffn.fuses_norm and self.ffn.takes_prenormed(rows)
         if fuse and self.mixer.fuses_norm:
-            x = stream.norm_input(self.pre_mixer, lazy=True)
-            self.mixer.forward(x, step, cache, into=stream.sink(self.pre_ffn))
+            x = stream.norm_input(self.pre_mixer, lazy=self.mixer.takes_prenormed(rows))
+            self.mixer.forward(x, step, cache, into=stream.sink(self.pre_ffn if ffn_lazy else None))
         else:
             x = stream.norm(self.pre_mixer)
             stream.add(self.mixer.forward(x, step, cache), self.post_mixer)
         if fuse and self.ffn.fuses_norm:
-            y = stream.norm_input(self.pre_ffn, lazy=True)
+            y = stream.norm_input(self.pre_ffn, lazy=ffn_lazy)
             self.ffn.forward(y, step, into=stream.sink(next_norm))
         else:
             y = stream.norm(self.pre_ffn)

@@ -46,6 +46,9 @@ class ShortConvMixer(Mixer):
         self.b_conv = rt.vector(weights[n["conv_bias"]]) if spec.bias else None
         self.b_out = rt.vector(weights[n["out_bias"]]) if spec.bias else None
 
+    def takes_prenormed(self, rows: int) -> bool:
+        return self.rt.few_rows_shape(rows, self.w_in) and self.w_in.shape[1] % 8 == 0
+
     def forward(self, x, step, cache, into=None) -> torch.Tensor:
         rt, H = self.rt, self.spec.hidden
         if cache is None or cache.storage is None or not cache.owner:

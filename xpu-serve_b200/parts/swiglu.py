@@ -39,6 +39,9 @@ class SwiGLU(FeedForward):
         self.w_gate_up = rt.matrix(stacked)
         self.w_down = rt.matrix(weights[n["down"]])
 
+    def takes_prenormed(self, rows: int) -> bool:
+        return bool(self.interleave) and self.rt.few_rows_shape(rows, self.w_gate_up) and self.w_gate_up.shape[1] % 8 == 0
+
     def forward(self, y, step, into=None) -> torch.Tensor:
         rt, F = self.rt, self.spec.intermediate
         act = rt.ws.get("ffn_act", (y.shape[0], F), rt.act_dtype)
