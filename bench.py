@@ -419,8 +419,8 @@ def main() -> int:
             return 0
         around = ClockSampler()          # clocks during the prefill and the batch 1 / 64 points (`clocks_points`)
         around.start()
-        prefill_ms = time_prefill(model, V, warmup=3, runs=5)
-        short_ms = time_prefill(model, V, warmup=3, runs=5, tokens=128)
+        prefill_ms = time_prefill(model, V, warmup=5, runs=9)
+        short_ms = time_prefill(model, V, warmup=5, runs=9, tokens=128)
         around.pause()
         pf = prefill_flops(cfg, nums, PROMPT)
 
