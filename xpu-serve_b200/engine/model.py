@@ -331,6 +331,8 @@ class Model:
             starts = cache.begin_step(slots, [1] * n)
         except CacheError:
             return None
+        self._uses += 1
+        g.last_use = self._uses                  # (so that a capture for another batch does not take this graph for unused)
         if int(np.max(starts)) + 1 > g.kv_limit:
             # the sequences have outgrown the key lengths this graph was sized for: the next graph (tokens_dev, the
             # old graph's buffer, is copied into the new graph's description before `last_greedy` moves on)
