@@ -89,7 +89,7 @@ class Runtime:
         self.narrow_m = int(os.environ.get("XS_NARROW_M", "16"))
         if not 0 <= self.narrow_m <= 16:
             raise ValueError("XS_NARROW_M must be 0 to 16")
-        self.narrow_n = 8192
+        self.narrow_n = int(os.environ.get("XS_NARROW_N", "8192"))
         # decode: RMSNorm carried by the products on either side of it instead of a kernel of its own
         self.fuse_norms = os.environ.get("XS_NO_NORM_FUSION", "0") != "1"
         # Products with more rows. "auto": this library's tcgen05 kernel where it fuses an epilogue that the
