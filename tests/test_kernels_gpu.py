@@ -170,8 +170,9 @@ def test_gemm_generic_rows_do_not_depend_on_the_batch():
 @pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
 # the two widest: more row tiles than CTAs fit on the device at once; (2048, 8192), (4096, 1024): no edge anywhere;
 # (2048, 8192), (3072, 2048), (512, 4096): few row tiles and K a multiple of 2,048, the variant of sixteen loads a round
+# (256, 1536), (2048, 10752), (48, 192), (64, 64): no edge but K is no multiple of 1,024: a short last round
 @pytest.mark.parametrize("N,K", [(16, 32), (100, 96), (1000, 200), (2048, 8192), (333, 2056), (10007, 200), (20000, 1096), (4096, 1024),
-                                 (3072, 2048), (512, 4096)])
+                                 (3072, 2048), (512, 4096), (256, 1536), (2048, 10752), (48, 192), (64, 64)])
 def test_gemm_small_m(M, N, K):
     lib = ops()
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -195,7 +196,8 @@ def test_gemm_small_m(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K,ksplit", [(8, 2048, 8192, 4), (3, 100, 4104, 3), (16, 256, 2048, 8), (1, 48, 512, 2), (5, 2048, 2048, 7),
-                                          (8, 2048, 8192, 2), (6, 1024, 6144, 3)])
+                                          (8, 2048, 8192, 2), (6, 1024, 6144, 3), (8, 2048, 10752, 4), (4, 512, 6656, 2),
+                                          (16, 256, 1536, 3)])
 def test_gemm_small_m_k_slices(M, N, K, ksplit):
     """K cut into slices over several CTAs: the last CTA of a tile to arrive adds the slices in slice order, so
     the bits do not depend on which one that was; a second and third call find the counters reset."""

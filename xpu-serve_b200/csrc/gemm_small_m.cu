@@ -10,9 +10,11 @@
 // all a contraction needs.
 //
 // Narrow outputs with a long K (the feed-forward's down projection) would leave most SMs
-// idle, so K is cut into `ksplit` slices over blockIdx.y. Each slice's CTA writes its 16 x M
-// partial to scratch; the CTA that arrives last (a counter per row tile) adds the slices in
-// slice order, so the sum does not depend on which CTA that was, and resets the counter.
+// idle, so K is cut into `ksplit` slices over blockIdx.y. Two to eight slices of a tile are the CTAs of one
+// thread-block cluster: each puts its 16 x M sums into slice 0's shared memory, the cluster's barrier says that all
+// have, and slice 0 adds them in slice order (no global memory, no counter; a slice more then costs 0.3 instead of
+// 2.4 us). More slices than that: each slice's CTA writes its partial to scratch; the CTA that arrives last (a counter
+// per row tile) adds the slices in slice order, so the sum does not depend on which CTA that was, and resets the counter.
 //
 // Epilogues: bias[N]; `residual` (float32 [M, N]) += result; or SwiGLU for a weight stacked in
 // blocks of 8 gate rows and 8 up rows: out[M, N / 2] = silu(gate) * up.
@@ -71,6 +73,8 @@ struct SmallMParams {
     float* partials;          // [tiles, ksplit, ROWS, 8 * NT] when ksplit > 1
     unsigned int* counters;   // [tiles], zero between calls
     int M, N, K, ksplit, swiglu, wave;
+    int cluster;              // the K slices of a tile are the CTAs of one thread-block cluster: they meet in slice 0's shared memory
+    int ragged;               // unpredicated instances: a K slice is a multiple of 64 but not of 1,024, so its last round is short
     int64_t ldx, ldw, ldo;
     // RMSNorm across the product (null / 0 when unused)
     const float* in_ssq;      // [in_tiles, 16]: sums of squares of x's stream rows, one row per producer tile
@@ -230,7 +234,7 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
     if (p.amax_out != nullptr) argmax_tail<NT>(p, sum, inv, n0);
 }
 
-// EXACT: N is a multiple of 16 and every K slice a multiple of 1,024 (8 warps x 4 blocks x 32), so no row is
+// EXACT: N is a multiple of 16 and every K slice a multiple of 64 (of 1,024 = 8 warps x 4 blocks x 32 unless `ragged`), so no row is
 // clamped and no load is predicated: a third fewer instructions in the loop that feeds the memory system.
 // UNROLL 8 (EXACT only, K slices that are multiples of 2,048): sixteen loads a lane in flight instead of eight, so a
 // slice of 2,048 is one round, all of it requested before the wait for the previous kernel; twice the registers
@@ -286,12 +290,21 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     constexpr int ws = kBlocked ? UNROLL_DEFAULT : 1, us = kBlocked ? 1 : WARPS;
     auto slot = [](int u) { return (u / UNROLL_DEFAULT) * (WARPS * UNROLL_DEFAULT) + (u % UNROLL_DEFAULT) * us; };
     int kb = kb_begin + warp * ws;
-    if (EXACT) {
+    // (unpredicated instances: a pair of k blocks is all inside the slice or all outside, the same for every lane of
+    // the warp, and only a slice whose length is no multiple of 1,024 has pairs outside, in its last round)
+    auto load_w32 = [&](int at) {
 #pragma unroll
         for (int u = 0; u < UNROLL; u += 2) {
-            ld_stream32(wa_p + (kb + slot(u)) * 32, wa[u], wa[u + 1]);
-            ld_stream32(wb_p + (kb + slot(u)) * 32, wb[u], wb[u + 1]);
+            if (!p.ragged || at + slot(u) < kb_end) {
+                ld_stream32(wa_p + (at + slot(u)) * 32, wa[u], wa[u + 1]);
+                ld_stream32(wb_p + (at + slot(u)) * 32, wb[u], wb[u + 1]);
+            } else {
+                wa[u] = wa[u + 1] = wb[u] = wb[u + 1] = zero;
+            }
         }
+    };
+    if (EXACT) {
+        load_w32(kb);
     } else {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -334,7 +347,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         for (int u = 0; u < UNROLL; u += 2) {
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                if (x_ok[t]) ld_act32(x_p[t] + (at + slot(u)) * 32, xv[u][t], xv[u + 1][t]);
+                if (x_ok[t] && (!p.ragged || at + slot(u) < kb_end)) ld_act32(x_p[t] + (at + slot(u)) * 32, xv[u][t], xv[u + 1][t]);
                 else xv[u][t] = xv[u + 1][t] = zero;
             }
         }
@@ -437,11 +450,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         if (EXACT) {
             if (nkb - warp * ws < kb_end) {       // the same for the whole CTA
                 if (kXAhead) load_x32(nkb);
-#pragma unroll
-                for (int u = 0; u < UNROLL; u += 2) {
-                    ld_stream32(wa_p + (nkb + slot(u)) * 32, wa[u], wa[u + 1]);
-                    ld_stream32(wb_p + (nkb + slot(u)) * 32, wb[u], wb[u + 1]);
-                }
+                load_w32(nkb);
             }
         } else {
 #pragma unroll
@@ -490,6 +499,28 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
         return;
     }
+    if (p.cluster) {
+        // ---- several K slices as one cluster: every slice puts its sums into slice 0's shared memory (its own place
+        // there), the cluster's barrier says that all have, and slice 0 adds them in slice order. No global memory, no
+        // fence, no counter; nobody polls.
+        __shared__ float parts[8][ROWS][8 * NT + 1];
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(&parts[slice][0][0])));
+        for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32)
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(((i / (8 * NT)) * (8 * NT + 1) + i % (8 * NT)) * 4)),
+                         "f"(sum[i / (8 * NT)][i % (8 * NT)]) : "memory");
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (slice != 0) return;
+        for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
+            float v = 0.0f;
+            for (int s = 0; s < p.ksplit; ++s) v += parts[s][i / (8 * NT)][i % (8 * NT)];     // slice order
+            sum[i / (8 * NT)][i % (8 * NT)] = v;
+        }
+        __syncthreads();
+        epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
+        return;
+    }
     // ---- several K slices: leave this slice's partial, and let the last CTA to arrive add them all
     float* mine = p.partials + ((int64_t)tile * p.ksplit + slice) * (ROWS * 8 * NT);
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) mine[i] = sum[i / (8 * NT)][i % (8 * NT)];
@@ -521,27 +552,30 @@ XS_API int xs_gemm_small_m_supports(int M, int K, int64_t ldx, int64_t ldw) {
 
 int g_small_m_ksplit_max = 4;
 XS_API void xs_gemm_small_m_set_ksplit_max(int n) { g_small_m_ksplit_max = n; }
+int g_small_m_cluster = 1;        // K slices (2 to 8) of a tile as one thread-block cluster
+XS_API void xs_gemm_small_m_set_cluster(int on) { g_small_m_cluster = on; }
 int g_small_m_one_round = 1;      // 0: off; 1: on, for grids of at most two CTAs an SM; n > 1: for grids of at most n CTAs
 XS_API void xs_gemm_small_m_set_one_round(int on) { g_small_m_one_round = on; }
 
 // How many K slices the kernel would like for this shape on a device with `sms` SMs, and the
 // scratch (bytes) that needs: partial sums, then one counter per row tile. 0 bytes when 1 slice.
 XS_API int xs_gemm_small_m_ksplit(int M, int N, int K, int sms) {
-    // Measured on B200 inside a CUDA graph (M 8): N 2048, K 8192 takes 24.5 us in one slice, 15.9 in two,
-    // 11.4 in four; N 2048, K 2048 takes 7.4, 7.0, 6.1; N 16384, K 2048 gets slower with every slice.
-    // In the whole decode step (1.2B shape, batch 8): slicing K 2048 products makes the step slower, the
-    // K 8192 one is best in four slices.
-    // With sixteen loads a round (the variant for at most one wave of two CTAs an SM, see the kernel): the same
-    // product in two slices of two rounds each, 256 CTAs, makes the step 1.4 % faster than four slices of 512.
+    // Measured on B200 inside a CUDA graph (M 8, us). With the slices of a tile as one cluster that meets in shared
+    // memory: N 2048, K 8192: 9.2 in one slice, 7.7 in two, 7.3 in four, 9.5 in eight; N 2048, K 2048: 2.5, 3.4, 3.5;
+    // N 3072, K 2048: 3.0, 3.8; N 6144, K 2048: 5.1, 7.9; N 2048, K 10752: 14.6, 12.4, 10.5 (three), 9.8 (four), 11.5
+    // (six). (With scratch memory and a counter instead, a slice more cost 2.4 us: 8.6, 8.6, 9.1 for the first shape,
+    // 2.5 against 4.9 for the second.) So: one slice for K up to 2,048 and for outputs wide enough to fill the device
+    // twice; otherwise about 2,048 of K a slice, at most `ksplit_max` slices and at most four CTAs an SM, and slices
+    // that the unpredicated instances take (whole pairs of k blocks) where there are such.
     const int tiles = ceil_div_i(N, ROWS);
     if (tiles >= 2 * sms) return 1;
     int ks = K / 2048;                // at least 2048 of K a slice
     if (ks > g_small_m_ksplit_max) ks = g_small_m_ksplit_max;
+    while (ks > 1 && (int64_t)tiles * ks > 4 * (int64_t)sms) --ks;
     if (ks < 1) ks = 1;
-    if (M <= 8 && N % ROWS == 0 && g_small_m_one_round == 1) {
-        for (int k2 = ks; k2 >= 1; --k2)
-            if (K % k2 == 0 && (K / k2) % (2 * K_PER_CTA) == 0 && (int64_t)tiles * k2 <= 2 * (int64_t)sms) return k2;
-    }
+    if (N % ROWS == 0)
+        for (int k2 = ks; k2 > 1; --k2)
+            if (K % k2 == 0 && (K / k2) % 64 == 0) return k2;
     return ks;
 }
 
@@ -638,16 +672,20 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
     // Measured on the whole decode step, 1.2B shape, batch 16: 1.05 ms predicated, 1.03 unpredicated, 0.99 with sixteen
     // loads, against 0.93 with the library product, which is why the default keeps this kernel to 8 rows.)
     // (the unpredicated instances load 32 bytes a lane: operands and rows on 32-byte boundaries)
-    const bool exact = N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % K_PER_CTA == 0 && (uintptr_t)x % 32 == 0 &&
+    // and K slices of whole pairs of k blocks; a slice that is no multiple of 1,024 has a short last round (`ragged`)
+    const bool exact = N % ROWS == 0 && K % ksplit == 0 && (K / ksplit) % 64 == 0 && (uintptr_t)x % 32 == 0 &&
                        (uintptr_t)w % 32 == 0 && ldx % 16 == 0 && ldw % 16 == 0;
+    p.ragged = exact && (K / ksplit) % K_PER_CTA != 0;
+    p.cluster = (g_small_m_cluster && ksplit >= 2 && ksplit <= 8) ? 1 : 0;
     // sixteen loads a round: slices that are multiples of 2,048 and at most one wave of two CTAs an SM
     const bool one_round = exact && g_small_m_one_round && (K / ksplit) % (2 * K_PER_CTA) == 0 &&
                            (int64_t)tiles * ksplit <= (g_small_m_one_round > 1 ? g_small_m_one_round : (int64_t)(g_small_m_wave / 4) * 2);
+    const dim3 cl(1, p.cluster ? ksplit : 1, 1);
 #define XS_GO(NT, TO)                                                                                       \
-    ((one_round && NT == 1) ? xs_launch(gemm_small_m_kernel<1, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, p) \
-     : (exact && NT == 2 && (K / ksplit) % (2 * K_PER_CTA) == 0) ? xs_launch(gemm_small_m_kernel<2, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, p) \
-     : exact ? xs_launch(gemm_small_m_kernel<NT, TO, true>, grid, dim3(WARPS * 32), 0, stream, p)  \
-             : xs_launch(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, p))
+    ((one_round && NT == 1) ? xs_launch_cluster(gemm_small_m_kernel<1, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
+     : (exact && NT == 2 && (K / ksplit) % (2 * K_PER_CTA) == 0) ? xs_launch_cluster(gemm_small_m_kernel<2, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
+     : exact ? xs_launch_cluster(gemm_small_m_kernel<NT, TO, true>, grid, dim3(WARPS * 32), 0, stream, cl, p)  \
+             : xs_launch_cluster(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, cl, p))
     if (out_dtype == XS_F32 || residual != nullptr) {
         if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
     } else if (out_dtype == XS_BF16) {
