@@ -253,6 +253,10 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int tile = blockIdx.x, slice = blockIdx.y;
+    // K slices as one cluster (see the reduction below): a CTA may write to another's shared memory only when that one
+    // has started; every CTA says so here, first thing, and looks for the others' word just before it writes
+    const bool clustered = p.ksplit > 1 && p.cluster;
+    if (clustered) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const int n0 = tile * ROWS;
     // clamped: out-of-range rows are not stored
     const int ra = EXACT ? n0 + g : min(n0 + g, p.N - 1), rb = EXACT ? n0 + g + 8 : min(n0 + g + 8, p.N - 1);
@@ -471,13 +475,23 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         red[warp][g + 8][t * 8 + q * 2] = acc[t][2];
         red[warp][g + 8][t * 8 + q * 2 + 1] = acc[t][3];
     }
+    // Several K slices as one cluster (2 to 8 of them): every slice puts its sums straight into slice 0's shared memory
+    // (its own place there), the cluster's barrier says that all have, and slice 0 adds them in slice order. No global
+    // memory, no fence, no counter; nobody polls.
+    __shared__ float parts[8][ROWS][8 * NT + 1];
+    uint32_t remote = 0;
+    if (clustered) {
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");          // (all have started: long true)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(&parts[slice][0][0])));
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
         const int r = i / (8 * NT), m = i % (8 * NT);
         float v = 0.0f;
 #pragma unroll
         for (int wv = 0; wv < WARPS; ++wv) v += red[wv][r][m];
-        sum[r][m] = v;
+        if (clustered) asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((r * (8 * NT + 1) + m) * 4)), "f"(v) : "memory");
+        else sum[r][m] = v;
     }
     if (threadIdx.x >= WARPS * 32 - 16) {      // the last 16 threads (idle above for up to 8 rows): each batch row's 1 / rms
         const int m = threadIdx.x - (WARPS * 32 - 16);
@@ -490,25 +504,8 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         }
         inv[m] = v;
     }
-    __syncthreads();
-    if (stage_tail) {       // (long landed; a barrier follows on both paths below or has just passed)
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        __syncthreads();
-    }
-    if (p.ksplit == 1) {
-        epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
-        return;
-    }
-    if (p.cluster) {
-        // ---- several K slices as one cluster: every slice puts its sums into slice 0's shared memory (its own place
-        // there), the cluster's barrier says that all have, and slice 0 adds them in slice order. No global memory, no
-        // fence, no counter; nobody polls.
-        __shared__ float parts[8][ROWS][8 * NT + 1];
-        uint32_t remote;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(&parts[slice][0][0])));
-        for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32)
-            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(((i / (8 * NT)) * (8 * NT + 1) + i % (8 * NT)) * 4)),
-                         "f"(sum[i / (8 * NT)][i % (8 * NT)]) : "memory");
+    if (stage_tail) asm volatile("cp.async.wait_all;" ::: "memory");      // (this thread's; the barrier below shows them to all)
+    if (clustered) {
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (slice != 0) return;
@@ -521,7 +518,12 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
         epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
         return;
     }
-    // ---- several K slices: leave this slice's partial, and let the last CTA to arrive add them all
+    __syncthreads();
+    if (p.ksplit == 1) {
+        epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
+        return;
+    }
+    // ---- more slices than a cluster holds: leave this slice's partial, and let the last CTA to arrive add them all
     float* mine = p.partials + ((int64_t)tile * p.ksplit + slice) * (ROWS * 8 * NT);
     for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) mine[i] = sum[i / (8 * NT)][i % (8 * NT)];
     __threadfence();
