@@ -103,44 +103,62 @@ __device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* p) {
     return __bfloat162float(__ushort_as_bfloat16(raw));
 }
 
-// The convolution that follows in_proj, by whichever of the three CTAs that own a group of 16 channels (its B, its
-// C and its X rows: tiles g, g + H / 16, g + 2 H / 16) stores its part last; nobody waits for anybody. Every sequence
-// brings one token (batch row m is sequence m): g = bfloat16(B * X); out = C * (bias + sum_j tap_j * state_j + tap_last * g);
-// the state moves up by one row and takes g. The same arithmetic, in the same order, as the kernel of its own
-// (short_conv.cu), so a sequence's values do not depend on which of them ran.
+// The convolution that follows in_proj, inside the product's kernel. The three CTAs that own a group of 16 channels
+// (its B, its C and its X rows: tiles g, g + H / 16, g + 2 H / 16) are one thread-block cluster (the kernel maps
+// blockIdx.x to tiles that way); the C and the X CTA put their values into the B CTA's shared memory, the cluster's
+// barrier says that they have, and the B CTA finishes: every sequence brings one token (batch row m is sequence m),
+// g = bfloat16(B * X); out = C * (bias + sum_j tap_j * state_j + tap_last * g); the state moves up by one row and takes
+// g. The same arithmetic on the same rounded values, in the same order, as the kernel of its own (short_conv.cu), so a
+// sequence's values do not depend on which of them ran. (Every CTA said at its start that it runs: the first cluster
+// barrier's arrival; nobody writes into another's shared memory before it has seen that.)
 template <int NT>
-__device__ __forceinline__ void conv_tail(const SmallMParams& p) {
-    __shared__ bool is_last;
-    __threadfence();
-    __syncthreads();
-    const int groups = p.conv_h / ROWS;
-    const int group = (int)(blockIdx.x % (unsigned)groups);
-    if (threadIdx.x == 0) is_last = atomicAdd(&p.conv_counters[group], 1u) == 2u;
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
+__device__ __forceinline__ void conv_tail(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0) {
+    __shared__ float cx[2][ROWS][8 * NT + 1];
+    const int rank = (int)(blockIdx.x % 3u), group = (int)(blockIdx.x / 3u);
     const int H = p.conv_h, K = p.conv_k;
-    const __nv_bfloat16* bcx = reinterpret_cast<const __nv_bfloat16*>(p.out);
-    for (int i = threadIdx.x; i < ROWS * 8 * NT; i += WARPS * 32) {
-        const int r = i % ROWS, m = i / ROWS;
-        if (m >= p.M) continue;
-        const int c = group * ROWS + r;
-        const __nv_bfloat16* row = bcx + (int64_t)m * p.ldo;
-        const float b = ldcg_bf16(row + c), gate = ldcg_bf16(row + H + c), x = ldcg_bf16(row + 2 * H + c);
-        const __nv_bfloat16 g16 = __float2bfloat16_rn(b * x);
-        const float g = __bfloat162float(g16);
-        __nv_bfloat16* st = p.conv_state + (int64_t)p.conv_slots[m] * (K - 1) * H + c;
-        float acc = p.conv_bias != nullptr ? p.conv_bias[c] : 0.0f;
-        for (int j = 0; j < K - 1; ++j) {
-            const __nv_bfloat16 old = st[(int64_t)j * H];
-            acc = fmaf(p.conv_taps[(int64_t)j * H + c], __bfloat162float(old), acc);
-            if (j > 0) st[(int64_t)(j - 1) * H] = old;        // row j moves to j - 1
-        }
-        acc = fmaf(p.conv_taps[(int64_t)(K - 1) * H + c], g, acc);
-        st[(int64_t)(K - 2) * H] = g16;
-        p.conv_out[(int64_t)m * H + c] = __float2bfloat16_rn(acc * gate);
+    const int i = threadIdx.x;
+    const int r = i % ROWS, m = i / ROWS;
+    const bool mine = i < ROWS * 8 * NT && m < p.M;
+    float v = 0.0f;
+    if (mine) {
+        v = sum[r][m] * inv[m];
+        if (p.bias != nullptr) v += p.bias[n0 + r];
+        v = __bfloat162float(__float2bfloat16_rn(v));          // as the stored [B | C | X] holds it
     }
-    if (threadIdx.x == 0) p.conv_counters[group] = 0;        // ready for the next call
+    // the leader's own loads do not wait for the others
+    const int c = group * ROWS + r;
+    __nv_bfloat16* st = nullptr;
+    float acc = 0.0f;
+    __nv_bfloat16 old[7];
+    if (rank == 0 && mine) {
+        st = p.conv_state + (int64_t)p.conv_slots[m] * (K - 1) * H + c;
+        acc = p.conv_bias != nullptr ? p.conv_bias[c] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 7; ++j)
+            if (j < K - 1) old[j] = st[(int64_t)j * H];
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");              // all three have started
+    if (rank != 0 && mine) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(&cx[rank - 1][r][m])));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank != 0 || !mine) return;
+    const float gate = cx[0][r][m], x = cx[1][r][m];
+    const __nv_bfloat16 g16 = __float2bfloat16_rn(v * x);
+    const float g = __bfloat162float(g16);
+#pragma unroll
+    for (int j = 0; j < 7; ++j) {
+        if (j < K - 1) {
+            acc = fmaf(p.conv_taps[(int64_t)j * H + c], __bfloat162float(old[j]), acc);
+            if (j > 0) st[(int64_t)(j - 1) * H] = old[j];        // row j moves to j - 1
+        }
+    }
+    acc = fmaf(p.conv_taps[(int64_t)(K - 1) * H + c], g, acc);
+    st[(int64_t)(K - 2) * H] = g16;
+    p.conv_out[(int64_t)m * H + c] = __float2bfloat16_rn(acc * gate);
 }
 
 // Each batch row's largest output and its column, the lowest column among equals: every CTA folds its 16 columns into one
@@ -230,7 +248,7 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
             if (r == 0) p.out_ssq[(int64_t)blockIdx.x * 16 + m] = sq;
         }
     }
-    if (p.conv_out != nullptr) conv_tail<NT>(p);
+    if (p.conv_out != nullptr) conv_tail<NT>(p, sum, inv, n0);
     if (p.amax_out != nullptr) argmax_tail<NT>(p, sum, inv, n0);
 }
 
@@ -252,11 +270,13 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     __shared__ bool last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
-    const int tile = blockIdx.x, slice = blockIdx.y;
+    // (with the convolution behind the product, three neighbouring CTAs are the B, C and X tiles of one group of channels)
+    const int tile = p.conv_out != nullptr ? (int)(blockIdx.x % 3u) * (p.conv_h / ROWS) + (int)(blockIdx.x / 3u) : (int)blockIdx.x;
+    const int slice = blockIdx.y;
     // K slices as one cluster (see the reduction below): a CTA may write to another's shared memory only when that one
     // has started; every CTA says so here, first thing, and looks for the others' word just before it writes
     const bool clustered = p.ksplit > 1 && p.cluster;
-    if (clustered) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    if (clustered || p.conv_out != nullptr) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const int n0 = tile * ROWS;
     // clamped: out-of-range rows are not stored
     const int ra = EXACT ? n0 + g : min(n0 + g, p.N - 1), rb = EXACT ? n0 + g + 8 : min(n0 + g + 8, p.N - 1);
@@ -682,7 +702,8 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
     // sixteen loads a round: slices that are multiples of 2,048 and at most one wave of two CTAs an SM
     const bool one_round = exact && g_small_m_one_round && (K / ksplit) % (2 * K_PER_CTA) == 0 &&
                            (int64_t)tiles * ksplit <= (g_small_m_one_round > 1 ? g_small_m_one_round : (int64_t)(g_small_m_wave / 4) * 2);
-    const dim3 cl(1, p.cluster ? ksplit : 1, 1);
+    // (the convolution behind the product: clusters of the three CTAs of a group of channels; its K is one slice)
+    const dim3 cl(conv_out != nullptr ? 3 : 1, p.cluster ? ksplit : 1, 1);
 #define XS_GO(NT, TO)                                                                                       \
     ((one_round && NT == 1) ? xs_launch_cluster(gemm_small_m_kernel<1, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
      : (exact && NT == 2 && (K / ksplit) % (2 * K_PER_CTA) == 0) ? xs_launch_cluster(gemm_small_m_kernel<2, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
