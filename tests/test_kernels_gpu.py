@@ -672,6 +672,72 @@ def test_qk_norm_rope_store(dtype, D, pairs, Hq, Hkv):
         close(q_out[..., pairs:D // 2], tail, dtype)
 
 
+@pytest.mark.parametrize("M,D,pairs,Hq,Hkv,K,gate_rows,norm,rotate,write_kv", [
+    (8, 64, 32, 32, 8, 2048, 32, True, True, True),        # the 1.2B shape: sixteen loads a round, clusters of four
+    (3, 32, 10, 4, 2, 96, 0, True, True, True),            # predicated loads, clusters of two, partial rotation
+    (13, 128, 64, 6, 3, 256, 16, False, True, True),       # 16-row instance, clusters of eight, no norm
+    (5, 64, 32, 8, 2, 1024, 0, True, False, True),         # no rotation
+    (8, 64, 20, 8, 4, 1024, 16, True, True, False)])       # a reader of another layer's cache: queries only
+def test_gemm_small_m_with_the_rotation_behind_it(M, D, pairs, Hq, Hkv, K, gate_rows, norm, rotate, write_kv):
+    """An attention layer's q/k/v product of a decode step with the per-head norm, the rotation and the cache write in
+    its own kernel (the CTAs of a head as one cluster), against a float64 restatement; the columns behind the heads come
+    out as the plain product leaves them, and no cache row of another position is touched."""
+    lib = ops()
+    starts = [3 + 67 * i for i in range(M)]
+    pg = Paged(starts, [1] * M, Hq, Hkv, D, "bfloat16")
+    pg.fill_pool(upto_start_only=True)
+    d = pg.dev()
+    width = (Hq + (2 * Hkv if write_kv else 0)) * D
+    N = width + gate_rows
+    g = torch.Generator(device="cpu").manual_seed(M * D + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K) * 3).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV) if K == 96 else None
+    qw = (torch.rand(D, generator=g) + 0.5).to(DEV) if norm else None
+    kw = (torch.rand(D, generator=g) + 0.5).to(DEV) if norm else None
+    eps, theta = 1e-6, 10000.0
+    inv = torch.zeros(D // 2, dtype=torch.float64)
+    inv[:pairs] = (1.0 / theta ** (2.0 * torch.arange(pairs, dtype=torch.float64) / D)).float().double()
+    ang = torch.arange(1024, dtype=torch.float64)[:, None] * inv[None, :]
+    rope = torch.stack([ang.cos(), ang.sin()], -1).float().to(DEV) if rotate else None
+    q_out = torch.full((M, Hq, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    before = d["pool"].clone()
+    lib.gemm_small_m_rope(x, w, out, bias, q_out, d["pool"] if write_kv else None, d["table"] if write_kv else None,
+                          d["seq_of"], d["pos"], qw, kw, rope, Hq, Hkv, D, 64, eps)
+    plain = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    lib.gemm_small_m(x, w, plain, bias)
+    assert torch.equal(out, plain), "the product's own output changed"
+    y = plain.double().cpu()
+    pos = torch.tensor(pg.pos)
+
+    def norm_rope(v, wt):     # v [M, heads, D]
+        if wt is not None:
+            v = rms_norm(v, wt.double().cpu(), eps)
+        if not rotate:
+            return v
+        c, s_ = ang[pos].cos()[:, None, :], ang[pos].sin()[:, None, :]
+        a, b = v[..., :D // 2], v[..., D // 2:]
+        return torch.cat([a * c - b * s_, b * c + a * s_], -1)
+
+    close(q_out, norm_rope(y[:, :Hq * D].reshape(M, Hq, D), qw), "bfloat16")
+    if not write_kv:
+        assert torch.equal(d["pool"], before)
+        return
+    k_ref = norm_rope(y[:, Hq * D:(Hq + Hkv) * D].reshape(M, Hkv, D), kw)
+    v_ref = y[:, (Hq + Hkv) * D:width].reshape(M, Hkv, D)
+    pool = d["pool"].double().cpu()
+    touched = torch.zeros(pool.shape[0], 64, dtype=torch.bool)
+    for t in range(M):
+        s_, p_ = int(pg.seq_of[t]), int(pg.pos[t])
+        page, r = int(pg.table[s_, p_ // 64]), p_ % 64
+        close(pool[page, 0, :, r], k_ref[t], "bfloat16")
+        assert torch.equal(pool[page, 1, :, r], v_ref[t]), "values are copied as they are"
+        touched[page, r] = True
+    same = (d["pool"] == before).all(-1).all(1).all(1).cpu()
+    assert same[~touched].all(), "a cache row of another position was written"
+
+
 # ------------------------------------------------------------------------------ short convolution
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,K", [(96, 3), (200, 4), (64, 7), (40, 2), (72, 8), (48, 6)])

@@ -92,6 +92,18 @@ struct SmallMParams {
     __nv_bfloat16* conv_out;     // [M, conv_h]
     unsigned int* conv_counters; // [conv_h / 16], zero between calls
     int conv_k, conv_h;
+    // Per-head norm, rotation and cache write behind the product (an attention layer's q/k/v product in a decode step;
+    // rope_q null when unused): out is [M, (Hq + 2 Hkv) D + ...] = [q heads | k heads | v heads | more]
+    __nv_bfloat16* rope_q;          // [M, Hq, D]: normed, rotated queries
+    __nv_bfloat16* rope_pool;       // [pages, 2, Hkv, page, D]: the cache; null: queries only (out is [q heads | more])
+    const int32_t* rope_table;      // [n_seqs, rope_P] page numbers
+    const int32_t* rope_seq;        // [M] sequence of a batch row
+    const int32_t* rope_pos;        // [M] position of a batch row
+    const float* rope_qw;           // [D] norm weights of q heads, or null: no norm
+    const float* rope_kw;           // [D] of k heads
+    const float2* rope_cs;          // [positions, D / 2] (cos, sin), or null: no rotation
+    int rope_P, rope_hq, rope_hkv, rope_d, rope_page;
+    float rope_eps;
     // Argmax of every batch row behind the product (the head; null when unused)
     unsigned long long* amax_keys;   // [16], zero between calls
     unsigned int* amax_counter;      // [1], zero between calls
@@ -161,6 +173,88 @@ __device__ __forceinline__ void conv_tail(const SmallMParams& p, const float (*s
     p.conv_out[(int64_t)m * H + c] = __float2bfloat16_rn(acc * gate);
 }
 
+// An attention layer's q/k/v product in a decode step, finished inside the product's kernel: the D / 16 CTAs that own
+// a head's rows are one thread-block cluster (heads lie one after another in the output, so they are neighbours). Every
+// CTA rounds its 16 x M values as the stored output holds them, sends its sums of squares to all CTAs of the head and
+// its values to the CTA that owns the other half of its rotation pairs (i and i + D / 2), and after the cluster's
+// barrier finishes its own 16 channels: RMSNorm over the head (q and k heads), rotation by the position's (cos, sin),
+// then the queries go to rope_q and keys and raw values into the cache's page, as qk_norm_rope_store (the kernel of
+// its own, attention_generic.cu) does. Tiles behind the heads (the head gate's rows) take no part.
+template <int NT>
+__device__ __forceinline__ void rope_tail(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0) {
+    __shared__ float part_ss[8][8 * NT];                  // [quarter of the head][batch row]
+    __shared__ float partner[ROWS][8 * NT + 1];
+    const int D = p.rope_d, per_head = D / ROWS;
+    const int heads = p.rope_hq + (p.rope_pool != nullptr ? 2 * p.rope_hkv : 0);
+    const int tile = n0 / ROWS;
+    if (tile >= heads * per_head) return;                 // (whole clusters: heads * per_head is a multiple of per_head)
+    const int hh = tile / per_head, qd = tile % per_head, half_q = per_head / 2;
+    const int which = hh < p.rope_hq ? -1 : (hh - p.rope_hq) / p.rope_hkv;      // -1 q, 0 k, 1 v
+    const float* w = which < 0 ? p.rope_qw : which == 0 ? p.rope_kw : nullptr;
+    const bool rotate = which <= 0 && p.rope_cs != nullptr;
+    const int i = threadIdx.x, r = i % ROWS, m = i / ROWS;
+    const bool mine = i < ROWS * 8 * NT && m < p.M;
+    float v = 0.0f;
+    if (mine) {
+        v = sum[r][m] * inv[m];
+        if (p.bias != nullptr) v += p.bias[n0 + r];
+        v = __bfloat162float(__float2bfloat16_rn(v));
+    }
+    // what does not wait for the others: the position's (cos, sin), the norm weights, where the result goes
+    const int dim = qd * ROWS + r, pair = dim % (D / 2);
+    float2 cs = make_float2(1.0f, 0.0f);
+    float w_own = 1.0f, w_other = 1.0f;
+    __nv_bfloat16* dst = nullptr;
+    if (mine) {
+        const int pos = p.rope_pos[m];
+        if (rotate) cs = p.rope_cs[(int64_t)pos * (D / 2) + pair];
+        if (w != nullptr) {
+            w_own = w[dim];
+            w_other = w[dim < D / 2 ? dim + D / 2 : dim - D / 2];
+        }
+        if (which < 0) {
+            dst = p.rope_q + ((int64_t)m * p.rope_hq + hh) * D + dim;
+        } else {
+            const int kvh = (hh - p.rope_hq) % p.rope_hkv;
+            const int page = p.rope_table[(int64_t)p.rope_seq[m] * p.rope_P + pos / p.rope_page];
+            dst = p.rope_pool + ((((int64_t)page * 2 + which) * p.rope_hkv + kvh) * p.rope_page + pos % p.rope_page) * D + dim;
+        }
+    }
+    // sums of squares of this CTA's 16 channels per batch row: the 16 lanes of a row's channels sit side by side
+    float sq = v * v;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");              // every CTA of the head has started
+    if (mine) {
+        if (r == 0) {
+            for (int c = 0; c < per_head; ++c) {
+                uint32_t at;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(at) : "r"((uint32_t)__cvta_generic_to_shared(&part_ss[qd][m])), "r"(c));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(at), "f"(sq) : "memory");
+            }
+        }
+        if (rotate) {
+            uint32_t at;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(at) : "r"((uint32_t)__cvta_generic_to_shared(&partner[r][m])),
+                         "r"(qd < half_q ? qd + half_q : qd - half_q));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(at), "f"(v) : "memory");
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (!mine) return;
+    float x = v, y = rotate ? partner[r][m] : 0.0f;
+    if (w != nullptr) {
+        float ss = 0.0f;
+        for (int c = 0; c < per_head; ++c) ss += part_ss[c][m];
+        const float scale = 1.0f / sqrtf(ss / (float)D + p.rope_eps);
+        x = x * scale * w_own;
+        y = y * scale * w_other;
+    }
+    if (rotate) x = dim < D / 2 ? x * cs.x - y * cs.y : x * cs.x + y * cs.y;
+    *dst = __float2bfloat16_rn(x);
+}
+
 // Each batch row's largest output and its column, the lowest column among equals: every CTA folds its 16 columns into one
 // 64-bit key per batch row (the value's bits made monotone, then the column counted down), the keys meet by atomicMax,
 // and the CTA that stores last unpacks them and clears them for the next call.
@@ -202,7 +296,9 @@ __device__ __forceinline__ void argmax_tail(const SmallMParams& p, const float (
 
 // `staged` (8 batch rows only): this tile's old stream values [m][16] and the next norm's weights [16], fetched into
 // shared memory while the weights streamed, so that the CTA's tail does not begin with a trip to L2.
-template <int NT, typename TO>
+// TAIL: what runs behind the product in its kernel (0 nothing, 1 the short convolution, 2 the heads' norm, rotation and
+// cache write, 3 the argmax): instances of their own, so that the products without a tail do not carry its registers.
+template <int NT, typename TO, int TAIL>
 __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*sum)[8 * NT + 1], const float* inv, int n0,
                                          const float* staged = nullptr) {
     TO* out = reinterpret_cast<TO*>(p.out);
@@ -248,8 +344,9 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
             if (r == 0) p.out_ssq[(int64_t)blockIdx.x * 16 + m] = sq;
         }
     }
-    if (p.conv_out != nullptr) conv_tail<NT>(p, sum, inv, n0);
-    if (p.amax_out != nullptr) argmax_tail<NT>(p, sum, inv, n0);
+    if (TAIL == 1) conv_tail<NT>(p, sum, inv, n0);
+    if (TAIL == 2) rope_tail<NT>(p, sum, inv, n0);
+    if (TAIL == 3) argmax_tail<NT>(p, sum, inv, n0);
 }
 
 // EXACT: N is a multiple of 16 and every K slice a multiple of 64 (of 1,024 = 8 warps x 4 blocks x 32 unless `ragged`), so no row is
@@ -259,7 +356,7 @@ __device__ __forceinline__ void epilogue(const SmallMParams& p, const float (*su
 // for weights, two CTAs an SM instead of four. For grids of at most one such wave (the narrow outputs, which are
 // bound by latency, not bandwidth): measured on the whole decode step, 1.2B shape, batch 8: 0.811 -> 0.773 ms with
 // it on the attention and convolution output projections and the q/k/v product; on grids of more CTAs it loses.
-template <int NT, typename TO, bool EXACT, int UNROLL = UNROLL_DEFAULT>
+template <int NT, typename TO, bool EXACT, int UNROLL = UNROLL_DEFAULT, int TAIL = 0>
 __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) ? 3 : 4) : 2) gemm_small_m_kernel(const SmallMParams p) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float sum[ROWS][8 * NT + 1];
@@ -271,12 +368,16 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     // (with the convolution behind the product, three neighbouring CTAs are the B, C and X tiles of one group of channels)
-    const int tile = p.conv_out != nullptr ? (int)(blockIdx.x % 3u) * (p.conv_h / ROWS) + (int)(blockIdx.x / 3u) : (int)blockIdx.x;
+    const int tile = TAIL == 1 ? (int)(blockIdx.x % 3u) * (p.conv_h / ROWS) + (int)(blockIdx.x / 3u) : (int)blockIdx.x;
     const int slice = blockIdx.y;
     // K slices as one cluster (see the reduction below): a CTA may write to another's shared memory only when that one
     // has started; every CTA says so here, first thing, and looks for the others' word just before it writes
     const bool clustered = p.ksplit > 1 && p.cluster;
-    if (clustered || p.conv_out != nullptr) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    // (with the rotation behind the product the grid is rounded up to whole clusters: CTAs past the last tile leave; the
+    // tiles of a head are a cluster that meets, those behind the heads do not)
+    if (TAIL == 2 && tile * ROWS >= p.N) return;
+    const bool rope_head = TAIL == 2 && tile < (p.rope_hq + (p.rope_pool != nullptr ? 2 * p.rope_hkv : 0)) * (p.rope_d / ROWS);
+    if (clustered || TAIL == 1 || rope_head) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const int n0 = tile * ROWS;
     // clamped: out-of-range rows are not stored
     const int ra = EXACT ? n0 + g : min(n0 + g, p.N - 1), rb = EXACT ? n0 + g + 8 : min(n0 + g + 8, p.N - 1);
@@ -535,12 +636,12 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
             sum[i / (8 * NT)][i % (8 * NT)] = v;
         }
         __syncthreads();
-        epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
+        epilogue<NT, TO, TAIL>(p, sum, inv, n0, stage_tail ? staged : nullptr);
         return;
     }
     __syncthreads();
     if (p.ksplit == 1) {
-        epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
+        epilogue<NT, TO, TAIL>(p, sum, inv, n0, stage_tail ? staged : nullptr);
         return;
     }
     // ---- more slices than a cluster holds: leave this slice's partial, and let the last CTA to arrive add them all
@@ -560,7 +661,7 @@ __global__ void __launch_bounds__(WARPS * 32, UNROLL == 4 ? ((NT == 2 && EXACT) 
     }
     if (threadIdx.x == 0) p.counters[tile] = 0;    // ready for the next call
     __syncthreads();
-    epilogue<NT, TO>(p, sum, inv, n0, stage_tail ? staged : nullptr);
+    epilogue<NT, TO, TAIL>(p, sum, inv, n0, stage_tail ? staged : nullptr);
 }
 
 }  // namespace
@@ -629,14 +730,40 @@ XS_API int64_t xs_gemm_small_m_scratch_bytes(int M, int N, int ksplit) {
 //     conv_slots [M]) goes to conv_out [M, H] and the state moves on. conv_counters: H / 16 zeroed words, left zeroed.
 //   amax_*: amax_out [M] takes each batch row's column of the largest output (the lowest among equals); amax_keys:
 //     16 zeroed 64-bit words and amax_counter one zeroed word, left zeroed.
-XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, void* out, float* residual,
-                              int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
-                              int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
-                              int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
-                              float* out_ssq, const float* conv_taps, const float* conv_bias, void* conv_state,
-                              const int32_t* conv_slots, void* conv_out, void* conv_counters, int conv_k, int conv_h,
-                              void* amax_keys, void* amax_counter, int32_t* amax_out, cudaStream_t stream) {
+//   rope (xs_gemm_small_m_rope): the product is an attention layer's q/k/v product for one token a sequence (out bfloat16
+//     [M, (Hq + 2 Hkv) D + more], or [M, Hq D + more] without a cache to write; D 32, 64 or 128; one K slice): per-head
+//     RMSNorm (q_w, k_w: [D] or null), rotation (cs: [positions, D / 2, 2] or null), queries to q_out [M, Hq, D], keys
+//     and raw values into the cache's pages, as xs_qk_norm_rope_store does.
+struct XsRopeTail {
+    void* q_out;
+    void* pool;
+    const int32_t* page_table;
+    const int32_t* seq_of_token;
+    const int32_t* positions;
+    const float* q_w;
+    const float* k_w;
+    const float* cs;
+    int P, Hq, Hkv, D, page_size;
+    float eps;
+};
+
+static int small_m_launch(const void* x, const void* w, const float* bias, void* out, float* residual,
+                          int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
+                          int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
+                          int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
+                          float* out_ssq, const float* conv_taps, const float* conv_bias, void* conv_state,
+                          const int32_t* conv_slots, void* conv_out, void* conv_counters, int conv_k, int conv_h,
+                          void* amax_keys, void* amax_counter, int32_t* amax_out, const XsRopeTail* rope,
+                          cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    XS_REQUIRE(rope == nullptr ||
+                   (rope->q_out != nullptr && rope->positions != nullptr && rope->seq_of_token != nullptr &&
+                    (rope->D == 32 || rope->D == 64 || rope->D == 128) && rope->Hq > 0 && rope->Hkv > 0 &&
+                    (rope->pool == nullptr || (rope->page_table != nullptr && rope->P > 0 && rope->page_size > 0)) &&
+                    N >= (rope->Hq + (rope->pool != nullptr ? 2 * rope->Hkv : 0)) * rope->D && N % ROWS == 0 && ksplit == 1 &&
+                    !swiglu && residual == nullptr && conv_out == nullptr && out != nullptr && out_dtype == XS_BF16),
+               "gemm (few rows): the rotation behind the product needs a bfloat16 output that begins with the heads "
+               "(size 32, 64 or 128) and one K slice");
     XS_REQUIRE(conv_out == nullptr ||
                    (conv_taps != nullptr && conv_state != nullptr && conv_slots != nullptr && conv_counters != nullptr &&
                     conv_k >= 2 && conv_h > 0 && conv_h % ROWS == 0 && N == 3 * conv_h && ksplit == 1 && !swiglu &&
@@ -680,6 +807,13 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
     p.conv_taps = conv_taps; p.conv_bias = conv_bias; p.conv_state = (__nv_bfloat16*)conv_state; p.conv_slots = conv_slots;
     p.conv_out = (__nv_bfloat16*)conv_out; p.conv_counters = (unsigned int*)conv_counters; p.conv_k = conv_k; p.conv_h = conv_h;
     p.amax_keys = (unsigned long long*)amax_keys; p.amax_counter = (unsigned int*)amax_counter; p.amax_out = amax_out;
+    p.rope_q = nullptr;
+    if (rope != nullptr) {
+        p.rope_q = (__nv_bfloat16*)rope->q_out; p.rope_pool = (__nv_bfloat16*)rope->pool; p.rope_table = rope->page_table;
+        p.rope_seq = rope->seq_of_token; p.rope_pos = rope->positions; p.rope_qw = rope->q_w; p.rope_kw = rope->k_w;
+        p.rope_cs = (const float2*)rope->cs; p.rope_P = rope->P; p.rope_hq = rope->Hq; p.rope_hkv = rope->Hkv;
+        p.rope_d = rope->D; p.rope_page = rope->page_size; p.rope_eps = rope->eps;
+    }
     if (ksplit > 1) {
         const int64_t need = xs_gemm_small_m_scratch_bytes(M, N, ksplit);
         XS_REQUIRE(scratch != nullptr && scratch_bytes >= need && (uintptr_t)scratch % 16 == 0 && scratch_bytes % 16 == 0,
@@ -689,7 +823,9 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
         p.partials = (float*)scratch;
         p.counters = (unsigned int*)((char*)scratch + scratch_bytes - kCounterBytes);
     }
-    const dim3 grid(tiles, ksplit);
+    // (the rotation behind the product: clusters of the D / 16 CTAs of a head; the grid is rounded up to whole clusters)
+    const int per_head = rope != nullptr ? rope->D / ROWS : 1;
+    const dim3 grid(ceil_div_i(tiles, per_head) * per_head, ksplit);
     // (9 to 16 rows: the unpredicated loop needs 78 registers, three CTAs an SM; with sixteen loads a round, 128 and two.
     // Measured on the whole decode step, 1.2B shape, batch 16: 1.05 ms predicated, 1.03 unpredicated, 0.99 with sixteen
     // loads, against 0.93 with the library product, which is why the default keeps this kernel to 8 rows.)
@@ -703,22 +839,54 @@ XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, v
     const bool one_round = exact && g_small_m_one_round && (K / ksplit) % (2 * K_PER_CTA) == 0 &&
                            (int64_t)tiles * ksplit <= (g_small_m_one_round > 1 ? g_small_m_one_round : (int64_t)(g_small_m_wave / 4) * 2);
     // (the convolution behind the product: clusters of the three CTAs of a group of channels; its K is one slice)
-    const dim3 cl(conv_out != nullptr ? 3 : 1, p.cluster ? ksplit : 1, 1);
-#define XS_GO(NT, TO)                                                                                       \
-    ((one_round && NT == 1) ? xs_launch_cluster(gemm_small_m_kernel<1, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
-     : (exact && NT == 2 && (K / ksplit) % (2 * K_PER_CTA) == 0) ? xs_launch_cluster(gemm_small_m_kernel<2, TO, true, 8>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
-     : exact ? xs_launch_cluster(gemm_small_m_kernel<NT, TO, true>, grid, dim3(WARPS * 32), 0, stream, cl, p)  \
-             : xs_launch_cluster(gemm_small_m_kernel<NT, TO, false>, grid, dim3(WARPS * 32), 0, stream, cl, p))
+    const dim3 cl(conv_out != nullptr ? 3 : per_head, p.cluster ? ksplit : 1, 1);
+#define XS_GO(NT, TO, TAIL)                                                                                 \
+    ((one_round && NT == 1) ? xs_launch_cluster(gemm_small_m_kernel<1, TO, true, 8, TAIL>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
+     : (exact && NT == 2 && (K / ksplit) % (2 * K_PER_CTA) == 0) ? xs_launch_cluster(gemm_small_m_kernel<2, TO, true, 8, TAIL>, grid, dim3(WARPS * 32), 0, stream, cl, p) \
+     : exact ? xs_launch_cluster(gemm_small_m_kernel<NT, TO, true, UNROLL_DEFAULT, TAIL>, grid, dim3(WARPS * 32), 0, stream, cl, p)  \
+             : xs_launch_cluster(gemm_small_m_kernel<NT, TO, false, UNROLL_DEFAULT, TAIL>, grid, dim3(WARPS * 32), 0, stream, cl, p))
+#define XS_GO_NT(TO, TAIL) do { if (M <= 8) XS_GO(1, TO, TAIL); else XS_GO(2, TO, TAIL); } while (0)
     if (out_dtype == XS_F32 || residual != nullptr) {
-        if (M <= 8) XS_GO(1, float); else XS_GO(2, float);
+        if (amax_out != nullptr) XS_GO_NT(float, 3); else XS_GO_NT(float, 0);
     } else if (out_dtype == XS_BF16) {
-        if (M <= 8) XS_GO(1, __nv_bfloat16); else XS_GO(2, __nv_bfloat16);
+        if (conv_out != nullptr) XS_GO_NT(__nv_bfloat16, 1);
+        else if (rope != nullptr) XS_GO_NT(__nv_bfloat16, 2);
+        else if (amax_out != nullptr) XS_GO_NT(__nv_bfloat16, 3);
+        else XS_GO_NT(__nv_bfloat16, 0);
     } else {
         XS_REQUIRE(false, "gemm (few rows): output type code %d", out_dtype);
     }
+#undef XS_GO_NT
 #undef XS_GO
     XS_LAUNCH_CHECK("gemm_small_m");
     return 0;
+}
+
+XS_API int xs_gemm_small_m_ex(const void* x, const void* w, const float* bias, void* out, float* residual,
+                              int out_dtype, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int swiglu,
+                              int ksplit, void* scratch, int64_t scratch_bytes, const float* in_ssq, int in_tiles,
+                              int in_width, float in_eps, const float* next_w, void* next_x, int64_t ld_next,
+                              float* out_ssq, const float* conv_taps, const float* conv_bias, void* conv_state,
+                              const int32_t* conv_slots, void* conv_out, void* conv_counters, int conv_k, int conv_h,
+                              void* amax_keys, void* amax_counter, int32_t* amax_out, cudaStream_t stream) {
+    return small_m_launch(x, w, bias, out, residual, out_dtype, M, N, K, ldx, ldw, ldo, swiglu, ksplit, scratch, scratch_bytes,
+                          in_ssq, in_tiles, in_width, in_eps, next_w, next_x, ld_next, out_ssq, conv_taps, conv_bias, conv_state,
+                          conv_slots, conv_out, conv_counters, conv_k, conv_h, amax_keys, amax_counter, amax_out, nullptr, stream);
+}
+
+// The q/k/v product of a decode step with the per-head norm, the rotation and the cache write behind it (see XsRopeTail).
+XS_API int xs_gemm_small_m_rope(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, int64_t ldx,
+                                int64_t ldw, int64_t ldo, const float* in_ssq, int in_tiles, int in_width, float in_eps,
+                                void* q_out, void* pool, const int32_t* page_table, int P, const int32_t* seq_of_token,
+                                const int32_t* positions, const float* q_w, const float* k_w, const float* cs, int Hq,
+                                int Hkv, int D, int page_size, float eps, cudaStream_t stream) {
+    XsRopeTail rope;
+    rope.q_out = q_out; rope.pool = pool; rope.page_table = page_table; rope.seq_of_token = seq_of_token;
+    rope.positions = positions; rope.q_w = q_w; rope.k_w = k_w; rope.cs = cs; rope.P = P; rope.Hq = Hq; rope.Hkv = Hkv;
+    rope.D = D; rope.page_size = page_size; rope.eps = eps;
+    return small_m_launch(x, w, bias, out, nullptr, XS_BF16, M, N, K, ldx, ldw, ldo, 0, 1, nullptr, 0, in_ssq, in_tiles,
+                          in_width, in_eps, nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                          0, 0, nullptr, nullptr, nullptr, &rope, stream);
 }
 
 XS_API int xs_gemm_small_m_normed(const void* x, const void* w, const float* bias, void* out, float* residual,

@@ -106,16 +106,20 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
         # Work done behind its producer inside the producer's kernel; XS_TAILS names what runs so (a comma list of conv,
-        # attn, argmax), the rest stay kernels of their own; XS_NO_TAILS=1: none. conv: the short convolution behind
+        # attn, argmax, rope), the rest stay kernels of their own; XS_NO_TAILS=1: none. Each tail of the few-row product
+        # is a kernel instance of its own: with the tails' code in every instance, the products without a tail carried
+        # its registers and the whole step took 0.642 instead of 0.628 ms. conv: the short convolution behind
         # in_proj, by the three CTAs of a group of channels as one thread-block cluster that meets in shared memory
         # (measured on B200, 1.2B shape, decode at batch 8: 0.650 -> 0.642 ms a step; when the three still met through
         # global memory and a counter it cost 17 us instead). attn: the merge of decode attention's key splits by the
         # CTA of a (sequence, kv head) that stores last (the same time with six launches fewer). argmax: behind the
-        # head product through atomics on one word (+8 us: off). The zeroed words below are what the counting tails
+        # head product through atomics on one word (+8 us: off). rope: an attention layer's per-head norms, rotation and cache
+        # write behind its q/k/v product, the CTAs of a head as one cluster (+10 us: off). The zeroed words below are what the counting tails
         # count in and leave zeroed.
         self.fuse_tails = os.environ.get("XS_NO_TAILS", "0") != "1"
         tails = os.environ.get("XS_TAILS", "conv,attn").split(",")
         self.tail_conv, self.tail_attn, self.tail_argmax = ["conv" in tails, "attn" in tails, "argmax" in tails]
+        self.tail_rope = "rope" in tails
         self.conv_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=self.device)
         self.amax_keys = torch.zeros(16, dtype=torch.int64, device=self.device)
@@ -176,6 +180,19 @@ class Runtime:
                          scratch=self.gemm_scratch if ksplit > 1 else None, next_w=next_w, next_x=next_x, out_ssq=out_ssq,
                          conv=conv, argmax=None if argmax_into is None else (argmax_into, self.amax_keys, self.amax_counter),
                          **norm)
+
+    def rope_behind_product(self, x, w, head_dim: int) -> bool:
+        """Whether an attention layer's per-head norm, rotation and cache write (one token a sequence) can run behind its
+        q/k/v product in the product's kernel."""
+        return self.fuse_tails and self.tail_rope and self.few_rows(x, w) and head_dim in (32, 64, 128) and w.shape[0] % 16 == 0
+
+    def few_rows_rope(self, x, w, out, bias, **rope) -> None:
+        """ops.gemm_small_m_rope; `x` may be a Prenormed input."""
+        norm = {}
+        if hasattr(x, "ssq"):
+            norm = dict(in_ssq=x.ssq, in_width=x.width, in_eps=x.eps)
+            x = x.x
+        ops.gemm_small_m_rope(x, w, out, bias, **rope, **norm)
 
     def conv_behind_product(self, x, w, channels: int) -> bool:
         """Whether a short convolution of one token a sequence can run in the tail of its in_proj product."""

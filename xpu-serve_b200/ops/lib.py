@@ -46,6 +46,7 @@ def _signatures(lib) -> None:
         "xs_gemm_small_m_normed": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P, P],
         "xs_gemm_small_m_ex": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P,
                                P, P, P, P, P, P, I, I, P, P, P, P],
+        "xs_gemm_small_m_rope": [P, P, P, P, I, I, I, L, L, L, P, I, I, F, P, P, P, I, P, P, P, P, P, I, I, I, I, F, P],
         "xs_attention_mma_merged": [P, P, P, I, P, P, P, L, P, P, L, P, L, P, I, I, I, I, I, I, I, F, I, I, P],
         "xs_gemm_tc": [P, P, P, P, I, I, I, I, I, L, L, L, I, P, L, P, P],
         "xs_argmax": [P, L, I, I, P, P, P],
@@ -529,6 +530,60 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         x.stride(0), w.stride(0), target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
         0 if scratch is None else scratch.numel() * scratch.element_size(), _ptr(in_ssq), in_tiles, int(in_width),
         float(in_eps), _ptr(next_w), _ptr(next_x), ld_next, _ptr(out_ssq), *cv, *am, _stream()))
+
+
+def gemm_small_m_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor],
+                      q_out: torch.Tensor, pool: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                      seq_of_token: torch.Tensor, positions: torch.Tensor, q_w: Optional[torch.Tensor],
+                      k_w: Optional[torch.Tensor], rope: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int,
+                      page_size: int, eps: float, in_ssq: Optional[torch.Tensor] = None, in_width: int = 0,
+                      in_eps: float = 0.0) -> None:
+    """An attention layer's q/k/v product for one token a sequence (M <= 16, bfloat16) with what qk_norm_rope_store does
+    behind it in the same kernel: out [M, N] = x . w^T (+ bias) as gemm_small_m leaves it (its columns behind the heads,
+    the head gate's, are what the caller still reads), and from its columns (heads x head_dim of q, then, with `pool`,
+    kv_heads x head_dim of k and of v): per-head RMSNorm (q_w, k_w), rotation by `rope` [positions, head_dim / 2, 2],
+    queries to q_out [M, heads, head_dim], keys and raw values into the cache's pages. Head sizes 32, 64, 128."""
+    for t, name in ((x, "x"), (w, "w"), (out, "out"), (q_out, "q_out")):
+        _need(t, name, torch.bfloat16)
+    M, K = x.shape
+    N = w.shape[0]
+    width = (heads + (2 * kv_heads if pool is not None else 0)) * head_dim
+    if (x.stride(1) != 1 or w.stride(1) != 1 or w.shape[1] != K or tuple(out.shape) != (M, N) or out.stride(1) != 1
+            or N < width or tuple(q_out.shape) != (M, heads, head_dim) or not q_out.is_contiguous()
+            or head_dim not in (32, 64, 128) or M > 16):
+        raise KernelError(f"gemm (few rows) with rotation: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
+                          f"q_out {tuple(q_out.shape)}, {heads} + 2 x {kv_heads} heads of {head_dim}")
+    _need(seq_of_token, "seq_of_token", torch.int32); _need(positions, "positions", torch.int32)
+    if seq_of_token.numel() < M or positions.numel() < M:
+        raise KernelError("gemm (few rows) with rotation: a sequence and a position per row")
+    P_ = 0
+    if pool is not None:
+        _need(pool, "cache", torch.bfloat16); _need(page_table, "page table", torch.int32)
+        if tuple(pool.shape[1:]) != (2, kv_heads, page_size, head_dim):
+            raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 2, {kv_heads}, {page_size}, {head_dim}]")
+        P_ = page_table.shape[1]
+    for v, name in ((q_w, "q_norm"), (k_w, "k_norm")):
+        if v is not None:
+            _need(v, name, torch.float32)
+            if v.numel() != head_dim:
+                raise KernelError(f"{name} has {v.numel()} elements for heads of {head_dim}")
+    if rope is not None:
+        _need(rope, "rope table", torch.float32)
+        if tuple(rope.shape[1:]) != (head_dim // 2, 2):
+            raise KernelError(f"rope table is {tuple(rope.shape)}, expected [*, {head_dim // 2}, 2]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    in_tiles = 0
+    if in_ssq is not None:
+        _need(in_ssq, "in_ssq", torch.float32)
+        if in_ssq.dim() != 2 or in_ssq.shape[1] != 16 or not in_ssq.is_contiguous() or in_width <= 0:
+            raise KernelError(f"gemm (few rows): sums of squares {tuple(in_ssq.shape)} over a width of {in_width}")
+        in_tiles = in_ssq.shape[0]
+    _check(load().xs_gemm_small_m_rope(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+        _ptr(in_ssq), in_tiles, int(in_width), float(in_eps), q_out.data_ptr(), _ptr(pool), _ptr(page_table), P_,
+        seq_of_token.data_ptr(), positions.data_ptr(), _ptr(q_w), _ptr(k_w), _ptr(rope), heads, kv_heads, head_dim,
+        page_size, float(eps), _stream()))
 
 
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2

@@ -120,21 +120,28 @@ class AttentionMixer(Mixer):
         if cache is None or cache.storage is None:
             raise RuntimeError("attention needs a key/value cache")
         if cache.owner:
-            proj = rt.linear(x, self.w_qkvg, "attn_qkv", self.b_qkvg)
-            gate_at = self.q_dim + 2 * self.kv_dim
+            w_in, b_in, gate_at = self.w_qkvg, self.b_qkvg, self.q_dim + 2 * self.kv_dim
         else:
             if self.w_qg is None:
                 self.w_qg = rt.matrix(torch.cat([r.to(torch.float32) for r in self._q_rows], 0))
                 if self._q_biases is not None:
                     self.b_qg = rt.vector(torch.cat([b.to(torch.float32) for b in self._q_biases]))
-            proj = rt.linear(x, self.w_qg, "attn_qkv", self.b_qg)
-            gate_at = self.q_dim
+            w_in, b_in, gate_at = self.w_qg, self.b_qg, self.q_dim
         table = step.page_tables[cache.group]
         rope = self.position.table(step.max_positions) if self.position is not None else None
         q = rt.ws.get("attn_q", (T, s.heads, s.head_dim), rt.act_dtype)
-        ops.qk_norm_rope_store(proj, q, cache.storage, table, step.seq_of_token, step.positions, self.q_norm,
-                               self.k_norm, rope, s.heads, s.kv_heads, s.head_dim, step.page_size, s.qk_norm_eps,
-                               write_kv=cache.owner)
+        if step.decode and rt.rope_behind_product(x, w_in, s.head_dim):
+            # one token a sequence: the per-head norms, the rotation and the cache write run behind the product, in its kernel
+            proj = rt.ws.get("attn_qkv", (T, w_in.shape[0]), rt.act_dtype)
+            rt.few_rows_rope(x, w_in, proj, b_in, q_out=q, pool=cache.storage if cache.owner else None,
+                             page_table=table if cache.owner else None, seq_of_token=step.seq_of_token,
+                             positions=step.positions, q_w=self.q_norm, k_w=self.k_norm, rope=rope, heads=s.heads,
+                             kv_heads=s.kv_heads, head_dim=s.head_dim, page_size=step.page_size, eps=s.qk_norm_eps)
+        else:
+            proj = rt.linear(x, w_in, "attn_qkv", b_in)
+            ops.qk_norm_rope_store(proj, q, cache.storage, table, step.seq_of_token, step.positions, self.q_norm,
+                                   self.k_norm, rope, s.heads, s.kv_heads, s.head_dim, step.page_size, s.qk_norm_eps,
+                                   write_kv=cache.owner)
         o = rt.ws.get("attn_o", (T, s.heads, s.head_dim), rt.act_dtype)
         gate = proj[:, gate_at:] if s.head_gate else None
         self.attend(q, cache, table, step, gate, o)
