@@ -440,18 +440,23 @@ def test_a_wrong_norm_in_one_layer_is_caught_in_bfloat16(name, fault, folders, r
     assert gap > 1.5 * tolerance(name, "bfloat16"), f"{name}: a wrong norm moved the logits by {gap:.3e} only"
 
 
-@pytest.mark.parametrize("name", ["A", "R", "H"])
+@pytest.mark.parametrize("name", ["A", "R", "H", "B"])
 def test_every_tail_on_the_model_path(name, folders, references, monkeypatch):
-    """XS_TAILS=conv,attn,argmax: the convolution in the tail of its in_proj product, decode attention's key splits
-    merged by the CTA that finishes last, the argmax behind the head product (by default only the second runs:
-    the other two measured slower than kernels of their own). The same batches, the same bounds; the tokens that
-    the decode graph chooses are the logits' largest."""
+    """XS_TAILS=conv,attn,argmax,rope: the convolution behind its in_proj product, decode attention's key splits
+    merged by the CTA that finishes last, the argmax behind the head product, and the heads' norm, rotation and cache
+    write behind the q/k/v product (head sizes 32 and 64 here: R, B and H; by default only the first two run: the
+    others measured slower than kernels of their own). The same batches, the same bounds; the tokens that the decode
+    graph chooses are the logits' largest."""
     from xpu_serve_b200.engine.model import load_model
     from xpu_serve_b200.engine.replay import Replayer
-    monkeypatch.setenv("XS_TAILS", "conv,attn,argmax")
+    from xpu_serve_b200.ops import lib as ops
+    monkeypatch.setenv("XS_TAILS", "conv,attn,argmax,rope")
     model = load_model(folders[(name, "bfloat16")], dtype="bfloat16")
     rt = model.rt
-    assert rt.tail_conv and rt.tail_attn and rt.tail_argmax
+    assert rt.tail_conv and rt.tail_attn and rt.tail_argmax and rt.tail_rope
+    roped = []
+    real = ops.gemm_small_m_rope
+    monkeypatch.setattr(ops, "gemm_small_m_rope", lambda *a, **k: (roped.append(1), real(*a, **k))[1])
     rp = Replayer(model, 1024, None)
     reqs = requests_for(name)
     vocab = tiny.CONFIGS[name]["vocab_size"]
@@ -469,6 +474,7 @@ def test_every_tail_on_the_model_path(name, folders, references, monkeypatch):
     cache.close(slots)
     assert int(rt.conv_counters.abs().sum()) == 0 and int(rt.attn_counters.abs().sum()) == 0
     assert int(rt.amax_keys.abs().sum()) == 0 and int(rt.amax_counter.item()) == 0
+    assert (len(roped) > 0) == (name in ("R", "H", "B")), "the rotation behind the product ran where it should not, or did not"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

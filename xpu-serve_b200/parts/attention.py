@@ -93,7 +93,7 @@ class AttentionMixer(Mixer):
             q_biases = [bq]
         if spec.head_gate:
             g = weights[n["gate"]]
-            pad = (-g.shape[0]) % 8
+            pad = (-g.shape[0]) % 16      # (whole 16-row tiles: what the few-row product's unpredicated instances and its tails ask for)
             if pad:
                 g = torch.cat([g, torch.zeros(pad, g.shape[1], dtype=g.dtype)], 0)
             rows.append(g)
