@@ -603,6 +603,8 @@ def test_attention_tc(case):
             close(out, ref, "bfloat16", factor=3)
             same = run_attention(lib, pg, "mma", scale, window, gt, 1)
             close(out, same.double(), "bfloat16", factor=3)
+            # the order in which the CTAs start changes no bit
+            assert torch.equal(out, run_attention(lib, pg, "tc_head_after_head", scale, window, gt, 1))
 
 
 def run_attention(lib, pg, kernel, scale, window, gate, splits, counters=None, tma=False):
@@ -610,9 +612,10 @@ def run_attention(lib, pg, kernel, scale, window, gate, splits, counters=None, t
     T = d["q"].shape[0]
     out = torch.full((T, pg.Hq, pg.D), float("nan"), device=DEV, dtype=d["q"].dtype)
     gt = None if gate is None else gate.to(DEV)[:, :pg.Hq]
-    if kernel == "tc":
+    if kernel in ("tc", "tc_head_after_head"):
+        # (a length beyond what L2 holds for all heads makes the kernel start its CTAs one kv head after the other)
         lib.attention_tc(d["q"], d["pool"], d["table"], d["cu"], d["kv_lens"], gt, out, len(pg.starts), max(pg.q_lens),
-                         pg.Hkv, 64, scale, window)
+                         pg.Hkv, 64, scale, window, max_kv_len=0 if kernel == "tc" else 1 << 24)
         assert lib.gemm_tc_status(DEV).item() == 0, "a wait inside the kernel gave up"
     elif kernel == "generic":
         lib.attention_generic(d["q"], d["pool"], d["table"], d["seq_of"], d["pos"], gt, out, pg.Hkv, 64, scale, window)

@@ -46,6 +46,7 @@ struct AttnTcParams {
     int* status;
     int Hq, Hkv, G, tokens_per_tile, window;
     float scale_log2;
+    int order;
 };
 
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
@@ -127,8 +128,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
 
     pdl_launch_dependents();
     pdl_wait();
-    // later tiles see more keys: they are started first, so that the short ones fill the tail
-    const int tile = gridDim.x - 1 - blockIdx.x, seq = blockIdx.y, kvh = blockIdx.z;
+    // later tiles see more keys: they are started first, so that the short ones fill the tail; with p.order those of
+    // all kv heads before any earlier tile (the grid is (tiles, sequences, kv heads); CTAs start in the order of their
+    // flat index)
+    int tile, seq, kvh;
+    if (p.order) {
+        const int flat = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        kvh = flat % (int)gridDim.z;
+        seq = (flat / (int)gridDim.z) % (int)gridDim.y;
+        tile = (int)gridDim.x - 1 - flat / (int)(gridDim.z * gridDim.y);
+    } else {
+        tile = gridDim.x - 1 - blockIdx.x, seq = blockIdx.y, kvh = blockIdx.z;
+    }
     const int tok_begin = p.cu_seqlens[seq];
     const int q_len = p.cu_seqlens[seq + 1] - tok_begin;
     const int t0 = tile * p.tokens_per_tile;
@@ -428,10 +439,11 @@ XS_API int xs_attention_tc_supports(int D, int page_size, int G) {
 
 // The same operation as xs_attention_mma with one key split, for prompts. pool: [pool_pages, 2, Hkv, 64, D].
 // status: one device int that the kernel sets non-zero if a wait inside it gave up (the result is then invalid).
+// max_kv_len: the longest sequence's keys, or 0 if the host does not know; it only picks the order in which CTAs start.
 XS_API int xs_attention_tc(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table, int P,
                            const int32_t* cu_seqlens, const int32_t* kv_lens, const void* gate, int64_t ld_gate, void* out,
                            int T, int n_seqs, int max_q_len, int Hq, int Hkv, int D, int page_size, float scale, int window,
-                           int* status, cudaStream_t stream) {
+                           int max_kv_len, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d heads over %d kv heads", Hq, Hkv);
     const int G = Hq / Hkv;
@@ -460,6 +472,10 @@ XS_API int xs_attention_tc(const void* q, const void* pool, int64_t pool_pages, 
     p.tokens_per_tile = TM / G;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    // All kv heads of the latest tiles first (5 to 15 % faster up to 8,192 keys: the long tiles of every head start
+    // before any short one) while the keys and values of all heads together stay well inside L2; one head after the
+    // other beyond that (1.5 % faster at 32,000 keys).
+    p.order = max_kv_len <= 0 || (int64_t)max_kv_len * Hkv * D * 4 <= (int64_t)32 << 20;
     const int max_tiles = ceil_div_i(max_q_len, p.tokens_per_tile);
     const size_t smem = (size_t)TM * D * 2 + (size_t)KV_STAGES * 4 * PAGE * D * 2 + 2 * (size_t)TM * TN * 2 + 1024;
     static bool opted = false;

@@ -41,7 +41,7 @@ def _signatures(lib) -> None:
         "xs_attention_generic": [P, P, P, I, P, P, P, L, P, I, I, I, I, I, F, I, I, P],
         "xs_short_conv": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_attention_mma": [P, P, P, I, P, P, P, L, P, P, L, I, I, I, I, I, I, I, F, I, I, P],
-        "xs_attention_tc": [P, P, L, P, I, P, P, P, L, P, I, I, I, I, I, I, I, F, I, P, P],
+        "xs_attention_tc": [P, P, L, P, I, P, P, P, L, P, I, I, I, I, I, I, I, F, I, I, P, P],
         "xs_gemm_small_m": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P],
         "xs_gemm_small_m_normed": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P, P],
         "xs_gemm_small_m_ex": [P, P, P, P, P, I, I, I, I, L, L, L, I, I, P, L, P, I, I, F, P, P, L, P,
@@ -420,9 +420,10 @@ def attention_tc_supports(head_dim: int, page_size: int, group: int) -> bool:
 
 def attention_tc(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor,
                  kv_lens: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, n_seqs: int, max_q_len: int,
-                 kv_heads: int, page_size: int, scale: float, window: int) -> None:
+                 kv_heads: int, page_size: int, scale: float, window: int, max_kv_len: int = 0) -> None:
     """Attention for prompts on the tcgen05 tensor cores (head size 64): the same operation as attention_mma with
-    one key split. A wait that gives up inside the kernel sets gemm_tc_status(device)."""
+    one key split. A wait that gives up inside the kernel sets gemm_tc_status(device). `max_kv_len` (the longest
+    sequence's keys, 0 if unknown) only picks the order in which the kernel's CTAs start."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "cache", torch.bfloat16)
     _need(page_table, "page table", torch.int32)
     T, heads, D = q.shape
@@ -437,7 +438,7 @@ def attention_tc(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, 
     _check(load().xs_attention_tc(
         q.data_ptr(), pool.data_ptr(), pool.shape[0], page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
         kv_lens.data_ptr(), _ptr(gate), ld_gate, out.data_ptr(), T, n_seqs, max_q_len, heads, kv_heads, D, page_size,
-        float(scale), int(window), gemm_tc_status(q.device).data_ptr(), _stream()))
+        float(scale), int(window), int(max_kv_len), gemm_tc_status(q.device).data_ptr(), _stream()))
 
 
 def gemm_small_m_supports(M: int, K: int, ldx: int, ldw: int) -> bool:

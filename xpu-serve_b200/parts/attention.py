@@ -155,7 +155,7 @@ class AttentionMixer(Mixer):
             # a step captured for any lengths up to its bounds: one key split, grids from the bounds
             if rt.prompt_attention == "tcgen05" and ops.attention_tc_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
                 ops.attention_tc(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, step.n_seqs,
-                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window)
+                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, step.max_kv_len)
             else:
                 ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, None, step.n_seqs,
                                   step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, 1)
@@ -178,7 +178,7 @@ class AttentionMixer(Mixer):
             if ((splits == 1 or step.max_kv_len <= 512) and not step.decode and rt.prompt_attention == "tcgen05"
                     and ops.attention_tc_supports(s.head_dim, step.page_size, s.heads // s.kv_heads)):
                 ops.attention_tc(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, step.n_seqs,
-                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window)
+                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, step.max_kv_len)
                 return
             scratch = None
             if splits > 1:
