@@ -74,15 +74,15 @@ class Runtime:
         self.attn_split_factor = int(os.environ.get("XS_ATTN_SPLIT_FACTOR", "0"))
         self.attn_fixed_cost = float(os.environ.get("XS_ATTN_FIXED_COST", "2"))
         # attention of prompts: "tcgen05" (head size 64 and groups that divide 128; everything else takes the
-        # mma.sync kernel anyway) or "mma". Measured on B200, 32 heads over 8: 2,048 tokens 67 against 97 us,
+        # mma.sync kernel anyway) or "mma". Measured on B200, 32 heads over 8: 2,048 tokens 62 against 97 us,
         # 2,048 tokens after 30,000: 1.01 against 1.87 ms.
         self.prompt_attention = os.environ.get("XS_PROMPT_ATTENTION", "tcgen05")
         if self.prompt_attention not in ("tcgen05", "mma"):
             raise ValueError("XS_PROMPT_ATTENTION must be 'tcgen05' or 'mma'")
-        # Products with at most this many rows use this library's weight-streaming kernel (it takes up to 16). The
-        # reference draws the same line: its own gemv up to 8 rows, the vendor's library above
-        # (src/backend/sycl/sycl_kernels.h:280). Measured on B200, 1.2B shape, whole decode step: 9 rows 1.05 ms on
-        # the streaming kernel against 0.95 ms on the library product, 16 rows 1.11 against 1.03 ms.
+        # Products with at most `small_m` rows use this library's weight-streaming kernel (it takes up to 16), and so do,
+        # up to `narrow_m` rows, the products whose outputs are at most `narrow_n` columns wide (few_rows_shape below
+        # has the measurements). The reference draws one line: its own gemv up to 8 rows, the vendor's library above
+        # (src/backend/sycl/sycl_kernels.h:280).
         self.small_m = int(os.environ.get("XS_SMALL_M", "8"))
         if not 0 <= self.small_m <= 16:
             raise ValueError("XS_SMALL_M must be 0 to 16")
@@ -105,17 +105,20 @@ class Runtime:
         ops.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
-        # Work done behind its producer inside the producer's kernel; XS_TAILS names what runs so (a comma list of conv,
-        # attn, argmax, rope), the rest stay kernels of their own; XS_NO_TAILS=1: none. Each tail of the few-row product
-        # is a kernel instance of its own: with the tails' code in every instance, the products without a tail carried
-        # its registers and the whole step took 0.642 instead of 0.628 ms. conv: the short convolution behind
-        # in_proj, by the three CTAs of a group of channels as one thread-block cluster that meets in shared memory
-        # (measured on B200, 1.2B shape, decode at batch 8: 0.650 -> 0.642 ms a step; when the three still met through
-        # global memory and a counter it cost 17 us instead). attn: the merge of decode attention's key splits by the
-        # CTA of a (sequence, kv head) that stores last (the same time with six launches fewer). argmax: behind the
-        # head product through atomics on one word (+8 us: off). rope: an attention layer's per-head norms, rotation and cache
-        # write behind its q/k/v product, the CTAs of a head as one cluster (+10 us: off). The zeroed words below are what the counting tails
-        # count in and leave zeroed.
+        # Work done behind its producer inside the producer's kernel. XS_TAILS names what runs so (a comma list of
+        # conv, attn, argmax, rope), the rest stay kernels of their own; XS_NO_TAILS=1: none. Each tail of the few-row
+        # product is a kernel instance of its own: with the tails' code in every instance, the products without a
+        # tail carried its registers and the whole step took 0.642 instead of 0.628 ms. Measured on B200, 1.2B shape,
+        # decode at batch 8:
+        #   conv    the short convolution behind in_proj, by the three CTAs of a group of channels as one thread-block
+        #           cluster that meets in shared memory: 0.650 -> 0.642 ms a step (when the three still met through
+        #           global memory and a counter it cost 17 us instead)
+        #   attn    the merge of decode attention's key splits by the CTA of a (sequence, kv head) that stores last:
+        #           the same time with six launches fewer
+        #   argmax  behind the head product through atomics on one word: +8 us, off
+        #   rope    an attention layer's per-head norms, rotation and cache write behind its q/k/v product, the CTAs
+        #           of a head as one cluster: +10 us, off
+        # The zeroed words below are what the counting tails count in and leave zeroed.
         self.fuse_tails = os.environ.get("XS_NO_TAILS", "0") != "1"
         tails = os.environ.get("XS_TAILS", "conv,attn").split(",")
         self.tail_conv, self.tail_attn, self.tail_argmax = ["conv" in tails, "attn" in tails, "argmax" in tails]
@@ -182,9 +185,10 @@ class Runtime:
                          **norm)
 
     def rope_behind_product(self, x, w, head_dim: int) -> bool:
-        """Whether an attention layer's per-head norm, rotation and cache write (one token a sequence) can run behind its
-        q/k/v product in the product's kernel."""
-        return self.fuse_tails and self.tail_rope and self.few_rows(x, w) and head_dim in (32, 64, 128) and w.shape[0] % 16 == 0
+        """Whether an attention layer's per-head norm, rotation and cache write (one token a sequence) can run behind
+        its q/k/v product in the product's kernel."""
+        return (self.fuse_tails and self.tail_rope and self.few_rows(x, w) and head_dim in (32, 64, 128)
+                and w.shape[0] % 16 == 0)
 
     def few_rows_rope(self, x, w, out, bias, **rope) -> None:
         """ops.gemm_small_m_rope; `x` may be a Prenormed input."""
@@ -198,8 +202,8 @@ class Runtime:
         """Whether a short convolution of one token a sequence can run in the tail of its in_proj product."""
         # (up to 8 rows: at 9 to 16 the kernel of its own is the faster way, 0.819 against 0.830 ms a step at batch 12)
         rows = getattr(x, "x", x).shape[0]
-        return (self.fuse_tails and self.tail_conv and rows <= 8 and self.few_rows(x, w) and channels % 16 == 0 and channels // 16 <= self.conv_counters.numel()
-                and w.shape[0] == 3 * channels)
+        return (self.fuse_tails and self.tail_conv and rows <= 8 and self.few_rows(x, w) and channels % 16 == 0
+                and channels // 16 <= self.conv_counters.numel() and w.shape[0] == 3 * channels)
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None, argmax_into: Optional[torch.Tensor] = None) -> torch.Tensor:
