@@ -107,13 +107,23 @@ class StateGroup:
         self.need = need
         self.calls = list(calls)
         dtype = torch.float32 if need.dtype == "float32" else compute_dtype
-        # one row more than there are slots: the state of padding rows
+        # One row more than there are slots: the state of padding rows. The calls' tensors are pieces of one
+        # allocation, each from a 256-byte boundary on, so that a batch's slots are zeroed with one launch for the
+        # whole group instead of one a call.
+        row = 1
+        for n in need.shape:
+            row *= int(n)
+        item = torch.empty((), dtype=dtype).element_size()
+        piece = -(-((max_slots + 1) * row * item) // 256) * 256 // item
+        self._backing = torch.zeros(max(len(self.calls), 1) * piece, dtype=dtype, device=device)
+        self._rows = self._backing.as_strided((len(self.calls), max_slots + 1, row), (piece, row, 1))
         self.storage: Dict[Tuple[int, int], torch.Tensor] = {
-            c: torch.zeros((max_slots + 1, *need.shape), dtype=dtype, device=device) for c in calls}
+            c: self._backing[i * piece:i * piece + (max_slots + 1) * row].view(max_slots + 1, *need.shape)
+            for i, c in enumerate(self.calls)}
 
     def zero(self, slots: torch.Tensor) -> None:
-        for t in self.storage.values():
-            t.index_fill_(0, slots, 0)
+        if self.calls:
+            self._rows.index_fill_(1, slots, 0)
 
 
 @dataclass
