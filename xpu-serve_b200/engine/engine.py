@@ -83,8 +83,9 @@ class DeviceStepper:
     while sequences decode, the step after the one being asked for is started at once, fed on the device
     from the graph's own argmax (greedy sequences) or from what the sampling kernels chose (seeded draws,
     penalties; the draw for the step that runs ahead uses the sequence's next counter); by the time the loop
-    has looked at a step's tokens the next step is already running. A sequence that the loop ends (a stop token, its length, a callback) has then run one
-    step too many: a row of work that nobody reads, in a slot that the loop closes. The promise the loop
+    has looked at a step's tokens the next step is already running. A sequence that the loop ends (a stop
+    token, its length, a callback) has then run one step too many: a row of work that nobody reads, in a
+    slot that the loop closes. The promise the loop
     makes in return (`generate` keeps it): after decoding has begun, a sequence's next call brings the token
     the last call returned for it. A call that breaks it is refused."""
 
@@ -203,8 +204,9 @@ class DeviceStepper:
 
     def _copy_out(self, out: torch.Tensor):
         """Starts the step's only device-to-host copy (the chosen tokens, into pinned memory) and returns the
-        host buffer, the event that says it has landed and where in the buffer a status word lies (None: nowhere). Two buffers take turns: a step that runs ahead
-        copies out while the one before it is still being read. When a kernel with bounded waits ran since the
+        host buffer, the event that says it has landed and where in the buffer a status word lies (None:
+        nowhere). Two buffers take turns: a step that runs ahead copies out while the one before it is still
+        being read. When a kernel with bounded waits ran since the
         status word was last read (the tcgen05 kernels of prompt steps; decode attention at head size 64), the
         word travels behind the tokens and `_landed` looks at it."""
         n = out.numel()

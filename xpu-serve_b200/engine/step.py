@@ -111,8 +111,8 @@ class StepStager:
     def stage_prompt_fixed(self, cache, slot: int, tokens: Sequence[int], start: int, rows: int) -> StepContext:
         """One sequence's next `len(tokens)` tokens (at most `rows`), laid out as a step of exactly `rows` tokens in
         two sequences: the real one, then a padding sequence of the remaining rows (none when the piece fills the step)
-        in the cache's spare slot and page (nothing it computes is ever read). The layout, every address and every size that a kernel launch gets from the
-        host depend on `rows` and the cache alone, so a graph captured for `rows` serves any shorter prompt piece at any
+        in the cache's spare slot and page (nothing it computes is ever read). The layout, every address and every
+        size that a kernel launch gets from the host depend on `rows` and the cache alone, so a graph captured for `rows` serves any shorter prompt piece at any
         position. The logits wanted are the real sequence's last row's."""
         T = len(tokens)
         if not 0 < T <= rows:
