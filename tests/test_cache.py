@@ -281,3 +281,15 @@ def test_a_call_with_several_needs():
     (s2,) = c.open(1)
     assert s2 == s and all(float(v[k].storage[s].abs().sum()) == 0 for k in (0, 1))
     c.check()
+    # the calls of a state group are pieces of one allocation: opening a slot zeroes its row in every call's
+    # piece and no other row, and every piece is contiguous and starts on a 16-byte boundary
+    c.close([s2])
+    states = [c.views[i][k].storage for i, k in ((0, 0), (1, 0), (3, 0), (0, 1), (3, 1))]
+    for t in states:
+        t.fill_(5)
+        assert t.is_contiguous() and t.data_ptr() % 16 == 0
+    got = c.open(2)
+    for t in states:
+        rows = t.reshape(t.shape[0], -1).float().abs().sum(1)
+        assert all(float(rows[i]) == 0 for i in got)
+        assert all(float(rows[i]) > 0 for i in range(t.shape[0]) if i not in got)
